@@ -1,0 +1,203 @@
+/* kch_b200 — C ABI of the B200 (sm_100a) kernels for the forward path of the KDA + CSA + HCA
+ * hybrid attention stack of 183600/kda-csa-hca-fusion.
+ *
+ * Conventions
+ *  - Every pointer is a DEVICE pointer unless stated otherwise; the library never allocates or
+ *    frees device memory (except kch_*_workspace_bytes helpers, which only compute sizes) and keeps
+ *    no state between calls other than a cache of TMA descriptors and one device status word.
+ *  - `stream` is a cudaStream_t passed as void*.  Calls are asynchronous on that stream.
+ *  - dtype tags: KCH_F32, KCH_BF16 for activations / weights; KCH_FP8_E4M3, KCH_INT8 only for
+ *    block-scaled compressed rows (one fp32 scale per 64 elements).
+ *  - Return value: KCH_OK (0); KCH_ERR_INVALID (<0) for a rejected argument — the message
+ *    (kch_last_error) names the offending parameter the way the reference's ValueError does;
+ *    KCH_ERR_CUDA (>0) for a CUDA failure.  Device-side bounded waits that expire set a status word
+ *    readable with kch_device_status.
+ *  - Reference citations are file:line inside the reference project.
+ */
+#ifndef KCH_B200_H
+#define KCH_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define KCH_OK 0
+#define KCH_ERR_INVALID (-1)
+#define KCH_ERR_CUDA 1
+
+#define KCH_F32 0
+#define KCH_BF16 1
+#define KCH_FP8_E4M3 2
+#define KCH_INT8 3
+
+#define KCH_ACT_SILU 1
+#define KCH_ACT_SIGMOID 2
+#define KCH_ACT_NEG_SOFTPLUS 3
+#define KCH_ACT_SILU_L2NORM 4
+
+/* Library / error plumbing. */
+int kch_abi_version(void);
+const char* kch_last_error(void);           /* host string, thread-local, valid until the next call */
+unsigned int kch_device_status(int reset);  /* synchronising read of the device status word (0 = clean) */
+
+/* ---- layer glue ---------------------------------------------------------------------------- */
+
+/* _Fp32LayerNorm.forward, ops_fused.py:52-60: LayerNorm in fp32, stored in `dtype`. x,y [rows,d]. */
+int kch_layernorm(const void* x, const void* weight, const void* bias, void* y, int64_t rows, int d,
+                  float eps, int dtype, int wdtype, void* stream);
+
+/* KDAHybridLayer short conv, ops_fused.py:505-527: causal depthwise kernel-3 convolution + bias.
+ * x,y [B,T,d]; lookback [B,2,d] or NULL (zeros); weight [d,3]; bias [d]; all in `dtype`. */
+int kch_short_conv(const void* x, const void* lookback, const void* weight, const void* bias, void* y,
+                   int B, int T, int d, int dtype, void* stream);
+
+/* F.linear at ops_fused.py:571-581,609,713,739 and ops_csa.py:841-878, ops_hca.py:132-141:
+ * C[M,N] = A[M,K] . W[N,K]^T, fp32 accumulation, rounded to `dtype`; if `residual` is given the
+ * rounded product is added to it in fp32 and rounded again (x = residual + proj, ops_fused.py:1091).
+ * Leading dimensions are in elements.  bf16 with K,lda,ldw multiples of 8 runs on tcgen05 tensor
+ * cores; everything else on CUDA cores. */
+int kch_linear(const void* A, const void* W, void* C, const void* residual, int64_t M, int N, int K,
+               int64_t lda, int64_t ldw, int64_t ldc, int64_t ldr, int dtype, void* stream);
+
+/* Activation epilogues with the reference's rounding points, ops_fused.py:571-581.
+ * x,y [rows,cols] in `dtype`, rows ldx / ldy elements apart (x may be a column slice of a fused
+ * projection); `param` is the decay scale for KCH_ACT_NEG_SOFTPLUS; `group` is the head width for
+ * KCH_ACT_SILU_L2NORM. */
+int kch_activation(const void* x, void* y, int64_t rows, int cols, int act, float param, int group,
+                   int dtype, int64_t ldx, int64_t ldy, void* stream);
+
+/* F.normalize(x.float(), dim=-1), ops_csa.py:927-936,1110-1113, ops_hca.py:135,141,155:
+ * y[rows,c] fp32 = x / max(||x||,1e-12); x rows are `ld` elements apart.  `norms` (optional)
+ * receives the clamped norms; y may be NULL. */
+int kch_rownorm(const void* x, int64_t ld, float* y, float* norms, int64_t rows, int c, int dtype,
+                void* stream);
+
+/* ---- KDA ----------------------------------------------------------------------------------- */
+
+/* naive_recurrent_kda, ops_kda.py:175-267.  q,k [B,T,H,K]; v [B,T,HV,V]; g [B,T,HV,K];
+ * beta [B,T,HV]; all `dtype`, contiguous.  initial_state / final_state fp32 [B,HV,K,V] (either may
+ * be NULL).  o [B,T,HV,V] in `dtype`.  g is clamped below at g_clamp_min (pass -INFINITY to disable). */
+int kch_kda_recurrent(const void* q, const void* k, const void* v, const void* g, const void* beta,
+                      const float* initial_state, void* o, float* final_state, int B, int T, int H,
+                      int HV, int K, int V, float scale, float g_clamp_min, int dtype, void* stream);
+
+/* naive_chunk_kda, ops_kda.py:340-536 (prepare 375-424, chain 509-535, finalize 440-461).  Same
+ * tensors as above.  Needs a workspace of kch_kda_chunk_workspace_bytes(...) bytes. */
+int64_t kch_kda_chunk_workspace_bytes(int B, int T, int HV, int K, int V, int chunk_size);
+int kch_kda_chunk(const void* q, const void* k, const void* v, const void* g, const void* beta,
+                  const float* initial_state, void* o, float* final_state, int B, int T, int H, int HV,
+                  int K, int V, int chunk_size, float scale, float g_clamp_min, int dtype,
+                  void* workspace, int64_t workspace_bytes, void* stream);
+
+/* ---- compression ------------------------------------------------------------------------------ */
+
+/* csa_compress_kv, ops_csa.py:198-234.  C,Z: rows of c elements, `ld` apart, batch b starts at row
+ * b*batch_stride_rows; B_pos [m,c]; out fp32, batch b at element b*out_batch_stride_elems. */
+int kch_compress_kv(const void* C, const void* Z, const void* B_pos, float* out, int B, int64_t T, int c,
+                    int m, int64_t ld, int64_t batch_stride_rows, int64_t out_batch_stride_elems,
+                    int dtype, int bias_dtype, void* stream);
+
+/* csa_compress_kv_overlapped, ops_csa.py:237-305.  prev_Cb/prev_Zb [B,m,c] (rows prev_ld apart)
+ * supply the b-branch of the block preceding block 0 (NULL: none, as at the sequence start), which
+ * is how _csa_compress_kv_overlapped_single (ops_decoding_cache.py:128-195) continues a stream. */
+int kch_compress_kv_overlapped(const void* Ca, const void* Cb, const void* Za, const void* Zb,
+                               const void* Ba, const void* Bb, const void* prev_Cb, const void* prev_Zb,
+                               int64_t prev_ld, float* out, int B, int64_t T, int c, int m, int64_t ld,
+                               int64_t batch_stride_rows, int64_t out_batch_stride_elems, int dtype,
+                               int bias_dtype, void* stream);
+
+/* ---- lightning indexer + top-k ------------------------------------------------------------------ */
+
+/* csa_lightning_indexer, ops_csa.py:330-573 (scores 529-536, top-k 550-554).
+ * q_idx fp32 [B,T,HI,DI], k_idx fp32 [B,n_blocks,DI] (both already normalised when cosine scoring is
+ * on), w_idx fp32 [B,T,HI] or NULL.  Block n is visible to query row t iff n < (t0+t+1)/m, or iff
+ * n < n_visible when n_visible >= 0 (m <= 0 and n_visible < 0: everything visible).
+ * indices int32 [B,T,topk], -1 padded; ties go to the lower block index; `sorted` orders the picks
+ * by descending logit as torch.topk does.  k_batch_stride: elements between the key blocks of
+ * consecutive batch entries (0 = n_blocks*DI).  Workspace: kch_indexer_workspace_bytes. */
+int64_t kch_indexer_workspace_bytes(int B, int T, int n_blocks);
+int kch_indexer_topk(const float* q_idx, const float* k_idx, const float* w_idx, int32_t* indices, int B,
+                     int T, int n_blocks, int HI, int DI, int topk, float scale, int m, int64_t t0,
+                     int n_visible, int sorted, int64_t k_batch_stride, void* workspace,
+                     int64_t workspace_bytes, void* stream);
+
+/* ---- attention core ------------------------------------------------------------------------------- */
+
+/* Joint-softmax MQA over [selected | all visible] compressed entries and the sliding window, with
+ * the sink logit in the denominator: naive_csa ops_csa.py:923-1155, naive_hca ops_hca.py:139-192,
+ * CSADecodingCache.forward_step ops_decoding_cache.py:891-1070, HCADecodingCache.forward_step
+ * 1318-1395. */
+typedef struct kch_attend_args {
+  const void* q;            /* [B*T, nh*c] rows q_ld apart, q_dtype */
+  int q_dtype;
+  int64_t q_ld;
+  int q_normalize;          /* 1: L2-normalise each head's query in fp32 first */
+  int B, T, nh, c;
+  const void* comp;         /* compressed rows, comp_ld elements apart; batch b starts at row b*comp_batch_rows */
+  int comp_dtype;           /* KCH_F32 / KCH_BF16 / KCH_FP8_E4M3 / KCH_INT8 */
+  int64_t comp_ld;
+  int64_t comp_batch_rows;
+  int n_comp;               /* rows per batch element */
+  const float* comp_norms;  /* optional per-row divisor (same row indexing as comp) */
+  const float* comp_scales; /* [rows, c/64] for the 8-bit kinds */
+  const int32_t* sel_indices; /* [B,T,topk] or NULL = dense over every visible row (HCA) */
+  int topk;
+  int m;                    /* visibility: row n visible to query t iff n < (t0+t+1)/m ... */
+  int64_t t0;
+  int n_visible;            /* ... or n < n_visible when >= 0 */
+  const void* win;          /* window keys; NULL or sliding_window 0 disables */
+  int win_dtype;
+  int64_t win_ld;
+  int64_t win_batch_rows;
+  int sliding_window;
+  int win_mode;             /* 0: row s of `win` is position s of the sequence; 1: ring buffer, rows 0..win_len-1 all valid */
+  int win_len;
+  const void* sink;         /* [nh] or NULL */
+  int sink_dtype;
+  float scale;
+  void* out;                /* [B,T,nh*c] */
+  int out_dtype;
+} kch_attend_args;
+int kch_attend(const kch_attend_args* args, void* stream);
+
+/* ---- decode caches ---------------------------------------------------------------------------------- */
+
+/* One appended token for every sequence of the batch: CSADecodingCache.append_step
+ * (ops_decoding_cache.py:704-779) when Cb/Zb/K_idx/Z_idx are given, HCADecodingCache.append_step
+ * (1238-1264) when they are NULL.  Host-side counters (acc_len, n_blocks, ring_pos, has_prev) are
+ * owned by the caller, as in the reference's cache objects. */
+typedef struct kch_cache_append_args {
+  int B, c, c_I, m, win;
+  int dtype;                 /* dtype of projections, accumulators, ring, kcomp (KCH_F32 / KCH_BF16) */
+  const void *Ca, *Cb, *Za, *Zb, *K_idx, *Z_idx;  /* token rows: row b at element b*ld_c (b*ld_i) */
+  int64_t ld_c, ld_i;
+  void *acc_Ca, *acc_Cb, *acc_Za, *acc_Zb, *acc_K_idx, *acc_Z_idx;  /* [B,m,c] / [B,m,c_I] */
+  int acc_len;
+  void *prev_Cb, *prev_Zb;   /* [B,m,c] */
+  int has_prev;
+  const void *Ba, *Bb, *B_idx;  /* [m,c], [m,c], [m,c_I] in `dtype` */
+  void* comp;                /* [B,capacity,c] in comp_kind */
+  int comp_kind;             /* == dtype, or KCH_FP8_E4M3 / KCH_INT8 */
+  float* comp_scales;        /* [B,capacity,c/64] for 8-bit kinds */
+  float* comp_norms;         /* [B,capacity] */
+  void* kcomp;               /* [B,capacity,c_I] in dtype */
+  float* kcomp_normalized;   /* [B,capacity,c_I] fp32 scoring copy */
+  int64_t capacity;
+  int n_blocks;
+  void* ring;                /* [B,win,c] in dtype */
+  int ring_pos;
+  int normalize;
+} kch_cache_append_args;
+int kch_cache_append_token(const kch_cache_append_args* args, void* stream);
+
+/* Block-scaled 8-bit encoding of rows (no counterpart in the reference; it stores the cache dtype only):
+ * payload [rows,c], scales [rows,c/64], norms [rows] = max(||dequantised row||, 1e-12). */
+int kch_quantize_rows(const void* x, int64_t ld, void* payload, float* scales, float* norms, int64_t rows,
+                      int c, int kind, int dtype, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* KCH_B200_H */

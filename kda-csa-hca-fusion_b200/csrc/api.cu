@@ -1,0 +1,41 @@
+// Error plumbing and dispatch shared by the C-ABI entry points.
+#include <stdarg.h>
+#include <stdio.h>
+#include <stdlib.h>
+
+#include "kch_common.cuh"
+
+static thread_local char g_err[512] = "";
+
+void kch_set_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+}
+
+extern "C" const char* kch_last_error(void) { return g_err; }
+extern "C" int kch_abi_version(void) { return 1; }
+
+int kch_linear_simt(const void* A, const void* W, void* C, const void* residual, int64_t M, int N, int K,
+                    int64_t lda, int64_t ldw, int64_t ldc, int64_t ldr, int dtype, void* stream);
+bool kch_linear_tcgen05_supported(const void* A, const void* W, const void* C, const void* R, int64_t M, int N,
+                                  int K, int64_t lda, int64_t ldw, int64_t ldc, int64_t ldr, int dtype);
+int kch_linear_tcgen05(const void* A, const void* W, void* C, const void* R, int64_t M, int N, int K, int64_t lda,
+                       int64_t ldw, int64_t ldc, int64_t ldr, void* stream);
+
+extern "C" int kch_linear(const void* A, const void* W, void* C, const void* residual, int64_t M, int N, int K,
+                          int64_t lda, int64_t ldw, int64_t ldc, int64_t ldr, int dtype, void* stream) {
+  KCH_REQUIRE(M >= 0 && N >= 0 && K >= 1, "kch_linear: M=%lld N=%d K=%d", (long long)M, N, K);
+  KCH_REQUIRE(lda >= K && ldw >= K && ldc >= N, "kch_linear: leading dimensions lda=%lld ldw=%lld ldc=%lld too small",
+              (long long)lda, (long long)ldw, (long long)ldc);
+  KCH_REQUIRE(dtype == KCH_F32 || dtype == KCH_BF16, "kch_linear: unsupported dtype tag %d", dtype);
+  if (M == 0 || N == 0) return KCH_OK;
+  // CUDA-core kernel for fp32, for shapes the TMA descriptors cannot express, and for very narrow
+  // outputs; KCH_LINEAR=simt forces it (a debugging aid: still a CUDA kernel, never a host path).
+  static const bool force_simt = [] { const char* e = getenv("KCH_LINEAR"); return e && e[0] == 's'; }();
+  if (!force_simt && N >= 32 &&
+      kch_linear_tcgen05_supported(A, W, C, residual, M, N, K, lda, ldw, ldc, ldr, dtype))
+    return kch_linear_tcgen05(A, W, C, residual, M, N, K, lda, ldw, ldc, ldr, stream);
+  return kch_linear_simt(A, W, C, residual, M, N, K, lda, ldw, ldc, ldr, dtype, stream);
+}

@@ -1,0 +1,326 @@
+// bf16 linear layer on the 5th-generation tensor cores (sm_100a):
+//   C[M,N] = A[M,K] . W[N,K]^T, fp32 accumulation in tensor memory, one rounding to bf16,
+//   optional residual add.  Every dense projection of the hybrid layer goes through here
+//   (q/k/v/g/beta, the fused CSA 6-way KV/indexer projection, W_DQ/W_UQ/W_IUQ, o_proj).
+//
+// Structure (one persistent CTA per SM, 192 threads):
+//   warp 0      : TMA producer — cp.async.bulk.tensor tiles of A (128x64) and W (BNx64), 128-byte
+//                 swizzle, into a 4-stage shared-memory ring (no multicast: every CTA fetches its own).
+//   warp 1      : allocates tensor memory, then one elected lane issues tcgen05.mma (M=128, N=BN,
+//                 K=16 per instruction, four per stage) and tcgen05.commit to release stages.
+//   warps 2..5  : epilogue — tcgen05.ld of the fp32 accumulator (each warp its 32-lane quarter),
+//                 bf16 rounding, residual, 64-byte vector stores.
+// Two accumulator buffers in tensor memory let the epilogue of tile i overlap the main loop of
+// tile i+1.  Every wait on an mbarrier is bounded; on expiry the kernel records a status word,
+// leaves its loops, frees tensor memory and returns.
+#include <cuda.h>
+#include <cudaTypedefs.h>
+#include <mutex>
+#include <unordered_map>
+
+#include "kch_common.cuh"
+
+#define TG_BM 128
+#define TG_BK 64
+#define TG_STAGES 4
+#define TG_THREADS 192
+#define TG_SPIN_LIMIT (1u << 24)
+
+__device__ unsigned int g_kch_status = 0;  // nonzero: a bounded wait expired (see kch_device_status)
+
+// ---- PTX wrappers ------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// bounded wait; returns false (and records `code`) if the phase never completes
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, unsigned code) {
+  uint32_t addr = smem_u32(bar);
+  for (uint32_t it = 0; it < TG_SPIN_LIMIT; ++it) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(addr), "r"(parity) : "memory");
+    if (ok) return true;
+    if (*((volatile unsigned int*)&g_kch_status) != 0) return false;  // someone else already gave up
+  }
+  atomicCAS(&g_kch_status, 0u, code);
+  return false;
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int c0, int c1, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_mma_bf16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// K-major operand tile, rows of 64 bf16 (128 bytes) under the 128-byte swizzle: 8-row groups are
+// 1024 bytes apart (stride byte offset); the leading byte offset is not used for this layout.
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr & 0x3FFFF) >> 4);
+  d |= (uint64_t)1 << 16;            // leading byte offset (ignored for swizzled K-major)
+  d |= (uint64_t)(1024 >> 4) << 32;  // stride byte offset
+  d |= (uint64_t)1 << 46;            // descriptor version for sm_100
+  d |= (uint64_t)2 << 61;            // SWIZZLE_128B
+  return d;
+}
+
+template <int BN>
+struct TgSmem {
+  alignas(1024) bf16 a[TG_STAGES][TG_BM * TG_BK];
+  alignas(1024) bf16 b[TG_STAGES][BN * TG_BK];
+  alignas(8) uint64_t full[TG_STAGES];
+  uint64_t empty[TG_STAGES];
+  uint64_t acc_full[2];
+  uint64_t acc_empty[2];
+  uint32_t tmem_base;
+};
+
+template <int BN>
+__global__ void __launch_bounds__(TG_THREADS, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+                    bf16* __restrict__ C, const bf16* __restrict__ R, int64_t M, int N, int K,
+                    int64_t ldc, int64_t ldr, int vec_ok) {
+  extern __shared__ uint8_t smem_raw[];
+  TgSmem<BN>& sm = *reinterpret_cast<TgSmem<BN>*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n_tiles = (N + BN - 1) / BN;
+  const int64_t m_tiles = (M + TG_BM - 1) / TG_BM;
+  const int64_t total_tiles = m_tiles * n_tiles;
+  const int kblocks = (K + TG_BK - 1) / TG_BK;
+  constexpr uint32_t ACC_COLS = BN;                 // fp32 accumulator columns per buffer
+  constexpr uint32_t TMEM_COLS = (2 * ACC_COLS) < 32 ? 32 : 2 * ACC_COLS;  // power of two >= 32
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < TG_STAGES; ++s) { mbar_init(&sm.full[s], 1); mbar_init(&sm.empty[s], 1); }
+    for (int i = 0; i < 2; ++i) { mbar_init(&sm.acc_full[i], 1); mbar_init(&sm.acc_empty[i], 4); }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm.tmem_base)), "r"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = sm.tmem_base;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int64_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        const int64_t mb = tile / n_tiles;
+        const int nb = (int)(tile % n_tiles);
+        for (int kb = 0; kb < kblocks; ++kb, ++it) {
+          const uint32_t s = it % TG_STAGES, ph = (it / TG_STAGES) & 1;
+          if (!mbar_wait(&sm.empty[s], ph ^ 1, 1)) { ok = false; break; }
+          mbar_expect_tx(&sm.full[s], (TG_BM + BN) * TG_BK * 2);
+          tma_load_2d(sm.a[s], &map_a, kb * TG_BK, (int)(mb * TG_BM), &sm.full[s]);
+          tma_load_2d(sm.b[s], &map_w, kb * TG_BK, nb * BN, &sm.full[s]);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer ---------------------------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(TG_BM >> 4) << 24);
+      uint32_t it = 0, tcount = 0;
+      bool ok = true;
+      for (int64_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++tcount) {
+        const uint32_t acc = tcount & 1, aph = (tcount >> 1) & 1;
+        if (!mbar_wait(&sm.acc_empty[acc], aph ^ 1, 2)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * ACC_COLS;
+        for (int kb = 0; kb < kblocks; ++kb, ++it) {
+          const uint32_t s = it % TG_STAGES, ph = (it / TG_STAGES) & 1;
+          if (!mbar_wait(&sm.full[s], ph, 3)) { ok = false; break; }
+          tc_fence_after();
+          const uint64_t adesc = make_smem_desc(smem_u32(sm.a[s]));
+          const uint64_t bdesc = make_smem_desc(smem_u32(sm.b[s]));
+#pragma unroll
+          for (int k = 0; k < TG_BK / 16; ++k)
+            tc_mma_bf16(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) ? 1u : 0u);
+          tc_commit(&sm.empty[s]);  // stage reusable once these MMAs have read it
+        }
+        if (ok) tc_commit(&sm.acc_full[acc]);
+      }
+    }
+  } else {
+    // ------------------------------ epilogue warps ------------------------------
+    const int quarter = warp & 3;  // tensor-memory lanes 32*quarter .. 32*quarter+31
+    uint32_t tcount = 0;
+    bool ok = true;
+    for (int64_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++tcount) {
+      const int64_t mb = tile / n_tiles;
+      const int nb = (int)(tile % n_tiles);
+      const uint32_t acc = tcount & 1, aph = (tcount >> 1) & 1;
+      if (!mbar_wait(&sm.acc_full[acc], aph, 4)) { ok = false; break; }
+      tc_fence_after();
+      const int64_t row = mb * TG_BM + quarter * 32 + lane;
+      const uint32_t tbase = tmem_base + acc * ACC_COLS + ((uint32_t)(quarter * 32) << 16);
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        uint32_t r[32];
+        tc_ld32(tbase + c0, r);
+        tc_wait_ld();
+        const int col = nb * BN + c0;
+        if (row < M && col < N) {
+          bf16* cp = C + row * ldc + col;
+          const bf16* rp = R ? R + row * ldr + col : nullptr;
+          if (vec_ok && col + 32 <= N) {
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              uint4 resv;
+              if (rp) resv = *reinterpret_cast<const uint4*>(rp + 8 * v);
+              uint32_t o[4];
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                float f0 = __uint_as_float(r[8 * v + 2 * j]), f1 = __uint_as_float(r[8 * v + 2 * j + 1]);
+                __nv_bfloat162 h = __floats2bfloat162_rn(f0, f1);
+                if (rp) {
+                  uint32_t rw = (&resv.x)[j];
+                  __nv_bfloat162 rr = *reinterpret_cast<__nv_bfloat162*>(&rw);
+                  h = __floats2bfloat162_rn(__bfloat162float(h.x) + __bfloat162float(rr.x),
+                                            __bfloat162float(h.y) + __bfloat162float(rr.y));
+                }
+                o[j] = *reinterpret_cast<uint32_t*>(&h);
+              }
+              *reinterpret_cast<uint4*>(cp + 8 * v) = make_uint4(o[0], o[1], o[2], o[3]);
+            }
+          } else {
+            for (int j = 0; j < 32 && col + j < N; ++j) {
+              float f = __bfloat162float(__float2bfloat16_rn(__uint_as_float(r[j])));
+              if (rp) f += __bfloat162float(rp[j]);
+              cp[j] = __float2bfloat16_rn(f);
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&sm.acc_empty[acc]);
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+}
+
+// ---- host side -----------------------------------------------------------------------------------
+static PFN_cuTensorMapEncodeTiled_v12000 get_encode_fn() {
+  static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = (PFN_cuTensorMapEncodeTiled_v12000)p;
+  });
+  return fn;
+}
+
+static int make_map_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint64_t ld_elems,
+                       uint32_t box_rows, uint32_t box_cols) {
+  PFN_cuTensorMapEncodeTiled_v12000 enc = get_encode_fn();
+  if (!enc) { kch_set_error("cuTensorMapEncodeTiled is not available from the driver"); return KCH_ERR_CUDA; }
+  cuuint64_t gdim[2] = {cols, rows};
+  cuuint64_t gstr[1] = {ld_elems * 2};
+  cuuint32_t box[2] = {box_cols, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), gdim, gstr, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) { kch_set_error("cuTensorMapEncodeTiled failed with code %d", (int)r); return KCH_ERR_CUDA; }
+  return KCH_OK;
+}
+
+bool kch_linear_tcgen05_supported(const void* A, const void* W, const void* C, const void* R, int64_t M, int N,
+                                  int K, int64_t lda, int64_t ldw, int64_t ldc, int64_t ldr, int dtype) {
+  if (dtype != KCH_BF16) return false;
+  if (M < 1 || N < 1 || K < 8) return false;
+  if ((K % 8) || (lda % 8) || (ldw % 8)) return false;
+  if (((uintptr_t)A & 15) || ((uintptr_t)W & 15)) return false;
+  if (M > 0x7FFFFFFFLL) return false;
+  (void)C; (void)R; (void)ldc; (void)ldr;
+  return true;
+}
+
+template <int BN>
+static int launch_tg(const void* A, const void* W, void* C, const void* R, int64_t M, int N, int K, int64_t lda,
+                     int64_t ldw, int64_t ldc, int64_t ldr, cudaStream_t s) {
+  CUtensorMap ma, mw;
+  int rc = make_map_2d(&ma, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, TG_BM, TG_BK);
+  if (rc) return rc;
+  rc = make_map_2d(&mw, W, (uint64_t)N, (uint64_t)K, (uint64_t)ldw, BN, TG_BK);
+  if (rc) return rc;
+  static int sms = 0;
+  if (!sms) {
+    int dev = 0;
+    KCH_CUDA_OK(cudaGetDevice(&dev));
+    KCH_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  }
+  size_t smem = sizeof(TgSmem<BN>) + 1024;
+  KCH_CUDA_OK(cudaFuncSetAttribute(gemm_tcgen05_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  int64_t tiles = ((M + TG_BM - 1) / TG_BM) * ((N + BN - 1) / BN);
+  int grid = (int)(tiles < sms ? tiles : sms);
+  int vec_ok = (ldc % 8 == 0) && (((uintptr_t)C & 15) == 0) && (!R || ((ldr % 8 == 0) && (((uintptr_t)R & 15) == 0)));
+  gemm_tcgen05_kernel<BN><<<grid, TG_THREADS, smem, s>>>(ma, mw, (bf16*)C, (const bf16*)R, M, N, K, ldc, ldr, vec_ok);
+  KCH_LAUNCH_OK();
+  return KCH_OK;
+}
+
+int kch_linear_tcgen05(const void* A, const void* W, void* C, const void* R, int64_t M, int N, int K, int64_t lda,
+                       int64_t ldw, int64_t ldc, int64_t ldr, void* stream) {
+  cudaStream_t s = kch_stream(stream);
+  if (N > 128) return launch_tg<256>(A, W, C, R, M, N, K, lda, ldw, ldc, ldr, s);
+  if (N > 64) return launch_tg<128>(A, W, C, R, M, N, K, lda, ldw, ldc, ldr, s);
+  if (N > 32) return launch_tg<64>(A, W, C, R, M, N, K, lda, ldw, ldc, ldr, s);
+  return launch_tg<32>(A, W, C, R, M, N, K, lda, ldw, ldc, ldr, s);
+}
+
+extern "C" unsigned int kch_device_status(int reset) {
+  unsigned int v = 0;
+  if (cudaMemcpyFromSymbol(&v, g_kch_status, sizeof(v)) != cudaSuccess) return 0xFFFFFFFFu;
+  if (reset && v) {
+    unsigned int z = 0;
+    cudaMemcpyToSymbol(g_kch_status, &z, sizeof(z));
+  }
+  return v;
+}

@@ -1,0 +1,260 @@
+// Lightning indexer and exact top-k selection  (csa_lightning_indexer, ops_csa.py:503-554).
+//   logits[t,n] = sum_h w[t,h] * relu(scale * q[t,h] . k[n])      fp32 FMA throughout
+//   block n is visible to the query at absolute position t iff n < (t+1)/m
+//   select the min(topk, n_blocks) largest visible logits; slots without a visible block are -1
+// Tie rule: equal logits are taken in ascending block index (the reference leaves tie order to
+// its array library).  Selection is an exact 4x8-bit radix select on the order-preserving integer
+// image of the fp32 logits, so the selected SET is a pure function of the logits.
+#include <math.h>
+
+#include "kch_common.cuh"
+
+// ---------------------------------------------------------------------------------------
+// Logits: 64 queries x 64 blocks per CTA, 16x16 threads, 4x4 outputs per thread.
+// q: [B,T,HI,DI] fp32, k: [B,n,DI] fp32 (both already normalised when cosine scoring is on).
+// ---------------------------------------------------------------------------------------
+#define IDX_TQ 64
+#define IDX_TN 64
+#define IDX_DK 32
+
+__global__ void __launch_bounds__(256)
+indexer_logits_kernel(const float* __restrict__ q, const float* __restrict__ k,
+                      const float* __restrict__ w, float* __restrict__ logits, int T, int n, int HI,
+                      int DI, int64_t n_ld, float scale, int m, int64_t t0, int nvis_fixed,
+                      int64_t k_bstride) {
+  const int nt = blockIdx.x, qt = blockIdx.y, b = blockIdx.z;
+  const int tq0 = qt * IDX_TQ, n0 = nt * IDX_TN;
+  // visibility of the last query of the tile bounds the useful block range
+  int tlast = min(T, tq0 + IDX_TQ) - 1;
+  int64_t vis_last = nvis_fixed >= 0 ? nvis_fixed : (m > 0 ? (t0 + tlast + 1) / m : n);
+  if (n0 >= vis_last) return;
+  __shared__ float sq[IDX_DK][IDX_TQ + 1];
+  __shared__ float sk[IDX_DK][IDX_TN + 1];
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+  float out[4][4] = {};
+  for (int h = 0; h < HI; ++h) {
+    float acc[4][4] = {};
+    for (int d0 = 0; d0 < DI; d0 += IDX_DK) {
+      for (int idx = threadIdx.x; idx < IDX_TQ * IDX_DK; idx += 256) {
+        int r = idx / IDX_DK, d = idx % IDX_DK;
+        int t = tq0 + r;
+        sq[d][r] = (t < T && d0 + d < DI) ? q[(((int64_t)b * T + t) * HI + h) * DI + d0 + d] : 0.f;
+      }
+      for (int idx = threadIdx.x; idx < IDX_TN * IDX_DK; idx += 256) {
+        int r = idx / IDX_DK, d = idx % IDX_DK;
+        int nn = n0 + r;
+        sk[d][r] = (nn < n && d0 + d < DI) ? k[(int64_t)b * k_bstride + (int64_t)nn * DI + d0 + d] : 0.f;
+      }
+      __syncthreads();
+#pragma unroll 8
+      for (int d = 0; d < IDX_DK; ++d) {
+        float qa[4], ka[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { qa[i] = sq[d][ty * 4 + i]; ka[i] = sk[d][tx * 4 + i]; }
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+          for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(qa[i], ka[j], acc[i][j]);
+      }
+      __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      int t = tq0 + ty * 4 + i;
+      float wh = 1.f;
+      if (w) wh = t < T ? w[((int64_t)b * T + t) * HI + h] : 0.f;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) out[i][j] = fmaf(fmaxf(acc[i][j] * scale, 0.f), wh, out[i][j]);
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    int t = tq0 + ty * 4 + i;
+    if (t >= T) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      int nn = n0 + tx * 4 + j;
+      if (nn < n) logits[((int64_t)b * T + t) * n_ld + nn] = out[i][j];
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// Selection: one CTA per query row.
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t f2ord(float f) {
+  uint32_t u = __float_as_uint(f);
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+
+// inclusive-exclusive block scan helper over 256 threads: returns exclusive prefix of `v`,
+// total in *total.  `buf` has 9 words.
+__device__ __forceinline__ int block_excl_scan(int v, int* buf, int* total) {
+  int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  int inc = v;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    int y = __shfl_up_sync(0xffffffffu, inc, o);
+    if (lane >= o) inc += y;
+  }
+  if (lane == 31) buf[warp] = inc;
+  __syncthreads();
+  if (warp == 0) {
+    int x = lane < 8 ? buf[lane] : 0;
+    int xi = x;
+#pragma unroll
+    for (int o = 1; o < 8; o <<= 1) {
+      int y = __shfl_up_sync(0xffffffffu, xi, o);
+      if (lane >= o) xi += y;
+    }
+    if (lane < 8) buf[lane] = xi - x;
+    if (lane == 7) buf[8] = xi;
+  }
+  __syncthreads();
+  int res = buf[warp] + inc - v;
+  *total = buf[8];
+  __syncthreads();
+  return res;
+}
+
+__global__ void __launch_bounds__(256)
+topk_select_kernel(const float* __restrict__ logits, int32_t* __restrict__ out, int T, int n,
+                   int64_t n_ld, int topk, int m, int64_t t0, int nvis_fixed, int sorted) {
+  extern __shared__ unsigned long long ssort[];  // only when sorted
+  const int64_t row = blockIdx.x;  // b*T + t
+  const int t = (int)(row % T);
+  const float* lg = logits + row * n_ld;
+  int32_t* orow = out + row * topk;
+  int64_t nv64 = nvis_fixed >= 0 ? nvis_fixed : (m > 0 ? (t0 + t + 1) / m : n);
+  const int nv = (int)(nv64 < n ? nv64 : n);
+  const int ksel = topk < n ? topk : n;
+  const int tid = threadIdx.x;
+  __shared__ int hist[256];
+  __shared__ int sbuf[9];
+  __shared__ uint32_t s_prefix;
+  __shared__ int s_need;
+  int nsel;
+  if (nv <= ksel) {
+    for (int i = tid; i < topk; i += 256) orow[i] = i < nv ? i : -1;
+    nsel = nv;
+  } else {
+    uint32_t prefix = 0, pmask = 0;
+    int need = ksel;  // how many still to take from the current prefix class
+    for (int pass = 0; pass < 4; ++pass) {
+      const int shift = 24 - 8 * pass;
+      hist[tid] = 0;
+      __syncthreads();
+      for (int i = tid; i < nv; i += 256) {
+        uint32_t u = f2ord(lg[i]);
+        if ((u & pmask) == prefix) atomicAdd(&hist[(u >> shift) & 255], 1);
+      }
+      __syncthreads();
+      if (tid == 0) {
+        int cum = 0, bsel = 0;
+        for (int bin = 255; bin >= 0; --bin) {
+          int cnt = hist[bin];
+          if (cum + cnt >= need) { bsel = bin; break; }
+          cum += cnt;
+        }
+        s_prefix = prefix | ((uint32_t)bsel << shift);
+        s_need = need - cum;
+      }
+      __syncthreads();
+      prefix = s_prefix;
+      need = s_need;
+      pmask |= 0xFFu << shift;
+      __syncthreads();
+    }
+    // prefix = key of the k-th largest logit; `need` of the entries equal to it are taken,
+    // lowest index first; everything strictly greater is taken.
+    const int n_gt = ksel - need;
+    int run_gt = 0, run_eq = 0;
+    for (int base = 0; base < nv; base += 256) {
+      int i = base + tid;
+      uint32_t u = i < nv ? f2ord(lg[i]) : 0u;
+      int is_gt = (i < nv && u > prefix) ? 1 : 0;
+      int is_eq = (i < nv && u == prefix) ? 1 : 0;
+      int tot_gt, tot_eq;
+      int pg = block_excl_scan(is_gt, sbuf, &tot_gt);
+      int pe = block_excl_scan(is_eq, sbuf, &tot_eq);
+      if (is_gt) orow[run_gt + pg] = i;
+      if (is_eq && run_eq + pe < need) orow[n_gt + run_eq + pe] = i;
+      run_gt += tot_gt;
+      run_eq += tot_eq;
+    }
+    for (int i = ksel + tid; i < topk; i += 256) orow[i] = -1;
+    nsel = ksel;
+  }
+  if (!sorted) return;
+  // descending by logit, ascending block index among equals (bitonic sort on 64-bit keys)
+  __syncthreads();
+  int P = 1;
+  while (P < nsel) P <<= 1;
+  for (int i = tid; i < P; i += 256) {
+    unsigned long long key = 0ull;
+    if (i < nsel) {
+      int id = orow[i];
+      key = ((unsigned long long)f2ord(lg[id]) << 32) | (uint32_t)(0x7FFFFFFF - id);
+    }
+    ssort[i] = key;
+  }
+  __syncthreads();
+  for (int size = 2; size <= P; size <<= 1)
+    for (int stride = size >> 1; stride > 0; stride >>= 1) {
+      for (int i = tid; i < P; i += 256) {
+        int j = i ^ stride;
+        if (j > i) {
+          unsigned long long a = ssort[i], c = ssort[j];
+          bool desc = (i & size) == 0;
+          if (desc ? (a < c) : (a > c)) { ssort[i] = c; ssort[j] = a; }
+        }
+      }
+      __syncthreads();
+    }
+  for (int i = tid; i < nsel; i += 256) orow[i] = 0x7FFFFFFF - (int)(uint32_t)(ssort[i] & 0xFFFFFFFFu);
+}
+
+extern "C" int64_t kch_indexer_workspace_bytes(int B, int T, int n) {
+  if (B <= 0 || T <= 0 || n <= 0) return 0;
+  int64_t n_ld = ((int64_t)n + 3) & ~3LL;
+  return (int64_t)B * T * n_ld * 4;
+}
+
+extern "C" int kch_indexer_topk(const float* q_idx, const float* k_idx, const float* w_idx,
+                                int32_t* indices, int B, int T, int n_blocks, int HI, int DI, int topk,
+                                float scale, int m, int64_t t0, int n_visible, int sorted,
+                                int64_t k_batch_stride, void* workspace, int64_t workspace_bytes,
+                                void* stream) {
+  KCH_REQUIRE(topk >= 0, "topk=%d must be >= 0 (0 selects zero blocks)", topk);
+  KCH_REQUIRE(DI >= 1, "q_idx.shape[-1]=%d must be >= 1 (indexer key dimension c_I must be positive)", DI);
+  KCH_REQUIRE(HI >= 1, "nIh=%d must be >= 1 (indexer head count)", HI);
+  KCH_REQUIRE(B >= 0 && T >= 0 && n_blocks >= 0, "kch_indexer_topk: B=%d T=%d n=%d", B, T, n_blocks);
+  if (B == 0 || T == 0 || topk == 0) return KCH_OK;
+  cudaStream_t s = kch_stream(stream);
+  if (n_blocks == 0) {
+    KCH_CUDA_OK(cudaMemsetAsync(indices, 0xFF, (size_t)B * T * topk * sizeof(int32_t), s));
+    return KCH_OK;
+  }
+  int64_t need = kch_indexer_workspace_bytes(B, T, n_blocks);
+  KCH_REQUIRE(workspace && workspace_bytes >= need, "kch_indexer_topk: workspace %lld < %lld bytes",
+              (long long)workspace_bytes, (long long)need);
+  int64_t n_ld = ((int64_t)n_blocks + 3) & ~3LL;
+  float* logits = (float*)workspace;
+  dim3 g1((n_blocks + IDX_TN - 1) / IDX_TN, (T + IDX_TQ - 1) / IDX_TQ, B);
+  indexer_logits_kernel<<<g1, 256, 0, s>>>(q_idx, k_idx, w_idx, logits, T, n_blocks, HI, DI, n_ld, scale,
+                                            m, t0, n_visible, k_batch_stride > 0 ? k_batch_stride : (int64_t)n_blocks * DI);
+  KCH_LAUNCH_OK();
+  size_t smem = 0;
+  if (sorted) {
+    int ks = topk < n_blocks ? topk : n_blocks;
+    int P = 1;
+    while (P < ks) P <<= 1;
+    KCH_REQUIRE(P <= 8192, "kch_indexer_topk: sorted output supports topk <= 8192 (got %d)", ks);
+    smem = (size_t)P * 8;
+    KCH_CUDA_OK(cudaFuncSetAttribute(topk_select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  }
+  topk_select_kernel<<<(unsigned)((int64_t)B * T), 256, smem, s>>>(logits, indices, T, n_blocks, n_ld, topk, m,
+                                                                    t0, n_visible, sorted);
+  KCH_LAUNCH_OK();
+  return KCH_OK;
+}

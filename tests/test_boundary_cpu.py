@@ -1,0 +1,133 @@
+"""Host-side checks that need no GPU: the C-ABI library loads and exports every symbol the header
+declares, host validation rejects bad arguments with the reference's exception types before any
+launch, CPU tensors are refused (no fallback), and the backend installer is reversible."""
+import ctypes
+import os
+import re
+
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _header_symbols():
+    src = open(os.path.join(ROOT, "include", "kch_b200.h")).read()
+    src = re.sub(r"/\*.*?\*/", "", src, flags=re.S)
+    return sorted(set(re.findall(r"\b(kch_[a-z0-9_]+)\s*\(", src)))
+
+
+def test_library_exports_every_declared_symbol():
+    from kch_b200 import _lib
+    lib = _lib.load()
+    syms = _header_symbols()
+    assert len(syms) >= 18
+    for s in syms:
+        assert hasattr(lib, s), f"{s} declared in include/kch_b200.h but not exported"
+        assert s in _lib.PROTOTYPES, f"{s} has no ctypes prototype"
+    assert sorted(_lib.PROTOTYPES) == syms
+    assert lib.kch_abi_version() == 1
+
+
+def test_argument_errors_come_back_as_codes_without_a_gpu():
+    from kch_b200 import _lib
+    lib = _lib.load()
+    # every one of these is rejected on the host before any CUDA call
+    rc = lib.kch_compress_kv(None, None, None, None, 1, 10, 8, 0, 8, 10, 0, 0, 0, None)
+    assert rc < 0 and b"m=0" in lib.kch_last_error()
+    rc = lib.kch_compress_kv(None, None, None, None, 1, 10, 8, 4, 8, 10, 0, 0, 0, None)
+    assert rc < 0 and b"divisible" in lib.kch_last_error()
+    rc = lib.kch_kda_recurrent(*([None] * 8), 1, 4, 2, 3, 8, 8, 1.0, -10.0, 0, None)
+    assert rc < 0 and b"HV=3" in lib.kch_last_error()
+    rc = lib.kch_indexer_topk(None, None, None, None, 1, 4, 4, 2, 0, 3, 1.0, 4, 0, -1, 0, 0, None, 0, None)
+    assert rc < 0 and b"c_I" in lib.kch_last_error()
+    rc = lib.kch_linear(None, None, None, None, 4, 4, 4, 2, 4, 4, 0, 0, None)
+    assert rc < 0 and b"lda" in lib.kch_last_error()
+    with pytest.raises(ValueError, match="lda"):
+        _lib.check(rc)
+    assert lib.kch_kda_chunk_workspace_bytes(4, 32768, 16, 128, 128, 64) > 0
+    assert lib.kch_indexer_workspace_bytes(1, 4096, 1024) == 4096 * 1024 * 4
+
+
+def test_cpu_tensors_are_refused_not_silently_computed():
+    import kch_b200
+    q = torch.randn(1, 4, 2, 8)
+    with pytest.raises(RuntimeError, match="CUDA"):
+        kch_b200.naive_recurrent_kda(q, q, q, q, torch.rand(1, 4, 2))
+    with pytest.raises(RuntimeError, match="CUDA"):
+        kch_b200.kda_forward(q, q, q, q, torch.rand(1, 4, 2))
+    H = torch.randn(1, 8, 16)
+    W = torch.randn(4, 16)
+    with pytest.raises(RuntimeError, match="CUDA"):
+        kch_b200.naive_hca(H, W, W, torch.zeros(4, 4), torch.randn(4, 16), torch.randn(8, 4), m2=4, nh=2, c=4, dc=4)
+    with pytest.raises(RuntimeError, match="CUDA"):
+        kch_b200.CSADecodingCache(1, 8, 4, 4, 4, "cpu", torch.float32)
+
+
+def test_validation_matches_reference_types_and_names():
+    import kch_b200
+    q = torch.randn(1, 4, 2, 8)
+    with pytest.raises(ValueError, match="rank"):
+        kch_b200.naive_recurrent_kda(q[0], q, q, q, torch.rand(1, 4, 2))
+    with pytest.raises(ValueError, match="beta"):
+        kch_b200.naive_chunk_kda(q, q, q, q, torch.rand(1, 4, 3))
+    with pytest.raises(ValueError, match="kda_backend"):
+        kch_b200.kda_forward(q, q, q, q, torch.rand(1, 4, 2), backend="fla")
+    with pytest.raises(TypeError):
+        kch_b200.kda_forward(q, q, q, q, torch.rand(1, 4, 2), g_clamp_min="x")
+    with pytest.raises(ValueError, match="m=0"):
+        kch_b200.csa_compress_kv(torch.zeros(1, 4, 4), torch.zeros(1, 4, 4), torch.zeros(1, 4), 0)
+    with pytest.raises(ValueError, match="topk"):
+        kch_b200.csa_lightning_indexer(torch.zeros(1, 2, 1, 4), torch.zeros(1, 2, 4), None, -1)
+    with pytest.raises(NotImplementedError):
+        kch_b200.csa_lightning_indexer(torch.zeros(1, 2, 1, 4), torch.zeros(1, 2, 4), None, 1, ste_mode="aux_contrastive")
+    with pytest.raises(ValueError, match="n_heads_v"):
+        kch_b200.HybridConfig(n_heads_qk=3, n_heads_v=4)
+    with pytest.raises(ValueError, match="kda_backend"):
+        kch_b200.HybridConfig(kda_backend="triton")
+    with pytest.raises(ValueError, match="win"):
+        kch_b200.CSADecodingCache(1, 8, 4, 4, -1, "cuda", torch.float32)
+    with pytest.raises(TypeError):
+        kch_b200.HCADecodingCache(1, 8, 4, 4, "cuda", torch.int32)
+
+
+def test_module_tree_uses_reference_state_dict_names():
+    import kch_b200
+    from kch_b200 import synthetic as syn
+    cfg = kch_b200.HybridConfig(d_model=32, n_heads_qk=2, n_heads_v=2, head_dim_k=8, head_dim_v=8, csa_c=8, csa_dc=8,
+                                csa_cI=4, csa_nh=2, hca_c=8, hca_dc=8, hca_nh=2, csa_m=4, hca_m2=8)
+    model = kch_b200.HybridKCHAttention(cfg, total_layers=5)
+    assert model.layout == ["kda", "kda", "kda", "csa", "hca"]
+    params = syn.hybrid_params(1, cfg, 5, dtype=torch.float32)
+    assert set(params) == set(model.state_dict())
+    model.load_state_dict(params, strict=True)
+
+
+def test_install_is_reversible_when_reference_is_importable():
+    import sys
+    ref = os.environ.get("KCH_REFERENCE_DIR", "/root/reference")
+    if not os.path.isdir(ref):
+        pytest.skip("reference checkout not present")
+    sys.path.insert(0, ref)
+    try:
+        import kch_b200
+        import ops_fused
+        import ops_kda_backend
+        before = (ops_kda_backend.kda_forward, ops_fused.naive_csa, ops_fused.naive_hca)
+        done = kch_b200.install()
+        assert "ops_kda_backend.kda_forward" in done and "ops_fused.naive_csa" in done
+        assert ops_kda_backend.validate_kda_backend("b200") == "b200"
+        cfg = ops_fused.HybridConfig(kda_backend="b200")
+        assert cfg.kda_backend == "b200"
+        # CPU tensors still reach the reference implementation through the rebound globals
+        q = torch.nn.functional.normalize(torch.randn(1, 4, 2, 8), dim=-1)
+        o, _ = ops_kda_backend.kda_forward(q, q, q, -torch.rand(1, 4, 2, 8), torch.rand(1, 4, 2), backend="reference")
+        assert o.shape == (1, 4, 2, 8)
+        with pytest.raises(RuntimeError, match="CUDA"):
+            ops_kda_backend.kda_forward(q, q, q, -torch.rand(1, 4, 2, 8), torch.rand(1, 4, 2), backend="b200")
+        kch_b200.uninstall()
+        assert (ops_kda_backend.kda_forward, ops_fused.naive_csa, ops_fused.naive_hca) == before
+        with pytest.raises(ValueError):
+            ops_kda_backend.validate_kda_backend("b200")
+    finally:
+        sys.path.remove(ref)
