@@ -1,0 +1,338 @@
+"""Benchmark of the hot path: hybrid-layer prefill tokens/s.
+
+    python bench.py --gpus 1 --steps 5 --warmup 3
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
+        --master-port P bench.py --gpus N --steps K --warmup W
+    python bench.py --impl reference --gpus 1 --steps 2 --warmup 1      # CPU arm (oracle port)
+
+Workload ("hybrid_prefill_c4"): the 5-layer KDA-KDA-KDA-CSA-HCA stack, d_model 2048, 16 heads x 128,
+KDA chunk 64, CSA m=4 / top-k 1024 / 4x64 indexer / window 128 / sink, HCA ratio 128 / window 128 / sink,
+bf16, batch 4 x T=32768 of synthetic N(0,1) hidden states, random-init N(0,0.02) weights.  One step is
+one forward pass over the whole batch.  With N > 1 the heads are tensor-parallel across the GPUs (total
+work fixed: strong scaling) with one all-gather of head outputs per layer.
+
+The JSON line carries: the device-timed value, `e2e` (host buffers, H2D + D2H inside the timed region,
+through the public module API), `roofline` for the dominant kernel (the tcgen05 GEMM) measured with CUDA
+events around every launch of it during the timed steps, `cpu_baseline` (the CPU oracle port timed on a
+bounded sample on this box's cores), the clocks seen under load and the kernel-launch count.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+for _p in (os.path.join(ROOT, "kda-csa-hca-fusion_b200"), ROOT):
+    if _p not in sys.path:
+        sys.path.insert(0, _p)
+
+import torch  # noqa: E402
+
+METRIC = "hybrid_prefill_tokens_per_s"
+UNIT = "tokens/s"
+
+C4 = dict(d_model=2048, n_heads_qk=16, n_heads_v=16, head_dim_k=128, head_dim_v=128, kda_chunk_size=64, csa_m=4,
+          csa_topk=1024, csa_nh=16, csa_c=128, csa_dc=128, csa_nIh=4, csa_cI=64, csa_sliding_window=128, hca_m2=128,
+          hca_nh=16, hca_c=128, hca_dc=128, hca_sliding_window=128, n_kda=3, n_csa=1, n_hca=1)
+LAYERS = 5
+SEED = 3
+
+
+def algorithmic_flops_per_token(cfg, T):
+    """Closed-form forward FLOPs per token of one sequence of length T (multiply-add = 2), counted the way
+    the reference's analytic model does (run_kv_cache.py:286-496): dense projections, the KDA recurrence
+    and chunk terms, causal indexer entries, selected / dense compressed entries and window entries (score
+    and value products), o_proj."""
+    d, H, HV, K, V, C = (cfg[k] for k in ("d_model", "n_heads_qk", "n_heads_v", "head_dim_k", "head_dim_v",
+                                          "kda_chunk_size"))
+    kda = 2 * d * (2 * H * K + HV * V + K + HV) + 2 * K * HV * K + 2 * 3 * d      # projections + conv
+    kda += 6 * HV * K * V + HV * (3 * C * K + C * C)                               # recurrence + chunk terms
+    kda += 2 * HV * V * d                                                          # o_proj
+    m, c, cI, nIh, nh, dc, topk, win = (cfg[k] for k in ("csa_m", "csa_c", "csa_cI", "csa_nIh", "csa_nh", "csa_dc",
+                                                          "csa_topk", "csa_sliding_window"))
+    nb = T // m
+    csa = 2 * d * (4 * c + 2 * cI + dc + nIh) + 2 * dc * (nh * c + nIh * cI)
+    vis = sum((t + 1) // m for t in range(0, T, max(1, T // 4096))) / len(range(0, T, max(1, T // 4096)))
+    sel = sum(min((t + 1) // m, topk) for t in range(0, T, max(1, T // 4096))) / len(range(0, T, max(1, T // 4096)))
+    wn = sum(min(t + 1, win) for t in range(0, T, max(1, T // 4096))) / len(range(0, T, max(1, T // 4096)))
+    csa += 2 * nIh * cI * vis + 4 * nh * c * (sel + wn) + 2 * nh * c * d
+    m2, c2, nh2, dc2, win2 = (cfg[k] for k in ("hca_m2", "hca_c", "hca_nh", "hca_dc", "hca_sliding_window"))
+    vis2 = sum((t + 1) // m2 for t in range(0, T, max(1, T // 4096))) / len(range(0, T, max(1, T // 4096)))
+    wn2 = sum(min(t + 1, win2) for t in range(0, T, max(1, T // 4096))) / len(range(0, T, max(1, T // 4096)))
+    hca = 2 * d * (2 * c2 + dc2) + 2 * dc2 * nh2 * c2 + 4 * nh2 * c2 * (vis2 + wn2) + 2 * nh2 * c2 * d
+    del nb
+    return cfg["n_kda"] * kda + cfg["n_csa"] * csa + cfg["n_hca"] * hca
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks / throttle reasons while the timed region runs."""
+
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.samples, self._stop, self._t = index, [], threading.Event(), None
+
+    def _run(self):
+        while not self._stop.is_set():
+            try:
+                out = subprocess.run(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                      "-i", str(self.index)], capture_output=True, text=True, timeout=5).stdout
+                f = [s.strip() for s in out.strip().split(",")]
+                if len(f) >= 7:
+                    self.samples.append(f)
+            except Exception:
+                pass
+            self._stop.wait(0.2)
+
+    def __enter__(self):
+        self._t = threading.Thread(target=self._run, daemon=True)
+        self._t.start()
+        return self
+
+    def __exit__(self, *a):
+        self._stop.set()
+        self._t.join(timeout=6)
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        sm = sorted(float(s[0]) for s in self.samples if s[0].replace(".", "").isdigit())
+        reasons = []
+        for i, name in ((3, "hw_slowdown"), (4, "hw_thermal_slowdown"), (5, "sw_thermal_slowdown"), (6, "sw_power_cap")):
+            if any(s[i].lower().startswith("active") for s in self.samples):
+                reasons.append(name)
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": float(self.samples[0][1]),
+                "power_w_max": max(float(s[2]) for s in self.samples), "samples": len(self.samples),
+                "reasons": reasons}
+
+
+class GemmProbe:
+    """CUDA events around every kch_linear launch during the timed steps (the dominant kernel)."""
+
+    def __init__(self):
+        self.calls = []
+        self.enabled = False
+
+    def wrap(self, fn):
+        def linear(x, W, residual=None):
+            if not self.enabled:
+                return fn(x, W, residual)
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            y = fn(x, W, residual)
+            b.record()
+            M = x.numel() // x.shape[-1]
+            self.calls.append((a, b, 2.0 * M * W.shape[0] * W.shape[1], M, W.shape[0], W.shape[1]))
+            return y
+        return linear
+
+    def summary(self):
+        ms = sum(a.elapsed_time(b) for a, b, *_ in self.calls)
+        fl = sum(c[2] for c in self.calls)
+        return ms, fl, len(self.calls)
+
+
+def cpu_baseline_sample(seconds_hint=20):
+    """The oracle port of the same stack on the host cores, on a bounded sample: B=1, T=2048 of the
+    same geometry, all host threads."""
+    from kch_b200 import synthetic as syn
+    from oracle import kch_oracle as orc
+    spec = orc.HybridSpec(**C4)
+    spec.build_layout(LAYERS)
+    params = syn.hybrid_params(SEED, spec, LAYERS, dtype=torch.bfloat16)
+    T = 2048
+    x = syn.hidden_states(SEED, 1, T, C4["d_model"], torch.bfloat16)
+    with torch.no_grad():
+        t0 = time.perf_counter()
+        orc.hybrid_forward(spec, params, x)
+        dt = time.perf_counter() - t0
+    return {"value": T / dt, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
+            "sample": f"oracle port, same stack, B=1 T={T} bf16, one pass, {dt:.1f} s"}
+
+
+def run_reference(args):
+    """CPU arm: the oracle port of the reference's PyTorch path on the host cores (the reference is Python
+    and is not present on the GPU box).  Each step is a bounded sample of the workload."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from kch_b200 import synthetic as syn
+    from oracle import kch_oracle as orc
+    spec = orc.HybridSpec(**C4)
+    spec.build_layout(LAYERS)
+    params = syn.hybrid_params(SEED, spec, LAYERS, dtype=torch.bfloat16)
+    T = 1024
+    x = syn.hidden_states(SEED, 1, T, C4["d_model"], torch.bfloat16)
+    times = []
+    with torch.no_grad():
+        for i in range(args.warmup + args.steps):
+            t0 = time.perf_counter()
+            orc.hybrid_forward(spec, params, x)
+            if i >= args.warmup:
+                times.append(time.perf_counter() - t0)
+    ms = 1e3 * sum(times) / len(times)
+    val = T / (ms / 1e3)
+    sample = f"oracle port of the reference path, B=1 T={T} per step (bounded sample of B=4 T=32768)"
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "hybrid_prefill_c4", "B": 4, "T": 32768, "layers": LAYERS, **C4},
+        "cpu_baseline": {"value": val, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port", "sample": sample},
+        "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+def run_b200(args):
+    import torch.distributed as dist
+
+    import kch_b200
+    from kch_b200 import _lib, csa as csa_mod, fused as fused_mod, hca as hca_mod, synthetic as syn
+    from kch_b200.tp import TPContext, build_tp_model
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} needs {args.gpus} ranks (launch with torch.distributed.run); "
+                         f"WORLD_SIZE={world}")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    B, T = args.batch, args.seq_len
+    cfg = kch_b200.HybridConfig(**C4)
+    params = syn.hybrid_params(SEED, cfg, LAYERS, dtype=torch.bfloat16)
+    if world > 1:
+        model = build_tp_model(cfg, params, LAYERS, TPContext(rank, world, None), dev, torch.bfloat16)
+    else:
+        model = kch_b200.HybridKCHAttention(cfg, LAYERS)
+        model.load_state_dict(params, strict=True)
+        model = model.bfloat16().to(dev).eval()
+    del params
+    x_host = syn.hidden_states(SEED, B, T, cfg.d_model, torch.bfloat16).pin_memory()
+    x = x_host.to(dev)
+
+    probe = GemmProbe()
+    wrapped = probe.wrap(csa_mod.linear)
+    for mod in (csa_mod, hca_mod, fused_mod):
+        mod.linear = wrapped
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def step():
+        model.reset_state()
+        return model(x)
+
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    lib = _lib.load()
+    lib.kch_launch_count(1)
+    probe.enabled = rank == 0
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local_rank) as clocks:
+        barrier()
+        ev0.record()
+        for _ in range(args.steps):
+            y = step()
+        ev1.record()
+        barrier()
+    probe.enabled = False
+    launches = int(lib.kch_launch_count(0))
+    ms_total = ev0.elapsed_time(ev1)
+    if world > 1:
+        t = torch.tensor([ms_total], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_total = float(t.item())
+    ms = ms_total / args.steps
+    tokens = B * T
+    value = tokens / (ms / 1e3)
+
+    # end to end: host buffers in, host buffer out, copies inside the timed region
+    y_host = torch.empty(B, T, cfg.d_model, dtype=torch.bfloat16).pin_memory()
+    e2e_steps = max(1, min(args.steps, 3))
+
+    def e2e_step():
+        xd = x_host.to(dev, non_blocking=True)
+        model.reset_state()
+        yd = model(xd)
+        y_host.copy_(yd, non_blocking=True)
+
+    e2e_step()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    e1.record()
+    barrier()
+    e2e_ms = e0.elapsed_time(e1) / e2e_steps
+    if world > 1:
+        t = torch.tensor([e2e_ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t.item())
+    status = _lib.device_status()
+    if rank == 0:
+        peaks = {}
+        try:
+            peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+        except Exception:
+            pass
+        peak_tf = float(peaks.get("bf16_tflops_sustained", 1400.0))
+        peak_src = "measured (MEASURED_PEAKS.json bf16_tflops_sustained)" if peaks else "fallback 1.4 PFLOP/s sustained"
+        gemm_ms, gemm_flops, gemm_calls = probe.summary()
+        achieved = gemm_flops / (gemm_ms / 1e3) / 1e12 if gemm_ms > 0 else 0.0
+        fpt = algorithmic_flops_per_token(C4, T)
+        out = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic",
+            "config": {"workload": "hybrid_prefill_c4", "B": B, "T": T, "layers": LAYERS, "layout": model.layout_str(),
+                       "parallelism": f"tp{world}_by_heads", "l2": "inputs larger than L2 (537 MB hidden states)", **C4},
+            "e2e": {"value": tokens / (e2e_ms / 1e3), "unit": UNIT, "h2d_bytes_per_step": x_host.numel() * 2,
+                    "d2h_bytes_per_step": y_host.numel() * 2, "steps": e2e_steps, "ms_per_step": e2e_ms},
+            "gpu_launches": launches,
+            "roofline": {"bound": "tensor", "kernel": "gemm_tcgen05_kernel (all dense projections)",
+                         "achieved": achieved, "peak": peak_tf, "unit": "TFLOP/s", "frac": achieved / peak_tf,
+                         "peak_source": peak_src, "traffic": None, "launches": gemm_calls,
+                         "flops_per_step": gemm_flops / max(1, args.steps), "ms_per_step": gemm_ms / max(1, args.steps)},
+            "layer_roofline": {"flops_per_token": fpt, "achieved_tflops": value * fpt / 1e12,
+                               "frac_of_tensor_peak": value * fpt / 1e12 / peak_tf},
+            "clocks": clocks.summary(), "device_status": status,
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            out["cpu_baseline"] = cpu_baseline_sample()
+        print(json.dumps(out))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=3)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--batch", type=int, default=4)
+    ap.add_argument("--seq-len", type=int, default=32768)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_b200(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -41,6 +41,7 @@ extern "C" {
 int kch_abi_version(void);
 const char* kch_last_error(void);           /* host string, thread-local, valid until the next call */
 unsigned int kch_device_status(int reset);  /* synchronising read of the device status word (0 = clean) */
+long long kch_launch_count(int reset);      /* kernels launched by this library in this process so far */
 
 /* ---- layer glue ---------------------------------------------------------------------------- */
 

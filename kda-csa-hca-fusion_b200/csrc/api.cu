@@ -1,4 +1,5 @@
 // Error plumbing and dispatch shared by the C-ABI entry points.
+#include <atomic>
 #include <stdarg.h>
 #include <stdio.h>
 #include <stdlib.h>
@@ -12,6 +13,12 @@ void kch_set_error(const char* fmt, ...) {
   va_start(ap, fmt);
   vsnprintf(g_err, sizeof(g_err), fmt, ap);
   va_end(ap);
+}
+
+static std::atomic<long long> g_launches{0};
+void kch_note_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+extern "C" long long kch_launch_count(int reset) {
+  return reset ? g_launches.exchange(0) : g_launches.load();
 }
 
 extern "C" const char* kch_last_error(void) { return g_err; }

@@ -175,11 +175,15 @@ extern "C" int kch_cache_append_token(const kch_cache_append_args* p, void* stre
   KCH_REQUIRE(p->m >= 1, "m=%d must be >= 1", p->m);
   KCH_REQUIRE(p->acc_len >= 0 && p->acc_len < p->m, "acc_len=%d out of range for m=%d", p->acc_len, p->m);
   KCH_REQUIRE(p->dtype == KCH_F32 || p->dtype == KCH_BF16, "cache dtype tag %d unsupported", p->dtype);
+  const bool closes = p->acc_len + 1 == p->m;
   if (p->comp_kind == KCH_FP8_E4M3 || p->comp_kind == KCH_INT8)
-    KCH_REQUIRE(p->c % 64 == 0 && p->comp_scales, "block-scaled 8-bit rows need c %% 64 == 0 (c=%d) and a scale buffer", p->c);
+    KCH_REQUIRE(p->c % 64 == 0 && (!closes || p->comp_scales),
+                "block-scaled 8-bit rows need c %% 64 == 0 (c=%d) and a scale buffer", p->c);
   else
     KCH_REQUIRE(p->comp_kind == p->dtype, "comp_kind=%d must equal the cache dtype or be an 8-bit kind", p->comp_kind);
-  if (p->acc_len + 1 == p->m) KCH_REQUIRE(p->n_blocks < p->capacity, "compressed-row capacity %lld exhausted", (long long)p->capacity);
+  if (closes)
+    KCH_REQUIRE(p->comp && p->comp_norms && p->n_blocks < p->capacity, "compressed-row capacity %lld exhausted",
+                (long long)p->capacity);
   AppendArgs a;
   a.Ca = p->Ca; a.Cb = p->Cb; a.Za = p->Za; a.Zb = p->Zb; a.Ki = p->K_idx; a.Zi = p->Z_idx;
   a.ld_c = p->ld_c; a.ld_i = p->ld_i;

@@ -9,6 +9,7 @@
 
 // ---- error reporting -----------------------------------------------------------------
 void kch_set_error(const char* fmt, ...);
+void kch_note_launch(int n);   // host-side count of kernels launched by this library
 
 #define KCH_REQUIRE(cond, ...)            \
   do {                                    \
@@ -29,6 +30,7 @@ void kch_set_error(const char* fmt, ...);
 
 #define KCH_LAUNCH_OK()                                                          \
   do {                                                                           \
+    kch_note_launch(1);                                                          \
     cudaError_t _e = cudaGetLastError();                                         \
     if (_e != cudaSuccess) {                                                     \
       kch_set_error("kernel launch failed at %s:%d: %s", __FILE__, __LINE__,     \

@@ -457,6 +457,7 @@ extern "C" int kch_kda_chunk(const void* q, const void* k, const void* v, const 
   } while (0)
   KCH_DISPATCH_FLOAT(dtype, T_, GO(T_));
 #undef GO
+  kch_note_launch(1);  // two kernels per call
   KCH_LAUNCH_OK();
   return KCH_OK;
 }

@@ -47,6 +47,7 @@ PROTOTYPES = {
     "kch_abi_version": (_i, []),
     "kch_last_error": (C.c_char_p, []),
     "kch_device_status": (C.c_uint, [_i]),
+    "kch_launch_count": (C.c_longlong, [_i]),
     "kch_layernorm": (_i, [_vp, _vp, _vp, _vp, _i64, _i, _f, _i, _i, _vp]),
     "kch_short_conv": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp]),
     "kch_linear": (_i, [_vp, _vp, _vp, _vp, _i64, _i, _i, _i64, _i64, _i64, _i64, _i, _vp]),

@@ -22,6 +22,7 @@ from .csa import attend, linear, naive_csa, rownorm
 from .decoding_cache import CSADecodingCache, HCADecodingCache
 from .hca import naive_hca
 from .kda import kda_forward, validate_kda_backend
+from .tp import gather_heads
 
 
 @dataclass
@@ -177,7 +178,7 @@ class KDAHybridLayer(nn.Module):
         self.register_buffer("scale", torch.tensor(K ** -0.5), persistent=False)
         self._conv_lookback = None
         self._fused = _FusedWeights()
-        self.head_slice = None      # (first value head, count) under tensor parallelism
+        self.tp = None              # TPContext when heads are sharded across GPUs
 
     def reset_conv_state(self):
         self._conv_lookback = None
@@ -221,7 +222,8 @@ class KDAHybridLayer(nn.Module):
         o, new_state = kda_forward(q, k, v, g, beta, scale=self.scale, initial_state=state,
                                    output_final_state=True, chunk_size=cfg.kda_chunk_size, use_chunk=use_chunk,
                                    backend=cfg.kda_backend)
-        out = linear(o.reshape(B, T, HV * V), self.o_proj.weight, residual=residual)
+        o = gather_heads(o.reshape(B, T, HV * V), self.tp)
+        out = linear(o, self.o_proj.weight, residual=residual)
         return out, new_state, new_lb
 
 
@@ -248,6 +250,7 @@ class CSAHybridLayer(nn.Module):
         self.sink = nn.Parameter(torch.zeros(cfg.csa_nh))
         self.o_proj = nn.Linear(c * cfg.csa_nh, d, bias=False)
         self.use_ste = True
+        self.tp = None
         self._fused = _FusedWeights()
         self._fused_q = _FusedWeights()
 
@@ -269,7 +272,7 @@ class CSAHybridLayer(nn.Module):
                          _fused_weight=self.fused_weight(), _fused_q_weight=self.q_weight())
 
     def forward(self, x, state=None, residual=None):
-        return linear(self.core(x), self.o_proj.weight, residual=residual), None
+        return linear(gather_heads(self.core(x), self.tp), self.o_proj.weight, residual=residual), None
 
 
 class HCAHybridLayer(nn.Module):
@@ -286,6 +289,7 @@ class HCAHybridLayer(nn.Module):
         self.W_UQ = nn.Linear(cfg.hca_dc, c * cfg.hca_nh, bias=False)
         self.sink = nn.Parameter(torch.zeros(cfg.hca_nh))
         self.o_proj = nn.Linear(c * cfg.hca_nh, d, bias=False)
+        self.tp = None
         self._fused = _FusedWeights()
 
     def fused_weight(self):
@@ -299,7 +303,7 @@ class HCAHybridLayer(nn.Module):
                          return_projections=return_projections, _fused_weight=self.fused_weight())
 
     def forward(self, x, state=None, residual=None):
-        return linear(self.core(x), self.o_proj.weight, residual=residual), None
+        return linear(gather_heads(self.core(x), self.tp), self.o_proj.weight, residual=residual), None
 
 
 class _Fp32LayerNorm(nn.LayerNorm):
@@ -438,7 +442,7 @@ class HybridDecoding(nn.Module):
             o = cache.forward_step(qn, q_idx.contiguous().view(B, 1, nIh, cI).float(), w_idx.float(), topk=cfg.csa_topk,
                                    nh=nh, nIh=nIh, scale=1.0, sink_logits=layer.sink, use_ste=False, normalize_qk=True)
             o_core = o.reshape(B, 1, nh * c).to(h.dtype)
-        return linear(o_core, layer.o_proj.weight, residual=residual)
+        return linear(gather_heads(o_core, layer.tp), layer.o_proj.weight, residual=residual)
 
     def _hca(self, i, layer, h, residual):
         cfg = self.cfg
@@ -456,7 +460,7 @@ class HybridDecoding(nn.Module):
             qn = rownorm(q.view(B, 1, nh, c), True)
             o = cache.forward_step(qn, nh=nh, scale=1.0, sink_logits=layer.sink)
             o_core = o.reshape(B, 1, nh * c).to(h.dtype)
-        return linear(o_core, layer.o_proj.weight, residual=residual)
+        return linear(gather_heads(o_core, layer.tp), layer.o_proj.weight, residual=residual)
 
     @torch.no_grad()
     def forward(self, x):
