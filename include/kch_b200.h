@@ -70,10 +70,11 @@ int kch_activation(const void* x, void* y, int64_t rows, int cols, int act, floa
                    int dtype, int64_t ldx, int64_t ldy, void* stream);
 
 /* F.normalize(x.float(), dim=-1), ops_csa.py:927-936,1110-1113, ops_hca.py:135,141,155:
- * y[rows,c] fp32 = x / max(||x||,1e-12); x rows are `ld` elements apart.  `norms` (optional)
- * receives the clamped norms; y may be NULL. */
-int kch_rownorm(const void* x, int64_t ld, float* y, float* norms, int64_t rows, int c, int dtype,
-                void* stream);
+ * y[rows,c] = x / max(||x||,1e-12) evaluated in fp32 and stored as out_dtype (fp32, or bf16 for the
+ * tensor-core attention path); x rows are `ld` elements apart.  `norms` (optional) receives the
+ * clamped norms; y may be NULL. */
+int kch_rownorm(const void* x, int64_t ld, void* y, float* norms, int64_t rows, int c, int dtype,
+                int out_dtype, void* stream);
 
 /* ---- KDA ----------------------------------------------------------------------------------- */
 

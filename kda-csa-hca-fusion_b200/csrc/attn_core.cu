@@ -9,6 +9,7 @@
 // bf16 or block-scaled 8-bit (e4m3 / int8 with one fp32 scale per 64 elements), optionally divided
 // by a per-row norm (decode caches keep the stored row and its norm instead of a normalised copy).
 #include <math.h>
+#include <stdlib.h>
 
 #include "kch_common.cuh"
 
@@ -187,6 +188,9 @@ __global__ void __launch_bounds__(256) attn_generic_kernel(AttnArgs a) {
   }
 }
 
+bool kch_attend_mma_supported(const kch_attend_args* p);
+int kch_attend_mma(const kch_attend_args* p, void* stream);
+
 extern "C" int kch_attend(const kch_attend_args* p, void* stream) {
   KCH_REQUIRE(p != nullptr, "kch_attend: null args");
   KCH_REQUIRE(p->nh >= 1, "nh=%d must be >= 1", p->nh);
@@ -197,6 +201,9 @@ extern "C" int kch_attend(const kch_attend_args* p, void* stream) {
   if ((p->comp_dtype == KCH_FP8_E4M3 || p->comp_dtype == KCH_INT8))
     KCH_REQUIRE(p->comp_scales && p->c % 64 == 0, "block-scaled 8-bit rows need scales and c %% 64 == 0 (c=%d)", p->c);
   if (p->B == 0 || p->T == 0) return KCH_OK;
+  // tensor-core kernel for the production geometry; KCH_ATTEND=generic forces the fp32 CUDA-core kernel
+  static const bool force_generic = [] { const char* e = getenv("KCH_ATTEND"); return e && e[0] == 'g'; }();
+  if (!force_generic && kch_attend_mma_supported(p)) return kch_attend_mma(p, stream);
   AttnArgs a;
   a.q = p->q; a.q_dtype = p->q_dtype; a.q_ld = p->q_ld; a.q_normalize = p->q_normalize;
   a.B = p->B; a.T = p->T; a.nh = p->nh; a.c = p->c;

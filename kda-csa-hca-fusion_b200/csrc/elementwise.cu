@@ -168,8 +168,8 @@ extern "C" int kch_activation(const void* x, void* y, int64_t rows, int cols, in
 // Input rows may be strided (ld elements between rows); one warp per row.
 // `norms` (optional) receives max(||x||,eps) per row; `y` may be null when only norms are wanted.
 // ---------------------------------------------------------------------------------------
-template <typename T>
-__global__ void rownorm_kernel(const T* __restrict__ x, int64_t ld, float* __restrict__ y,
+template <typename T, typename TO>
+__global__ void rownorm_kernel(const T* __restrict__ x, int64_t ld, TO* __restrict__ y,
                                float* __restrict__ norms, int64_t rows, int c) {
   int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   int lane = threadIdx.x & 31;
@@ -183,17 +183,17 @@ __global__ void rownorm_kernel(const T* __restrict__ x, int64_t ld, float* __res
   float nrm = fmaxf(sqrtf(warp_sum(ss)), 1e-12f);
   if (norms && lane == 0) norms[row] = nrm;
   if (y)
-    for (int i = lane; i < c; i += 32) y[row * c + i] = ldf(xr + i) / nrm;
+    for (int i = lane; i < c; i += 32) stf(y + row * c + i, ldf(xr + i) / nrm);
 }
 
-extern "C" int kch_rownorm(const void* x, int64_t ld, float* y, float* norms, int64_t rows, int c,
-                           int dtype, void* stream) {
+extern "C" int kch_rownorm(const void* x, int64_t ld, void* y, float* norms, int64_t rows, int c,
+                           int dtype, int out_dtype, void* stream) {
   KCH_REQUIRE(rows >= 0 && c >= 1 && ld >= c, "kch_rownorm: rows=%lld c=%d ld=%lld", (long long)rows, c,
               (long long)ld);
   if (rows == 0) return KCH_OK;
   dim3 grid((unsigned)ceil_div64(rows, 8)), block(256);
-  KCH_DISPATCH_FLOAT(dtype, T, (rownorm_kernel<T><<<grid, block, 0, kch_stream(stream)>>>(
-      (const T*)x, ld, y, norms, rows, c)));
+  KCH_DISPATCH_FLOAT(dtype, T, KCH_DISPATCH_FLOAT(out_dtype, TO,
+      (rownorm_kernel<T, TO><<<grid, block, 0, kch_stream(stream)>>>((const T*)x, ld, (TO*)y, norms, rows, c))));
   KCH_LAUNCH_OK();
   return KCH_OK;
 }

@@ -58,11 +58,11 @@ def linear(x, W, residual=None):
     return out.reshape(*lead, N)
 
 
-def rownorm(x, normalize=True):
-    """fp32 ``F.normalize(x.float(), dim=-1)`` of a ``[..., c]`` tensor (row-strided 3-D views are read
-    in place)."""
+def rownorm(x, normalize=True, out_dtype=torch.float32):
+    """``F.normalize(x.float(), dim=-1)`` of a ``[..., c]`` tensor, evaluated in fp32 and stored as
+    ``out_dtype`` (row-strided 3-D views are read in place)."""
     if not normalize:
-        return x.float()
+        return x.to(out_dtype)
     lib = _lib.load()
     c = x.shape[-1]
     lead = x.shape[:-1]
@@ -74,10 +74,10 @@ def rownorm(x, normalize=True):
     if bsr != x3.shape[1]:
         x3, ld = x3.contiguous(), c
     rows = x3.shape[0] * x3.shape[1]
-    y = torch.empty(rows, c, dtype=torch.float32, device=x.device)
+    y = torch.empty(rows, c, dtype=out_dtype, device=x.device)
     with torch.cuda.device(x.device):
         _lib.check(lib.kch_rownorm(_lib.ptr(x3), ld, _lib.ptr(y), None, rows, c, _lib.dtype_tag(x.dtype),
-                                   _lib.stream()))
+                                   _lib.dtype_tag(out_dtype), _lib.stream()))
     return y.reshape(*lead, c)
 
 
@@ -222,6 +222,11 @@ def csa_lightning_indexer(q_idx, k_idx, w_idx, topk: int, scale=None, causal_blo
     return idx.long()
 
 
+def mma_attention_eligible(dtype, c, nh, normalize_qk, scale):
+    """Geometry served by the tensor-core attention kernel: bf16, c=128, <=16 heads, cosine scoring."""
+    return dtype == torch.bfloat16 and c == 128 and nh <= 16 and bool(normalize_qk) and abs(float(scale)) <= 16.0
+
+
 def attend(q, comp, *, nh, c, sel=None, m=0, t0=0, n_visible=-1, q_normalize=False, comp_norms=None,
            comp_scales=None, comp_kind=None, win=None, sliding_window=0, win_mode=0, win_len=0, sink=None,
            scale=1.0, out_dtype=torch.float32):
@@ -343,10 +348,12 @@ def naive_csa(H, W_aKV, W_bKV, W_aZ, W_bZ, Ba, Bb, W_DQ, W_UQ, W_IUQ, W_w, W_KV_
         indices = indexer_topk(q_idx, K_IComp, w_idx, topk, m=m, normalize_qk=normalize_qk, sorted_output=False)
     if scale is None:
         scale = 1.0 if normalize_qk else c ** -0.5
-    C_comp_n = rownorm(C_comp, normalize_qk)
+    # production geometry in bf16: unit keys are kept in bf16 for the tensor-core attention kernel
+    kdt = torch.bfloat16 if mma_attention_eligible(H.dtype, c, nh, normalize_qk, scale) else torch.float32
+    C_comp_n = rownorm(C_comp, normalize_qk, kdt)
     local = None
     if sliding_window > 0:
-        local = rownorm(Ca, normalize_qk) if normalize_qk else Ca
+        local = rownorm(Ca, normalize_qk, kdt) if normalize_qk else Ca
     out = attend(q, C_comp_n if topk > 0 else None, nh=nh, c=c, sel=indices, m=m, q_normalize=normalize_qk,
                  win=local, sliding_window=sliding_window, sink=sink_logits, scale=scale, out_dtype=H.dtype)
     out_final = out[:, :original_T]

@@ -111,7 +111,7 @@ class _CacheBase:
             if self._kind is None:
                 self._comp[:, start:start + nb] = r
                 _lib.check(lib.kch_rownorm(_lib.ptr(r), c, None, _lib.ptr(tmp_norm), B * nb, c,
-                                           _lib.dtype_tag(self.dtype), _lib.stream()))
+                                           _lib.dtype_tag(self.dtype), _lib.KCH_F32, _lib.stream()))
             else:
                 payload = torch.empty(B, nb, c, dtype=torch.uint8, device=self.device)
                 sc = torch.empty(B, nb, c // 64, dtype=torch.float32, device=self.device)

@@ -9,7 +9,7 @@ from __future__ import annotations
 import torch
 
 from . import _lib
-from .csa import attend, csa_compress_kv, linear, rownorm
+from .csa import attend, csa_compress_kv, linear, mma_attention_eligible, rownorm
 
 
 def naive_hca(H, W_KV, W_Z, B_pos, W_DQ, W_UQ, *, m2: int, nh: int, c: int, dc: int, scale: float = 1.0,
@@ -67,9 +67,10 @@ def naive_hca(H, W_KV, W_Z, B_pos, W_DQ, W_UQ, *, m2: int, nh: int, c: int, dc: 
         C, Z, cQ = proj.split([c, c, dc], dim=-1)
         C_loc = C
     C_comp = csa_compress_kv(C, Z, B_pos, m2)
-    C_comp_n = rownorm(C_comp, True)
+    kdt = torch.bfloat16 if mma_attention_eligible(H.dtype, c, nh, True, scale) else torch.float32
+    C_comp_n = rownorm(C_comp, True, kdt)
     q = linear(cQ, W_UQ)
-    local = rownorm(C_loc, True) if sliding_window > 0 else None
+    local = rownorm(C_loc, True, kdt) if sliding_window > 0 else None
     out = attend(q, C_comp_n, nh=nh, c=c, sel=None, m=m2, q_normalize=True, win=local,
                  sliding_window=sliding_window, sink=sink_logits, scale=scale, out_dtype=H.dtype)
     out_final = out[:, :original_T]

@@ -1,0 +1,116 @@
+"""Single-kernel micro-benchmarks (CUDA-event timed) for profiling one kernel of the path in isolation.
+
+    python -m kch_b200.microbench linear --M 16384 --N 2048 --K 2048
+    python -m kch_b200.microbench kda_chunk --B 1 --T 4096 --H 16
+    python -m kch_b200.microbench csa_attend --B 1 --T 4096 --topk 1024
+    python -m kch_b200.microbench compress --B 4 --T 32768
+    python -m kch_b200.microbench indexer --B 1 --T 4096
+
+Each prints one JSON line with the average launch time and the achieved algorithmic rate.  Inputs are
+seeded synthetic tensors of the benchmark geometry (K=V=c=128, 16 heads, m=4, 4x64 indexer).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+
+import torch
+
+_HERE = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+if _HERE not in sys.path:
+    sys.path.insert(0, _HERE)
+
+
+def _time(fn, iters, warmup):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(iters):
+        fn()
+    b.record()
+    torch.cuda.synchronize()
+    return a.elapsed_time(b) / iters
+
+
+def main():
+    import kch_b200
+    from kch_b200 import csa, synthetic as syn
+
+    ap = argparse.ArgumentParser()
+    ap.add_argument("kernel", choices=["linear", "kda_chunk", "kda_recurrent", "csa_attend", "hca_attend", "compress",
+                                       "indexer"])
+    ap.add_argument("--M", type=int, default=16384)
+    ap.add_argument("--N", type=int, default=2048)
+    ap.add_argument("--K", type=int, default=2048)
+    ap.add_argument("--B", type=int, default=1)
+    ap.add_argument("--T", type=int, default=4096)
+    ap.add_argument("--H", type=int, default=16)
+    ap.add_argument("--topk", type=int, default=1024)
+    ap.add_argument("--iters", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=2)
+    a = ap.parse_args()
+    dev = "cuda:0"
+    g = torch.Generator().manual_seed(1)
+    out = {"kernel": a.kernel}
+    if a.kernel == "linear":
+        x = torch.randn(a.M, a.K, generator=g).bfloat16().to(dev)
+        w = (torch.randn(a.N, a.K, generator=g) * 0.02).bfloat16().to(dev)
+        ms = _time(lambda: csa.linear(x, w), a.iters, a.warmup)
+        fl = 2.0 * a.M * a.N * a.K
+        out.update(M=a.M, N=a.N, K=a.K, ms=ms, tflops=fl / ms / 1e9, algorithmic_bytes=2.0 * (a.M * a.K + a.N * a.K + a.M * a.N))
+    elif a.kernel in ("kda_chunk", "kda_recurrent"):
+        q, k, v, gg, beta = (t.to(dev) for t in syn.kda_inputs(0, a.B, a.T, a.H, 128, 128, dtype=torch.bfloat16))
+        if a.kernel == "kda_chunk":
+            fn = lambda: kch_b200.naive_chunk_kda(q, k, v, gg, beta, output_final_state=True)  # noqa: E731
+        else:
+            fn = lambda: kch_b200.naive_recurrent_kda(q, k, v, gg, beta, output_final_state=True)  # noqa: E731
+        ms = _time(fn, a.iters, a.warmup)
+        fl = a.B * a.T * a.H * (6.0 * 128 * 128 + 3 * 64 * 128 + 64 * 64)
+        out.update(B=a.B, T=a.T, H=a.H, ms=ms, tflops=fl / ms / 1e9, tokens_per_s=a.B * a.T / ms * 1e3)
+    elif a.kernel in ("csa_attend", "hca_attend"):
+        nh, c, m = 16, 128, (4 if a.kernel == "csa_attend" else 128)
+        n = a.T // m
+        q = torch.randn(a.B, a.T, nh * c, generator=g).bfloat16().to(dev)
+        comp = csa.rownorm(torch.randn(a.B, n, c, generator=g).to(dev), True, torch.bfloat16)
+        win = csa.rownorm(torch.randn(a.B, a.T, c, generator=g).to(dev), True, torch.bfloat16)
+        sink = torch.zeros(nh, dtype=torch.bfloat16, device=dev)
+        sel = None
+        if a.kernel == "csa_attend":
+            # a valid selection per query: the first min(topk, visible) blocks, the rest -1
+            ar = torch.arange(a.topk, device=dev).view(1, 1, -1).expand(a.B, a.T, -1)
+            vis = ((torch.arange(a.T, device=dev) + 1) // m).view(1, -1, 1)
+            sel = torch.where(ar < vis, ar, torch.full_like(ar, -1)).to(torch.int32).contiguous()
+        fn = lambda: csa.attend(q, comp, nh=nh, c=c, sel=sel, m=m, q_normalize=True, win=win, sliding_window=128,  # noqa: E731
+                                sink=sink, scale=1.0, out_dtype=torch.bfloat16)
+        ms = _time(fn, a.iters, a.warmup)
+        t = torch.arange(a.T, dtype=torch.float64)
+        ent = (torch.minimum((t + 1) // m, torch.tensor(float(a.topk if sel is not None else n))) +
+               torch.minimum(t + 1, torch.tensor(128.0))).sum().item() * a.B
+        out.update(B=a.B, T=a.T, ms=ms, entries=ent, tflops=ent * 4.0 * nh * c / ms / 1e9,
+                   gather_gbs=ent * c * 2 / ms / 1e6)
+    elif a.kernel == "compress":
+        c, m = 128, 4
+        t4 = [torch.randn(a.B, a.T, c, generator=g).bfloat16().to(dev) for _ in range(4)]
+        Ba, Bb = [(torch.randn(m, c, generator=g) * 0.02).bfloat16().to(dev) for _ in range(2)]
+        ms = _time(lambda: kch_b200.csa_compress_kv_overlapped(*t4, Ba, Bb, m), a.iters, a.warmup)
+        by = a.B * a.T * c * 2 * 4 + a.B * (a.T // m) * c * 4
+        out.update(B=a.B, T=a.T, ms=ms, algorithmic_bytes=by, gbs=by / ms / 1e6)
+    elif a.kernel == "indexer":
+        HI, DI, m = 4, 64, 4
+        n = a.T // m
+        qi = torch.randn(a.B, a.T, HI, DI, generator=g).to(dev)
+        ki = torch.randn(a.B, n, DI, generator=g).to(dev)
+        wi = (torch.randn(a.B, a.T, HI, generator=g) * 0.1).to(dev)
+        ms = _time(lambda: csa.indexer_topk(qi, ki, wi, a.topk, m=m, normalize_qk=True, sorted_output=False),
+                   a.iters, a.warmup)
+        vis = float(((torch.arange(a.T, dtype=torch.float64) + 1) // m).sum()) * a.B
+        out.update(B=a.B, T=a.T, ms=ms, tflops=vis * 2 * HI * DI / ms / 1e9)
+    print(json.dumps(out))
+
+
+if __name__ == "__main__":
+    main()
