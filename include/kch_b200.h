@@ -125,6 +125,17 @@ int kch_indexer_topk(const float* q_idx, const float* k_idx, const float* w_idx,
                      int n_visible, int sorted, int64_t k_batch_stride, void* workspace,
                      int64_t workspace_bytes, void* stream);
 
+/* No counterpart in the reference (it allocates freely through PyTorch).  Same selection as
+ * kch_indexer_topk (unsorted picks), for callers that must not allocate device memory while serving:
+ * the logits live in a 16 MiB array built into the library instead of a caller workspace.  Limit:
+ * B*T*round_up(n_blocks,4) <= kch_indexer_topk_static_capacity() (4 Mi fp32); larger requests are
+ * rejected.  The first call on each device resolves the array's device address (make it before any
+ * stream capture); calls on one device share the array, so calls that overlap on the GPU race. */
+int64_t kch_indexer_topk_static_capacity(void);
+int kch_indexer_topk_static(const float* q_idx, const float* k_idx, const float* w_idx, int32_t* indices,
+                            int B, int T, int n_blocks, int HI, int DI, int topk, float scale, int m,
+                            int64_t t0, int n_visible, int64_t k_batch_stride, void* stream);
+
 /* ---- attention core ------------------------------------------------------------------------------- */
 
 /* Joint-softmax MQA over [selected | all visible] compressed entries and the sliding window, with

@@ -258,3 +258,74 @@ extern "C" int kch_indexer_topk(const float* q_idx, const float* k_idx, const fl
   KCH_LAUNCH_OK();
   return KCH_OK;
 }
+
+// ---------------------------------------------------------------------------------------
+// Allocation-free variant.
+//
+// Some callers cannot obtain device memory at the moment they need the indexer: a decode loop that
+// runs inside a serving runtime whose memory pool is frozen after start-up, or a host thread that is
+// not allowed to touch the CUDA allocator (cudaMalloc synchronises the whole device and would stall
+// every other stream of the server).  kch_indexer_topk needs a logits workspace from such a caller;
+// this entry point instead keeps the logits in a fixed array that is part of the loaded library
+// image: KCH_INDEXER_STATIC_FLOATS fp32 values (16 MiB) per GPU that loads the library, held until the
+// process exits.  That covers B*T*round_up(n_blocks,4) <= 4 Mi, e.g. a batch-64 decode step over 32768
+// cached blocks per sequence; larger requests are rejected, not truncated.
+//
+// The array name is only a host-side handle.  The device address is looked up with
+// cudaGetSymbolAddress once per device, on the first call made while that device is current, and cached.
+// Make that first call outside any stream capture (symbol lookup is not a capturable operation).
+// Every call on a device uses the same array and overwrites whatever the previous call left there; the
+// selection only reads logits written by the same call, so nothing has to be cleared in between.  Two
+// calls that overlap on the GPU (different streams, no dependency) would race on the array: order them.
+// ---------------------------------------------------------------------------------------
+#define KCH_INDEXER_STATIC_FLOATS (4u << 20)
+static __device__ __align__(256) float g_indexer_static_logits[KCH_INDEXER_STATIC_FLOATS];
+
+static int indexer_static_address(float** out) {
+  static float* cached[64] = {nullptr};
+  int dev = 0;
+  KCH_CUDA_OK(cudaGetDevice(&dev));
+  KCH_REQUIRE(dev >= 0 && dev < 64, "kch_indexer_topk_static: device ordinal %d out of range", dev);
+  if (!cached[dev]) {
+    float* p = nullptr;
+    KCH_CUDA_OK(cudaGetSymbolAddress((void**)&p, g_indexer_static_logits));
+    cached[dev] = p;
+  }
+  *out = cached[dev];
+  return KCH_OK;
+}
+
+extern "C" int64_t kch_indexer_topk_static_capacity(void) { return (int64_t)KCH_INDEXER_STATIC_FLOATS; }
+
+extern "C" int kch_indexer_topk_static(const float* q_idx, const float* k_idx, const float* w_idx,
+                                       int32_t* indices, int B, int T, int n_blocks, int HI, int DI, int topk,
+                                       float scale, int m, int64_t t0, int n_visible, int64_t k_batch_stride,
+                                       void* stream) {
+  KCH_REQUIRE(topk >= 0, "topk=%d must be >= 0 (0 selects zero blocks)", topk);
+  KCH_REQUIRE(DI >= 1, "q_idx.shape[-1]=%d must be >= 1 (indexer key dimension c_I must be positive)", DI);
+  KCH_REQUIRE(HI >= 1, "nIh=%d must be >= 1 (indexer head count)", HI);
+  KCH_REQUIRE(B >= 0 && T >= 0 && n_blocks >= 0, "kch_indexer_topk_static: B=%d T=%d n=%d", B, T, n_blocks);
+  if (B == 0 || T == 0 || topk == 0) return KCH_OK;
+  cudaStream_t s = kch_stream(stream);
+  if (n_blocks == 0) {
+    KCH_CUDA_OK(cudaMemsetAsync(indices, 0xFF, (size_t)B * T * topk * sizeof(int32_t), s));
+    return KCH_OK;
+  }
+  const int64_t n_ld = ((int64_t)n_blocks + 3) & ~3LL;
+  const int64_t need = (int64_t)B * T * n_ld;
+  KCH_REQUIRE(need <= (int64_t)KCH_INDEXER_STATIC_FLOATS,
+              "kch_indexer_topk_static: B*T*round_up(n_blocks,4) = %lld logits exceed the built-in scratch of %lld; "
+              "use kch_indexer_topk with a caller-provided workspace",
+              (long long)need, (long long)KCH_INDEXER_STATIC_FLOATS);
+  float* logits = nullptr;
+  int rc = indexer_static_address(&logits);
+  if (rc != KCH_OK) return rc;
+  dim3 g1((n_blocks + IDX_TN - 1) / IDX_TN, (T + IDX_TQ - 1) / IDX_TQ, B);
+  indexer_logits_kernel<<<g1, 256, 0, s>>>(q_idx, k_idx, w_idx, logits, T, n_blocks, HI, DI, n_ld, scale, m, t0,
+                                            n_visible, k_batch_stride > 0 ? k_batch_stride : (int64_t)n_blocks * DI);
+  KCH_LAUNCH_OK();
+  topk_select_kernel<<<(unsigned)((int64_t)B * T), 256, 0, s>>>(logits, indices, T, n_blocks, n_ld, topk, m, t0,
+                                                                 n_visible, 0);
+  KCH_LAUNCH_OK();
+  return KCH_OK;
+}

@@ -60,6 +60,8 @@ PROTOTYPES = {
     "kch_compress_kv_overlapped": (_i, [_vp] * 8 + [_i64, _vp, _i, _i64, _i, _i, _i64, _i64, _i64, _i, _i, _vp]),
     "kch_indexer_workspace_bytes": (_i64, [_i, _i, _i]),
     "kch_indexer_topk": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _i64, _i, _i, _i64, _vp, _i64, _vp]),
+    "kch_indexer_topk_static_capacity": (_i64, []),
+    "kch_indexer_topk_static": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _i64, _i, _i64, _vp]),
     "kch_attend": (_i, [C.POINTER(AttendArgs), _vp]),
     "kch_cache_append_token": (_i, [C.POINTER(CacheAppendArgs), _vp]),
     "kch_quantize_rows": (_i, [_vp, _i64, _vp, _vp, _vp, _i64, _i, _i, _i, _vp]),
