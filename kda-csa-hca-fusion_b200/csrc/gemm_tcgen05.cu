@@ -315,6 +315,18 @@ int kch_linear_tcgen05(const void* A, const void* W, void* C, const void* R, int
   return launch_tg<32>(A, W, C, R, M, N, K, lda, ldw, ldc, ldr, s);
 }
 
+unsigned int* kch_status_device_ptr() {
+  static unsigned int* cached[64] = {nullptr};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  if (!cached[dev]) {
+    unsigned int* p = nullptr;
+    if (cudaGetSymbolAddress((void**)&p, g_kch_status) != cudaSuccess) return nullptr;
+    cached[dev] = p;
+  }
+  return cached[dev];
+}
+
 extern "C" unsigned int kch_device_status(int reset) {
   unsigned int v = 0;
   if (cudaMemcpyFromSymbol(&v, g_kch_status, sizeof(v)) != cudaSuccess) return 0xFFFFFFFFu;

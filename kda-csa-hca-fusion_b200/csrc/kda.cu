@@ -403,11 +403,24 @@ static int kda_chunk_effective(int K, int chunk) {
   return C < 1 ? 1 : C;
 }
 
+// tensor-core path (kda_mma.cu)
+bool kch_kda_mma_supported(int K, int V, int chunk_size, float g_clamp_min, int dtype);
+int64_t kch_kda_mma_workspace_bytes(int B, int T, int HV);
+int kch_kda_chunk_mma(const void* q, const void* k, const void* v, const void* g, const void* beta,
+                      const float* initial_state, void* o, float* final_state, int B, int T, int H, int HV,
+                      float scale, float g_clamp_min, void* workspace, int64_t workspace_bytes, void* stream);
+
 extern "C" int64_t kch_kda_chunk_workspace_bytes(int B, int T, int HV, int K, int V, int chunk_size) {
   if (B <= 0 || T <= 0 || HV <= 0 || K <= 0 || V <= 0 || chunk_size < 1) return 0;
   int C = kda_chunk_effective(K, chunk_size);
   int NT = (T + C - 1) / C;
-  return (int64_t)kda_ws_layout(nullptr, nullptr, B, HV, K, V, C, NT);
+  int64_t need = (int64_t)kda_ws_layout(nullptr, nullptr, B, HV, K, V, C, NT);
+  // the dtype is not known here: size for whichever path may run
+  if (kch_kda_mma_supported(K, V, chunk_size, 0.f, KCH_BF16)) {
+    int64_t m = kch_kda_mma_workspace_bytes(B, T, HV);
+    if (m > need) need = m;
+  }
+  return need;
 }
 
 extern "C" int kch_kda_chunk(const void* q, const void* k, const void* v, const void* g,
@@ -425,6 +438,9 @@ extern "C" int kch_kda_chunk(const void* q, const void* k, const void* v, const 
     return kch_kda_recurrent(q, k, v, g, beta, initial_state, o, final_state, B, T, H, HV, K, V, scale,
                              g_clamp_min, dtype, stream);
   if (B == 0) return KCH_OK;
+  if (T > 0 && kch_kda_mma_supported(K, V, chunk_size, g_clamp_min, dtype))
+    return kch_kda_chunk_mma(q, k, v, g, beta, initial_state, o, final_state, B, T, H, HV, scale, g_clamp_min,
+                             workspace, workspace_bytes, stream);
   if (T == 0) {
     if (final_state) {
       size_t nb = (size_t)B * HV * K * V * sizeof(float);

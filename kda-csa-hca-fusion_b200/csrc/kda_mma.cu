@@ -1,0 +1,609 @@
+// Chunked KDA (naive_chunk_kda, ops_kda.py:340-536) on tensor cores for the production geometry:
+// bf16 inputs, K = V = 128, chunks of 64 tokens.  Same mathematics as the fp32 CUDA-core kernels in
+// kda.cu; every tensor-core product uses a two-term bf16 split of both operands (hi*hi + lo*hi + hi*lo,
+// ~16 bits of mantissa) with fp32 accumulation, so results stay within fp32 round-off of the exact form.
+//
+// Stage 1, kda_prepare_mma_kernel (one CTA per (batch, value head, chunk), fully parallel):
+//   gamma = cumsum(g).  A[i,j] = beta_i sum_k k_i k_j e^{gamma_i - gamma_j} and Aqk are built in 16x16
+//   blocks; the exponent difference is factored around a reference row that lies between j and i (the
+//   last row of the column block, or the middle row of a diagonal block), so both factors stay
+//   representable for every log-decay down to -10 per token.  (I+A)^-1 by block forward substitution,
+//   then w = T diag(beta) (e^gamma k) and u = T diag(beta) v as tensor-core products.  Everything the
+//   sequential stage needs is written as ready-to-use shared-memory images (swizzled bf16 hi/lo tiles).
+// Stage 2, kda_scan_mma_kernel (one CTA per (batch, value head, 64 value columns), sequential in chunks):
+//   the state slice S^T [64 v x 128 k] lives in fp32 MMA accumulators for the whole sequence; a producer
+//   warp streams the chunk's tiles with 1-D TMA bulk copies through a 12-stage mbarrier ring:
+//     vt^T = u^T - S^T w^T ;  o^T = S^T qg^T + vt^T Aqk^T ;  S^T <- S^T diag(dl) + vt^T kg
+//   Accumulator fragments are re-used directly as A operands (their column index is the next product's
+//   contraction index), so the state never leaves registers.
+#include <math.h>
+#include <stdlib.h>
+
+#include "mma_utils.cuh"
+
+#define KM_K 128
+#define KM_V 128
+#define KM_C 64
+#define KM_TILE 16384          // one [64][128] bf16 tile
+#define KM_OFF_WHI 0
+#define KM_OFF_WLO 16384
+#define KM_OFF_QHI 32768
+#define KM_OFF_QLO 49152
+#define KM_OFF_AQK 65536       // hi [64][64] bf16 then lo
+#define KM_OFF_KHI 81920
+#define KM_OFF_KLO 98304
+#define KM_OFF_U 114688        // per 64-column slice: u^T [64 v][64 tok] fp32, then dl [128] fp32
+#define KM_U_SLICE 16896
+#define KM_CHUNK_BYTES (KM_OFF_U + (KM_V / 64) * KM_U_SLICE)
+#define KM_STAGES 12
+#define KM_STAGE_BYTES KM_U_SLICE
+#define KM_SPIN (1u << 26)
+
+// =====================================================================================
+// Stage 1
+// =====================================================================================
+struct PrepArgs {
+  const bf16 *q, *k, *v, *g, *beta;
+  uint8_t* ws;
+  int T, H, HV, NT;
+  float scale, g_min;
+};
+
+// shared-memory map of the prepare kernel (bytes)
+#define PS_G 0                                  // gamma fp32 [64][128]            32768
+#define PS_A (PS_G + 32768)                     // A fp32 [64][68]                 17408
+#define PS_T (PS_A + 17408)                     // (I+A)^-1 fp32 [64][68]          17408
+#define PS_ST (PS_T + 17408)                    // 6 staging tiles [16][128] bf16  24576
+#define PS_Q (PS_ST + 24576)                    // Aqk fp32 [64][68]               17408
+#define PS_BETA (PS_Q + 17408)                  // beta [64], scratch P [3][16][17]
+#define PS_TOTAL (PS_BETA + 256 + 3 * 16 * 17 * 4)
+#define PS_LD 68
+// aliases (valid after the producers of the aliased regions are dead)
+#define PS_EK PS_ST                             // e^gamma k hi [64][128] bf16 then lo   (over ST + Q)
+#define PS_V PS_G                               // v bf16 [64][128]                     (over gamma, first half)
+#define PS_TB (PS_G + 16384)                    // T diag(beta) hi [64][64] bf16 then lo (over gamma, second half)
+#define PS_U PS_A                               // u^T staging 2 x [64][64] fp32        (over A + T)
+
+__global__ void __launch_bounds__(128) kda_prepare_mma_kernel(PrepArgs a) {
+  extern __shared__ __align__(128) uint8_t sm[];
+  float* sG = reinterpret_cast<float*>(sm + PS_G);
+  float* sA = reinterpret_cast<float*>(sm + PS_A);
+  float* sT = reinterpret_cast<float*>(sm + PS_T);
+  float* sQ = reinterpret_cast<float*>(sm + PS_Q);
+  float* sbeta = reinterpret_cast<float*>(sm + PS_BETA);
+  float* sP = sbeta + 64;
+  const int n = blockIdx.x, hv = blockIdx.y, b = blockIdx.z;
+  const int G = a.HV / a.H, h = hv / G;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g4 = lane >> 2, j4 = lane & 3;
+  const int t0 = n * KM_C;
+  const int64_t bh = (int64_t)b * a.HV + hv;
+  uint8_t* wsc = a.ws + (bh * a.NT + n) * (int64_t)KM_CHUNK_BYTES;
+  auto qk_off = [&](int i) { return (((int64_t)b * a.T + t0 + i) * a.H + h) * KM_K; };
+  auto gv_off = [&](int i) { return (((int64_t)b * a.T + t0 + i) * a.HV + hv) * (int64_t)KM_K; };
+
+  // ---- gamma = running sum of the clamped log-decay; thread = channel ----------------------------
+  {
+    float acc = 0.f;
+    for (int i = 0; i < KM_C; ++i) {
+      float gi = (t0 + i < a.T) ? fmaxf(__bfloat162float(a.g[gv_off(i) + tid]), a.g_min) : 0.f;
+      acc += gi;
+      sG[i * KM_K + tid] = acc;
+    }
+    if (tid < KM_C) sbeta[tid] = (t0 + tid < a.T) ? __bfloat162float(a.beta[((int64_t)b * a.T + t0 + tid) * a.HV + hv]) : 0.f;
+    for (int idx = tid; idx < KM_C * PS_LD; idx += 128) { sA[idx] = 0.f; sQ[idx] = 0.f; sT[idx] = 0.f; }
+  }
+  __syncthreads();
+
+  // ---- A and Aqk, block by block ------------------------------------------------------------------
+  // staging tiles: 0 Krow hi, 1 Krow lo, 2 Qrow hi, 3 Qrow lo, 4 Kcol hi, 5 Kcol lo
+  uint8_t* st = sm + PS_ST;
+  const int pa[10] = {0, 1, 2, 3, 1, 2, 3, 2, 3, 3};
+  const int pb[10] = {0, 1, 2, 3, 0, 1, 2, 0, 1, 0};
+  for (int p = 0; p < 10; ++p) {
+    const int ba = pa[p], bb = pb[p];
+    {
+      const int c = tid;
+      const float ref = sG[((ba == bb) ? (16 * ba + 8) : (16 * bb + 15)) * KM_K + c];
+      const uint32_t cb = (uint32_t)((c & 7) * 2);
+      for (int r = 0; r < 16; ++r) {
+        const uint32_t off = swz<256>(r, c >> 3) + cb;
+        const int i = 16 * ba + r;
+        float kv = 0.f, qv = 0.f;
+        if (t0 + i < a.T) {
+          kv = __bfloat162float(a.k[qk_off(i) + c]);
+          qv = __bfloat162float(a.q[qk_off(i) + c]) * a.scale;
+        }
+        const float e = expf(sG[i * KM_K + c] - ref);
+        bf16 hi, lo;
+        split1_bf16(kv * e, hi, lo);
+        *reinterpret_cast<bf16*>(st + 0 * 4096 + off) = hi;
+        *reinterpret_cast<bf16*>(st + 1 * 4096 + off) = lo;
+        split1_bf16(qv * e, hi, lo);
+        *reinterpret_cast<bf16*>(st + 2 * 4096 + off) = hi;
+        *reinterpret_cast<bf16*>(st + 3 * 4096 + off) = lo;
+        const int jr = 16 * bb + r;
+        float kc = (ba == bb) ? kv : ((t0 + jr < a.T) ? __bfloat162float(a.k[qk_off(jr) + c]) : 0.f);
+        const float ec = expf(ref - sG[jr * KM_K + c]);
+        split1_bf16(kc * ec, hi, lo);
+        *reinterpret_cast<bf16*>(st + 4 * 4096 + off) = hi;
+        *reinterpret_cast<bf16*>(st + 5 * 4096 + off) = lo;
+      }
+    }
+    __syncthreads();
+    {
+      const int nt = warp & 1, which = warp >> 1;   // which: 0 -> A (k rows), 1 -> Aqk (q rows)
+      const uint32_t rhi = smem_addr_u32(st + (which ? 2 : 0) * 4096), rlo = rhi + 4096;
+      const uint32_t chi = smem_addr_u32(st + 4 * 4096), clo = chi + 4096;
+      float acc[4] = {0.f, 0.f, 0.f, 0.f};
+      const int arow = (lane & 7) + ((lane >> 3) & 1) * 8;
+      const int brow = 8 * nt + (lane & 7);
+#pragma unroll
+      for (int qd = 0; qd < 4; ++qd) {
+        uint32_t ah[2][4], al[2][4], bh_[4], bl_[4];
+#pragma unroll
+        for (int kk = 0; kk < 2; ++kk) {
+          const uint32_t o = swz<256>(arow, 2 * (2 * qd + kk) + (lane >> 4));
+          ldmatrix_x4(rhi + o, ah[kk][0], ah[kk][1], ah[kk][2], ah[kk][3]);
+          ldmatrix_x4(rlo + o, al[kk][0], al[kk][1], al[kk][2], al[kk][3]);
+        }
+        const uint32_t ob = swz<256>(brow, 4 * qd + (lane >> 3));
+        ldmatrix_x4(chi + ob, bh_[0], bh_[1], bh_[2], bh_[3]);
+        ldmatrix_x4(clo + ob, bl_[0], bl_[1], bl_[2], bl_[3]);
+#pragma unroll
+        for (int kk = 0; kk < 2; ++kk) {
+          mma_bf16_16816(acc, ah[kk], bh_[2 * kk], bh_[2 * kk + 1]);
+          mma_bf16_16816(acc, al[kk], bh_[2 * kk], bh_[2 * kk + 1]);
+          mma_bf16_16816(acc, ah[kk], bl_[2 * kk], bl_[2 * kk + 1]);
+        }
+      }
+      const int i0 = 16 * ba + g4, i1 = i0 + 8;
+      const int jc = 16 * bb + 8 * nt + 2 * j4;
+      if (which == 0) {
+        sA[i0 * PS_LD + jc] = (jc < i0) ? acc[0] * sbeta[i0] : 0.f;
+        sA[i0 * PS_LD + jc + 1] = (jc + 1 < i0) ? acc[1] * sbeta[i0] : 0.f;
+        sA[i1 * PS_LD + jc] = (jc < i1) ? acc[2] * sbeta[i1] : 0.f;
+        sA[i1 * PS_LD + jc + 1] = (jc + 1 < i1) ? acc[3] * sbeta[i1] : 0.f;
+      } else {
+        sQ[i0 * PS_LD + jc] = (jc <= i0) ? acc[0] : 0.f;
+        sQ[i0 * PS_LD + jc + 1] = (jc + 1 <= i0) ? acc[1] : 0.f;
+        sQ[i1 * PS_LD + jc] = (jc <= i1) ? acc[2] : 0.f;
+        sQ[i1 * PS_LD + jc + 1] = (jc + 1 <= i1) ? acc[3] : 0.f;
+      }
+    }
+    __syncthreads();
+  }
+
+  // ---- Aqk -> workspace as swizzled bf16 hi/lo tiles [64][64] --------------------------------------
+  for (int idx = tid; idx < KM_C * 8; idx += 128) {
+    const int i = idx >> 3, ch = idx & 7;
+    uint32_t hi[4], lo[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) split2_bf16(sQ[i * PS_LD + 8 * ch + 2 * e], sQ[i * PS_LD + 8 * ch + 2 * e + 1], hi[e], lo[e]);
+    const uint32_t off = swz<128>(i, ch);
+    *reinterpret_cast<uint4*>(wsc + KM_OFF_AQK + off) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+    *reinterpret_cast<uint4*>(wsc + KM_OFF_AQK + 8192 + off) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+  }
+  __syncthreads();   // sQ is dead from here: the e^gamma k tiles may overwrite it
+
+  // ---- qg, kg (workspace), e^gamma k (shared), dl ------------------------------------------------------
+  for (int idx = tid; idx < KM_C * 16; idx += 128) {
+    const int i = idx >> 4, ch = idx & 15;
+    float kf[8], qf[8];
+    if (t0 + i < a.T) {
+      uint4 kr = *reinterpret_cast<const uint4*>(a.k + qk_off(i) + 8 * ch);
+      uint4 qr = *reinterpret_cast<const uint4*>(a.q + qk_off(i) + 8 * ch);
+      const bf16* kp = reinterpret_cast<const bf16*>(&kr);
+      const bf16* qp = reinterpret_cast<const bf16*>(&qr);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) { kf[e] = __bfloat162float(kp[e]); qf[e] = __bfloat162float(qp[e]) * a.scale; }
+    } else {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) { kf[e] = 0.f; qf[e] = 0.f; }
+    }
+    uint32_t qh[4], ql[4], kh[4], kl[4], eh[4], el[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int c0 = 8 * ch + 2 * e;
+      const float g0 = sG[i * KM_K + c0], g1 = sG[i * KM_K + c0 + 1];
+      const float gl0 = sG[(KM_C - 1) * KM_K + c0], gl1 = sG[(KM_C - 1) * KM_K + c0 + 1];
+      const float e0 = expf(g0), e1 = expf(g1);
+      split2_bf16(qf[2 * e] * e0, qf[2 * e + 1] * e1, qh[e], ql[e]);
+      split2_bf16(kf[2 * e] * expf(gl0 - g0), kf[2 * e + 1] * expf(gl1 - g1), kh[e], kl[e]);
+      split2_bf16(kf[2 * e] * e0, kf[2 * e + 1] * e1, eh[e], el[e]);
+    }
+    const uint32_t off = swz<256>(i, ch);
+    *reinterpret_cast<uint4*>(wsc + KM_OFF_QHI + off) = make_uint4(qh[0], qh[1], qh[2], qh[3]);
+    *reinterpret_cast<uint4*>(wsc + KM_OFF_QLO + off) = make_uint4(ql[0], ql[1], ql[2], ql[3]);
+    *reinterpret_cast<uint4*>(wsc + KM_OFF_KHI + off) = make_uint4(kh[0], kh[1], kh[2], kh[3]);
+    *reinterpret_cast<uint4*>(wsc + KM_OFF_KLO + off) = make_uint4(kl[0], kl[1], kl[2], kl[3]);
+    *reinterpret_cast<uint4*>(sm + PS_EK + off) = make_uint4(eh[0], eh[1], eh[2], eh[3]);
+    *reinterpret_cast<uint4*>(sm + PS_EK + KM_TILE + off) = make_uint4(el[0], el[1], el[2], el[3]);
+  }
+  {
+    const float dl = expf(sG[(KM_C - 1) * KM_K + tid]);
+#pragma unroll
+    for (int s = 0; s < KM_V / 64; ++s)
+      reinterpret_cast<float*>(wsc + KM_OFF_U + s * KM_U_SLICE + 16384)[tid] = dl;
+  }
+
+  // ---- (I + A)^-1 by block forward substitution (fp32, CUDA cores) ------------------------------------
+  // diagonal 16x16 blocks: one thread per (block, column)
+  if (tid < 64) {
+    const int blk = tid >> 4, cc = tid & 15, base = 16 * blk;
+    for (int r = 0; r < 16; ++r) {
+      float x = (r == cc) ? 1.f : 0.f;
+      if (r > cc) {
+        float acc = 0.f;
+        for (int s = cc; s < r; ++s) acc = fmaf(sA[(base + r) * PS_LD + base + s], sT[(base + s) * PS_LD + base + cc], acc);
+        x = -acc;
+      }
+      sT[(base + r) * PS_LD + base + cc] = x;
+    }
+  }
+  __syncthreads();
+  // off-diagonal blocks, by distance d from the diagonal:  T_ab = -T_aa (sum_{b<=c<a} A_ac T_cb)
+  for (int d = 1; d < 4; ++d) {
+    const int nblk = 4 - d;
+    for (int idx = tid; idx < nblk * 256; idx += 128) {
+      const int bi = idx >> 8, r = (idx >> 4) & 15, cc = idx & 15;
+      const int ba = bi + d, bb = bi;
+      float acc = 0.f;
+      for (int cblk = bb; cblk < ba; ++cblk)
+#pragma unroll 4
+        for (int s = 0; s < 16; ++s)
+          acc = fmaf(sA[(16 * ba + r) * PS_LD + 16 * cblk + s], sT[(16 * cblk + s) * PS_LD + 16 * bb + cc], acc);
+      sP[(bi * 16 + r) * 17 + cc] = acc;
+    }
+    __syncthreads();
+    for (int idx = tid; idx < nblk * 256; idx += 128) {
+      const int bi = idx >> 8, r = (idx >> 4) & 15, cc = idx & 15;
+      const int ba = bi + d, bb = bi;
+      float acc = 0.f;
+#pragma unroll 4
+      for (int s = 0; s <= r; ++s) acc = fmaf(sT[(16 * ba + r) * PS_LD + 16 * ba + s], sP[(bi * 16 + s) * 17 + cc], acc);
+      sT[(16 * ba + r) * PS_LD + 16 * bb + cc] = -acc;
+    }
+    __syncthreads();
+  }
+  // T diag(beta) as swizzled bf16 hi/lo tiles (over the dead gamma buffer), v tile next to it
+  for (int idx = tid; idx < KM_C * 8; idx += 128) {
+    const int i = idx >> 3, ch = idx & 7;
+    uint32_t hi[4], lo[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int jj = 8 * ch + 2 * e;
+      split2_bf16(sT[i * PS_LD + jj] * sbeta[jj], sT[i * PS_LD + jj + 1] * sbeta[jj + 1], hi[e], lo[e]);
+    }
+    const uint32_t off = swz<128>(i, ch);
+    *reinterpret_cast<uint4*>(sm + PS_TB + off) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+    *reinterpret_cast<uint4*>(sm + PS_TB + 8192 + off) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+  }
+  for (int idx = tid; idx < KM_C * 16; idx += 128) {
+    const int i = idx >> 4, ch = idx & 15;
+    uint4 vr = make_uint4(0u, 0u, 0u, 0u);
+    if (t0 + i < a.T) vr = *reinterpret_cast<const uint4*>(a.v + gv_off(i) + 8 * ch);   // V == K here
+    *reinterpret_cast<uint4*>(sm + PS_V + swz<256>(i, ch)) = vr;
+  }
+  __syncthreads();
+
+  // ---- w = Tb (e^gamma k), u = Tb v : warp = 16-row tile, lower-triangular k-steps only ---------------
+  float wacc[16][4], uacc[16][4];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) { wacc[i][0] = wacc[i][1] = wacc[i][2] = wacc[i][3] = 0.f; uacc[i][0] = uacc[i][1] = uacc[i][2] = uacc[i][3] = 0.f; }
+  {
+    const uint32_t tbh = smem_addr_u32(sm + PS_TB), tbl = tbh + 8192;
+    const uint32_t ekh = smem_addr_u32(sm + PS_EK), ekl = ekh + KM_TILE, vv = smem_addr_u32(sm + PS_V);
+    const int arow = 16 * warp + (lane & 7) + ((lane >> 3) & 1) * 8;
+    for (int ks = 0; ks <= warp; ++ks) {
+      uint32_t ah[4], al[4];
+      const uint32_t oa = swz<128>(arow, 2 * ks + (lane >> 4));
+      ldmatrix_x4(tbh + oa, ah[0], ah[1], ah[2], ah[3]);
+      ldmatrix_x4(tbl + oa, al[0], al[1], al[2], al[3]);
+      const int brow = 16 * ks + ((lane >> 3) & 1) * 8 + (lane & 7);
+#pragma unroll
+      for (int dp = 0; dp < 8; ++dp) {
+        const uint32_t ob = swz<256>(brow, 2 * dp + (lane >> 4));
+        uint32_t h0, h1, h2, h3, l0, l1, l2, l3, v0, v1, v2, v3;
+        ldmatrix_x4_trans(ekh + ob, h0, h1, h2, h3);
+        ldmatrix_x4_trans(ekl + ob, l0, l1, l2, l3);
+        ldmatrix_x4_trans(vv + ob, v0, v1, v2, v3);
+        mma_bf16_16816(wacc[2 * dp], ah, h0, h1);     mma_bf16_16816(wacc[2 * dp + 1], ah, h2, h3);
+        mma_bf16_16816(wacc[2 * dp], al, h0, h1);     mma_bf16_16816(wacc[2 * dp + 1], al, h2, h3);
+        mma_bf16_16816(wacc[2 * dp], ah, l0, l1);     mma_bf16_16816(wacc[2 * dp + 1], ah, l2, l3);
+        mma_bf16_16816(uacc[2 * dp], ah, v0, v1);     mma_bf16_16816(uacc[2 * dp + 1], ah, v2, v3);
+        mma_bf16_16816(uacc[2 * dp], al, v0, v1);     mma_bf16_16816(uacc[2 * dp + 1], al, v2, v3);
+      }
+    }
+  }
+  // w -> workspace (swizzled hi/lo); u^T -> shared staging (over A and T, dead now) -> workspace
+  {
+    const int i0 = 16 * warp + g4, i1 = i0 + 8;
+    float* us = reinterpret_cast<float*>(sm + PS_U);
+#pragma unroll
+    for (int nt = 0; nt < 16; ++nt) {
+      uint32_t hi, lo;
+      split2_bf16(wacc[nt][0], wacc[nt][1], hi, lo);
+      *reinterpret_cast<uint32_t*>(wsc + KM_OFF_WHI + swz<256>(i0, nt) + 4 * j4) = hi;
+      *reinterpret_cast<uint32_t*>(wsc + KM_OFF_WLO + swz<256>(i0, nt) + 4 * j4) = lo;
+      split2_bf16(wacc[nt][2], wacc[nt][3], hi, lo);
+      *reinterpret_cast<uint32_t*>(wsc + KM_OFF_WHI + swz<256>(i1, nt) + 4 * j4) = hi;
+      *reinterpret_cast<uint32_t*>(wsc + KM_OFF_WLO + swz<256>(i1, nt) + 4 * j4) = lo;
+    }
+    __syncthreads();   // every warp has finished reading T/A-aliased operands? (T, A are not read by the MMAs) -> staging is free
+#pragma unroll
+    for (int nt = 0; nt < 16; ++nt) {
+      const int c0 = 8 * nt + 2 * j4;            // value column
+      float* s0 = us + (c0 >> 6) * 4096 + (c0 & 63) * 64;
+      s0[i0] = uacc[nt][0];
+      s0[64 + i0] = uacc[nt][1];
+      s0[i1] = uacc[nt][2];
+      s0[64 + i1] = uacc[nt][3];
+    }
+  }
+  __syncthreads();
+  {
+    const float4* us4 = reinterpret_cast<const float4*>(sm + PS_U);
+#pragma unroll
+    for (int s = 0; s < KM_V / 64; ++s) {
+      float4* dst = reinterpret_cast<float4*>(wsc + KM_OFF_U + s * KM_U_SLICE);
+      for (int idx = tid; idx < 1024; idx += 128) dst[idx] = us4[s * 1024 + idx];
+    }
+  }
+}
+
+// =====================================================================================
+// Stage 2
+// =====================================================================================
+struct ScanArgs {
+  const uint8_t* ws;
+  const float* S0;
+  bf16* o;
+  float* S_out;
+  unsigned int* status;
+  int T, HV, NT;
+};
+
+#define SC_OSTAGE (KM_STAGES * KM_STAGE_BYTES)          // 4 warps x [64 tok][16 v] bf16
+#define SC_BARS (SC_OSTAGE + 4 * 64 * 16 * 2)
+#define SC_TOTAL (SC_BARS + 2 * KM_STAGES * 8)
+
+__global__ void __launch_bounds__(160, 1) kda_scan_mma_kernel(ScanArgs a) {
+  extern __shared__ __align__(1024) uint8_t sm[];
+  uint64_t* full = reinterpret_cast<uint64_t*>(sm + SC_BARS);
+  uint64_t* empty = full + KM_STAGES;
+  const int vs = blockIdx.x, hv = blockIdx.y, b = blockIdx.z;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g4 = lane >> 2, j4 = lane & 3;
+  const int64_t bh = (int64_t)b * a.HV + hv;
+  const uint8_t* wsb = a.ws + bh * a.NT * (int64_t)KM_CHUNK_BYTES;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < KM_STAGES; ++s) { mbarrier_init(&full[s], 1); mbarrier_init(&empty[s], 4); }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+
+  if (warp == 4) {
+    // ---------------- producer: one elected lane streams 8 tiles per chunk ----------------
+    if (lane == 0) {
+      const uint32_t src_off[8] = {KM_OFF_WHI, KM_OFF_WLO, KM_OFF_QHI, KM_OFF_QLO,
+                                   (uint32_t)(KM_OFF_U + vs * KM_U_SLICE), KM_OFF_AQK, KM_OFF_KHI, KM_OFF_KLO};
+      uint32_t it = 0;
+      bool ok = true;
+      for (int n = 0; n < a.NT && ok; ++n) {
+        const uint8_t* src = wsb + (int64_t)n * KM_CHUNK_BYTES;
+        for (int tl = 0; tl < 8; ++tl, ++it) {
+          const uint32_t s = it % KM_STAGES, ph = (it / KM_STAGES) & 1;
+          if (!mbarrier_wait_bounded(&empty[s], ph ^ 1, 11, KM_SPIN, a.status)) { ok = false; break; }
+          const uint32_t bytes = (tl == 4) ? KM_U_SLICE : KM_TILE;
+          mbarrier_expect_tx(&full[s], bytes);
+          bulk_copy_g2s(sm + s * KM_STAGE_BYTES, src + src_off[tl], bytes, &full[s]);
+        }
+      }
+      if (!ok) {   // let copies already issued land before the CTA retires
+        for (uint32_t back = 0; back < KM_STAGES && back < it; ++back) {
+          const uint32_t jt = it - 1 - back;
+          mbarrier_wait_bounded(&full[jt % KM_STAGES], (jt / KM_STAGES) & 1, 12, 1u << 20, a.status);
+        }
+      }
+    }
+    return;
+  }
+
+  // ---------------- consumers: warp w owns value columns vs*64 + 16w .. +15 ----------------
+  const int vrow = vs * 64 + 16 * warp;            // global value column of accumulator row 0
+  float sacc[16][4];                               // S^T rows (v) g4, g4+8; cols (k) 8nt + 2j4, +1
+#pragma unroll
+  for (int nt = 0; nt < 16; ++nt) {
+    const int kc = 8 * nt + 2 * j4;
+    if (a.S0) {
+      const float* s0 = a.S0 + bh * (KM_K * KM_V);
+      sacc[nt][0] = s0[(int64_t)kc * KM_V + vrow + g4];
+      sacc[nt][1] = s0[(int64_t)(kc + 1) * KM_V + vrow + g4];
+      sacc[nt][2] = s0[(int64_t)kc * KM_V + vrow + g4 + 8];
+      sacc[nt][3] = s0[(int64_t)(kc + 1) * KM_V + vrow + g4 + 8];
+    } else {
+      sacc[nt][0] = sacc[nt][1] = sacc[nt][2] = sacc[nt][3] = 0.f;
+    }
+  }
+  bf16* ost = reinterpret_cast<bf16*>(sm + SC_OSTAGE) + warp * (64 * 16);
+  bool ok = true;
+  auto wait_tile = [&](uint32_t it) -> uint32_t {
+    const uint32_t s = it % KM_STAGES;
+    if (ok && !mbarrier_wait_bounded(&full[s], (it / KM_STAGES) & 1, 13, KM_SPIN, a.status)) ok = false;
+    return smem_addr_u32(sm + s * KM_STAGE_BYTES);
+  };
+  auto release_tile = [&](uint32_t it) {
+    __syncwarp();
+    if (lane == 0) mbarrier_arrive(&empty[it % KM_STAGES]);
+  };
+
+  for (int n = 0; n < a.NT && ok; ++n) {
+    const uint32_t it0 = (uint32_t)n * 8;
+    // ======== phase 1: -(S^T w^T) and S^T qg^T =========================================================
+    const uint32_t whi = wait_tile(it0 + 0), wlo = wait_tile(it0 + 1), qhi = wait_tile(it0 + 2), qlo = wait_tile(it0 + 3);
+    if (!ok) break;
+    float accw[8][4], accq[8][4];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { accw[i][0] = accw[i][1] = accw[i][2] = accw[i][3] = 0.f; accq[i][0] = accq[i][1] = accq[i][2] = accq[i][3] = 0.f; }
+#pragma unroll
+    for (int qd = 0; qd < 4; ++qd) {
+      uint32_t ah[2][4], al[2][4];
+#pragma unroll
+      for (int kk = 0; kk < 2; ++kk) {
+        const int n0 = 4 * qd + 2 * kk;
+        split2_bf16(sacc[n0][0], sacc[n0][1], ah[kk][0], al[kk][0]);
+        split2_bf16(sacc[n0][2], sacc[n0][3], ah[kk][1], al[kk][1]);
+        split2_bf16(sacc[n0 + 1][0], sacc[n0 + 1][1], ah[kk][2], al[kk][2]);
+        split2_bf16(sacc[n0 + 1][2], sacc[n0 + 1][3], ah[kk][3], al[kk][3]);
+      }
+#pragma unroll
+      for (int nt = 0; nt < 8; ++nt) {
+        const uint32_t off = swz<256>(8 * nt + (lane & 7), 4 * qd + (lane >> 3));
+        uint32_t h0, h1, h2, h3, l0, l1, l2, l3;
+        ldmatrix_x4(whi + off, h0, h1, h2, h3);
+        ldmatrix_x4(wlo + off, l0, l1, l2, l3);
+        mma_bf16_16816(accw[nt], ah[0], h0, h1); mma_bf16_16816(accw[nt], ah[1], h2, h3);
+        mma_bf16_16816(accw[nt], al[0], h0, h1); mma_bf16_16816(accw[nt], al[1], h2, h3);
+        mma_bf16_16816(accw[nt], ah[0], l0, l1); mma_bf16_16816(accw[nt], ah[1], l2, l3);
+        ldmatrix_x4(qhi + off, h0, h1, h2, h3);
+        ldmatrix_x4(qlo + off, l0, l1, l2, l3);
+        mma_bf16_16816(accq[nt], ah[0], h0, h1); mma_bf16_16816(accq[nt], ah[1], h2, h3);
+        mma_bf16_16816(accq[nt], al[0], h0, h1); mma_bf16_16816(accq[nt], al[1], h2, h3);
+        mma_bf16_16816(accq[nt], ah[0], l0, l1); mma_bf16_16816(accq[nt], ah[1], l2, l3);
+      }
+    }
+    release_tile(it0 + 0); release_tile(it0 + 1); release_tile(it0 + 2); release_tile(it0 + 3);
+    // ======== vt^T = u^T - S^T w^T, kept as split A fragments for the next two products ================
+    const uint32_t ut_addr = wait_tile(it0 + 4);
+    if (!ok) break;
+    const float* ut = reinterpret_cast<const float*>(sm + (it0 + 4) % KM_STAGES * KM_STAGE_BYTES);
+    (void)ut_addr;
+    uint32_t vh[4][4], vl[4][4];
+#pragma unroll
+    for (int ks = 0; ks < 4; ++ks) {
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        const int nt = 2 * ks + half;
+        const float2 u0 = *reinterpret_cast<const float2*>(ut + (16 * warp + g4) * 64 + 8 * nt + 2 * j4);
+        const float2 u1 = *reinterpret_cast<const float2*>(ut + (16 * warp + g4 + 8) * 64 + 8 * nt + 2 * j4);
+        split2_bf16(u0.x - accw[nt][0], u0.y - accw[nt][1], vh[ks][2 * half], vl[ks][2 * half]);
+        split2_bf16(u1.x - accw[nt][2], u1.y - accw[nt][3], vh[ks][2 * half + 1], vl[ks][2 * half + 1]);
+      }
+    }
+    // ======== phase 2: o^T = S^T qg^T + vt^T Aqk^T ====================================================
+    const uint32_t aqh = wait_tile(it0 + 5);
+    if (!ok) break;
+    const uint32_t aql = aqh + 8192;
+#pragma unroll
+    for (int qd = 0; qd < 2; ++qd) {
+#pragma unroll
+      for (int nt = 0; nt < 8; ++nt) {
+        if (8 * nt + 7 < 32 * qd) continue;          // block entirely above the diagonal: zeros
+        const uint32_t off = swz<128>(8 * nt + (lane & 7), 4 * qd + (lane >> 3));
+        uint32_t h0, h1, h2, h3, l0, l1, l2, l3;
+        ldmatrix_x4(aqh + off, h0, h1, h2, h3);
+        ldmatrix_x4(aql + off, l0, l1, l2, l3);
+        mma_bf16_16816(accq[nt], vh[2 * qd], h0, h1); mma_bf16_16816(accq[nt], vh[2 * qd + 1], h2, h3);
+        mma_bf16_16816(accq[nt], vl[2 * qd], h0, h1); mma_bf16_16816(accq[nt], vl[2 * qd + 1], h2, h3);
+        mma_bf16_16816(accq[nt], vh[2 * qd], l0, l1); mma_bf16_16816(accq[nt], vh[2 * qd + 1], l2, l3);
+      }
+    }
+    release_tile(it0 + 5);
+    // o^T fragments -> [tok][16 v] bf16 staging -> 32-byte row segments of o[b, t, hv, :]
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt) {
+      const int tk = 8 * nt + 2 * j4;
+      ost[tk * 16 + g4] = __float2bfloat16_rn(accq[nt][0]);
+      ost[(tk + 1) * 16 + g4] = __float2bfloat16_rn(accq[nt][1]);
+      ost[tk * 16 + g4 + 8] = __float2bfloat16_rn(accq[nt][2]);
+      ost[(tk + 1) * 16 + g4 + 8] = __float2bfloat16_rn(accq[nt][3]);
+    }
+    __syncwarp();
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int tk = lane + 32 * half;
+      const int t = n * KM_C + tk;
+      if (t < a.T) {
+        const uint4* src = reinterpret_cast<const uint4*>(ost + tk * 16);
+        uint4* dst = reinterpret_cast<uint4*>(a.o + (((int64_t)b * a.T + t) * a.HV + hv) * KM_V + vrow);
+        dst[0] = src[0];
+        dst[1] = src[1];
+      }
+    }
+    __syncwarp();
+    // ======== phase 3: S^T <- S^T diag(dl) + vt^T kg ====================================================
+    {
+      const float* dl = ut + 4096;
+#pragma unroll
+      for (int nt = 0; nt < 16; ++nt) {
+        const float2 d = *reinterpret_cast<const float2*>(dl + 8 * nt + 2 * j4);
+        sacc[nt][0] *= d.x; sacc[nt][1] *= d.y; sacc[nt][2] *= d.x; sacc[nt][3] *= d.y;
+      }
+    }
+    release_tile(it0 + 4);
+    const uint32_t khi = wait_tile(it0 + 6), klo = wait_tile(it0 + 7);
+    if (!ok) break;
+#pragma unroll
+    for (int ks = 0; ks < 4; ++ks) {
+      const int brow = 16 * ks + ((lane >> 3) & 1) * 8 + (lane & 7);
+#pragma unroll
+      for (int dp = 0; dp < 8; ++dp) {
+        const uint32_t off = swz<256>(brow, 2 * dp + (lane >> 4));
+        uint32_t h0, h1, h2, h3, l0, l1, l2, l3;
+        ldmatrix_x4_trans(khi + off, h0, h1, h2, h3);
+        ldmatrix_x4_trans(klo + off, l0, l1, l2, l3);
+        mma_bf16_16816(sacc[2 * dp], vh[ks], h0, h1); mma_bf16_16816(sacc[2 * dp + 1], vh[ks], h2, h3);
+        mma_bf16_16816(sacc[2 * dp], vl[ks], h0, h1); mma_bf16_16816(sacc[2 * dp + 1], vl[ks], h2, h3);
+        mma_bf16_16816(sacc[2 * dp], vh[ks], l0, l1); mma_bf16_16816(sacc[2 * dp + 1], vh[ks], l2, l3);
+      }
+    }
+    release_tile(it0 + 6); release_tile(it0 + 7);
+  }
+  if (a.S_out && ok) {
+    float* so = a.S_out + bh * (KM_K * KM_V);
+#pragma unroll
+    for (int nt = 0; nt < 16; ++nt) {
+      const int kc = 8 * nt + 2 * j4;
+      so[(int64_t)kc * KM_V + vrow + g4] = sacc[nt][0];
+      so[(int64_t)(kc + 1) * KM_V + vrow + g4] = sacc[nt][1];
+      so[(int64_t)kc * KM_V + vrow + g4 + 8] = sacc[nt][2];
+      so[(int64_t)(kc + 1) * KM_V + vrow + g4 + 8] = sacc[nt][3];
+    }
+  }
+}
+
+// ---- host -------------------------------------------------------------------------------------------
+bool kch_kda_mma_supported(int K, int V, int chunk_size, float g_clamp_min, int dtype) {
+  static const bool force_generic = [] { const char* e = getenv("KCH_KDA"); return e && e[0] == 'g'; }();
+  return !force_generic && dtype == KCH_BF16 && K == KM_K && V == KM_V && chunk_size == KM_C && g_clamp_min >= -10.0f;
+}
+
+int64_t kch_kda_mma_workspace_bytes(int B, int T, int HV) {
+  int64_t NT = (T + KM_C - 1) / KM_C;
+  return (int64_t)B * HV * NT * KM_CHUNK_BYTES;
+}
+
+int kch_kda_chunk_mma(const void* q, const void* k, const void* v, const void* g, const void* beta,
+                      const float* initial_state, void* o, float* final_state, int B, int T, int H, int HV,
+                      float scale, float g_clamp_min, void* workspace, int64_t workspace_bytes, void* stream) {
+  const int NT = (T + KM_C - 1) / KM_C;
+  KCH_REQUIRE(workspace && workspace_bytes >= kch_kda_mma_workspace_bytes(B, T, HV),
+              "kch_kda_chunk: workspace %lld < %lld bytes", (long long)workspace_bytes,
+              (long long)kch_kda_mma_workspace_bytes(B, T, HV));
+  KCH_REQUIRE(((uintptr_t)workspace & 15) == 0, "kch_kda_chunk: workspace must be 16-byte aligned");
+  unsigned int* status = kch_status_device_ptr();
+  KCH_REQUIRE(status != nullptr, "kch_kda_chunk: cannot resolve the device status word");
+  cudaStream_t s = kch_stream(stream);
+  PrepArgs pa;
+  pa.q = (const bf16*)q; pa.k = (const bf16*)k; pa.v = (const bf16*)v; pa.g = (const bf16*)g; pa.beta = (const bf16*)beta;
+  pa.ws = (uint8_t*)workspace; pa.T = T; pa.H = H; pa.HV = HV; pa.NT = NT; pa.scale = scale; pa.g_min = g_clamp_min;
+  KCH_CUDA_OK(cudaFuncSetAttribute(kda_prepare_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PS_TOTAL));
+  kda_prepare_mma_kernel<<<dim3(NT, HV, B), 128, PS_TOTAL, s>>>(pa);
+  KCH_LAUNCH_OK();
+  ScanArgs sa;
+  sa.ws = (const uint8_t*)workspace; sa.S0 = initial_state; sa.o = (bf16*)o; sa.S_out = final_state; sa.status = status;
+  sa.T = T; sa.HV = HV; sa.NT = NT;
+  KCH_CUDA_OK(cudaFuncSetAttribute(kda_scan_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SC_TOTAL));
+  kda_scan_mma_kernel<<<dim3(KM_V / 64, HV, B), 160, SC_TOTAL, s>>>(sa);
+  KCH_LAUNCH_OK();
+  return KCH_OK;
+}

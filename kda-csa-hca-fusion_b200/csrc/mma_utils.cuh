@@ -1,0 +1,80 @@
+// Warp-level tensor-core and async-copy helpers shared by the attention and KDA kernels.
+#pragma once
+#include "kch_common.cuh"
+
+__device__ __forceinline__ uint32_t smem_addr_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+// D[16x8] += A[16x16] * B[16x8], bf16 operands, fp32 accumulation
+__device__ __forceinline__ void mma_bf16_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack2_bf16(float lo, float hi) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+// Two-term bf16 split of a pair of fp32 values: x ~= hi + lo with ~16 bits of mantissa in total.
+__device__ __forceinline__ void split2_bf16(float x0, float x1, uint32_t& hi, uint32_t& lo) {
+  __nv_bfloat16 h0 = __float2bfloat16_rn(x0), h1 = __float2bfloat16_rn(x1);
+  __nv_bfloat162 hh, ll;
+  hh.x = h0; hh.y = h1;
+  ll.x = __float2bfloat16_rn(x0 - __bfloat162float(h0));
+  ll.y = __float2bfloat16_rn(x1 - __bfloat162float(h1));
+  hi = *reinterpret_cast<uint32_t*>(&hh);
+  lo = *reinterpret_cast<uint32_t*>(&ll);
+}
+__device__ __forceinline__ void split1_bf16(float x, bf16& hi, bf16& lo) {
+  hi = __float2bfloat16_rn(x);
+  lo = __float2bfloat16_rn(x - __bfloat162float(hi));
+}
+
+// Byte offset of 16-byte chunk `chunk` of row `row` in a tile whose rows are ROWBYTES long, with the
+// chunk index XOR-swizzled by the low row bits (conflict-free ldmatrix for 128- and 256-byte rows).
+template <int ROWBYTES>
+__device__ __forceinline__ uint32_t swz(int row, int chunk) {
+  return (uint32_t)(row * ROWBYTES + ((chunk ^ (row & 7)) << 4));
+}
+
+// ---- mbarrier + bulk-copy helpers; every wait is bounded and reports through `status` ----------
+unsigned int* kch_status_device_ptr();   // host: device address of the library's status word
+
+__device__ __forceinline__ void mbarrier_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbarrier_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_addr_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void mbarrier_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbarrier_wait_bounded(uint64_t* bar, uint32_t parity, unsigned code, uint32_t limit,
+                                                      unsigned int* status) {
+  uint32_t addr = smem_addr_u32(bar);
+  for (uint32_t it = 0; it < limit; ++it) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(addr), "r"(parity) : "memory");
+    if (ok) return true;
+    if ((it & 1023) == 1023 && *((volatile unsigned int*)status) != 0) return false;
+  }
+  atomicCAS(status, 0u, code);
+  return false;
+}
+// 1-D bulk copy global -> shared of `bytes` (multiple of 16), completion counted on `bar`
+__device__ __forceinline__ void bulk_copy_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(smem_addr_u32(dst)), "l"(src), "r"(bytes), "r"(smem_addr_u32(bar)) : "memory");
+}

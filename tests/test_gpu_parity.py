@@ -99,6 +99,34 @@ def test_kda_config1_full_size(kch):
     assert md(o2, o0) <= 1e-5 and md(s2, s0) <= 1e-5
 
 
+@pytest.mark.parametrize("B,T,H,HV,state", [(2, 300, 2, 4, True), (1, 64, 1, 1, False), (1, 1000, 2, 2, True)])
+def test_kda_chunk_tensor_core_path(kch, B, T, H, HV, state):
+    """bf16, K=V=128, chunk 64 takes the tensor-core kernels (two-term bf16 split, fp32 accumulation):
+    state within fp32-level round-off of the oracle, output within one bf16 rounding of it."""
+    q, k, v, g, beta, S0 = syn.kda_inputs(40 + T, B, T, H, 128, 128, HV, torch.bfloat16, with_state=True)
+    S0 = S0 if state else None
+    o_ref, s_ref = orc.chunk_kda(q, k, v, g, beta, initial_state=S0, chunk_size=64)
+    o, s = kch.naive_chunk_kda(*(x.to(DEV) for x in (q, k, v, g, beta)), initial_state=None if S0 is None else S0.to(DEV),
+                               output_final_state=True, chunk_size=64)
+    assert o.dtype == torch.bfloat16 and s.dtype == torch.float32
+    assert md(s, s_ref) <= 2e-4, md(s, s_ref)
+    d = (o.float().cpu() - o_ref.float()).abs()
+    assert bool((d <= o_ref.float().abs() * 2 ** -7 + 2e-3).all()), float(d.max())
+    # the token recurrence on the same inputs agrees as well
+    o2, s2 = kch.naive_recurrent_kda(*(x.to(DEV) for x in (q, k, v, g, beta)),
+                                     initial_state=None if S0 is None else S0.to(DEV), output_final_state=True)
+    assert md(s, s2) <= 2e-4
+    # the slow-decay regime of the model (g = -0.1 softplus) and a hard-decay regime near the clamp
+    for gscale in (0.1, 6.0):
+        g2 = (g.float() * gscale).bfloat16()
+        o_ref, s_ref = orc.chunk_kda(q, k, v, g2, beta, initial_state=S0, chunk_size=64)
+        o, s = kch.naive_chunk_kda(*(x.to(DEV) for x in (q, k, v, g2, beta)),
+                                   initial_state=None if S0 is None else S0.to(DEV), output_final_state=True)
+        assert md(s, s_ref) <= 5e-4, (gscale, md(s, s_ref))
+        d = (o.float().cpu() - o_ref.float()).abs()
+        assert bool((d <= o_ref.float().abs() * 2 ** -7 + 3e-3).all()), (gscale, float(d.max()))
+
+
 def test_kda_edges(kch):
     q, k, v, g, beta = (x.to(DEV) for x in syn.kda_inputs(3, 2, 0, 2, 16, 16))
     S0 = torch.randn(2, 2, 16, 16, device=DEV)
