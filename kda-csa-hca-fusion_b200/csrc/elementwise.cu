@@ -31,12 +31,62 @@ __global__ void layernorm_kernel(const T* __restrict__ x, const TW* __restrict__
     stf(yr + i, (ldf(xr + i) - mean) * rstd * ldf(w + i) + ldf(b + i));
 }
 
+// bf16 fast path for d % 256 == 0 and d <= 4096: 8 values per lane per 256 columns, row kept in registers
+template <typename TW, int NV>
+__global__ void layernorm_kernel_bf16_vec(const bf16* __restrict__ x, const TW* __restrict__ w,
+                                          const TW* __restrict__ b, bf16* __restrict__ y, int64_t rows, int d,
+                                          float eps) {
+  int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  int lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  const bf16* xr = x + row * d;
+  float v[NV][8];
+  float s = 0.f;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    uint4 raw = *reinterpret_cast<const uint4*>(xr + i * 256 + lane * 8);
+    const bf16* e = reinterpret_cast<const bf16*>(&raw);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) { v[i][k] = __bfloat162float(e[k]); s += v[i][k]; }
+  }
+  const float mean = warp_sum(s) / (float)d;
+  float q = 0.f;
+#pragma unroll
+  for (int i = 0; i < NV; ++i)
+#pragma unroll
+    for (int k = 0; k < 8; ++k) { float t = v[i][k] - mean; q += t * t; }
+  const float rstd = 1.0f / sqrtf(warp_sum(q) / (float)d + eps);
+  bf16* yr = y + row * d;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    uint4 outv;
+    bf16* out = reinterpret_cast<bf16*>(&outv);
+    const int c0 = i * 256 + lane * 8;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) out[k] = __float2bfloat16_rn((v[i][k] - mean) * rstd * ldf(w + c0 + k) + ldf(b + c0 + k));
+    *reinterpret_cast<uint4*>(yr + c0) = outv;
+  }
+}
+
 extern "C" int kch_layernorm(const void* x, const void* weight, const void* bias, void* y,
                              int64_t rows, int d, float eps, int dtype, int wdtype, void* stream) {
   KCH_REQUIRE(rows >= 0 && d >= 1, "kch_layernorm: rows=%lld d=%d", (long long)rows, d);
   if (rows == 0) return KCH_OK;
   const int wpb = 8;
   dim3 grid((unsigned)ceil_div64(rows, wpb)), block(wpb * 32);
+  if (dtype == KCH_BF16 && (d % 256) == 0 && d <= 2048 && (((uintptr_t)x | (uintptr_t)y) & 15) == 0) {
+    cudaStream_t s = kch_stream(stream);
+#define LNV(NV)                                                                                              \
+    KCH_DISPATCH_FLOAT(wdtype, TW, (layernorm_kernel_bf16_vec<TW, NV><<<grid, block, 0, s>>>(                 \
+        (const bf16*)x, (const TW*)weight, (const TW*)bias, (bf16*)y, rows, d, eps)))
+    switch (d / 256) {
+      case 1: LNV(1); break; case 2: LNV(2); break; case 3: LNV(3); break; case 4: LNV(4); break;
+      case 5: LNV(5); break; case 6: LNV(6); break; case 7: LNV(7); break; default: LNV(8); break;
+    }
+#undef LNV
+    KCH_LAUNCH_OK();
+    return KCH_OK;
+  }
   KCH_DISPATCH_FLOAT(dtype, T, KCH_DISPATCH_FLOAT(wdtype, TW,
       (layernorm_kernel<T, TW><<<grid, block, 0, kch_stream(stream)>>>(
           (const T*)x, (const TW*)weight, (const TW*)bias, (T*)y, rows, d, eps))));
@@ -74,15 +124,78 @@ __global__ void short_conv_kernel(const T* __restrict__ x, const T* __restrict__
   stf(y + i, acc + ldf(bias + ch));
 }
 
+// bf16 fast path: 8 channels (16 bytes) per thread
+__global__ void short_conv_kernel_bf16x8(const bf16* __restrict__ x, const bf16* __restrict__ lb,
+                                         const bf16* __restrict__ w, const bf16* __restrict__ bias,
+                                         bf16* __restrict__ y, int B, int T_, int d) {
+  const int d8 = d >> 3;
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (int64_t)B * T_ * d8) return;
+  const int c0 = (int)(i % d8) * 8;
+  const int64_t bt = i / d8;
+  const int t = (int)(bt % T_), b = (int)(bt / T_);
+  const bf16* xb = x + (int64_t)b * T_ * d;
+  auto ld8 = [&](const bf16* p, float (&o)[8]) {
+    uint4 raw = *reinterpret_cast<const uint4*>(p);
+    const bf16* e = reinterpret_cast<const bf16*>(&raw);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) o[k] = __bfloat162float(e[k]);
+  };
+  float x0[8], x1[8], x2[8], bb[8];
+  ld8(xb + (int64_t)t * d + c0, x0);
+  if (t >= 1) ld8(xb + (int64_t)(t - 1) * d + c0, x1);
+  else if (lb) ld8(lb + ((int64_t)b * 2 + 1) * d + c0, x1);
+  else {
+#pragma unroll
+    for (int k = 0; k < 8; ++k) x1[k] = 0.f;
+  }
+  if (t >= 2) ld8(xb + (int64_t)(t - 2) * d + c0, x2);
+  else if (lb) ld8(lb + ((int64_t)b * 2 + t) * d + c0, x2);
+  else {
+#pragma unroll
+    for (int k = 0; k < 8; ++k) x2[k] = 0.f;
+  }
+  ld8(bias + c0, bb);
+  // taps of 8 channels: 24 consecutive bf16 (48 bytes, 16-byte aligned because c0 % 8 == 0)
+  float wt[24];
+  {
+    const uint4* wp = reinterpret_cast<const uint4*>(w + c0 * 3);
+#pragma unroll
+    for (int v = 0; v < 3; ++v) {
+      uint4 raw = wp[v];
+      const bf16* e = reinterpret_cast<const bf16*>(&raw);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) wt[8 * v + k] = __bfloat162float(e[k]);
+    }
+  }
+  uint4 outv;
+  bf16* out = reinterpret_cast<bf16*>(&outv);
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    float acc = wt[3 * k] * x2[k];
+    acc = fmaf(wt[3 * k + 1], x1[k], acc);
+    acc = fmaf(wt[3 * k + 2], x0[k], acc);
+    out[k] = __float2bfloat16_rn(acc + bb[k]);
+  }
+  *reinterpret_cast<uint4*>(y + bt * d + c0) = outv;
+}
+
 extern "C" int kch_short_conv(const void* x, const void* lookback, const void* weight,
                               const void* bias, void* y, int B, int T, int d, int dtype,
                               void* stream) {
   KCH_REQUIRE(B >= 0 && T >= 0 && d >= 1, "kch_short_conv: B=%d T=%d d=%d", B, T, d);
   int64_t total = (int64_t)B * T * d;
   if (total == 0) return KCH_OK;
-  dim3 grid((unsigned)ceil_div64(total, 256)), block(256);
-  KCH_DISPATCH_FLOAT(dtype, T_, (short_conv_kernel<T_><<<grid, block, 0, kch_stream(stream)>>>(
-      (const T_*)x, (const T_*)lookback, (const T_*)weight, (const T_*)bias, (T_*)y, B, T, d)));
+  const uintptr_t al = (uintptr_t)x | (uintptr_t)y | (uintptr_t)weight | (uintptr_t)bias | (uintptr_t)lookback;
+  if (dtype == KCH_BF16 && (d % 8) == 0 && (al & 15) == 0) {
+    dim3 grid((unsigned)ceil_div64(total / 8, 256)), block(256);
+    short_conv_kernel_bf16x8<<<grid, block, 0, kch_stream(stream)>>>((const bf16*)x, (const bf16*)lookback,
+                                                                    (const bf16*)weight, (const bf16*)bias, (bf16*)y, B, T, d);
+  } else {
+    dim3 grid((unsigned)ceil_div64(total, 256)), block(256);
+    KCH_DISPATCH_FLOAT(dtype, T_, (short_conv_kernel<T_><<<grid, block, 0, kch_stream(stream)>>>(
+        (const T_*)x, (const T_*)lookback, (const T_*)weight, (const T_*)bias, (T_*)y, B, T, d)));
+  }
   KCH_LAUNCH_OK();
   return KCH_OK;
 }
@@ -113,6 +226,49 @@ __global__ void act_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t r
   else if (act == KCH_ACT_SIGMOID) o = sigmoid_f(v);
   else o = -round_to<T>(softplus_f(v)) * param;
   stf(y + r * ldy + cidx, o);
+}
+
+// bf16 fast path: 8 consecutive columns (16 bytes) per thread
+__global__ void act_kernel_bf16x8(const bf16* __restrict__ x, bf16* __restrict__ y, int64_t rows, int cols8,
+                                  int64_t ldx, int64_t ldy, int act, float param) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= rows * cols8) return;
+  int64_t r = i / cols8;
+  int c8 = (int)(i % cols8) * 8;
+  uint4 raw = *reinterpret_cast<const uint4*>(x + r * ldx + c8);
+  const bf16* in = reinterpret_cast<const bf16*>(&raw);
+  uint4 outv;
+  bf16* out = reinterpret_cast<bf16*>(&outv);
+#pragma unroll
+  for (int e = 0; e < 8; ++e) {
+    float v = __bfloat162float(in[e]), o;
+    if (act == KCH_ACT_SILU) o = silu_f(v);
+    else if (act == KCH_ACT_SIGMOID) o = sigmoid_f(v);
+    else o = -round_to<bf16>(softplus_f(v)) * param;
+    out[e] = __float2bfloat16_rn(o);
+  }
+  *reinterpret_cast<uint4*>(y + r * ldy + c8) = outv;
+}
+
+// bf16 fast path of silu + L2 norm for groups of 128 columns: one warp per (row, group), 4 columns per lane
+__global__ void silu_l2norm_kernel_bf16_g128(const bf16* __restrict__ x, bf16* __restrict__ y, int64_t rows,
+                                             int gpr, int64_t ldx, int64_t ldy) {
+  int64_t gidx = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  int lane = threadIdx.x & 31;
+  if (gidx >= rows * gpr) return;
+  int64_t r = gidx / gpr;
+  int g0 = (int)(gidx % gpr) * 128 + lane * 4;
+  uint2 raw = *reinterpret_cast<const uint2*>(x + r * ldx + g0);
+  const bf16* in = reinterpret_cast<const bf16*>(&raw);
+  float s[4], ss = 0.f;
+#pragma unroll
+  for (int e = 0; e < 4; ++e) { s[e] = round_to<bf16>(silu_f(__bfloat162float(in[e]))); ss += s[e] * s[e]; }
+  float nrm = fmaxf(round_to<bf16>(sqrtf(warp_sum(ss))), 1e-12f);
+  uint2 outv;
+  bf16* out = reinterpret_cast<bf16*>(&outv);
+#pragma unroll
+  for (int e = 0; e < 4; ++e) out[e] = __float2bfloat16_rn(s[e] / nrm);
+  *reinterpret_cast<uint2*>(y + r * ldy + g0) = outv;
 }
 
 // one warp per (row, group)
@@ -150,14 +306,26 @@ extern "C" int kch_activation(const void* x, void* y, int64_t rows, int cols, in
     KCH_REQUIRE(group >= 1 && cols % group == 0, "kch_activation: group=%d must divide cols=%d", group, cols);
     int64_t ng = n / group;
     dim3 grid((unsigned)ceil_div64(ng, 8)), block(256);
-    KCH_DISPATCH_FLOAT(dtype, T, (silu_l2norm_kernel<T><<<grid, block, 0, kch_stream(stream)>>>(
-        (const T*)x, (T*)y, rows, cols, ldx, ldy, group)));
+    if (dtype == KCH_BF16 && group == 128 && (ldx % 4) == 0 && (ldy % 4) == 0 && (((uintptr_t)x | (uintptr_t)y) & 7) == 0) {
+      silu_l2norm_kernel_bf16_g128<<<grid, block, 0, kch_stream(stream)>>>((const bf16*)x, (bf16*)y, rows, cols / 128,
+                                                                          ldx, ldy);
+    } else {
+      KCH_DISPATCH_FLOAT(dtype, T, (silu_l2norm_kernel<T><<<grid, block, 0, kch_stream(stream)>>>(
+          (const T*)x, (T*)y, rows, cols, ldx, ldy, group)));
+    }
   } else {
     KCH_REQUIRE(act == KCH_ACT_SILU || act == KCH_ACT_SIGMOID || act == KCH_ACT_NEG_SOFTPLUS,
                 "kch_activation: unknown act %d", act);
-    dim3 grid((unsigned)ceil_div64(n, 256)), block(256);
-    KCH_DISPATCH_FLOAT(dtype, T, (act_kernel<T><<<grid, block, 0, kch_stream(stream)>>>(
-        (const T*)x, (T*)y, rows, cols, ldx, ldy, act, param)));
+    if (dtype == KCH_BF16 && (cols % 8) == 0 && (ldx % 8) == 0 && (ldy % 8) == 0 &&
+        (((uintptr_t)x | (uintptr_t)y) & 15) == 0) {
+      dim3 grid((unsigned)ceil_div64(n / 8, 256)), block(256);
+      act_kernel_bf16x8<<<grid, block, 0, kch_stream(stream)>>>((const bf16*)x, (bf16*)y, rows, cols / 8, ldx, ldy,
+                                                               act, param);
+    } else {
+      dim3 grid((unsigned)ceil_div64(n, 256)), block(256);
+      KCH_DISPATCH_FLOAT(dtype, T, (act_kernel<T><<<grid, block, 0, kch_stream(stream)>>>(
+          (const T*)x, (T*)y, rows, cols, ldx, ldy, act, param)));
+    }
   }
   KCH_LAUNCH_OK();
   return KCH_OK;

@@ -64,9 +64,11 @@ struct PrepArgs {
 #define PS_TB (PS_G + 16384)                    // T diag(beta) hi [64][64] bf16 then lo (over gamma, second half)
 #define PS_U PS_A                               // u^T staging 2 x [64][64] fp32        (over A + T)
 
-__global__ void __launch_bounds__(128) kda_prepare_mma_kernel(PrepArgs a) {
+#define KM_LOG2E 1.4426950408889634f
+
+__global__ void __launch_bounds__(256) kda_prepare_mma_kernel(PrepArgs a) {
   extern __shared__ __align__(128) uint8_t sm[];
-  float* sG = reinterpret_cast<float*>(sm + PS_G);
+  float* sG = reinterpret_cast<float*>(sm + PS_G);     // gamma in log2 units: exp(x) == exp2f(x')
   float* sA = reinterpret_cast<float*>(sm + PS_A);
   float* sT = reinterpret_cast<float*>(sm + PS_T);
   float* sQ = reinterpret_cast<float*>(sm + PS_Q);
@@ -80,57 +82,92 @@ __global__ void __launch_bounds__(128) kda_prepare_mma_kernel(PrepArgs a) {
   uint8_t* wsc = a.ws + (bh * a.NT + n) * (int64_t)KM_CHUNK_BYTES;
   auto qk_off = [&](int i) { return (((int64_t)b * a.T + t0 + i) * a.H + h) * KM_K; };
   auto gv_off = [&](int i) { return (((int64_t)b * a.T + t0 + i) * a.HV + hv) * (int64_t)KM_K; };
+  auto load8 = [&](const bf16* p, bool ok, float (&out)[8]) {
+    uint4 raw = make_uint4(0u, 0u, 0u, 0u);
+    if (ok) raw = *reinterpret_cast<const uint4*>(p);
+    const bf16* e = reinterpret_cast<const bf16*>(&raw);
+#pragma unroll
+    for (int x = 0; x < 8; ++x) out[x] = __bfloat162float(e[x]);
+  };
 
-  // ---- gamma = running sum of the clamped log-decay; thread = channel ----------------------------
-  {
+  // ---- clamped log-decay into shared memory (log2 units), then the running sum per channel --------
+#pragma unroll
+  for (int it = 0; it < 4; ++it) {
+    const int idx = tid + 256 * it, i = idx >> 4, ch = idx & 15;
+    float gv[8];
+    load8(a.g + gv_off(i) + 8 * ch, t0 + i < a.T, gv);
+#pragma unroll
+    for (int x = 0; x < 8; ++x) gv[x] = (t0 + i < a.T) ? fmaxf(gv[x], a.g_min) * KM_LOG2E : 0.f;
+    float4* dst = reinterpret_cast<float4*>(sG + i * KM_K + 8 * ch);
+    dst[0] = make_float4(gv[0], gv[1], gv[2], gv[3]);
+    dst[1] = make_float4(gv[4], gv[5], gv[6], gv[7]);
+  }
+  if (tid < KM_C) sbeta[tid] = (t0 + tid < a.T) ? __bfloat162float(a.beta[((int64_t)b * a.T + t0 + tid) * a.HV + hv]) : 0.f;
+  for (int idx = tid; idx < KM_C * PS_LD; idx += 256) { sA[idx] = 0.f; sQ[idx] = 0.f; sT[idx] = 0.f; }
+  __syncthreads();
+  if (tid < KM_K) {
     float acc = 0.f;
+#pragma unroll 8
     for (int i = 0; i < KM_C; ++i) {
-      float gi = (t0 + i < a.T) ? fmaxf(__bfloat162float(a.g[gv_off(i) + tid]), a.g_min) : 0.f;
-      acc += gi;
+      acc += sG[i * KM_K + tid];
       sG[i * KM_K + tid] = acc;
     }
-    if (tid < KM_C) sbeta[tid] = (t0 + tid < a.T) ? __bfloat162float(a.beta[((int64_t)b * a.T + t0 + tid) * a.HV + hv]) : 0.f;
-    for (int idx = tid; idx < KM_C * PS_LD; idx += 128) { sA[idx] = 0.f; sQ[idx] = 0.f; sT[idx] = 0.f; }
   }
   __syncthreads();
 
   // ---- A and Aqk, block by block ------------------------------------------------------------------
-  // staging tiles: 0 Krow hi, 1 Krow lo, 2 Qrow hi, 3 Qrow lo, 4 Kcol hi, 5 Kcol lo
+  // staging tiles: 0 Krow hi, 1 Krow lo, 2 Qrow hi, 3 Qrow lo, 4 Kcol hi, 5 Kcol lo ([16][128] bf16, swizzled)
   uint8_t* st = sm + PS_ST;
   const int pa[10] = {0, 1, 2, 3, 1, 2, 3, 2, 3, 3};
   const int pb[10] = {0, 1, 2, 3, 0, 1, 2, 0, 1, 0};
   for (int p = 0; p < 10; ++p) {
     const int ba = pa[p], bb = pb[p];
     {
-      const int c = tid;
-      const float ref = sG[((ba == bb) ? (16 * ba + 8) : (16 * bb + 15)) * KM_K + c];
-      const uint32_t cb = (uint32_t)((c & 7) * 2);
-      for (int r = 0; r < 16; ++r) {
-        const uint32_t off = swz<256>(r, c >> 3) + cb;
-        const int i = 16 * ba + r;
-        float kv = 0.f, qv = 0.f;
-        if (t0 + i < a.T) {
-          kv = __bfloat162float(a.k[qk_off(i) + c]);
-          qv = __bfloat162float(a.q[qk_off(i) + c]) * a.scale;
-        }
-        const float e = expf(sG[i * KM_K + c] - ref);
-        bf16 hi, lo;
-        split1_bf16(kv * e, hi, lo);
-        *reinterpret_cast<bf16*>(st + 0 * 4096 + off) = hi;
-        *reinterpret_cast<bf16*>(st + 1 * 4096 + off) = lo;
-        split1_bf16(qv * e, hi, lo);
-        *reinterpret_cast<bf16*>(st + 2 * 4096 + off) = hi;
-        *reinterpret_cast<bf16*>(st + 3 * 4096 + off) = lo;
-        const int jr = 16 * bb + r;
-        float kc = (ba == bb) ? kv : ((t0 + jr < a.T) ? __bfloat162float(a.k[qk_off(jr) + c]) : 0.f);
-        const float ec = expf(ref - sG[jr * KM_K + c]);
-        split1_bf16(kc * ec, hi, lo);
-        *reinterpret_cast<bf16*>(st + 4 * 4096 + off) = hi;
-        *reinterpret_cast<bf16*>(st + 5 * 4096 + off) = lo;
+      const int r = tid >> 4, ch = tid & 15;
+      const int refrow = (ba == bb) ? (16 * ba + 8) : (16 * bb + 15);
+      const int i = 16 * ba + r, jr = 16 * bb + r;
+      float ref[8], gi[8], kv[8], qv[8];
+      {
+        const float4* p4 = reinterpret_cast<const float4*>(sG + refrow * KM_K + 8 * ch);
+        float4 x = p4[0], y = p4[1];
+        ref[0] = x.x; ref[1] = x.y; ref[2] = x.z; ref[3] = x.w; ref[4] = y.x; ref[5] = y.y; ref[6] = y.z; ref[7] = y.w;
+        p4 = reinterpret_cast<const float4*>(sG + i * KM_K + 8 * ch);
+        x = p4[0]; y = p4[1];
+        gi[0] = x.x; gi[1] = x.y; gi[2] = x.z; gi[3] = x.w; gi[4] = y.x; gi[5] = y.y; gi[6] = y.z; gi[7] = y.w;
       }
+      load8(a.k + qk_off(i) + 8 * ch, t0 + i < a.T, kv);
+      load8(a.q + qk_off(i) + 8 * ch, t0 + i < a.T, qv);
+      uint32_t kh[4], kl[4], qh[4], ql[4], ch_[4], cl_[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float e0 = exp2f(gi[2 * e] - ref[2 * e]), e1 = exp2f(gi[2 * e + 1] - ref[2 * e + 1]);
+        split2_bf16(kv[2 * e] * e0, kv[2 * e + 1] * e1, kh[e], kl[e]);
+        split2_bf16(qv[2 * e] * a.scale * e0, qv[2 * e + 1] * a.scale * e1, qh[e], ql[e]);
+      }
+      float gj[8], kc[8];
+      if (ba == bb) {
+#pragma unroll
+        for (int x = 0; x < 8; ++x) { gj[x] = gi[x]; kc[x] = kv[x]; }
+      } else {
+        const float4* p4 = reinterpret_cast<const float4*>(sG + jr * KM_K + 8 * ch);
+        float4 x = p4[0], y = p4[1];
+        gj[0] = x.x; gj[1] = x.y; gj[2] = x.z; gj[3] = x.w; gj[4] = y.x; gj[5] = y.y; gj[6] = y.z; gj[7] = y.w;
+        load8(a.k + qk_off(jr) + 8 * ch, t0 + jr < a.T, kc);
+      }
+#pragma unroll
+      for (int e = 0; e < 4; ++e)
+        split2_bf16(kc[2 * e] * exp2f(ref[2 * e] - gj[2 * e]), kc[2 * e + 1] * exp2f(ref[2 * e + 1] - gj[2 * e + 1]),
+                    ch_[e], cl_[e]);
+      const uint32_t off = swz<256>(r, ch);
+      *reinterpret_cast<uint4*>(st + 0 * 4096 + off) = make_uint4(kh[0], kh[1], kh[2], kh[3]);
+      *reinterpret_cast<uint4*>(st + 1 * 4096 + off) = make_uint4(kl[0], kl[1], kl[2], kl[3]);
+      *reinterpret_cast<uint4*>(st + 2 * 4096 + off) = make_uint4(qh[0], qh[1], qh[2], qh[3]);
+      *reinterpret_cast<uint4*>(st + 3 * 4096 + off) = make_uint4(ql[0], ql[1], ql[2], ql[3]);
+      *reinterpret_cast<uint4*>(st + 4 * 4096 + off) = make_uint4(ch_[0], ch_[1], ch_[2], ch_[3]);
+      *reinterpret_cast<uint4*>(st + 5 * 4096 + off) = make_uint4(cl_[0], cl_[1], cl_[2], cl_[3]);
     }
     __syncthreads();
-    {
+    if (warp < 4) {
       const int nt = warp & 1, which = warp >> 1;   // which: 0 -> A (k rows), 1 -> Aqk (q rows)
       const uint32_t rhi = smem_addr_u32(st + (which ? 2 : 0) * 4096), rlo = rhi + 4096;
       const uint32_t chi = smem_addr_u32(st + 4 * 4096), clo = chi + 4096;
@@ -174,7 +211,7 @@ __global__ void __launch_bounds__(128) kda_prepare_mma_kernel(PrepArgs a) {
   }
 
   // ---- Aqk -> workspace as swizzled bf16 hi/lo tiles [64][64] --------------------------------------
-  for (int idx = tid; idx < KM_C * 8; idx += 128) {
+  for (int idx = tid; idx < KM_C * 8; idx += 256) {
     const int i = idx >> 3, ch = idx & 7;
     uint32_t hi[4], lo[4];
 #pragma unroll
@@ -186,29 +223,26 @@ __global__ void __launch_bounds__(128) kda_prepare_mma_kernel(PrepArgs a) {
   __syncthreads();   // sQ is dead from here: the e^gamma k tiles may overwrite it
 
   // ---- qg, kg (workspace), e^gamma k (shared), dl ------------------------------------------------------
-  for (int idx = tid; idx < KM_C * 16; idx += 128) {
-    const int i = idx >> 4, ch = idx & 15;
-    float kf[8], qf[8];
-    if (t0 + i < a.T) {
-      uint4 kr = *reinterpret_cast<const uint4*>(a.k + qk_off(i) + 8 * ch);
-      uint4 qr = *reinterpret_cast<const uint4*>(a.q + qk_off(i) + 8 * ch);
-      const bf16* kp = reinterpret_cast<const bf16*>(&kr);
-      const bf16* qp = reinterpret_cast<const bf16*>(&qr);
-#pragma unroll
-      for (int e = 0; e < 8; ++e) { kf[e] = __bfloat162float(kp[e]); qf[e] = __bfloat162float(qp[e]) * a.scale; }
-    } else {
-#pragma unroll
-      for (int e = 0; e < 8; ++e) { kf[e] = 0.f; qf[e] = 0.f; }
+#pragma unroll 2
+  for (int it = 0; it < 4; ++it) {
+    const int idx = tid + 256 * it, i = idx >> 4, ch = idx & 15;
+    float kf[8], qf[8], gm[8], gl[8];
+    load8(a.k + qk_off(i) + 8 * ch, t0 + i < a.T, kf);
+    load8(a.q + qk_off(i) + 8 * ch, t0 + i < a.T, qf);
+    {
+      const float4* p4 = reinterpret_cast<const float4*>(sG + i * KM_K + 8 * ch);
+      float4 x = p4[0], y = p4[1];
+      gm[0] = x.x; gm[1] = x.y; gm[2] = x.z; gm[3] = x.w; gm[4] = y.x; gm[5] = y.y; gm[6] = y.z; gm[7] = y.w;
+      p4 = reinterpret_cast<const float4*>(sG + (KM_C - 1) * KM_K + 8 * ch);
+      x = p4[0]; y = p4[1];
+      gl[0] = x.x; gl[1] = x.y; gl[2] = x.z; gl[3] = x.w; gl[4] = y.x; gl[5] = y.y; gl[6] = y.z; gl[7] = y.w;
     }
     uint32_t qh[4], ql[4], kh[4], kl[4], eh[4], el[4];
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
-      const int c0 = 8 * ch + 2 * e;
-      const float g0 = sG[i * KM_K + c0], g1 = sG[i * KM_K + c0 + 1];
-      const float gl0 = sG[(KM_C - 1) * KM_K + c0], gl1 = sG[(KM_C - 1) * KM_K + c0 + 1];
-      const float e0 = expf(g0), e1 = expf(g1);
-      split2_bf16(qf[2 * e] * e0, qf[2 * e + 1] * e1, qh[e], ql[e]);
-      split2_bf16(kf[2 * e] * expf(gl0 - g0), kf[2 * e + 1] * expf(gl1 - g1), kh[e], kl[e]);
+      const float e0 = exp2f(gm[2 * e]), e1 = exp2f(gm[2 * e + 1]);
+      split2_bf16(qf[2 * e] * a.scale * e0, qf[2 * e + 1] * a.scale * e1, qh[e], ql[e]);
+      split2_bf16(kf[2 * e] * exp2f(gl[2 * e] - gm[2 * e]), kf[2 * e + 1] * exp2f(gl[2 * e + 1] - gm[2 * e + 1]), kh[e], kl[e]);
       split2_bf16(kf[2 * e] * e0, kf[2 * e + 1] * e1, eh[e], el[e]);
     }
     const uint32_t off = swz<256>(i, ch);
@@ -219,8 +253,8 @@ __global__ void __launch_bounds__(128) kda_prepare_mma_kernel(PrepArgs a) {
     *reinterpret_cast<uint4*>(sm + PS_EK + off) = make_uint4(eh[0], eh[1], eh[2], eh[3]);
     *reinterpret_cast<uint4*>(sm + PS_EK + KM_TILE + off) = make_uint4(el[0], el[1], el[2], el[3]);
   }
-  {
-    const float dl = expf(sG[(KM_C - 1) * KM_K + tid]);
+  if (tid < KM_K) {
+    const float dl = exp2f(sG[(KM_C - 1) * KM_K + tid]);
 #pragma unroll
     for (int s = 0; s < KM_V / 64; ++s)
       reinterpret_cast<float*>(wsc + KM_OFF_U + s * KM_U_SLICE + 16384)[tid] = dl;
@@ -244,7 +278,7 @@ __global__ void __launch_bounds__(128) kda_prepare_mma_kernel(PrepArgs a) {
   // off-diagonal blocks, by distance d from the diagonal:  T_ab = -T_aa (sum_{b<=c<a} A_ac T_cb)
   for (int d = 1; d < 4; ++d) {
     const int nblk = 4 - d;
-    for (int idx = tid; idx < nblk * 256; idx += 128) {
+    for (int idx = tid; idx < nblk * 256; idx += 256) {
       const int bi = idx >> 8, r = (idx >> 4) & 15, cc = idx & 15;
       const int ba = bi + d, bb = bi;
       float acc = 0.f;
@@ -255,7 +289,7 @@ __global__ void __launch_bounds__(128) kda_prepare_mma_kernel(PrepArgs a) {
       sP[(bi * 16 + r) * 17 + cc] = acc;
     }
     __syncthreads();
-    for (int idx = tid; idx < nblk * 256; idx += 128) {
+    for (int idx = tid; idx < nblk * 256; idx += 256) {
       const int bi = idx >> 8, r = (idx >> 4) & 15, cc = idx & 15;
       const int ba = bi + d, bb = bi;
       float acc = 0.f;
@@ -266,7 +300,7 @@ __global__ void __launch_bounds__(128) kda_prepare_mma_kernel(PrepArgs a) {
     __syncthreads();
   }
   // T diag(beta) as swizzled bf16 hi/lo tiles (over the dead gamma buffer), v tile next to it
-  for (int idx = tid; idx < KM_C * 8; idx += 128) {
+  for (int idx = tid; idx < KM_C * 8; idx += 256) {
     const int i = idx >> 3, ch = idx & 7;
     uint32_t hi[4], lo[4];
 #pragma unroll
@@ -278,66 +312,65 @@ __global__ void __launch_bounds__(128) kda_prepare_mma_kernel(PrepArgs a) {
     *reinterpret_cast<uint4*>(sm + PS_TB + off) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
     *reinterpret_cast<uint4*>(sm + PS_TB + 8192 + off) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
   }
-  for (int idx = tid; idx < KM_C * 16; idx += 128) {
-    const int i = idx >> 4, ch = idx & 15;
+#pragma unroll
+  for (int it = 0; it < 4; ++it) {
+    const int idx = tid + 256 * it, i = idx >> 4, ch = idx & 15;
     uint4 vr = make_uint4(0u, 0u, 0u, 0u);
     if (t0 + i < a.T) vr = *reinterpret_cast<const uint4*>(a.v + gv_off(i) + 8 * ch);   // V == K here
     *reinterpret_cast<uint4*>(sm + PS_V + swz<256>(i, ch)) = vr;
   }
   __syncthreads();
 
-  // ---- w = Tb (e^gamma k), u = Tb v : warp = 16-row tile, lower-triangular k-steps only ---------------
-  float wacc[16][4], uacc[16][4];
+  // ---- w = Tb (e^gamma k), u = Tb v : warp = (16-row tile, half of the 128 columns); lower-triangular k-steps ----
+  const int mt = warp & 3, nh = warp >> 2;
+  float wacc[8][4], uacc[8][4];
 #pragma unroll
-  for (int i = 0; i < 16; ++i) { wacc[i][0] = wacc[i][1] = wacc[i][2] = wacc[i][3] = 0.f; uacc[i][0] = uacc[i][1] = uacc[i][2] = uacc[i][3] = 0.f; }
+  for (int i = 0; i < 8; ++i) { wacc[i][0] = wacc[i][1] = wacc[i][2] = wacc[i][3] = 0.f; uacc[i][0] = uacc[i][1] = uacc[i][2] = uacc[i][3] = 0.f; }
   {
     const uint32_t tbh = smem_addr_u32(sm + PS_TB), tbl = tbh + 8192;
     const uint32_t ekh = smem_addr_u32(sm + PS_EK), ekl = ekh + KM_TILE, vv = smem_addr_u32(sm + PS_V);
-    const int arow = 16 * warp + (lane & 7) + ((lane >> 3) & 1) * 8;
-    for (int ks = 0; ks <= warp; ++ks) {
+    const int arow = 16 * mt + (lane & 7) + ((lane >> 3) & 1) * 8;
+    for (int ks = 0; ks <= mt; ++ks) {
       uint32_t ah[4], al[4];
       const uint32_t oa = swz<128>(arow, 2 * ks + (lane >> 4));
       ldmatrix_x4(tbh + oa, ah[0], ah[1], ah[2], ah[3]);
       ldmatrix_x4(tbl + oa, al[0], al[1], al[2], al[3]);
       const int brow = 16 * ks + ((lane >> 3) & 1) * 8 + (lane & 7);
 #pragma unroll
-      for (int dp = 0; dp < 8; ++dp) {
-        const uint32_t ob = swz<256>(brow, 2 * dp + (lane >> 4));
+      for (int dpl = 0; dpl < 4; ++dpl) {
+        const uint32_t ob = swz<256>(brow, 2 * (4 * nh + dpl) + (lane >> 4));
         uint32_t h0, h1, h2, h3, l0, l1, l2, l3, v0, v1, v2, v3;
         ldmatrix_x4_trans(ekh + ob, h0, h1, h2, h3);
         ldmatrix_x4_trans(ekl + ob, l0, l1, l2, l3);
         ldmatrix_x4_trans(vv + ob, v0, v1, v2, v3);
-        mma_bf16_16816(wacc[2 * dp], ah, h0, h1);     mma_bf16_16816(wacc[2 * dp + 1], ah, h2, h3);
-        mma_bf16_16816(wacc[2 * dp], al, h0, h1);     mma_bf16_16816(wacc[2 * dp + 1], al, h2, h3);
-        mma_bf16_16816(wacc[2 * dp], ah, l0, l1);     mma_bf16_16816(wacc[2 * dp + 1], ah, l2, l3);
-        mma_bf16_16816(uacc[2 * dp], ah, v0, v1);     mma_bf16_16816(uacc[2 * dp + 1], ah, v2, v3);
-        mma_bf16_16816(uacc[2 * dp], al, v0, v1);     mma_bf16_16816(uacc[2 * dp + 1], al, v2, v3);
+        mma_bf16_16816(wacc[2 * dpl], ah, h0, h1);     mma_bf16_16816(wacc[2 * dpl + 1], ah, h2, h3);
+        mma_bf16_16816(wacc[2 * dpl], al, h0, h1);     mma_bf16_16816(wacc[2 * dpl + 1], al, h2, h3);
+        mma_bf16_16816(wacc[2 * dpl], ah, l0, l1);     mma_bf16_16816(wacc[2 * dpl + 1], ah, l2, l3);
+        mma_bf16_16816(uacc[2 * dpl], ah, v0, v1);     mma_bf16_16816(uacc[2 * dpl + 1], ah, v2, v3);
+        mma_bf16_16816(uacc[2 * dpl], al, v0, v1);     mma_bf16_16816(uacc[2 * dpl + 1], al, v2, v3);
       }
     }
   }
   // w -> workspace (swizzled hi/lo); u^T -> shared staging (over A and T, dead now) -> workspace
   {
-    const int i0 = 16 * warp + g4, i1 = i0 + 8;
+    const int i0 = 16 * mt + g4, i1 = i0 + 8;
     float* us = reinterpret_cast<float*>(sm + PS_U);
 #pragma unroll
-    for (int nt = 0; nt < 16; ++nt) {
+    for (int ntl = 0; ntl < 8; ++ntl) {
+      const int nt = 8 * nh + ntl;
       uint32_t hi, lo;
-      split2_bf16(wacc[nt][0], wacc[nt][1], hi, lo);
+      split2_bf16(wacc[ntl][0], wacc[ntl][1], hi, lo);
       *reinterpret_cast<uint32_t*>(wsc + KM_OFF_WHI + swz<256>(i0, nt) + 4 * j4) = hi;
       *reinterpret_cast<uint32_t*>(wsc + KM_OFF_WLO + swz<256>(i0, nt) + 4 * j4) = lo;
-      split2_bf16(wacc[nt][2], wacc[nt][3], hi, lo);
+      split2_bf16(wacc[ntl][2], wacc[ntl][3], hi, lo);
       *reinterpret_cast<uint32_t*>(wsc + KM_OFF_WHI + swz<256>(i1, nt) + 4 * j4) = hi;
       *reinterpret_cast<uint32_t*>(wsc + KM_OFF_WLO + swz<256>(i1, nt) + 4 * j4) = lo;
-    }
-    __syncthreads();   // every warp has finished reading T/A-aliased operands? (T, A are not read by the MMAs) -> staging is free
-#pragma unroll
-    for (int nt = 0; nt < 16; ++nt) {
       const int c0 = 8 * nt + 2 * j4;            // value column
       float* s0 = us + (c0 >> 6) * 4096 + (c0 & 63) * 64;
-      s0[i0] = uacc[nt][0];
-      s0[64 + i0] = uacc[nt][1];
-      s0[i1] = uacc[nt][2];
-      s0[64 + i1] = uacc[nt][3];
+      s0[i0] = uacc[ntl][0];
+      s0[64 + i0] = uacc[ntl][1];
+      s0[i1] = uacc[ntl][2];
+      s0[64 + i1] = uacc[ntl][3];
     }
   }
   __syncthreads();
@@ -346,7 +379,7 @@ __global__ void __launch_bounds__(128) kda_prepare_mma_kernel(PrepArgs a) {
 #pragma unroll
     for (int s = 0; s < KM_V / 64; ++s) {
       float4* dst = reinterpret_cast<float4*>(wsc + KM_OFF_U + s * KM_U_SLICE);
-      for (int idx = tid; idx < 1024; idx += 128) dst[idx] = us4[s * 1024 + idx];
+      for (int idx = tid; idx < 1024; idx += 256) dst[idx] = us4[s * 1024 + idx];
     }
   }
 }
@@ -597,7 +630,7 @@ int kch_kda_chunk_mma(const void* q, const void* k, const void* v, const void* g
   pa.q = (const bf16*)q; pa.k = (const bf16*)k; pa.v = (const bf16*)v; pa.g = (const bf16*)g; pa.beta = (const bf16*)beta;
   pa.ws = (uint8_t*)workspace; pa.T = T; pa.H = H; pa.HV = HV; pa.NT = NT; pa.scale = scale; pa.g_min = g_clamp_min;
   KCH_CUDA_OK(cudaFuncSetAttribute(kda_prepare_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PS_TOTAL));
-  kda_prepare_mma_kernel<<<dim3(NT, HV, B), 128, PS_TOTAL, s>>>(pa);
+  kda_prepare_mma_kernel<<<dim3(NT, HV, B), 256, PS_TOTAL, s>>>(pa);
   KCH_LAUNCH_OK();
   ScanArgs sa;
   sa.ws = (const uint8_t*)workspace; sa.S0 = initial_state; sa.o = (bf16*)o; sa.S_out = final_state; sa.status = status;

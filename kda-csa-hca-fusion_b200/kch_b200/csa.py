@@ -58,6 +58,16 @@ def linear(x, W, residual=None):
     return out.reshape(*lead, N)
 
 
+def fuse_rows(*weights):
+    """Row-concatenate weight matrices and zero-pad the row count to a multiple of 8, so that every column
+    slice of the fused projection output keeps a 16-byte-aligned row stride (TMA-readable in place)."""
+    w = torch.cat([x.detach() for x in weights], dim=0)
+    pad = (-w.shape[0]) % 8
+    if pad:
+        w = torch.cat([w, w.new_zeros(pad, w.shape[1])], dim=0)
+    return w.contiguous()
+
+
 def rownorm(x, normalize=True, out_dtype=torch.float32):
     """``F.normalize(x.float(), dim=-1)`` of a ``[..., c]`` tensor, evaluated in fp32 and stored as
     ``out_dtype`` (row-strided 3-D views are read in place)."""
@@ -334,14 +344,15 @@ def naive_csa(H, W_aKV, W_bKV, W_aZ, W_bZ, Ba, Bb, W_DQ, W_UQ, W_IUQ, W_w, W_KV_
         T += pad
     n_blocks = T // m
     if _fused_weight is None:
-        _fused_weight = torch.cat([W_aKV, W_bKV, W_aZ, W_bZ, W_KV_idx, W_Z_idx, W_DQ, W_w], dim=0)
-    proj = linear(H, _fused_weight)                                     # [B,T,4c+2cI+dc+nIh]
-    Ca, Cb, Za, Zb, K_idx_raw, Z_idx, cQ, w_idx = proj.split([c, c, c, c, c_I, c_I, dc, nIh], dim=-1)
+        _fused_weight = fuse_rows(W_aKV, W_bKV, W_aZ, W_bZ, W_KV_idx, W_Z_idx, W_DQ, W_w)
+    proj = linear(H, _fused_weight)                                     # [B,T,4c+2cI+dc+nIh (+pad)]
+    Ca, Cb, Za, Zb, K_idx_raw, Z_idx, cQ, w_idx = proj[..., :4 * c + 2 * c_I + dc + nIh].split(
+        [c, c, c, c, c_I, c_I, dc, nIh], dim=-1)
     C_comp = csa_compress_kv_overlapped(Ca, Cb, Za, Zb, Ba, Bb, m)      # [B,n,c] fp32
     K_IComp = csa_compress_kv(K_idx_raw, Z_idx, B_idx, m)               # [B,n,cI] fp32
     W_q = _fused_q_weight if _fused_q_weight is not None else torch.cat([W_UQ, W_IUQ], dim=0)
     qq = linear(cQ, W_q)                                                # [B,T,nh*c + nIh*cI]
-    q, q_idx = qq.split([nh * c, nIh * c_I], dim=-1)
+    q, q_idx = qq[..., :nh * c + nIh * c_I].split([nh * c, nIh * c_I], dim=-1)
     q_idx = q_idx.reshape(B_, T, nIh, c_I) if q_idx.is_contiguous() else q_idx.contiguous().reshape(B_, T, nIh, c_I)
     indices = None
     if topk > 0:

@@ -18,7 +18,7 @@ import torch
 import torch.nn as nn
 
 from . import _lib
-from .csa import attend, linear, naive_csa, rownorm
+from .csa import attend, fuse_rows, linear, naive_csa, rownorm
 from .decoding_cache import CSADecodingCache, HCADecodingCache
 from .hca import naive_hca
 from .kda import kda_forward, validate_kda_backend
@@ -155,7 +155,7 @@ class _FusedWeights:
     def get(self, *weights):
         key = tuple((w.data_ptr(), w.dtype, w.device, w._version) for w in weights)
         if key != self._key:
-            self._w = torch.cat([w.detach() for w in weights], dim=0).contiguous()
+            self._w = fuse_rows(*weights)
             self._key = key
         return self._w
 
@@ -205,7 +205,7 @@ class KDAHybridLayer(nn.Module):
         W = self._fused.get(self.q_proj.weight, self.k_proj.weight, self.v_proj.weight, self.g_down.weight,
                             self.beta.weight)
         proj = linear(xc, W)
-        qr, kr, vr, gd, br = proj.split([H * K, H * K, HV * V, K, HV], dim=-1)
+        qr, kr, vr, gd, br = proj[..., :2 * H * K + HV * V + K + HV].split([H * K, H * K, HV * V, K, HV], dim=-1)
         q = activation(qr, _lib.ACT_SILU_L2NORM, group=K).view(B, T, H, K)
         k = activation(kr, _lib.ACT_SILU_L2NORM, group=K).view(B, T, H, K)
         v = activation(vr, _lib.ACT_SILU).view(B, T, HV, V)
@@ -434,9 +434,10 @@ class HybridDecoding(nn.Module):
         else:
             c, cI, dc, nIh, nh = cfg.csa_c, cfg.csa_cI, cfg.csa_dc, cfg.csa_nIh, cfg.csa_nh
             proj = linear(h, layer.fused_weight())
-            Ca, Cb, Za, Zb, K_idx, Z_idx, cQ, w_idx = proj.split([c, c, c, c, cI, cI, dc, nIh], dim=-1)
+            Ca, Cb, Za, Zb, K_idx, Z_idx, cQ, w_idx = proj[..., :4 * c + 2 * cI + dc + nIh].split(
+                [c, c, c, c, cI, cI, dc, nIh], dim=-1)
             qq = linear(cQ, layer.q_weight())
-            q, q_idx = qq.split([nh * c, nIh * cI], dim=-1)
+            q, q_idx = qq[..., :nh * c + nIh * cI].split([nh * c, nIh * cI], dim=-1)
             cache.append_step(Ca, Cb, Za, Zb, K_idx, Z_idx, layer.Ba, layer.Bb, layer.B_idx)
             qn = rownorm(q.contiguous().view(B, 1, nh, c), True)
             o = cache.forward_step(qn, q_idx.contiguous().view(B, 1, nIh, cI).float(), w_idx.float(), topk=cfg.csa_topk,
@@ -454,7 +455,7 @@ class HybridDecoding(nn.Module):
         else:
             c, dc, nh = cfg.hca_c, cfg.hca_dc, cfg.hca_nh
             proj = linear(h, layer.fused_weight())
-            C, Z, cQ = proj.split([c, c, dc], dim=-1)
+            C, Z, cQ = proj[..., :2 * c + dc].split([c, c, dc], dim=-1)
             q = linear(cQ, layer.W_UQ.weight)
             cache.append_step(C, Z, layer.B_pos)
             qn = rownorm(q.view(B, 1, nh, c), True)

@@ -9,7 +9,7 @@ from __future__ import annotations
 import torch
 
 from . import _lib
-from .csa import attend, csa_compress_kv, linear, mma_attention_eligible, rownorm
+from .csa import attend, csa_compress_kv, fuse_rows, linear, mma_attention_eligible, rownorm
 
 
 def naive_hca(H, W_KV, W_Z, B_pos, W_DQ, W_UQ, *, m2: int, nh: int, c: int, dc: int, scale: float = 1.0,
@@ -59,12 +59,12 @@ def naive_hca(H, W_KV, W_Z, B_pos, W_DQ, W_UQ, *, m2: int, nh: int, c: int, dc: 
         T += pad
     if _fused_weight is None:
         parts = [W_KV, W_Z, W_DQ] + ([W_KV_local] if W_KV_local is not None else [])
-        _fused_weight = torch.cat(parts, dim=0)
+        _fused_weight = fuse_rows(*parts)
     proj = linear(H, _fused_weight)
     if W_KV_local is not None:
-        C, Z, cQ, C_loc = proj.split([c, c, dc, c], dim=-1)
+        C, Z, cQ, C_loc = proj[..., :3 * c + dc].split([c, c, dc, c], dim=-1)
     else:
-        C, Z, cQ = proj.split([c, c, dc], dim=-1)
+        C, Z, cQ = proj[..., :2 * c + dc].split([c, c, dc], dim=-1)
         C_loc = C
     C_comp = csa_compress_kv(C, Z, B_pos, m2)
     kdt = torch.bfloat16 if mma_attention_eligible(H.dtype, c, nh, True, scale) else torch.float32

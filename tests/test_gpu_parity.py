@@ -67,6 +67,40 @@ def test_linear_f32_and_strided(kch):
     assert md(yb, (xb.cpu().float() @ wb.cpu().float().T).bfloat16()) <= 2e-2
 
 
+@pytest.mark.parametrize("d", [64, 512, 2048])
+def test_glue_kernels(kch, d):
+    """LayerNorm / short conv / activations (scalar and vectorised paths) against the oracle's formulas."""
+    import torch.nn.functional as F
+    from kch_b200 import _lib
+    from kch_b200.fused import activation, layernorm, short_conv
+    g = torch.Generator().manual_seed(d)
+    B, T = 2, 37
+    x = (torch.randn(B, T, d, generator=g) * 2).bfloat16()
+    w, b = (1 + 0.1 * torch.randn(d, generator=g)).bfloat16(), (0.1 * torch.randn(d, generator=g)).bfloat16()
+    y = layernorm(x.to(DEV), w.to(DEV), b.to(DEV))
+    assert md(y, orc.layernorm_fp32(x, w, b)) <= 4e-2            # 1 bf16 ulp at |y| ~ 4
+    assert (y.cpu().float() - orc.layernorm_fp32(x, w, b).float()).abs().mean() <= 2e-4
+    cw, cb = (torch.randn(d, 1, 3, generator=g) * 0.5).bfloat16(), (torch.randn(d, generator=g) * 0.5).bfloat16()
+    lb = torch.randn(B, 2, d, generator=g).bfloat16()
+    for look in (None, lb):
+        yc = short_conv(x.to(DEV), cw.to(DEV), cb.to(DEV), None if look is None else look.to(DEV))
+        ref, _ = orc.short_conv(x, cw, cb, look)
+        assert (yc.cpu().float() - ref.float()).abs().max() <= 6.3e-2 and \
+            ((yc.cpu() != ref).float().mean() <= 0.02)               # same fp32 formula: rare rounding flips only
+    xs = x.to(DEV)
+    assert md(activation(xs, _lib.ACT_SILU), F.silu(x)) <= 3.2e-2
+    assert md(activation(xs, _lib.ACT_SIGMOID), torch.sigmoid(x)) <= 4e-3
+    assert md(activation(xs, _lib.ACT_NEG_SOFTPLUS, param=0.1), -F.softplus(x) * 0.1) <= 4e-3
+    grp = 128 if d % 128 == 0 else 16
+    qn = activation(xs, _lib.ACT_SILU_L2NORM, group=grp).cpu()
+    ref = F.normalize(F.silu(x).view(B, T, d // grp, grp), dim=-1).view(B, T, d)
+    assert md(qn, ref) <= 4e-3 and ((qn != ref).float().mean() <= 0.02)
+    # strided input (column slice of a wider tensor)
+    wide = torch.randn(B, T, d + 64, generator=g).bfloat16().to(DEV)
+    sl = wide[..., 32:32 + d]
+    assert md(activation(sl, _lib.ACT_SILU), F.silu(sl.cpu())) <= 3.2e-2
+
+
 # ---------------------------------------------------------------------------------------------- KDA
 @pytest.mark.parametrize("name", list(KDA_CASES))
 def test_kda(kch, golden, name):
