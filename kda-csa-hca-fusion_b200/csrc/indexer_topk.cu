@@ -6,8 +6,9 @@
 // its array library).  Selection is an exact 4x8-bit radix select on the order-preserving integer
 // image of the fp32 logits, so the selected SET is a pure function of the logits.
 #include <math.h>
+#include <stdlib.h>
 
-#include "kch_common.cuh"
+#include "mma_utils.cuh"
 
 // ---------------------------------------------------------------------------------------
 // Logits: 64 queries x 64 blocks per CTA, 16x16 threads, 4x4 outputs per thread.
@@ -80,6 +81,164 @@ indexer_logits_kernel(const float* __restrict__ q, const float* __restrict__ k,
 }
 
 // ---------------------------------------------------------------------------------------
+// Tensor-core logits for DI = 64: 64 queries x 128 blocks per CTA, 4 warps (16 queries each).
+// fp32-grade accuracy from bf16 tensor cores: both operands are split into three bf16 terms
+// (hi + mid + lo = 24 bits of mantissa) and the six products that matter are accumulated in fp32:
+//   q.k ~= hi.hi + hi.mid + mid.hi + mid.mid + hi.lo + lo.hi      (dropped terms < 2^-24 |q||k|)
+// so the selection boundary rule (picks exact wherever the gap exceeds 1e-6 relative) still holds.
+// ---------------------------------------------------------------------------------------
+#define IM_TQ 64
+#define IM_TN 128
+#define IM_D 64
+
+__device__ __forceinline__ void split3_pair(float x0, float x1, uint32_t& hi, uint32_t& mid, uint32_t& lo) {
+  bf16 h0 = __float2bfloat16_rn(x0), h1 = __float2bfloat16_rn(x1);
+  float r0 = x0 - __bfloat162float(h0), r1 = x1 - __bfloat162float(h1);
+  bf16 m0 = __float2bfloat16_rn(r0), m1 = __float2bfloat16_rn(r1);
+  bf16 l0 = __float2bfloat16_rn(r0 - __bfloat162float(m0)), l1 = __float2bfloat16_rn(r1 - __bfloat162float(m1));
+  __nv_bfloat162 a, b2, c;
+  a.x = h0; a.y = h1; b2.x = m0; b2.y = m1; c.x = l0; c.y = l1;
+  hi = *reinterpret_cast<uint32_t*>(&a);
+  mid = *reinterpret_cast<uint32_t*>(&b2);
+  lo = *reinterpret_cast<uint32_t*>(&c);
+}
+
+__global__ void __launch_bounds__(128)
+indexer_logits_mma_kernel(const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ w,
+                          float* __restrict__ logits, int T, int n, int HI, int64_t n_ld, float scale, int m,
+                          int64_t t0, int nvis_fixed, int64_t k_bstride) {
+  extern __shared__ __align__(128) uint8_t sm[];
+  const int nt0 = blockIdx.x * IM_TN, tq0 = blockIdx.y * IM_TQ, b = blockIdx.z;
+  const int tlast = min(T, tq0 + IM_TQ) - 1;
+  const int64_t vis_last = nvis_fixed >= 0 ? nvis_fixed : (m > 0 ? (t0 + tlast + 1) / m : n);
+  if (nt0 >= vis_last) return;
+  uint8_t* kt = sm;                        // 3 x [128][64] bf16 (hi, mid, lo), 128-byte rows, swizzled
+  uint8_t* qt = sm + 3 * IM_TN * 128;      // 3 x [64][64] bf16
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g4 = lane >> 2, j4 = lane & 3;
+  // stage the key tile once
+  for (int idx = tid; idx < IM_TN * 8; idx += 128) {
+    const int r = idx >> 3, ch = idx & 7;
+    const int nn = nt0 + r;
+    float4 x = make_float4(0.f, 0.f, 0.f, 0.f), y = x;
+    if (nn < n) {
+      const float4* p = reinterpret_cast<const float4*>(k + (int64_t)b * k_bstride + (int64_t)nn * IM_D + 8 * ch);
+      x = p[0]; y = p[1];
+    }
+    uint32_t hi[4], mid[4], lo[4];
+    split3_pair(x.x, x.y, hi[0], mid[0], lo[0]); split3_pair(x.z, x.w, hi[1], mid[1], lo[1]);
+    split3_pair(y.x, y.y, hi[2], mid[2], lo[2]); split3_pair(y.z, y.w, hi[3], mid[3], lo[3]);
+    const uint32_t off = swz<128>(r, ch);
+    *reinterpret_cast<uint4*>(kt + off) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+    *reinterpret_cast<uint4*>(kt + IM_TN * 128 + off) = make_uint4(mid[0], mid[1], mid[2], mid[3]);
+    *reinterpret_cast<uint4*>(kt + 2 * IM_TN * 128 + off) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+  }
+  float out[16][4];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) { out[i][0] = out[i][1] = out[i][2] = out[i][3] = 0.f; }
+  const uint32_t kth = smem_addr_u32(kt), ktm = kth + IM_TN * 128, ktl = ktm + IM_TN * 128;
+  const uint32_t qth = smem_addr_u32(qt), qtm = qth + IM_TQ * 128, qtl = qtm + IM_TQ * 128;
+  const int r0 = tq0 + 16 * warp + g4, r1 = r0 + 8;
+  for (int h = 0; h < HI; ++h) {
+    __syncthreads();     // previous head's fragments are in registers; the query tile may be overwritten
+    for (int idx = tid; idx < IM_TQ * 8; idx += 128) {
+      const int r = idx >> 3, ch = idx & 7;
+      const int t = tq0 + r;
+      float4 x = make_float4(0.f, 0.f, 0.f, 0.f), y = x;
+      if (t < T) {
+        const float4* p = reinterpret_cast<const float4*>(q + (((int64_t)b * T + t) * HI + h) * IM_D + 8 * ch);
+        x = p[0]; y = p[1];
+      }
+      uint32_t hi[4], mid[4], lo[4];
+      split3_pair(x.x, x.y, hi[0], mid[0], lo[0]); split3_pair(x.z, x.w, hi[1], mid[1], lo[1]);
+      split3_pair(y.x, y.y, hi[2], mid[2], lo[2]); split3_pair(y.z, y.w, hi[3], mid[3], lo[3]);
+      const uint32_t off = swz<128>(r, ch);
+      *reinterpret_cast<uint4*>(qt + off) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+      *reinterpret_cast<uint4*>(qt + IM_TQ * 128 + off) = make_uint4(mid[0], mid[1], mid[2], mid[3]);
+      *reinterpret_cast<uint4*>(qt + 2 * IM_TQ * 128 + off) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+    }
+    __syncthreads();
+    uint32_t ah[4][4], am[4][4], al[4][4];
+    {
+      const int arow = 16 * warp + (lane & 7) + ((lane >> 3) & 1) * 8;
+#pragma unroll
+      for (int ks = 0; ks < 4; ++ks) {
+        const uint32_t o = swz<128>(arow, 2 * ks + (lane >> 4));
+        ldmatrix_x4(qth + o, ah[ks][0], ah[ks][1], ah[ks][2], ah[ks][3]);
+        ldmatrix_x4(qtm + o, am[ks][0], am[ks][1], am[ks][2], am[ks][3]);
+        ldmatrix_x4(qtl + o, al[ks][0], al[ks][1], al[ks][2], al[ks][3]);
+      }
+    }
+    float w0 = 1.f, w1 = 1.f;
+    if (w) {
+      w0 = r0 < T ? w[((int64_t)b * T + r0) * HI + h] : 0.f;
+      w1 = r1 < T ? w[((int64_t)b * T + r1) * HI + h] : 0.f;
+    }
+#pragma unroll
+    for (int nt = 0; nt < 16; ++nt) {
+      float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int qd = 0; qd < 2; ++qd) {
+        const uint32_t o = swz<128>(8 * nt + (lane & 7), 4 * qd + (lane >> 3));
+        uint32_t bh[4], bm[4], bl[4];
+        ldmatrix_x4(kth + o, bh[0], bh[1], bh[2], bh[3]);
+        ldmatrix_x4(ktm + o, bm[0], bm[1], bm[2], bm[3]);
+        ldmatrix_x4(ktl + o, bl[0], bl[1], bl[2], bl[3]);
+#pragma unroll
+        for (int kk = 0; kk < 2; ++kk) {
+          const int ks = 2 * qd + kk;
+          mma_bf16_16816(acc, al[ks], bh[2 * kk], bh[2 * kk + 1]);     // smallest terms first
+          mma_bf16_16816(acc, ah[ks], bl[2 * kk], bl[2 * kk + 1]);
+          mma_bf16_16816(acc, am[ks], bm[2 * kk], bm[2 * kk + 1]);
+          mma_bf16_16816(acc, am[ks], bh[2 * kk], bh[2 * kk + 1]);
+          mma_bf16_16816(acc, ah[ks], bm[2 * kk], bm[2 * kk + 1]);
+          mma_bf16_16816(acc, ah[ks], bh[2 * kk], bh[2 * kk + 1]);
+        }
+      }
+      out[nt][0] = fmaf(fmaxf(acc[0] * scale, 0.f), w0, out[nt][0]);
+      out[nt][1] = fmaf(fmaxf(acc[1] * scale, 0.f), w0, out[nt][1]);
+      out[nt][2] = fmaf(fmaxf(acc[2] * scale, 0.f), w1, out[nt][2]);
+      out[nt][3] = fmaf(fmaxf(acc[3] * scale, 0.f), w1, out[nt][3]);
+    }
+  }
+#pragma unroll
+  for (int nt = 0; nt < 16; ++nt) {
+    const int nn = nt0 + 8 * nt + 2 * j4;
+    if (r0 < T) {
+      float* p = logits + ((int64_t)b * T + r0) * n_ld + nn;
+      if (nn + 1 < n) *reinterpret_cast<float2*>(p) = make_float2(out[nt][0], out[nt][1]);
+      else if (nn < n) p[0] = out[nt][0];
+    }
+    if (r1 < T) {
+      float* p = logits + ((int64_t)b * T + r1) * n_ld + nn;
+      if (nn + 1 < n) *reinterpret_cast<float2*>(p) = make_float2(out[nt][2], out[nt][3]);
+      else if (nn < n) p[0] = out[nt][2];
+    }
+  }
+}
+
+// logits launcher shared by both entry points: tensor cores for DI == 64, CUDA cores otherwise
+static int launch_indexer_logits(const float* q_idx, const float* k_idx, const float* w_idx, float* logits, int B,
+                                 int T, int n_blocks, int HI, int DI, int64_t n_ld, float scale, int m, int64_t t0,
+                                 int n_visible, int64_t k_batch_stride, cudaStream_t s) {
+  const int64_t kbs = k_batch_stride > 0 ? k_batch_stride : (int64_t)n_blocks * DI;
+  static const bool force_simt = [] { const char* e = getenv("KCH_INDEXER"); return e && e[0] == 's'; }();
+  const bool aligned = (((uintptr_t)q_idx | (uintptr_t)k_idx) & 15) == 0 && (kbs % 4) == 0;
+  if (!force_simt && DI == IM_D && aligned) {
+    const int smem = 3 * (IM_TN + IM_TQ) * 128;
+    KCH_CUDA_OK(cudaFuncSetAttribute(indexer_logits_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    dim3 g((n_blocks + IM_TN - 1) / IM_TN, (T + IM_TQ - 1) / IM_TQ, B);
+    indexer_logits_mma_kernel<<<g, 128, smem, s>>>(q_idx, k_idx, w_idx, logits, T, n_blocks, HI, n_ld, scale, m, t0,
+                                                    n_visible, kbs);
+  } else {
+    dim3 g1((n_blocks + IDX_TN - 1) / IDX_TN, (T + IDX_TQ - 1) / IDX_TQ, B);
+    indexer_logits_kernel<<<g1, 256, 0, s>>>(q_idx, k_idx, w_idx, logits, T, n_blocks, HI, DI, n_ld, scale, m, t0,
+                                              n_visible, kbs);
+  }
+  KCH_LAUNCH_OK();
+  return KCH_OK;
+}
+
+// ---------------------------------------------------------------------------------------
 // Selection: one CTA per query row.
 // ---------------------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t f2ord(float f) {
@@ -119,8 +278,11 @@ __device__ __forceinline__ int block_excl_scan(int v, int* buf, int* total) {
 
 __global__ void __launch_bounds__(256)
 topk_select_kernel(const float* __restrict__ logits, int32_t* __restrict__ out, int T, int n,
-                   int64_t n_ld, int topk, int m, int64_t t0, int nvis_fixed, int sorted) {
-  extern __shared__ unsigned long long ssort[];  // only when sorted
+                   int64_t n_ld, int topk, int m, int64_t t0, int nvis_fixed, int sorted, int cache_cap) {
+  // dynamic shared memory: [cache_cap floats: the row's visible logits] [sort keys, only when sorted]
+  extern __shared__ __align__(16) uint8_t sel_smem[];
+  float* srow = reinterpret_cast<float*>(sel_smem);
+  unsigned long long* ssort = reinterpret_cast<unsigned long long*>(sel_smem + (size_t)cache_cap * 4);
   const int64_t row = blockIdx.x;  // b*T + t
   const int t = (int)(row % T);
   const float* lg = logits + row * n_ld;
@@ -129,6 +291,13 @@ topk_select_kernel(const float* __restrict__ logits, int32_t* __restrict__ out, 
   const int nv = (int)(nv64 < n ? nv64 : n);
   const int ksel = topk < n ? topk : n;
   const int tid = threadIdx.x;
+  if (nv > ksel && nv <= cache_cap) {
+    // every pass below re-reads the row: serve it from shared memory after one coalesced read
+    const float4* src = reinterpret_cast<const float4*>(lg);
+    for (int i = tid; i < (nv + 3) / 4; i += 256) reinterpret_cast<float4*>(srow)[i] = src[i];
+    __syncthreads();
+    lg = srow;
+  }
   __shared__ int hist[256];
   __shared__ int sbuf[9];
   __shared__ uint32_t s_prefix;
@@ -240,10 +409,11 @@ extern "C" int kch_indexer_topk(const float* q_idx, const float* k_idx, const fl
               (long long)workspace_bytes, (long long)need);
   int64_t n_ld = ((int64_t)n_blocks + 3) & ~3LL;
   float* logits = (float*)workspace;
-  dim3 g1((n_blocks + IDX_TN - 1) / IDX_TN, (T + IDX_TQ - 1) / IDX_TQ, B);
-  indexer_logits_kernel<<<g1, 256, 0, s>>>(q_idx, k_idx, w_idx, logits, T, n_blocks, HI, DI, n_ld, scale,
-                                            m, t0, n_visible, k_batch_stride > 0 ? k_batch_stride : (int64_t)n_blocks * DI);
-  KCH_LAUNCH_OK();
+  {
+    int rc = launch_indexer_logits(q_idx, k_idx, w_idx, logits, B, T, n_blocks, HI, DI, n_ld, scale, m, t0, n_visible,
+                                   k_batch_stride, s);
+    if (rc != KCH_OK) return rc;
+  }
   size_t smem = 0;
   if (sorted) {
     int ks = topk < n_blocks ? topk : n_blocks;
@@ -251,10 +421,13 @@ extern "C" int kch_indexer_topk(const float* q_idx, const float* k_idx, const fl
     while (P < ks) P <<= 1;
     KCH_REQUIRE(P <= 8192, "kch_indexer_topk: sorted output supports topk <= 8192 (got %d)", ks);
     smem = (size_t)P * 8;
-    KCH_CUDA_OK(cudaFuncSetAttribute(topk_select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   }
+  // row cache: up to 16384 logits (64 KiB); n_ld is a multiple of 4 so the float4 read stays in the row
+  const int cache_cap = (int)(n_ld <= 16384 ? n_ld : 0);
+  smem += (size_t)cache_cap * 4;
+  KCH_CUDA_OK(cudaFuncSetAttribute(topk_select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   topk_select_kernel<<<(unsigned)((int64_t)B * T), 256, smem, s>>>(logits, indices, T, n_blocks, n_ld, topk, m,
-                                                                    t0, n_visible, sorted);
+                                                                    t0, n_visible, sorted, cache_cap);
   KCH_LAUNCH_OK();
   return KCH_OK;
 }
@@ -320,12 +493,13 @@ extern "C" int kch_indexer_topk_static(const float* q_idx, const float* k_idx, c
   float* logits = nullptr;
   int rc = indexer_static_address(&logits);
   if (rc != KCH_OK) return rc;
-  dim3 g1((n_blocks + IDX_TN - 1) / IDX_TN, (T + IDX_TQ - 1) / IDX_TQ, B);
-  indexer_logits_kernel<<<g1, 256, 0, s>>>(q_idx, k_idx, w_idx, logits, T, n_blocks, HI, DI, n_ld, scale, m, t0,
-                                            n_visible, k_batch_stride > 0 ? k_batch_stride : (int64_t)n_blocks * DI);
-  KCH_LAUNCH_OK();
-  topk_select_kernel<<<(unsigned)((int64_t)B * T), 256, 0, s>>>(logits, indices, T, n_blocks, n_ld, topk, m, t0,
-                                                                 n_visible, 0);
+  rc = launch_indexer_logits(q_idx, k_idx, w_idx, logits, B, T, n_blocks, HI, DI, n_ld, scale, m, t0, n_visible,
+                             k_batch_stride, s);
+  if (rc != KCH_OK) return rc;
+  const int cache_cap = (int)(n_ld <= 16384 ? n_ld : 0);
+  KCH_CUDA_OK(cudaFuncSetAttribute(topk_select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, cache_cap * 4));
+  topk_select_kernel<<<(unsigned)((int64_t)B * T), 256, (size_t)cache_cap * 4, s>>>(logits, indices, T, n_blocks, n_ld,
+                                                                                     topk, m, t0, n_visible, 0, cache_cap);
   KCH_LAUNCH_OK();
   return KCH_OK;
 }
