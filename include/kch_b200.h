@@ -119,7 +119,7 @@ int kch_compress_kv_overlapped(const void* Ca, const void* Cb, const void* Za, c
  * indices int32 [B,T,topk], -1 padded; ties go to the lower block index; `sorted` orders the picks
  * by descending logit as torch.topk does.  k_batch_stride: elements between the key blocks of
  * consecutive batch entries (0 = n_blocks*DI).  Workspace: kch_indexer_workspace_bytes. */
-int64_t kch_indexer_workspace_bytes(int B, int T, int n_blocks);
+int64_t kch_indexer_workspace_bytes(int B, int T, int n_blocks, int HI, int DI);
 int kch_indexer_topk(const float* q_idx, const float* k_idx, const float* w_idx, int32_t* indices, int B,
                      int T, int n_blocks, int HI, int DI, int topk, float scale, int m, int64_t t0,
                      int n_visible, int sorted, int64_t k_batch_stride, void* workspace,

@@ -103,60 +103,126 @@ __device__ __forceinline__ void split3_pair(float x0, float x1, uint32_t& hi, ui
   lo = *reinterpret_cast<uint32_t*>(&c);
 }
 
+// Three-term split of fp32 rows into three bf16 row arrays (row r of batch b read at x + b*bstride + r*64).
+__global__ void split3_rows_kernel(const float* __restrict__ x, int64_t rows_per_batch, int64_t bstride, int64_t rows,
+                                   bf16* __restrict__ hi, bf16* __restrict__ mid, bf16* __restrict__ lo) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;   // one 8-element chunk
+  if (i >= rows * 8) return;
+  const int64_t r = i >> 3;
+  const int ch = (int)(i & 7);
+  const float4* p = reinterpret_cast<const float4*>(x + (r / rows_per_batch) * bstride + (r % rows_per_batch) * IM_D + 8 * ch);
+  const float4 a = p[0], c = p[1];
+  uint32_t h[4], m[4], l[4];
+  split3_pair(a.x, a.y, h[0], m[0], l[0]); split3_pair(a.z, a.w, h[1], m[1], l[1]);
+  split3_pair(c.x, c.y, h[2], m[2], l[2]); split3_pair(c.z, c.w, h[3], m[3], l[3]);
+  *reinterpret_cast<uint4*>(hi + i * 8) = make_uint4(h[0], h[1], h[2], h[3]);
+  *reinterpret_cast<uint4*>(mid + i * 8) = make_uint4(m[0], m[1], m[2], m[3]);
+  *reinterpret_cast<uint4*>(lo + i * 8) = make_uint4(l[0], l[1], l[2], l[3]);
+}
+
+__device__ __forceinline__ void cpa16(uint32_t dst, const void* src, int bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
+}
+
+struct IdxSplit {            // pre-split operands (PRE = true); rows are 64 bf16
+  const bf16 *qh, *qm, *ql;  // [B*T*HI][64]
+  const bf16 *kh, *km, *kl;  // [B*n][64]
+};
+
+// PRE = false: operands are split inside the kernel (no extra workspace); PRE = true: the three bf16 terms
+// were prepared once by split3_rows_kernel and are streamed in with cp.async (query tiles double-buffered).
+template <bool PRE>
 __global__ void __launch_bounds__(128)
 indexer_logits_mma_kernel(const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ w,
-                          float* __restrict__ logits, int T, int n, int HI, int64_t n_ld, float scale, int m,
-                          int64_t t0, int nvis_fixed, int64_t k_bstride) {
+                          IdxSplit sp, float* __restrict__ logits, int T, int n, int HI, int64_t n_ld, float scale,
+                          int m, int64_t t0, int nvis_fixed, int64_t k_bstride) {
   extern __shared__ __align__(128) uint8_t sm[];
   const int nt0 = blockIdx.x * IM_TN, tq0 = blockIdx.y * IM_TQ, b = blockIdx.z;
   const int tlast = min(T, tq0 + IM_TQ) - 1;
   const int64_t vis_last = nvis_fixed >= 0 ? nvis_fixed : (m > 0 ? (t0 + tlast + 1) / m : n);
   if (nt0 >= vis_last) return;
   uint8_t* kt = sm;                        // 3 x [128][64] bf16 (hi, mid, lo), 128-byte rows, swizzled
-  uint8_t* qt = sm + 3 * IM_TN * 128;      // 3 x [64][64] bf16
+  uint8_t* qt = sm + 3 * IM_TN * 128;      // (PRE: 2 x) 3 x [64][64] bf16
+  constexpr int QT_BYTES = 3 * IM_TQ * 128;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g4 = lane >> 2, j4 = lane & 3;
+
+  auto stage_q = [&](int h, int buf) {
+    uint8_t* dstb = qt + buf * QT_BYTES;
+    for (int idx = tid; idx < IM_TQ * 8; idx += 128) {
+      const int r = idx >> 3, ch = idx & 7;
+      const int t = tq0 + r;
+      const uint32_t off = swz<128>(r, ch);
+      if constexpr (PRE) {
+        const int64_t src = ((((int64_t)b * T + (t < T ? t : 0)) * HI + h) * IM_D + 8 * ch);
+        const int bytes = t < T ? 16 : 0;
+        cpa16(smem_addr_u32(dstb + off), sp.qh + src, bytes);
+        cpa16(smem_addr_u32(dstb + IM_TQ * 128 + off), sp.qm + src, bytes);
+        cpa16(smem_addr_u32(dstb + 2 * IM_TQ * 128 + off), sp.ql + src, bytes);
+      } else {
+        float4 x = make_float4(0.f, 0.f, 0.f, 0.f), y = x;
+        if (t < T) {
+          const float4* p = reinterpret_cast<const float4*>(q + (((int64_t)b * T + t) * HI + h) * IM_D + 8 * ch);
+          x = p[0]; y = p[1];
+        }
+        uint32_t hi[4], mid[4], lo[4];
+        split3_pair(x.x, x.y, hi[0], mid[0], lo[0]); split3_pair(x.z, x.w, hi[1], mid[1], lo[1]);
+        split3_pair(y.x, y.y, hi[2], mid[2], lo[2]); split3_pair(y.z, y.w, hi[3], mid[3], lo[3]);
+        *reinterpret_cast<uint4*>(dstb + off) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+        *reinterpret_cast<uint4*>(dstb + IM_TQ * 128 + off) = make_uint4(mid[0], mid[1], mid[2], mid[3]);
+        *reinterpret_cast<uint4*>(dstb + 2 * IM_TQ * 128 + off) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+      }
+    }
+    if constexpr (PRE) asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+
   // stage the key tile once
   for (int idx = tid; idx < IM_TN * 8; idx += 128) {
     const int r = idx >> 3, ch = idx & 7;
     const int nn = nt0 + r;
-    float4 x = make_float4(0.f, 0.f, 0.f, 0.f), y = x;
-    if (nn < n) {
-      const float4* p = reinterpret_cast<const float4*>(k + (int64_t)b * k_bstride + (int64_t)nn * IM_D + 8 * ch);
-      x = p[0]; y = p[1];
-    }
-    uint32_t hi[4], mid[4], lo[4];
-    split3_pair(x.x, x.y, hi[0], mid[0], lo[0]); split3_pair(x.z, x.w, hi[1], mid[1], lo[1]);
-    split3_pair(y.x, y.y, hi[2], mid[2], lo[2]); split3_pair(y.z, y.w, hi[3], mid[3], lo[3]);
     const uint32_t off = swz<128>(r, ch);
-    *reinterpret_cast<uint4*>(kt + off) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
-    *reinterpret_cast<uint4*>(kt + IM_TN * 128 + off) = make_uint4(mid[0], mid[1], mid[2], mid[3]);
-    *reinterpret_cast<uint4*>(kt + 2 * IM_TN * 128 + off) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
-  }
-  float out[16][4];
-#pragma unroll
-  for (int i = 0; i < 16; ++i) { out[i][0] = out[i][1] = out[i][2] = out[i][3] = 0.f; }
-  const uint32_t kth = smem_addr_u32(kt), ktm = kth + IM_TN * 128, ktl = ktm + IM_TN * 128;
-  const uint32_t qth = smem_addr_u32(qt), qtm = qth + IM_TQ * 128, qtl = qtm + IM_TQ * 128;
-  const int r0 = tq0 + 16 * warp + g4, r1 = r0 + 8;
-  for (int h = 0; h < HI; ++h) {
-    __syncthreads();     // previous head's fragments are in registers; the query tile may be overwritten
-    for (int idx = tid; idx < IM_TQ * 8; idx += 128) {
-      const int r = idx >> 3, ch = idx & 7;
-      const int t = tq0 + r;
+    if constexpr (PRE) {
+      const int64_t src = ((int64_t)b * n + (nn < n ? nn : 0)) * IM_D + 8 * ch;
+      const int bytes = nn < n ? 16 : 0;
+      cpa16(smem_addr_u32(kt + off), sp.kh + src, bytes);
+      cpa16(smem_addr_u32(kt + IM_TN * 128 + off), sp.km + src, bytes);
+      cpa16(smem_addr_u32(kt + 2 * IM_TN * 128 + off), sp.kl + src, bytes);
+    } else {
       float4 x = make_float4(0.f, 0.f, 0.f, 0.f), y = x;
-      if (t < T) {
-        const float4* p = reinterpret_cast<const float4*>(q + (((int64_t)b * T + t) * HI + h) * IM_D + 8 * ch);
+      if (nn < n) {
+        const float4* p = reinterpret_cast<const float4*>(k + (int64_t)b * k_bstride + (int64_t)nn * IM_D + 8 * ch);
         x = p[0]; y = p[1];
       }
       uint32_t hi[4], mid[4], lo[4];
       split3_pair(x.x, x.y, hi[0], mid[0], lo[0]); split3_pair(x.z, x.w, hi[1], mid[1], lo[1]);
       split3_pair(y.x, y.y, hi[2], mid[2], lo[2]); split3_pair(y.z, y.w, hi[3], mid[3], lo[3]);
-      const uint32_t off = swz<128>(r, ch);
-      *reinterpret_cast<uint4*>(qt + off) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
-      *reinterpret_cast<uint4*>(qt + IM_TQ * 128 + off) = make_uint4(mid[0], mid[1], mid[2], mid[3]);
-      *reinterpret_cast<uint4*>(qt + 2 * IM_TQ * 128 + off) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+      *reinterpret_cast<uint4*>(kt + off) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+      *reinterpret_cast<uint4*>(kt + IM_TN * 128 + off) = make_uint4(mid[0], mid[1], mid[2], mid[3]);
+      *reinterpret_cast<uint4*>(kt + 2 * IM_TN * 128 + off) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
     }
-    __syncthreads();
+  }
+  if constexpr (PRE) stage_q(0, 0);     // joins the key tile's copies in the first commit group
+  float out[16][4];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) { out[i][0] = out[i][1] = out[i][2] = out[i][3] = 0.f; }
+  const uint32_t kth = smem_addr_u32(kt), ktm = kth + IM_TN * 128, ktl = ktm + IM_TN * 128;
+  const int r0 = tq0 + 16 * warp + g4, r1 = r0 + 8;
+  for (int h = 0; h < HI; ++h) {
+    int buf = 0;
+    if constexpr (PRE) {
+      buf = h & 1;
+      if (h + 1 < HI) {
+        stage_q(h + 1, buf ^ 1);          // the other buffer was released by the barrier ending head h-1
+        asm volatile("cp.async.wait_group 1;" ::: "memory");
+      } else {
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+      }
+      __syncthreads();
+    } else {
+      __syncthreads();     // previous head's fragments are in registers; the query tile may be overwritten
+      stage_q(h, 0);
+      __syncthreads();
+    }
+    const uint32_t qth = smem_addr_u32(qt + buf * QT_BYTES), qtm = qth + IM_TQ * 128, qtl = qtm + IM_TQ * 128;
     uint32_t ah[4][4], am[4][4], al[4][4];
     {
       const int arow = 16 * warp + (lane & 7) + ((lane >> 3) & 1) * 8;
@@ -173,32 +239,48 @@ indexer_logits_mma_kernel(const float* __restrict__ q, const float* __restrict__
       w0 = r0 < T ? w[((int64_t)b * T + r0) * HI + h] : 0.f;
       w1 = r1 < T ? w[((int64_t)b * T + r1) * HI + h] : 0.f;
     }
+    // two 8-block column tiles at a time: two independent accumulator chains per warp
 #pragma unroll
-    for (int nt = 0; nt < 16; ++nt) {
-      float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int np = 0; np < 8; ++np) {
+      float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
 #pragma unroll
       for (int qd = 0; qd < 2; ++qd) {
-        const uint32_t o = swz<128>(8 * nt + (lane & 7), 4 * qd + (lane >> 3));
-        uint32_t bh[4], bm[4], bl[4];
-        ldmatrix_x4(kth + o, bh[0], bh[1], bh[2], bh[3]);
-        ldmatrix_x4(ktm + o, bm[0], bm[1], bm[2], bm[3]);
-        ldmatrix_x4(ktl + o, bl[0], bl[1], bl[2], bl[3]);
+        uint32_t bh[2][4], bm[2][4], bl[2][4];
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          const uint32_t o = swz<128>(8 * (2 * np + u) + (lane & 7), 4 * qd + (lane >> 3));
+          ldmatrix_x4(kth + o, bh[u][0], bh[u][1], bh[u][2], bh[u][3]);
+          ldmatrix_x4(ktm + o, bm[u][0], bm[u][1], bm[u][2], bm[u][3]);
+          ldmatrix_x4(ktl + o, bl[u][0], bl[u][1], bl[u][2], bl[u][3]);
+        }
 #pragma unroll
         for (int kk = 0; kk < 2; ++kk) {
           const int ks = 2 * qd + kk;
-          mma_bf16_16816(acc, al[ks], bh[2 * kk], bh[2 * kk + 1]);     // smallest terms first
-          mma_bf16_16816(acc, ah[ks], bl[2 * kk], bl[2 * kk + 1]);
-          mma_bf16_16816(acc, am[ks], bm[2 * kk], bm[2 * kk + 1]);
-          mma_bf16_16816(acc, am[ks], bh[2 * kk], bh[2 * kk + 1]);
-          mma_bf16_16816(acc, ah[ks], bm[2 * kk], bm[2 * kk + 1]);
-          mma_bf16_16816(acc, ah[ks], bh[2 * kk], bh[2 * kk + 1]);
+          // smallest terms first; the two column tiles alternate so consecutive MMAs are independent
+          mma_bf16_16816(acc[0], al[ks], bh[0][2 * kk], bh[0][2 * kk + 1]);
+          mma_bf16_16816(acc[1], al[ks], bh[1][2 * kk], bh[1][2 * kk + 1]);
+          mma_bf16_16816(acc[0], ah[ks], bl[0][2 * kk], bl[0][2 * kk + 1]);
+          mma_bf16_16816(acc[1], ah[ks], bl[1][2 * kk], bl[1][2 * kk + 1]);
+          mma_bf16_16816(acc[0], am[ks], bm[0][2 * kk], bm[0][2 * kk + 1]);
+          mma_bf16_16816(acc[1], am[ks], bm[1][2 * kk], bm[1][2 * kk + 1]);
+          mma_bf16_16816(acc[0], am[ks], bh[0][2 * kk], bh[0][2 * kk + 1]);
+          mma_bf16_16816(acc[1], am[ks], bh[1][2 * kk], bh[1][2 * kk + 1]);
+          mma_bf16_16816(acc[0], ah[ks], bm[0][2 * kk], bm[0][2 * kk + 1]);
+          mma_bf16_16816(acc[1], ah[ks], bm[1][2 * kk], bm[1][2 * kk + 1]);
+          mma_bf16_16816(acc[0], ah[ks], bh[0][2 * kk], bh[0][2 * kk + 1]);
+          mma_bf16_16816(acc[1], ah[ks], bh[1][2 * kk], bh[1][2 * kk + 1]);
         }
       }
-      out[nt][0] = fmaf(fmaxf(acc[0] * scale, 0.f), w0, out[nt][0]);
-      out[nt][1] = fmaf(fmaxf(acc[1] * scale, 0.f), w0, out[nt][1]);
-      out[nt][2] = fmaf(fmaxf(acc[2] * scale, 0.f), w1, out[nt][2]);
-      out[nt][3] = fmaf(fmaxf(acc[3] * scale, 0.f), w1, out[nt][3]);
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        const int nt = 2 * np + u;
+        out[nt][0] = fmaf(fmaxf(acc[u][0] * scale, 0.f), w0, out[nt][0]);
+        out[nt][1] = fmaf(fmaxf(acc[u][1] * scale, 0.f), w0, out[nt][1]);
+        out[nt][2] = fmaf(fmaxf(acc[u][2] * scale, 0.f), w1, out[nt][2]);
+        out[nt][3] = fmaf(fmaxf(acc[u][3] * scale, 0.f), w1, out[nt][3]);
+      }
     }
+    if constexpr (PRE) __syncthreads();   // every warp is done with this head's query buffer
   }
 #pragma unroll
   for (int nt = 0; nt < 16; ++nt) {
@@ -216,19 +298,46 @@ indexer_logits_mma_kernel(const float* __restrict__ q, const float* __restrict__
   }
 }
 
-// logits launcher shared by both entry points: tensor cores for DI == 64, CUDA cores otherwise
+static inline int64_t align256(int64_t x) { return (x + 255) & ~255LL; }
+
+// logits launcher shared by both entry points: tensor cores for DI == 64, CUDA cores otherwise.
+// `split_ws` (optional, split_bytes long) holds the pre-split operands when it is large enough.
+static int64_t indexer_split_bytes(int B, int T, int n_blocks, int HI, int DI) {
+  if (DI != IM_D) return 0;
+  return 3 * (align256((int64_t)B * T * HI * IM_D * 2) + align256((int64_t)B * n_blocks * IM_D * 2));
+}
+
 static int launch_indexer_logits(const float* q_idx, const float* k_idx, const float* w_idx, float* logits, int B,
                                  int T, int n_blocks, int HI, int DI, int64_t n_ld, float scale, int m, int64_t t0,
-                                 int n_visible, int64_t k_batch_stride, cudaStream_t s) {
+                                 int n_visible, int64_t k_batch_stride, void* split_ws, int64_t split_bytes,
+                                 cudaStream_t s) {
   const int64_t kbs = k_batch_stride > 0 ? k_batch_stride : (int64_t)n_blocks * DI;
   static const bool force_simt = [] { const char* e = getenv("KCH_INDEXER"); return e && e[0] == 's'; }();
   const bool aligned = (((uintptr_t)q_idx | (uintptr_t)k_idx) & 15) == 0 && (kbs % 4) == 0;
   if (!force_simt && DI == IM_D && aligned) {
-    const int smem = 3 * (IM_TN + IM_TQ) * 128;
-    KCH_CUDA_OK(cudaFuncSetAttribute(indexer_logits_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     dim3 g((n_blocks + IM_TN - 1) / IM_TN, (T + IM_TQ - 1) / IM_TQ, B);
-    indexer_logits_mma_kernel<<<g, 128, smem, s>>>(q_idx, k_idx, w_idx, logits, T, n_blocks, HI, n_ld, scale, m, t0,
-                                                    n_visible, kbs);
+    IdxSplit sp = {};
+    if (split_ws && split_bytes >= indexer_split_bytes(B, T, n_blocks, HI, DI) && (((uintptr_t)split_ws) & 15) == 0) {
+      const int64_t qrows = (int64_t)B * T * HI, krows = (int64_t)B * n_blocks;
+      const int64_t qb = align256(qrows * IM_D * 2), kb = align256(krows * IM_D * 2);
+      uint8_t* p = (uint8_t*)split_ws;
+      bf16* qh = (bf16*)p; bf16* qm = (bf16*)(p + qb); bf16* ql = (bf16*)(p + 2 * qb);
+      bf16* kh = (bf16*)(p + 3 * qb); bf16* km = (bf16*)(p + 3 * qb + kb); bf16* kl = (bf16*)(p + 3 * qb + 2 * kb);
+      split3_rows_kernel<<<(unsigned)ceil_div64(qrows * 8, 256), 256, 0, s>>>(q_idx, qrows, 0, qrows, qh, qm, ql);
+      KCH_LAUNCH_OK();
+      split3_rows_kernel<<<(unsigned)ceil_div64(krows * 8, 256), 256, 0, s>>>(k_idx, n_blocks, kbs, krows, kh, km, kl);
+      KCH_LAUNCH_OK();
+      sp.qh = qh; sp.qm = qm; sp.ql = ql; sp.kh = kh; sp.km = km; sp.kl = kl;
+      const int smem = 3 * IM_TN * 128 + 2 * 3 * IM_TQ * 128;
+      KCH_CUDA_OK(cudaFuncSetAttribute(indexer_logits_mma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+      indexer_logits_mma_kernel<true><<<g, 128, smem, s>>>(q_idx, k_idx, w_idx, sp, logits, T, n_blocks, HI, n_ld, scale,
+                                                           m, t0, n_visible, kbs);
+    } else {
+      const int smem = 3 * (IM_TN + IM_TQ) * 128;
+      KCH_CUDA_OK(cudaFuncSetAttribute(indexer_logits_mma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+      indexer_logits_mma_kernel<false><<<g, 128, smem, s>>>(q_idx, k_idx, w_idx, sp, logits, T, n_blocks, HI, n_ld, scale,
+                                                            m, t0, n_visible, kbs);
+    }
   } else {
     dim3 g1((n_blocks + IDX_TN - 1) / IDX_TN, (T + IDX_TQ - 1) / IDX_TQ, B);
     indexer_logits_kernel<<<g1, 256, 0, s>>>(q_idx, k_idx, w_idx, logits, T, n_blocks, HI, DI, n_ld, scale, m, t0,
@@ -291,13 +400,6 @@ topk_select_kernel(const float* __restrict__ logits, int32_t* __restrict__ out, 
   const int nv = (int)(nv64 < n ? nv64 : n);
   const int ksel = topk < n ? topk : n;
   const int tid = threadIdx.x;
-  if (nv > ksel && nv <= cache_cap) {
-    // every pass below re-reads the row: serve it from shared memory after one coalesced read
-    const float4* src = reinterpret_cast<const float4*>(lg);
-    for (int i = tid; i < (nv + 3) / 4; i += 256) reinterpret_cast<float4*>(srow)[i] = src[i];
-    __syncthreads();
-    lg = srow;
-  }
   __shared__ int hist[256];
   __shared__ int sbuf[9];
   __shared__ uint32_t s_prefix;
@@ -307,49 +409,59 @@ topk_select_kernel(const float* __restrict__ logits, int32_t* __restrict__ out, 
     for (int i = tid; i < topk; i += 256) orow[i] = i < nv ? i : -1;
     nsel = nv;
   } else {
+    // Thread t owns the contiguous index range [t*E, (t+1)*E): ordered compaction then needs one
+    // block scan in total.  The row is staged in shared memory transposed (element k of thread t at
+    // k*256 + t) so that those strided-by-E reads are bank-conflict free.
+    const int E = (nv + 255) >> 8;
+    const bool cached = E * 256 <= cache_cap;
+    if (cached) {
+      for (int i = tid; i < nv; i += 256) srow[(i % E) * 256 + i / E] = lg[i];
+      __syncthreads();
+    }
+    const int i0 = tid * E;
+    const int cnt_mine = max(0, min(E, nv - i0));
+    auto val = [&](int k) -> float { return cached ? srow[k * 256 + tid] : lg[i0 + k]; };
     uint32_t prefix = 0, pmask = 0;
     int need = ksel;  // how many still to take from the current prefix class
     for (int pass = 0; pass < 4; ++pass) {
       const int shift = 24 - 8 * pass;
       hist[tid] = 0;
       __syncthreads();
-      for (int i = tid; i < nv; i += 256) {
-        uint32_t u = f2ord(lg[i]);
+      for (int k = 0; k < cnt_mine; ++k) {
+        uint32_t u = f2ord(val(k));
         if ((u & pmask) == prefix) atomicAdd(&hist[(u >> shift) & 255], 1);
       }
       __syncthreads();
-      if (tid == 0) {
-        int cum = 0, bsel = 0;
-        for (int bin = 255; bin >= 0; --bin) {
-          int cnt = hist[bin];
-          if (cum + cnt >= need) { bsel = bin; break; }
-          cum += cnt;
-        }
-        s_prefix = prefix | ((uint32_t)bsel << shift);
+      // thread t looks at bin 255-t: an exclusive scan gives the population of all higher bins
+      const int bin = 255 - tid;
+      const int cnt = hist[bin];
+      int tot;
+      const int cum = block_excl_scan(cnt, sbuf, &tot);
+      if (cum < need && cum + cnt >= need) {
+        s_prefix = prefix | ((uint32_t)bin << shift);
         s_need = need - cum;
       }
       __syncthreads();
       prefix = s_prefix;
       need = s_need;
       pmask |= 0xFFu << shift;
-      __syncthreads();
     }
     // prefix = key of the k-th largest logit; `need` of the entries equal to it are taken,
     // lowest index first; everything strictly greater is taken.
     const int n_gt = ksel - need;
-    int run_gt = 0, run_eq = 0;
-    for (int base = 0; base < nv; base += 256) {
-      int i = base + tid;
-      uint32_t u = i < nv ? f2ord(lg[i]) : 0u;
-      int is_gt = (i < nv && u > prefix) ? 1 : 0;
-      int is_eq = (i < nv && u == prefix) ? 1 : 0;
-      int tot_gt, tot_eq;
-      int pg = block_excl_scan(is_gt, sbuf, &tot_gt);
-      int pe = block_excl_scan(is_eq, sbuf, &tot_eq);
-      if (is_gt) orow[run_gt + pg] = i;
-      if (is_eq && run_eq + pe < need) orow[n_gt + run_eq + pe] = i;
-      run_gt += tot_gt;
-      run_eq += tot_eq;
+    int c_gt = 0, c_eq = 0;
+    for (int k = 0; k < cnt_mine; ++k) {
+      uint32_t u = f2ord(val(k));
+      c_gt += (u > prefix);
+      c_eq += (u == prefix);
+    }
+    int tot_gt, tot_eq;
+    int p_gt = block_excl_scan(c_gt, sbuf, &tot_gt);
+    int p_eq = block_excl_scan(c_eq, sbuf, &tot_eq);
+    for (int k = 0; k < cnt_mine; ++k) {
+      uint32_t u = f2ord(val(k));
+      if (u > prefix) orow[p_gt++] = i0 + k;
+      else if (u == prefix) { if (p_eq < need) orow[n_gt + p_eq] = i0 + k; ++p_eq; }
     }
     for (int i = ksel + tid; i < topk; i += 256) orow[i] = -1;
     nsel = ksel;
@@ -383,10 +495,14 @@ topk_select_kernel(const float* __restrict__ logits, int32_t* __restrict__ out, 
   for (int i = tid; i < nsel; i += 256) orow[i] = 0x7FFFFFFF - (int)(uint32_t)(ssort[i] & 0xFFFFFFFFu);
 }
 
-extern "C" int64_t kch_indexer_workspace_bytes(int B, int T, int n) {
-  if (B <= 0 || T <= 0 || n <= 0) return 0;
+static int64_t indexer_logits_bytes(int B, int T, int n) {
   int64_t n_ld = ((int64_t)n + 3) & ~3LL;
-  return (int64_t)B * T * n_ld * 4;
+  return align256((int64_t)B * T * n_ld * 4);
+}
+
+extern "C" int64_t kch_indexer_workspace_bytes(int B, int T, int n, int HI, int DI) {
+  if (B <= 0 || T <= 0 || n <= 0) return 0;
+  return indexer_logits_bytes(B, T, n) + indexer_split_bytes(B, T, n, HI, DI);
 }
 
 extern "C" int kch_indexer_topk(const float* q_idx, const float* k_idx, const float* w_idx,
@@ -404,14 +520,17 @@ extern "C" int kch_indexer_topk(const float* q_idx, const float* k_idx, const fl
     KCH_CUDA_OK(cudaMemsetAsync(indices, 0xFF, (size_t)B * T * topk * sizeof(int32_t), s));
     return KCH_OK;
   }
-  int64_t need = kch_indexer_workspace_bytes(B, T, n_blocks);
-  KCH_REQUIRE(workspace && workspace_bytes >= need, "kch_indexer_topk: workspace %lld < %lld bytes",
-              (long long)workspace_bytes, (long long)need);
+  // the logits are mandatory; the pre-split operands are used when the workspace also has room for them
+  const int64_t need = indexer_logits_bytes(B, T, n_blocks);     // 256-byte aligned start of the split area
+  const int64_t logits_exact = (int64_t)B * T * (((int64_t)n_blocks + 3) & ~3LL) * 4;
+  KCH_REQUIRE(workspace && workspace_bytes >= logits_exact, "kch_indexer_topk: workspace %lld < %lld bytes",
+              (long long)workspace_bytes, (long long)logits_exact);
   int64_t n_ld = ((int64_t)n_blocks + 3) & ~3LL;
   float* logits = (float*)workspace;
   {
+    void* split_ws = workspace_bytes > need ? (void*)((uint8_t*)workspace + need) : nullptr;
     int rc = launch_indexer_logits(q_idx, k_idx, w_idx, logits, B, T, n_blocks, HI, DI, n_ld, scale, m, t0, n_visible,
-                                   k_batch_stride, s);
+                                   k_batch_stride, split_ws, workspace_bytes - need, s);
     if (rc != KCH_OK) return rc;
   }
   size_t smem = 0;
@@ -423,7 +542,7 @@ extern "C" int kch_indexer_topk(const float* q_idx, const float* k_idx, const fl
     smem = (size_t)P * 8;
   }
   // row cache: up to 16384 logits (64 KiB); n_ld is a multiple of 4 so the float4 read stays in the row
-  const int cache_cap = (int)(n_ld <= 16384 ? n_ld : 0);
+  const int cache_cap = (int)(n_ld <= 16384 ? ((n_ld + 255) & ~255LL) : 0);
   smem += (size_t)cache_cap * 4;
   KCH_CUDA_OK(cudaFuncSetAttribute(topk_select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   topk_select_kernel<<<(unsigned)((int64_t)B * T), 256, smem, s>>>(logits, indices, T, n_blocks, n_ld, topk, m,
@@ -494,9 +613,9 @@ extern "C" int kch_indexer_topk_static(const float* q_idx, const float* k_idx, c
   int rc = indexer_static_address(&logits);
   if (rc != KCH_OK) return rc;
   rc = launch_indexer_logits(q_idx, k_idx, w_idx, logits, B, T, n_blocks, HI, DI, n_ld, scale, m, t0, n_visible,
-                             k_batch_stride, s);
+                             k_batch_stride, nullptr, 0, s);
   if (rc != KCH_OK) return rc;
-  const int cache_cap = (int)(n_ld <= 16384 ? n_ld : 0);
+  const int cache_cap = (int)(n_ld <= 16384 ? ((n_ld + 255) & ~255LL) : 0);
   KCH_CUDA_OK(cudaFuncSetAttribute(topk_select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, cache_cap * 4));
   topk_select_kernel<<<(unsigned)((int64_t)B * T), 256, (size_t)cache_cap * 4, s>>>(logits, indices, T, n_blocks, n_ld,
                                                                                      topk, m, t0, n_visible, 0, cache_cap);

@@ -167,7 +167,7 @@ def indexer_topk(q_idx, k_idx, w_idx, topk, *, m=0, t0=0, n_visible=-1, normaliz
     else:
         kn = k_idx.float().contiguous()
     wf = None if w_idx is None else w_idx.float().contiguous()
-    nbytes = int(lib.kch_indexer_workspace_bytes(B, T, n))
+    nbytes = int(lib.kch_indexer_workspace_bytes(B, T, n, HI, DI))
     ws = torch.empty(max(nbytes, 1), dtype=torch.uint8, device=dev)
     with torch.cuda.device(dev):
         _lib.check(lib.kch_indexer_topk(_lib.ptr(qn), _lib.ptr(kn), _lib.ptr(wf), _lib.ptr(idx), B, T, n, HI, DI,

@@ -382,7 +382,8 @@ def _indexer_on_cache(q_idx, kcomp_n, nb, w_idx, topk, nvis, normalize_qk, kbs):
     qn = rownorm(q_idx.float().contiguous(), normalize_qk).contiguous()
     wf = None if w_idx is None else w_idx.float().contiguous()
     idx = torch.empty(B, T, topk, dtype=torch.int32, device=dev)
-    nbytes = int(lib.kch_indexer_workspace_bytes(B, T, nb))
+    # logits only: a single query row per sequence does not amortise pre-splitting the whole key cache
+    nbytes = B * T * ((nb + 3) // 4 * 4) * 4
     ws = torch.empty(max(nbytes, 1), dtype=torch.uint8, device=dev)
     scale = 1.0 if normalize_qk else DI ** -0.5
     with torch.cuda.device(dev):

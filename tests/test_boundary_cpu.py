@@ -46,7 +46,8 @@ def test_argument_errors_come_back_as_codes_without_a_gpu():
     with pytest.raises(ValueError, match="lda"):
         _lib.check(rc)
     assert lib.kch_kda_chunk_workspace_bytes(4, 32768, 16, 128, 128, 64) > 0
-    assert lib.kch_indexer_workspace_bytes(1, 4096, 1024) == 4096 * 1024 * 4
+    assert lib.kch_indexer_workspace_bytes(1, 4096, 1024, 4, 32) == 4096 * 1024 * 4
+    assert lib.kch_indexer_workspace_bytes(1, 4096, 1024, 4, 64) > 4096 * 1024 * 4
 
 
 def test_cpu_tensors_are_refused_not_silently_computed():

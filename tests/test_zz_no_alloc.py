@@ -30,7 +30,7 @@ def _both(lib, q, k, w, topk, m, n_visible):
     n = k.shape[1]
     stream = _lib.stream()
     ref = torch.empty(B, T, topk, dtype=torch.int32, device=DEV)
-    nbytes = int(lib.kch_indexer_workspace_bytes(B, T, n))
+    nbytes = int(lib.kch_indexer_workspace_bytes(B, T, n, HI, DI))
     ws = torch.empty(nbytes, dtype=torch.uint8, device=DEV)
     _lib.check(lib.kch_indexer_topk(_lib.ptr(q), _lib.ptr(k), _lib.ptr(w), _lib.ptr(ref), B, T, n, HI, DI, topk, 1.0,
                                     m, 0, n_visible, 0, 0, _lib.ptr(ws), nbytes, stream))
