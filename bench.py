@@ -121,12 +121,12 @@ class GemmProbe:
         self.enabled = False
 
     def wrap(self, fn):
-        def linear(x, W, residual=None):
+        def linear(x, W, residual=None, **kw):
             if not self.enabled:
-                return fn(x, W, residual)
+                return fn(x, W, residual, **kw)
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             a.record()
-            y = fn(x, W, residual)
+            y = fn(x, W, residual, **kw)
             b.record()
             M = x.numel() // x.shape[-1]
             self.calls.append((a, b, 2.0 * M * W.shape[0] * W.shape[1], M, W.shape[0], W.shape[1]))

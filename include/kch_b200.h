@@ -62,6 +62,23 @@ int kch_short_conv(const void* x, const void* lookback, const void* weight, cons
 int kch_linear(const void* A, const void* W, void* C, const void* residual, int64_t M, int N, int K,
                int64_t lda, int64_t ldw, int64_t ldc, int64_t ldr, int dtype, void* stream);
 
+/* kch_linear with activations fused into the store (ops_fused.py:571-581 applied to the fused q|k|v|g_down|beta
+ * projection): columns [seg_end[s-1], seg_end[s]) get activation seg_act[s] (0 = none, else KCH_ACT_*),
+ * with seg_param[s] (decay scale) and `group` (head width of KCH_ACT_SILU_L2NORM).  Rounding points are
+ * those of the unfused chain.  Runs inside the tcgen05 epilogue when the segment boundaries allow it (with
+ * fast exp/reciprocal intrinsics: at most one bf16 rounding away from the unfused chain), otherwise as
+ * separate in-place passes.  Not combinable with `residual`. */
+typedef struct kch_epilogue {
+  int n_segments;      /* <= 8 */
+  int seg_end[8];
+  int seg_act[8];
+  float seg_param[8];
+  int group;
+} kch_epilogue;
+int kch_linear_ex(const void* A, const void* W, void* C, const void* residual, int64_t M, int N, int K,
+                  int64_t lda, int64_t ldw, int64_t ldc, int64_t ldr, int dtype, const kch_epilogue* epilogue,
+                  void* stream);
+
 /* Activation epilogues with the reference's rounding points, ops_fused.py:571-581.
  * x,y [rows,cols] in `dtype`, rows ldx / ldy elements apart (x may be a column slice of a fused
  * projection); `param` is the decay scale for KCH_ACT_NEG_SOFTPLUS; `group` is the head width for
@@ -79,19 +96,23 @@ int kch_rownorm(const void* x, int64_t ld, void* y, float* norms, int64_t rows, 
 /* ---- KDA ----------------------------------------------------------------------------------- */
 
 /* naive_recurrent_kda, ops_kda.py:175-267.  q,k [B,T,H,K]; v [B,T,HV,V]; g [B,T,HV,K];
- * beta [B,T,HV]; all `dtype`, contiguous.  initial_state / final_state fp32 [B,HV,K,V] (either may
- * be NULL).  o [B,T,HV,V] in `dtype`.  g is clamped below at g_clamp_min (pass -INFINITY to disable). */
+ * beta [B,T,HV]; all `dtype`.  Heads are dense within a token; consecutive tokens are ld_qk / ld_v / ld_g /
+ * ld_beta elements apart (0 = contiguous), so q, k, v, beta may be column slices of one fused projection.
+ * initial_state / final_state fp32 [B,HV,K,V] (either may be NULL).  o [B,T,HV,V] contiguous in `dtype`.
+ * g is clamped below at g_clamp_min (pass -INFINITY to disable). */
 int kch_kda_recurrent(const void* q, const void* k, const void* v, const void* g, const void* beta,
                       const float* initial_state, void* o, float* final_state, int B, int T, int H,
-                      int HV, int K, int V, float scale, float g_clamp_min, int dtype, void* stream);
+                      int HV, int K, int V, float scale, float g_clamp_min, int dtype, int64_t ld_qk,
+                      int64_t ld_v, int64_t ld_g, int64_t ld_beta, void* stream);
 
 /* naive_chunk_kda, ops_kda.py:340-536 (prepare 375-424, chain 509-535, finalize 440-461).  Same
  * tensors as above.  Needs a workspace of kch_kda_chunk_workspace_bytes(...) bytes. */
 int64_t kch_kda_chunk_workspace_bytes(int B, int T, int HV, int K, int V, int chunk_size);
 int kch_kda_chunk(const void* q, const void* k, const void* v, const void* g, const void* beta,
                   const float* initial_state, void* o, float* final_state, int B, int T, int H, int HV,
-                  int K, int V, int chunk_size, float scale, float g_clamp_min, int dtype,
-                  void* workspace, int64_t workspace_bytes, void* stream);
+                  int K, int V, int chunk_size, float scale, float g_clamp_min, int dtype, int64_t ld_qk,
+                  int64_t ld_v, int64_t ld_g, int64_t ld_beta, void* workspace, int64_t workspace_bytes,
+                  void* stream);
 
 /* ---- compression ------------------------------------------------------------------------------ */
 

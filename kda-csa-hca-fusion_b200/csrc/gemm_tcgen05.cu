@@ -3,13 +3,13 @@
 //   optional residual add.  Every dense projection of the hybrid layer goes through here
 //   (q/k/v/g/beta, the fused CSA 6-way KV/indexer projection, W_DQ/W_UQ/W_IUQ, o_proj).
 //
-// Structure (one persistent CTA per SM, 192 threads):
+// Structure (one persistent CTA per SM, 320 threads):
 //   warp 0      : TMA producer — cp.async.bulk.tensor tiles of A (128x64) and W (BNx64), 128-byte
 //                 swizzle, into a 4-stage shared-memory ring (no multicast: every CTA fetches its own).
 //   warp 1      : allocates tensor memory, then one elected lane issues tcgen05.mma (M=128, N=BN,
 //                 K=16 per instruction, four per stage) and tcgen05.commit to release stages.
-//   warps 2..5  : epilogue — tcgen05.ld of the fp32 accumulator (each warp its 32-lane quarter),
-//                 bf16 rounding, residual, 64-byte vector stores.
+//   warps 2..9  : epilogue — tcgen05.ld of the fp32 accumulator (each warp its 32-lane quarter and one
+//                 half of the tile's columns), bf16 rounding, optional activations / residual, 64-byte stores.
 // Two accumulator buffers in tensor memory let the epilogue of tile i overlap the main loop of
 // tile i+1.  Every wait on an mbarrier is bounded; on expiry the kernel records a status word,
 // leaves its loops, frees tensor memory and returns.
@@ -23,7 +23,7 @@
 #define TG_BM 128
 #define TG_BK 64
 #define TG_STAGES 4
-#define TG_THREADS 192
+#define TG_THREADS 320
 #define TG_SPIN_LIMIT (1u << 24)
 
 __device__ unsigned int g_kch_status = 0;  // nonzero: a bounded wait expired (see kch_device_status)
@@ -96,6 +96,19 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr) {
   return d;
 }
 
+// Column-segment activations applied in the epilogue (the rounding points of the unfused chain are kept:
+// the product is rounded to bf16 first, every further step reads bf16, computes in fp32, rounds to bf16).
+struct TgEpilogue {
+  int nseg;            // 0: plain store
+  int seg_end[8];      // exclusive end column of segment s (ascending)
+  int seg_act[8];      // 0 none, KCH_ACT_*
+  float seg_param[8];
+};
+
+__device__ __forceinline__ float bf16r(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+// Fast intrinsics (ex2.approx, approximate reciprocal): a few fp32 ulp, far below the bf16 rounding
+// that follows every step, so a fused result differs from the unfused chain by at most one bf16 rounding.
+__device__ __forceinline__ float ep_silu(float x) { return __fdividef(x, 1.0f + __expf(-x)); }
 template <int BN>
 struct TgSmem {
   alignas(1024) bf16 a[TG_STAGES][TG_BM * TG_BK];
@@ -111,7 +124,7 @@ template <int BN>
 __global__ void __launch_bounds__(TG_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                     bf16* __restrict__ C, const bf16* __restrict__ R, int64_t M, int N, int K,
-                    int64_t ldc, int64_t ldr, int vec_ok) {
+                    int64_t ldc, int64_t ldr, int vec_ok, const TgEpilogue ep) {
   extern __shared__ uint8_t smem_raw[];
   TgSmem<BN>& sm = *reinterpret_cast<TgSmem<BN>*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -124,7 +137,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < TG_STAGES; ++s) { mbar_init(&sm.full[s], 1); mbar_init(&sm.empty[s], 1); }
-    for (int i = 0; i < 2; ++i) { mbar_init(&sm.acc_full[i], 1); mbar_init(&sm.acc_empty[i], 4); }
+    for (int i = 0; i < 2; ++i) { mbar_init(&sm.acc_full[i], 1); mbar_init(&sm.acc_empty[i], 8); }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
@@ -180,7 +193,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     }
   } else {
     // ------------------------------ epilogue warps ------------------------------
+    // 8 warps: warps 2..5 take the first half of a 256-column tile, warps 6..9 the second half (narrower
+    // tiles are handled by warps 2..5 alone); each warp reads its own 32-lane quarter of tensor memory
     const int quarter = warp & 3;  // tensor-memory lanes 32*quarter .. 32*quarter+31
+    const int half = (warp - 2) >> 2;
+    const int c_begin = (BN == 256) ? half * 128 : 0;
+    const int c_end = (BN == 256) ? c_begin + 128 : (half == 0 ? BN : 0);
     uint32_t tcount = 0;
     bool ok = true;
     for (int64_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++tcount) {
@@ -191,12 +209,53 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       tc_fence_after();
       const int64_t row = mb * TG_BM + quarter * 32 + lane;
       const uint32_t tbase = tmem_base + acc * ACC_COLS + ((uint32_t)(quarter * 32) << 16);
+      float nrm = 1.f;
 #pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 32) {
+      for (int c0 = c_begin; c0 < c_end; c0 += 32) {
         uint32_t r[32];
+        const int col = nb * BN + c0;
+        int act = 0;
+        float prm = 0.f;
+        if (ep.nseg) {
+          int sidx = 0;
+          while (sidx < ep.nseg - 1 && col >= ep.seg_end[sidx]) ++sidx;
+          act = ep.seg_act[sidx];
+          prm = ep.seg_param[sidx];
+          if (act == KCH_ACT_SILU_L2NORM && (c0 & 127) == 0) {
+            // norm of this row's 128-column head: a thread owns a whole accumulator row, no exchange needed
+            float ss = 0.f;
+            for (int qd = 0; qd < 4; ++qd) {
+              tc_ld32(tbase + c0 + 32 * qd, r);
+              tc_wait_ld();
+#pragma unroll
+              for (int j = 0; j < 32; ++j) {
+                const float sv = bf16r(ep_silu(bf16r(__uint_as_float(r[j]))));
+                ss = fmaf(sv, sv, ss);
+              }
+            }
+            nrm = __fdividef(1.0f, fmaxf(bf16r(sqrtf(ss)), 1e-12f));
+          }
+        }
         tc_ld32(tbase + c0, r);
         tc_wait_ld();
-        const int col = nb * BN + c0;
+        // the activation is uniform over the chunk: branch once, then 32 independent element pipelines
+        if (act == KCH_ACT_SILU_L2NORM) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(bf16r(ep_silu(bf16r(__uint_as_float(r[j])))) * nrm);
+        } else if (act == KCH_ACT_SILU) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(ep_silu(bf16r(__uint_as_float(r[j]))));
+        } else if (act == KCH_ACT_SIGMOID) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            r[j] = __float_as_uint(__fdividef(1.0f, 1.0f + __expf(-bf16r(__uint_as_float(r[j])))));
+        } else if (act == KCH_ACT_NEG_SOFTPLUS) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const float v = bf16r(__uint_as_float(r[j]));
+            r[j] = __float_as_uint(-bf16r(v > 20.f ? v : __logf(1.0f + __expf(v))) * prm);
+          }
+        }
         if (row < M && col < N) {
           bf16* cp = C + row * ldc + col;
           const bf16* rp = R ? R + row * ldr + col : nullptr;
@@ -284,7 +343,7 @@ bool kch_linear_tcgen05_supported(const void* A, const void* W, const void* C, c
 
 template <int BN>
 static int launch_tg(const void* A, const void* W, void* C, const void* R, int64_t M, int N, int K, int64_t lda,
-                     int64_t ldw, int64_t ldc, int64_t ldr, cudaStream_t s) {
+                     int64_t ldw, int64_t ldc, int64_t ldr, const TgEpilogue& ep, cudaStream_t s) {
   CUtensorMap ma, mw;
   int rc = make_map_2d(&ma, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, TG_BM, TG_BK);
   if (rc) return rc;
@@ -301,18 +360,40 @@ static int launch_tg(const void* A, const void* W, void* C, const void* R, int64
   int64_t tiles = ((M + TG_BM - 1) / TG_BM) * ((N + BN - 1) / BN);
   int grid = (int)(tiles < sms ? tiles : sms);
   int vec_ok = (ldc % 8 == 0) && (((uintptr_t)C & 15) == 0) && (!R || ((ldr % 8 == 0) && (((uintptr_t)R & 15) == 0)));
-  gemm_tcgen05_kernel<BN><<<grid, TG_THREADS, smem, s>>>(ma, mw, (bf16*)C, (const bf16*)R, M, N, K, ldc, ldr, vec_ok);
+  gemm_tcgen05_kernel<BN><<<grid, TG_THREADS, smem, s>>>(ma, mw, (bf16*)C, (const bf16*)R, M, N, K, ldc, ldr, vec_ok, ep);
   KCH_LAUNCH_OK();
   return KCH_OK;
 }
 
+// Can the epilogue described by `e` run fused?  Segment boundaries must fall on 32-column chunks and
+// L2-norm heads (128 columns) on 128-column boundaries of a tile that is at least 128 wide.
+bool kch_linear_tcgen05_epilogue_ok(const kch_epilogue* e, int N) {
+  if (!e || e->n_segments == 0) return true;
+  if (e->n_segments > 8) return false;
+  int start = 0;
+  for (int i = 0; i < e->n_segments; ++i) {
+    const int end = e->seg_end[i];
+    if (end <= start || end > N) return false;
+    if (i + 1 < e->n_segments && (end % 32) != 0) return false;
+    if (e->seg_act[i] == KCH_ACT_SILU_L2NORM && (e->group != 128 || (start % 128) != 0 || ((end - start) % 128) != 0 || N <= 64))
+      return false;
+    start = end;
+  }
+  return start == N;
+}
+
 int kch_linear_tcgen05(const void* A, const void* W, void* C, const void* R, int64_t M, int N, int K, int64_t lda,
-                       int64_t ldw, int64_t ldc, int64_t ldr, void* stream) {
+                       int64_t ldw, int64_t ldc, int64_t ldr, const kch_epilogue* e, void* stream) {
   cudaStream_t s = kch_stream(stream);
-  if (N > 128) return launch_tg<256>(A, W, C, R, M, N, K, lda, ldw, ldc, ldr, s);
-  if (N > 64) return launch_tg<128>(A, W, C, R, M, N, K, lda, ldw, ldc, ldr, s);
-  if (N > 32) return launch_tg<64>(A, W, C, R, M, N, K, lda, ldw, ldc, ldr, s);
-  return launch_tg<32>(A, W, C, R, M, N, K, lda, ldw, ldc, ldr, s);
+  TgEpilogue ep = {};
+  if (e && e->n_segments) {
+    ep.nseg = e->n_segments;
+    for (int i = 0; i < e->n_segments; ++i) { ep.seg_end[i] = e->seg_end[i]; ep.seg_act[i] = e->seg_act[i]; ep.seg_param[i] = e->seg_param[i]; }
+  }
+  if (N > 128) return launch_tg<256>(A, W, C, R, M, N, K, lda, ldw, ldc, ldr, ep, s);
+  if (N > 64) return launch_tg<128>(A, W, C, R, M, N, K, lda, ldw, ldc, ldr, ep, s);
+  if (N > 32) return launch_tg<64>(A, W, C, R, M, N, K, lda, ldw, ldc, ldr, ep, s);
+  return launch_tg<32>(A, W, C, R, M, N, K, lda, ldw, ldc, ldr, ep, s);
 }
 
 unsigned int* kch_status_device_ptr() {

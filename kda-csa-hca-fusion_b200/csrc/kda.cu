@@ -17,7 +17,8 @@ __global__ void __launch_bounds__(128)
 kda_recurrent_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v,
                      const T* __restrict__ g, const T* __restrict__ beta,
                      const float* __restrict__ S0, T* __restrict__ o, float* __restrict__ S_out,
-                     int T_, int H, int HV, int K, int V, float scale, float g_min) {
+                     int T_, int H, int HV, int K, int V, float scale, float g_min, int64_t ld_qk,
+                     int64_t ld_v, int64_t ld_g, int64_t ld_b) {
   const int vb = blockIdx.x, hv = blockIdx.y, b = blockIdx.z;
   const int G = HV / H, h = hv / G;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -34,8 +35,8 @@ kda_recurrent_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* 
     s[i] = (S0 && vok && kk < K) ? S0[sbase + (int64_t)kk * V + vcol] : 0.f;
   }
   auto load_tok = [&](int t, int buf) {
-    const int64_t qoff = (((int64_t)b * T_ + t) * H + h) * K;
-    const int64_t goff = (((int64_t)b * T_ + t) * HV + hv) * K;
+    const int64_t qoff = ((int64_t)b * T_ + t) * ld_qk + (int64_t)h * K;
+    const int64_t goff = ((int64_t)b * T_ + t) * ld_g + (int64_t)hv * K;
     for (int i = threadIdx.x; i < 4 * KPT; i += 128) {
       bool ok = i < K;
       sk[buf][i] = ok ? ldf(k + qoff + i) : 0.f;
@@ -58,8 +59,8 @@ kda_recurrent_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* 
     if (t + 1 < T_) load_tok(t + 1, buf ^ 1);
     __syncthreads();
     float pred = red[0][lane] + red[1][lane] + red[2][lane] + red[3][lane];
-    float vv = vok ? ldf(v + voff * V + vcol) : 0.f;
-    float delta = ldf(beta + voff) * (vv - pred);
+    float vv = vok ? ldf(v + ((int64_t)b * T_ + t) * ld_v + (int64_t)hv * V + vcol) : 0.f;
+    float delta = ldf(beta + ((int64_t)b * T_ + t) * ld_b + hv) * (vv - pred);
     float op = 0.f;
 #pragma unroll
     for (int i = 0; i < KPT; ++i) {
@@ -83,7 +84,12 @@ kda_recurrent_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* 
 extern "C" int kch_kda_recurrent(const void* q, const void* k, const void* v, const void* g,
                                  const void* beta, const float* initial_state, void* o,
                                  float* final_state, int B, int T, int H, int HV, int K, int V,
-                                 float scale, float g_clamp_min, int dtype, void* stream) {
+                                 float scale, float g_clamp_min, int dtype, int64_t ld_qk, int64_t ld_v,
+                                 int64_t ld_g, int64_t ld_beta, void* stream) {
+  if (ld_qk <= 0) ld_qk = (int64_t)H * K;
+  if (ld_v <= 0) ld_v = (int64_t)HV * V;
+  if (ld_g <= 0) ld_g = (int64_t)HV * K;
+  if (ld_beta <= 0) ld_beta = HV;
   KCH_REQUIRE(H >= 1, "H=%d must be >= 1", H);
   KCH_REQUIRE(K >= 1, "K=%d must be >= 1", K);
   KCH_REQUIRE(V >= 1, "V=%d must be >= 1", V);
@@ -98,7 +104,7 @@ extern "C" int kch_kda_recurrent(const void* q, const void* k, const void* v, co
 #define GO(T_, KPT)                                                                              \
   kda_recurrent_kernel<T_, KPT><<<grid, block, 0, s>>>((const T_*)q, (const T_*)k, (const T_*)v, \
       (const T_*)g, (const T_*)beta, initial_state, (T_*)o, final_state, T, H, HV, K, V, scale,  \
-      g_clamp_min)
+      g_clamp_min, ld_qk, ld_v, ld_g, ld_beta)
 #define GOK(T_)                      \
   do {                               \
     if (kpt <= 4) GO(T_, 4);         \
@@ -134,7 +140,8 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 kda_chunk_prepare_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v,
                          const T* __restrict__ g, const T* __restrict__ beta, KdaChunkWs ws, int T_,
-                         int H, int HV, int K, int V, int C, int NT, float scale, float g_min) {
+                         int H, int HV, int K, int V, int C, int NT, float scale, float g_min,
+                         int64_t ld_qk, int64_t ld_v, int64_t ld_g, int64_t ld_b) {
   extern __shared__ float smem[];
   const int n = blockIdx.x, hv = blockIdx.y, b = blockIdx.z;
   const int G = HV / H, h = hv / G;
@@ -152,8 +159,8 @@ kda_chunk_prepare_kernel(const T* __restrict__ q, const T* __restrict__ k, const
     int t = t0 + i;
     float kv = 0.f, qv = 0.f, gv = 0.f;
     if (t < T_) {
-      int64_t qoff = (((int64_t)b * T_ + t) * H + h) * K + kk;
-      int64_t goff = (((int64_t)b * T_ + t) * HV + hv) * K + kk;
+      int64_t qoff = ((int64_t)b * T_ + t) * ld_qk + (int64_t)h * K + kk;
+      int64_t goff = ((int64_t)b * T_ + t) * ld_g + (int64_t)hv * K + kk;
       kv = ldf(k + qoff);
       qv = ldf(q + qoff) * scale;
       gv = fmaxf(ldf(g + goff), g_min);
@@ -164,7 +171,7 @@ kda_chunk_prepare_kernel(const T* __restrict__ q, const T* __restrict__ k, const
   }
   for (int i = tid; i < C; i += 256) {
     int t = t0 + i;
-    sbeta[i] = t < T_ ? ldf(beta + ((int64_t)b * T_ + t) * HV + hv) : 0.f;
+    sbeta[i] = t < T_ ? ldf(beta + ((int64_t)b * T_ + t) * ld_b + hv) : 0.f;
   }
   __syncthreads();
   // running sum of g over the chunk, one channel per thread
@@ -248,7 +255,7 @@ kda_chunk_prepare_kernel(const T* __restrict__ q, const T* __restrict__ k, const
     float acc = 0.f;
     for (int j = 0; j <= i; ++j) {
       int t = t0 + j;
-      float x = t < T_ ? ldf(v + (((int64_t)b * T_ + t) * HV + hv) * V + vv) : 0.f;
+      float x = t < T_ ? ldf(v + ((int64_t)b * T_ + t) * ld_v + (int64_t)hv * V + vv) : 0.f;
       acc = fmaf(sT[i * CS + j], x, acc);
     }
     ws.u[(bh * Tp + t0 + i) * V + vv] = acc;
@@ -408,7 +415,8 @@ bool kch_kda_mma_supported(int K, int V, int chunk_size, float g_clamp_min, int 
 int64_t kch_kda_mma_workspace_bytes(int B, int T, int HV);
 int kch_kda_chunk_mma(const void* q, const void* k, const void* v, const void* g, const void* beta,
                       const float* initial_state, void* o, float* final_state, int B, int T, int H, int HV,
-                      float scale, float g_clamp_min, void* workspace, int64_t workspace_bytes, void* stream);
+                      float scale, float g_clamp_min, int64_t ld_qk, int64_t ld_v, int64_t ld_g, int64_t ld_beta,
+                      void* workspace, int64_t workspace_bytes, void* stream);
 
 extern "C" int64_t kch_kda_chunk_workspace_bytes(int B, int T, int HV, int K, int V, int chunk_size) {
   if (B <= 0 || T <= 0 || HV <= 0 || K <= 0 || V <= 0 || chunk_size < 1) return 0;
@@ -426,8 +434,13 @@ extern "C" int64_t kch_kda_chunk_workspace_bytes(int B, int T, int HV, int K, in
 extern "C" int kch_kda_chunk(const void* q, const void* k, const void* v, const void* g,
                              const void* beta, const float* initial_state, void* o,
                              float* final_state, int B, int T, int H, int HV, int K, int V,
-                             int chunk_size, float scale, float g_clamp_min, int dtype,
-                             void* workspace, int64_t workspace_bytes, void* stream) {
+                             int chunk_size, float scale, float g_clamp_min, int dtype, int64_t ld_qk,
+                             int64_t ld_v, int64_t ld_g, int64_t ld_beta, void* workspace,
+                             int64_t workspace_bytes, void* stream) {
+  if (ld_qk <= 0) ld_qk = (int64_t)H * K;
+  if (ld_v <= 0) ld_v = (int64_t)HV * V;
+  if (ld_g <= 0) ld_g = (int64_t)HV * K;
+  if (ld_beta <= 0) ld_beta = HV;
   KCH_REQUIRE(H >= 1, "H=%d must be >= 1", H);
   KCH_REQUIRE(K >= 1, "K=%d must be >= 1", K);
   KCH_REQUIRE(V >= 1, "V=%d must be >= 1", V);
@@ -436,11 +449,11 @@ extern "C" int kch_kda_chunk(const void* q, const void* k, const void* v, const 
   KCH_REQUIRE(B >= 0 && T >= 0, "B=%d T=%d", B, T);
   if (K > 128)  // state slice + staging tiles exceed shared memory: same maths, token form
     return kch_kda_recurrent(q, k, v, g, beta, initial_state, o, final_state, B, T, H, HV, K, V, scale,
-                             g_clamp_min, dtype, stream);
+                             g_clamp_min, dtype, ld_qk, ld_v, ld_g, ld_beta, stream);
   if (B == 0) return KCH_OK;
   if (T > 0 && kch_kda_mma_supported(K, V, chunk_size, g_clamp_min, dtype))
     return kch_kda_chunk_mma(q, k, v, g, beta, initial_state, o, final_state, B, T, H, HV, scale, g_clamp_min,
-                             workspace, workspace_bytes, stream);
+                             ld_qk, ld_v, ld_g, ld_beta, workspace, workspace_bytes, stream);
   if (T == 0) {
     if (final_state) {
       size_t nb = (size_t)B * HV * K * V * sizeof(float);
@@ -467,7 +480,8 @@ extern "C" int kch_kda_chunk(const void* q, const void* k, const void* v, const 
     KCH_CUDA_OK(cudaFuncSetAttribute(kda_chunk_scan_kernel<T_>,                                      \
                                      cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem2));      \
     kda_chunk_prepare_kernel<T_><<<g1, 256, smem1, s>>>((const T_*)q, (const T_*)k, (const T_*)v,    \
-        (const T_*)g, (const T_*)beta, ws, T, H, HV, K, V, C, NT, scale, g_clamp_min);               \
+        (const T_*)g, (const T_*)beta, ws, T, H, HV, K, V, C, NT, scale, g_clamp_min, ld_qk, ld_v,    \
+        ld_g, ld_beta);                                                                              \
     kda_chunk_scan_kernel<T_><<<g2, 256, smem2, s>>>(ws, initial_state, (T_*)o, final_state, T, HV,  \
         K, V, C, NT);                                                                                \
   } while (0)

@@ -47,6 +47,7 @@ struct PrepArgs {
   uint8_t* ws;
   int T, H, HV, NT;
   float scale, g_min;
+  int64_t ld_qk, ld_v, ld_g, ld_b;   // elements between consecutive tokens
 };
 
 // shared-memory map of the prepare kernel (bytes)
@@ -66,7 +67,7 @@ struct PrepArgs {
 
 #define KM_LOG2E 1.4426950408889634f
 
-__global__ void __launch_bounds__(256) kda_prepare_mma_kernel(PrepArgs a) {
+__global__ void __launch_bounds__(256, 2) kda_prepare_mma_kernel(PrepArgs a) {
   extern __shared__ __align__(128) uint8_t sm[];
   float* sG = reinterpret_cast<float*>(sm + PS_G);     // gamma in log2 units: exp(x) == exp2f(x')
   float* sA = reinterpret_cast<float*>(sm + PS_A);
@@ -80,8 +81,9 @@ __global__ void __launch_bounds__(256) kda_prepare_mma_kernel(PrepArgs a) {
   const int t0 = n * KM_C;
   const int64_t bh = (int64_t)b * a.HV + hv;
   uint8_t* wsc = a.ws + (bh * a.NT + n) * (int64_t)KM_CHUNK_BYTES;
-  auto qk_off = [&](int i) { return (((int64_t)b * a.T + t0 + i) * a.H + h) * KM_K; };
-  auto gv_off = [&](int i) { return (((int64_t)b * a.T + t0 + i) * a.HV + hv) * (int64_t)KM_K; };
+  auto qk_off = [&](int i) { return ((int64_t)b * a.T + t0 + i) * a.ld_qk + (int64_t)h * KM_K; };
+  auto g_off = [&](int i) { return ((int64_t)b * a.T + t0 + i) * a.ld_g + (int64_t)hv * KM_K; };
+  auto v_off = [&](int i) { return ((int64_t)b * a.T + t0 + i) * a.ld_v + (int64_t)hv * KM_V; };
   auto load8 = [&](const bf16* p, bool ok, float (&out)[8]) {
     uint4 raw = make_uint4(0u, 0u, 0u, 0u);
     if (ok) raw = *reinterpret_cast<const uint4*>(p);
@@ -95,15 +97,34 @@ __global__ void __launch_bounds__(256) kda_prepare_mma_kernel(PrepArgs a) {
   for (int it = 0; it < 4; ++it) {
     const int idx = tid + 256 * it, i = idx >> 4, ch = idx & 15;
     float gv[8];
-    load8(a.g + gv_off(i) + 8 * ch, t0 + i < a.T, gv);
+    load8(a.g + g_off(i) + 8 * ch, t0 + i < a.T, gv);
 #pragma unroll
     for (int x = 0; x < 8; ++x) gv[x] = (t0 + i < a.T) ? fmaxf(gv[x], a.g_min) * KM_LOG2E : 0.f;
     float4* dst = reinterpret_cast<float4*>(sG + i * KM_K + 8 * ch);
     dst[0] = make_float4(gv[0], gv[1], gv[2], gv[3]);
     dst[1] = make_float4(gv[4], gv[5], gv[6], gv[7]);
   }
-  if (tid < KM_C) sbeta[tid] = (t0 + tid < a.T) ? __bfloat162float(a.beta[((int64_t)b * a.T + t0 + tid) * a.HV + hv]) : 0.f;
+  if (tid < KM_C) sbeta[tid] = (t0 + tid < a.T) ? __bfloat162float(a.beta[((int64_t)b * a.T + t0 + tid) * a.ld_b + hv]) : 0.f;
   for (int idx = tid; idx < KM_C * PS_LD; idx += 256) { sA[idx] = 0.f; sQ[idx] = 0.f; sT[idx] = 0.f; }
+  // Every elementwise stage below maps thread -> (row r0 + 16*s, 8-channel chunk c8) with r0 = tid/16 and
+  // c8 = tid%16, so the k and q values a thread ever needs are these 4 x 8: keep them in registers.
+  const int r0 = tid >> 4, c8 = tid & 15;
+  uint4 kreg[4], qreg[4];
+#pragma unroll
+  for (int s4 = 0; s4 < 4; ++s4) {
+    const int i = r0 + 16 * s4;
+    kreg[s4] = make_uint4(0u, 0u, 0u, 0u);
+    qreg[s4] = make_uint4(0u, 0u, 0u, 0u);
+    if (t0 + i < a.T) {
+      kreg[s4] = *reinterpret_cast<const uint4*>(a.k + qk_off(i) + 8 * c8);
+      qreg[s4] = *reinterpret_cast<const uint4*>(a.q + qk_off(i) + 8 * c8);
+    }
+  }
+  auto unpack8 = [](const uint4& raw, float (&out)[8]) {
+    const bf16* e = reinterpret_cast<const bf16*>(&raw);
+#pragma unroll
+    for (int x = 0; x < 8; ++x) out[x] = __bfloat162float(e[x]);
+  };
   __syncthreads();
   if (tid < KM_K) {
     float acc = 0.f;
@@ -135,8 +156,13 @@ __global__ void __launch_bounds__(256) kda_prepare_mma_kernel(PrepArgs a) {
         x = p4[0]; y = p4[1];
         gi[0] = x.x; gi[1] = x.y; gi[2] = x.z; gi[3] = x.w; gi[4] = y.x; gi[5] = y.y; gi[6] = y.z; gi[7] = y.w;
       }
-      load8(a.k + qk_off(i) + 8 * ch, t0 + i < a.T, kv);
-      load8(a.q + qk_off(i) + 8 * ch, t0 + i < a.T, qv);
+      // (compile-time register selection: ba, bb are uniform, the switch keeps kreg/qreg in registers)
+      switch (ba) {
+        case 0: unpack8(kreg[0], kv); unpack8(qreg[0], qv); break;
+        case 1: unpack8(kreg[1], kv); unpack8(qreg[1], qv); break;
+        case 2: unpack8(kreg[2], kv); unpack8(qreg[2], qv); break;
+        default: unpack8(kreg[3], kv); unpack8(qreg[3], qv); break;
+      }
       uint32_t kh[4], kl[4], qh[4], ql[4], ch_[4], cl_[4];
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
@@ -152,7 +178,11 @@ __global__ void __launch_bounds__(256) kda_prepare_mma_kernel(PrepArgs a) {
         const float4* p4 = reinterpret_cast<const float4*>(sG + jr * KM_K + 8 * ch);
         float4 x = p4[0], y = p4[1];
         gj[0] = x.x; gj[1] = x.y; gj[2] = x.z; gj[3] = x.w; gj[4] = y.x; gj[5] = y.y; gj[6] = y.z; gj[7] = y.w;
-        load8(a.k + qk_off(jr) + 8 * ch, t0 + jr < a.T, kc);
+        switch (bb) {
+          case 0: unpack8(kreg[0], kc); break;
+          case 1: unpack8(kreg[1], kc); break;
+          default: unpack8(kreg[2], kc); break;
+        }
       }
 #pragma unroll
       for (int e = 0; e < 4; ++e)
@@ -223,12 +253,12 @@ __global__ void __launch_bounds__(256) kda_prepare_mma_kernel(PrepArgs a) {
   __syncthreads();   // sQ is dead from here: the e^gamma k tiles may overwrite it
 
   // ---- qg, kg (workspace), e^gamma k (shared), dl ------------------------------------------------------
-#pragma unroll 2
+#pragma unroll
   for (int it = 0; it < 4; ++it) {
     const int idx = tid + 256 * it, i = idx >> 4, ch = idx & 15;
     float kf[8], qf[8], gm[8], gl[8];
-    load8(a.k + qk_off(i) + 8 * ch, t0 + i < a.T, kf);
-    load8(a.q + qk_off(i) + 8 * ch, t0 + i < a.T, qf);
+    unpack8(kreg[it], kf);
+    unpack8(qreg[it], qf);
     {
       const float4* p4 = reinterpret_cast<const float4*>(sG + i * KM_K + 8 * ch);
       float4 x = p4[0], y = p4[1];
@@ -316,7 +346,7 @@ __global__ void __launch_bounds__(256) kda_prepare_mma_kernel(PrepArgs a) {
   for (int it = 0; it < 4; ++it) {
     const int idx = tid + 256 * it, i = idx >> 4, ch = idx & 15;
     uint4 vr = make_uint4(0u, 0u, 0u, 0u);
-    if (t0 + i < a.T) vr = *reinterpret_cast<const uint4*>(a.v + gv_off(i) + 8 * ch);   // V == K here
+    if (t0 + i < a.T) vr = *reinterpret_cast<const uint4*>(a.v + v_off(i) + 8 * ch);
     *reinterpret_cast<uint4*>(sm + PS_V + swz<256>(i, ch)) = vr;
   }
   __syncthreads();
@@ -617,7 +647,8 @@ int64_t kch_kda_mma_workspace_bytes(int B, int T, int HV) {
 
 int kch_kda_chunk_mma(const void* q, const void* k, const void* v, const void* g, const void* beta,
                       const float* initial_state, void* o, float* final_state, int B, int T, int H, int HV,
-                      float scale, float g_clamp_min, void* workspace, int64_t workspace_bytes, void* stream) {
+                      float scale, float g_clamp_min, int64_t ld_qk, int64_t ld_v, int64_t ld_g, int64_t ld_beta,
+                      void* workspace, int64_t workspace_bytes, void* stream) {
   const int NT = (T + KM_C - 1) / KM_C;
   KCH_REQUIRE(workspace && workspace_bytes >= kch_kda_mma_workspace_bytes(B, T, HV),
               "kch_kda_chunk: workspace %lld < %lld bytes", (long long)workspace_bytes,
@@ -629,6 +660,11 @@ int kch_kda_chunk_mma(const void* q, const void* k, const void* v, const void* g
   PrepArgs pa;
   pa.q = (const bf16*)q; pa.k = (const bf16*)k; pa.v = (const bf16*)v; pa.g = (const bf16*)g; pa.beta = (const bf16*)beta;
   pa.ws = (uint8_t*)workspace; pa.T = T; pa.H = H; pa.HV = HV; pa.NT = NT; pa.scale = scale; pa.g_min = g_clamp_min;
+  pa.ld_qk = ld_qk; pa.ld_v = ld_v; pa.ld_g = ld_g; pa.ld_b = ld_beta;
+  // 16-byte vector loads: token strides and base pointers must be multiples of 8 elements / 16 bytes
+  KCH_REQUIRE((ld_qk % 8) == 0 && (ld_v % 8) == 0 && (ld_g % 8) == 0 &&
+              ((((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)g) & 15) == 0),
+              "kch_kda_chunk: q/k/v/g must be 16-byte aligned with token strides that are multiples of 8 elements");
   KCH_CUDA_OK(cudaFuncSetAttribute(kda_prepare_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PS_TOTAL));
   kda_prepare_mma_kernel<<<dim3(NT, HV, B), 256, PS_TOTAL, s>>>(pa);
   KCH_LAUNCH_OK();

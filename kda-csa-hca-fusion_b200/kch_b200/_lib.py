@@ -30,6 +30,10 @@ class AttendArgs(C.Structure):
                 ("sink", _vp), ("sink_dtype", _i), ("scale", _f), ("out", _vp), ("out_dtype", _i)]
 
 
+class Epilogue(C.Structure):
+    _fields_ = [("n_segments", _i), ("seg_end", _i * 8), ("seg_act", _i * 8), ("seg_param", _f * 8), ("group", _i)]
+
+
 class CacheAppendArgs(C.Structure):
     _fields_ = [("B", _i), ("c", _i), ("c_I", _i), ("m", _i), ("win", _i), ("dtype", _i),
                 ("Ca", _vp), ("Cb", _vp), ("Za", _vp), ("Zb", _vp), ("K_idx", _vp), ("Z_idx", _vp),
@@ -51,11 +55,12 @@ PROTOTYPES = {
     "kch_layernorm": (_i, [_vp, _vp, _vp, _vp, _i64, _i, _f, _i, _i, _vp]),
     "kch_short_conv": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp]),
     "kch_linear": (_i, [_vp, _vp, _vp, _vp, _i64, _i, _i, _i64, _i64, _i64, _i64, _i, _vp]),
+    "kch_linear_ex": (_i, [_vp, _vp, _vp, _vp, _i64, _i, _i, _i64, _i64, _i64, _i64, _i, C.POINTER(Epilogue), _vp]),
     "kch_activation": (_i, [_vp, _vp, _i64, _i, _i, _f, _i, _i, _i64, _i64, _vp]),
     "kch_rownorm": (_i, [_vp, _i64, _vp, _vp, _i64, _i, _i, _i, _vp]),
-    "kch_kda_recurrent": (_i, [_vp] * 8 + [_i] * 6 + [_f, _f, _i, _vp]),
+    "kch_kda_recurrent": (_i, [_vp] * 8 + [_i] * 6 + [_f, _f, _i, _i64, _i64, _i64, _i64, _vp]),
     "kch_kda_chunk_workspace_bytes": (_i64, [_i] * 6),
-    "kch_kda_chunk": (_i, [_vp] * 8 + [_i] * 7 + [_f, _f, _i, _vp, _i64, _vp]),
+    "kch_kda_chunk": (_i, [_vp] * 8 + [_i] * 7 + [_f, _f, _i, _i64, _i64, _i64, _i64, _vp, _i64, _vp]),
     "kch_compress_kv": (_i, [_vp, _vp, _vp, _vp, _i, _i64, _i, _i, _i64, _i64, _i64, _i, _i, _vp]),
     "kch_compress_kv_overlapped": (_i, [_vp] * 8 + [_i64, _vp, _i, _i64, _i, _i, _i64, _i64, _i64, _i, _i, _vp]),
     "kch_indexer_workspace_bytes": (_i64, [_i, _i, _i, _i, _i]),

@@ -27,8 +27,10 @@ def _as_rows(t):
     return t, c, T
 
 
-def linear(x, W, residual=None):
-    """``F.linear(x, W)`` (+ residual) through the C ABI.  x ``[..., K]`` (last dim dense), W ``[N, K]``."""
+def linear(x, W, residual=None, epilogue=None, group=1):
+    """``F.linear(x, W)`` (+ residual) through the C ABI.  x ``[..., K]`` (last dim dense), W ``[N, K]``.
+    ``epilogue``: list of ``(width, act, param)`` column segments covering all N output columns, applied with
+    the rounding points of the unfused chain (``group`` = head width of the silu+L2-norm activation)."""
     _lib.require_cuda(x, W, fn="linear")
     lib = _lib.load()
     K = x.shape[-1]
@@ -52,9 +54,19 @@ def linear(x, W, residual=None):
         if r2.stride(-1) != 1:
             r2 = r2.contiguous()
         ldr = r2.stride(0) if M > 1 else N
+    ep = None
+    if epilogue:
+        ep = _lib.Epilogue()
+        ep.n_segments, ep.group = len(epilogue), int(group)
+        end = 0
+        for i, (width, act, param) in enumerate(epilogue):
+            end += int(width)
+            ep.seg_end[i], ep.seg_act[i], ep.seg_param[i] = end, int(act), float(param)
+        if end != N:
+            raise ValueError(f"linear: epilogue segments cover {end} columns, the weight has {N} rows")
     with torch.cuda.device(x.device):
-        _lib.check(lib.kch_linear(_lib.ptr(x2), _lib.ptr(W), _lib.ptr(out), _lib.ptr(r2), M, N, K, lda,
-                                  W.stride(0), N, ldr, _lib.dtype_tag(x.dtype), _lib.stream()))
+        _lib.check(lib.kch_linear_ex(_lib.ptr(x2), _lib.ptr(W), _lib.ptr(out), _lib.ptr(r2), M, N, K, lda,
+                                     W.stride(0), N, ldr, _lib.dtype_tag(x.dtype), ep, _lib.stream()))
     return out.reshape(*lead, N)
 
 

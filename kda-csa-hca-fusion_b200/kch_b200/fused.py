@@ -204,14 +204,16 @@ class KDAHybridLayer(nn.Module):
             new_lb = torch.cat([prev.to(x.dtype), x], dim=1)[:, -2:].clone()
         W = self._fused.get(self.q_proj.weight, self.k_proj.weight, self.v_proj.weight, self.g_down.weight,
                             self.beta.weight)
-        proj = linear(xc, W)
-        qr, kr, vr, gd, br = proj[..., :2 * H * K + HV * V + K + HV].split([H * K, H * K, HV * V, K, HV], dim=-1)
-        q = activation(qr, _lib.ACT_SILU_L2NORM, group=K).view(B, T, H, K)
-        k = activation(kr, _lib.ACT_SILU_L2NORM, group=K).view(B, T, H, K)
-        v = activation(vr, _lib.ACT_SILU).view(B, T, HV, V)
-        g = activation(linear(gd, self.g_up.weight), _lib.ACT_NEG_SOFTPLUS, param=cfg.kda_decay_scale).view(B, T, HV, K)
-        beta = activation(br, _lib.ACT_SIGMOID)
-        return q, k, v, g, beta, new_lb
+        # one GEMM for q|k|v|g_down|beta with the activations of ops_fused.py:571-581 applied in its epilogue
+        # (silu + per-head L2 norm, silu, none, sigmoid); q, k, v, beta stay column slices of its output
+        n_used = 2 * H * K + HV * V + K + HV
+        segs = [(H * K, _lib.ACT_SILU_L2NORM, 0.0), (H * K, _lib.ACT_SILU_L2NORM, 0.0), (HV * V, _lib.ACT_SILU, 0.0),
+                (K, 0, 0.0), (HV + (W.shape[0] - n_used), _lib.ACT_SIGMOID, 0.0)]
+        proj = linear(xc, W, epilogue=segs, group=K)
+        q, k, v, gd, beta = proj[..., :n_used].split([H * K, H * K, HV * V, K, HV], dim=-1)
+        g = linear(gd, self.g_up.weight, epilogue=[(HV * K, _lib.ACT_NEG_SOFTPLUS, cfg.kda_decay_scale)])
+        return (q.unflatten(-1, (H, K)), k.unflatten(-1, (H, K)), v.unflatten(-1, (HV, V)),
+                g.view(B, T, HV, K), beta, new_lb)
 
     def forward_functional(self, x, state, conv_lookback, *, detach_lookback=True, residual=None):
         cfg = self.cfg

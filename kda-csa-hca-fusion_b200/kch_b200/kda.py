@@ -66,6 +66,23 @@ def _validate_shapes(q, k, v, g, beta, fn_name, chunk_size=None):
                          f"(beta must be [B, T, HV], got {tuple(beta.shape)})")
 
 
+def _token_stride(x):
+    """``(tensor, elements between consecutive tokens)`` for a ``[B,T,H,K]`` / ``[B,T,HV]`` operand whose heads are
+    dense within a token (e.g. a column slice of a fused projection); anything else is made contiguous."""
+    inner = 1
+    ok = True
+    for d in range(x.dim() - 1, 1, -1):
+        ok = ok and (x.shape[d] == 1 or x.stride(d) == inner)
+        inner *= x.shape[d]
+    B, T = x.shape[0], x.shape[1]
+    if ok and T > 0 and B > 0:
+        ld = x.stride(1) if T > 1 else max(inner, x.stride(1))
+        if ld >= inner and (B == 1 or x.stride(0) == T * ld) and ld % 8 == 0 and x.data_ptr() % 16 == 0:
+            return x, ld
+    x = x.contiguous()
+    return x, inner
+
+
 def _scale_value(scale, K):
     if scale is None:
         return K ** -0.5
@@ -83,7 +100,10 @@ def _run(fn_name, q, k, v, g, beta, scale, initial_state, output_final_state, g_
     B, T, H, K = q.shape
     HV, V = v.shape[2], v.shape[-1]
     tag = _lib.dtype_tag(v.dtype)
-    q, k, v, g, beta = (x.contiguous() for x in (q, k, v, g, beta))
+    (q, ld_q), (k, ld_k), (v, ld_v), (g, ld_g), (beta, ld_b) = (_token_stride(x) for x in (q, k, v, g, beta))
+    if ld_q != ld_k:
+        q, k = q.contiguous(), k.contiguous()
+        ld_q = ld_k = H * K
     S0 = None
     if initial_state is not None:
         S0 = initial_state.to(device=q.device, dtype=torch.float32).contiguous()
@@ -98,13 +118,14 @@ def _run(fn_name, q, k, v, g, beta, scale, initial_state, output_final_state, g_
         if chunk_size is None:
             _lib.check(lib.kch_kda_recurrent(_lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(g), _lib.ptr(beta),
                                              _lib.ptr(S0), _lib.ptr(o), _lib.ptr(S), B, T, H, HV, K, V, sc, gmin,
-                                             tag, _lib.stream()))
+                                             tag, ld_q, ld_v, ld_g, ld_b, _lib.stream()))
         else:
             nbytes = lib.kch_kda_chunk_workspace_bytes(B, T, HV, K, V, int(chunk_size))
             ws = torch.empty(max(int(nbytes), 1), dtype=torch.uint8, device=q.device)
             _lib.check(lib.kch_kda_chunk(_lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(g), _lib.ptr(beta),
                                          _lib.ptr(S0), _lib.ptr(o), _lib.ptr(S), B, T, H, HV, K, V, int(chunk_size),
-                                         sc, gmin, tag, _lib.ptr(ws), int(nbytes), _lib.stream()))
+                                         sc, gmin, tag, ld_q, ld_v, ld_g, ld_b, _lib.ptr(ws), int(nbytes),
+                                         _lib.stream()))
     if S is not None and state_dtype is not None:
         S = S.to(state_dtype)
     return o, S

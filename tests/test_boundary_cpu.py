@@ -37,7 +37,7 @@ def test_argument_errors_come_back_as_codes_without_a_gpu():
     assert rc < 0 and b"m=0" in lib.kch_last_error()
     rc = lib.kch_compress_kv(None, None, None, None, 1, 10, 8, 4, 8, 10, 0, 0, 0, None)
     assert rc < 0 and b"divisible" in lib.kch_last_error()
-    rc = lib.kch_kda_recurrent(*([None] * 8), 1, 4, 2, 3, 8, 8, 1.0, -10.0, 0, None)
+    rc = lib.kch_kda_recurrent(*([None] * 8), 1, 4, 2, 3, 8, 8, 1.0, -10.0, 0, 0, 0, 0, 0, None)
     assert rc < 0 and b"HV=3" in lib.kch_last_error()
     rc = lib.kch_indexer_topk(None, None, None, None, 1, 4, 4, 2, 0, 3, 1.0, 4, 0, -1, 0, 0, None, 0, None)
     assert rc < 0 and b"c_I" in lib.kch_last_error()
