@@ -92,15 +92,10 @@ indexer_logits_kernel(const float* __restrict__ q, const float* __restrict__ k,
 #define IM_D 64
 
 __device__ __forceinline__ void split3_pair(float x0, float x1, uint32_t& hi, uint32_t& mid, uint32_t& lo) {
-  bf16 h0 = __float2bfloat16_rn(x0), h1 = __float2bfloat16_rn(x1);
-  float r0 = x0 - __bfloat162float(h0), r1 = x1 - __bfloat162float(h1);
-  bf16 m0 = __float2bfloat16_rn(r0), m1 = __float2bfloat16_rn(r1);
-  bf16 l0 = __float2bfloat16_rn(r0 - __bfloat162float(m0)), l1 = __float2bfloat16_rn(r1 - __bfloat162float(m1));
-  __nv_bfloat162 a, b2, c;
-  a.x = h0; a.y = h1; b2.x = m0; b2.y = m1; c.x = l0; c.y = l1;
-  hi = *reinterpret_cast<uint32_t*>(&a);
-  mid = *reinterpret_cast<uint32_t*>(&b2);
-  lo = *reinterpret_cast<uint32_t*>(&c);
+  hi = cvt_bf16x2(x0, x1);
+  const float r0 = x0 - __uint_as_float(hi << 16), r1 = x1 - __uint_as_float(hi & 0xFFFF0000u);
+  mid = cvt_bf16x2(r0, r1);
+  lo = cvt_bf16x2(r0 - __uint_as_float(mid << 16), r1 - __uint_as_float(mid & 0xFFFF0000u));
 }
 
 // Three-term split of fp32 rows into three bf16 row arrays (row r of batch b read at x + b*bstride + r*64).

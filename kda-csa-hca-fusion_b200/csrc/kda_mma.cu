@@ -69,7 +69,7 @@ struct PrepArgs {
 
 __global__ void __launch_bounds__(256, 2) kda_prepare_mma_kernel(PrepArgs a) {
   extern __shared__ __align__(128) uint8_t sm[];
-  float* sG = reinterpret_cast<float*>(sm + PS_G);     // gamma in log2 units: exp(x) == exp2f(x')
+  float* sG = reinterpret_cast<float*>(sm + PS_G);     // gamma in log2 units: exp(x) == ex2_fast(x')
   float* sA = reinterpret_cast<float*>(sm + PS_A);
   float* sT = reinterpret_cast<float*>(sm + PS_T);
   float* sQ = reinterpret_cast<float*>(sm + PS_Q);
@@ -166,7 +166,7 @@ __global__ void __launch_bounds__(256, 2) kda_prepare_mma_kernel(PrepArgs a) {
       uint32_t kh[4], kl[4], qh[4], ql[4], ch_[4], cl_[4];
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
-        const float e0 = exp2f(gi[2 * e] - ref[2 * e]), e1 = exp2f(gi[2 * e + 1] - ref[2 * e + 1]);
+        const float e0 = ex2_fast(gi[2 * e] - ref[2 * e]), e1 = ex2_fast(gi[2 * e + 1] - ref[2 * e + 1]);
         split2_bf16(kv[2 * e] * e0, kv[2 * e + 1] * e1, kh[e], kl[e]);
         split2_bf16(qv[2 * e] * a.scale * e0, qv[2 * e + 1] * a.scale * e1, qh[e], ql[e]);
       }
@@ -186,7 +186,7 @@ __global__ void __launch_bounds__(256, 2) kda_prepare_mma_kernel(PrepArgs a) {
       }
 #pragma unroll
       for (int e = 0; e < 4; ++e)
-        split2_bf16(kc[2 * e] * exp2f(ref[2 * e] - gj[2 * e]), kc[2 * e + 1] * exp2f(ref[2 * e + 1] - gj[2 * e + 1]),
+        split2_bf16(kc[2 * e] * ex2_fast(ref[2 * e] - gj[2 * e]), kc[2 * e + 1] * ex2_fast(ref[2 * e + 1] - gj[2 * e + 1]),
                     ch_[e], cl_[e]);
       const uint32_t off = swz<256>(r, ch);
       *reinterpret_cast<uint4*>(st + 0 * 4096 + off) = make_uint4(kh[0], kh[1], kh[2], kh[3]);
@@ -197,15 +197,18 @@ __global__ void __launch_bounds__(256, 2) kda_prepare_mma_kernel(PrepArgs a) {
       *reinterpret_cast<uint4*>(st + 5 * 4096 + off) = make_uint4(cl_[0], cl_[1], cl_[2], cl_[3]);
     }
     __syncthreads();
-    if (warp < 4) {
-      const int nt = warp & 1, which = warp >> 1;   // which: 0 -> A (k rows), 1 -> Aqk (q rows)
+    {
+      // 8 warps: (A | Aqk) x (column tile) x (half of the 8 k-steps); three independent accumulator chains
+      // per warp (hi.hi, lo.hi, hi.lo); the two k-halves meet in shared memory through atomic adds.
+      const int nt = warp & 1, which = (warp >> 1) & 1, khalf = warp >> 2;
       const uint32_t rhi = smem_addr_u32(st + (which ? 2 : 0) * 4096), rlo = rhi + 4096;
       const uint32_t chi = smem_addr_u32(st + 4 * 4096), clo = chi + 4096;
-      float acc[4] = {0.f, 0.f, 0.f, 0.f};
+      float a0[4] = {0.f, 0.f, 0.f, 0.f}, a1[4] = {0.f, 0.f, 0.f, 0.f}, a2[4] = {0.f, 0.f, 0.f, 0.f};
       const int arow = (lane & 7) + ((lane >> 3) & 1) * 8;
       const int brow = 8 * nt + (lane & 7);
 #pragma unroll
-      for (int qd = 0; qd < 4; ++qd) {
+      for (int q2 = 0; q2 < 2; ++q2) {
+        const int qd = 2 * khalf + q2;
         uint32_t ah[2][4], al[2][4], bh_[4], bl_[4];
 #pragma unroll
         for (int kk = 0; kk < 2; ++kk) {
@@ -218,23 +221,26 @@ __global__ void __launch_bounds__(256, 2) kda_prepare_mma_kernel(PrepArgs a) {
         ldmatrix_x4(clo + ob, bl_[0], bl_[1], bl_[2], bl_[3]);
 #pragma unroll
         for (int kk = 0; kk < 2; ++kk) {
-          mma_bf16_16816(acc, ah[kk], bh_[2 * kk], bh_[2 * kk + 1]);
-          mma_bf16_16816(acc, al[kk], bh_[2 * kk], bh_[2 * kk + 1]);
-          mma_bf16_16816(acc, ah[kk], bl_[2 * kk], bl_[2 * kk + 1]);
+          mma_bf16_16816(a0, ah[kk], bh_[2 * kk], bh_[2 * kk + 1]);
+          mma_bf16_16816(a1, al[kk], bh_[2 * kk], bh_[2 * kk + 1]);
+          mma_bf16_16816(a2, ah[kk], bl_[2 * kk], bl_[2 * kk + 1]);
         }
       }
+      float acc[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) acc[e] = a0[e] + (a1[e] + a2[e]);
       const int i0 = 16 * ba + g4, i1 = i0 + 8;
       const int jc = 16 * bb + 8 * nt + 2 * j4;
       if (which == 0) {
-        sA[i0 * PS_LD + jc] = (jc < i0) ? acc[0] * sbeta[i0] : 0.f;
-        sA[i0 * PS_LD + jc + 1] = (jc + 1 < i0) ? acc[1] * sbeta[i0] : 0.f;
-        sA[i1 * PS_LD + jc] = (jc < i1) ? acc[2] * sbeta[i1] : 0.f;
-        sA[i1 * PS_LD + jc + 1] = (jc + 1 < i1) ? acc[3] * sbeta[i1] : 0.f;
+        if (jc < i0) atomicAdd(&sA[i0 * PS_LD + jc], acc[0] * sbeta[i0]);
+        if (jc + 1 < i0) atomicAdd(&sA[i0 * PS_LD + jc + 1], acc[1] * sbeta[i0]);
+        if (jc < i1) atomicAdd(&sA[i1 * PS_LD + jc], acc[2] * sbeta[i1]);
+        if (jc + 1 < i1) atomicAdd(&sA[i1 * PS_LD + jc + 1], acc[3] * sbeta[i1]);
       } else {
-        sQ[i0 * PS_LD + jc] = (jc <= i0) ? acc[0] : 0.f;
-        sQ[i0 * PS_LD + jc + 1] = (jc + 1 <= i0) ? acc[1] : 0.f;
-        sQ[i1 * PS_LD + jc] = (jc <= i1) ? acc[2] : 0.f;
-        sQ[i1 * PS_LD + jc + 1] = (jc + 1 <= i1) ? acc[3] : 0.f;
+        if (jc <= i0) atomicAdd(&sQ[i0 * PS_LD + jc], acc[0]);
+        if (jc + 1 <= i0) atomicAdd(&sQ[i0 * PS_LD + jc + 1], acc[1]);
+        if (jc <= i1) atomicAdd(&sQ[i1 * PS_LD + jc], acc[2]);
+        if (jc + 1 <= i1) atomicAdd(&sQ[i1 * PS_LD + jc + 1], acc[3]);
       }
     }
     __syncthreads();
@@ -270,9 +276,9 @@ __global__ void __launch_bounds__(256, 2) kda_prepare_mma_kernel(PrepArgs a) {
     uint32_t qh[4], ql[4], kh[4], kl[4], eh[4], el[4];
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
-      const float e0 = exp2f(gm[2 * e]), e1 = exp2f(gm[2 * e + 1]);
+      const float e0 = ex2_fast(gm[2 * e]), e1 = ex2_fast(gm[2 * e + 1]);
       split2_bf16(qf[2 * e] * a.scale * e0, qf[2 * e + 1] * a.scale * e1, qh[e], ql[e]);
-      split2_bf16(kf[2 * e] * exp2f(gl[2 * e] - gm[2 * e]), kf[2 * e + 1] * exp2f(gl[2 * e + 1] - gm[2 * e + 1]), kh[e], kl[e]);
+      split2_bf16(kf[2 * e] * ex2_fast(gl[2 * e] - gm[2 * e]), kf[2 * e + 1] * ex2_fast(gl[2 * e + 1] - gm[2 * e + 1]), kh[e], kl[e]);
       split2_bf16(kf[2 * e] * e0, kf[2 * e + 1] * e1, eh[e], el[e]);
     }
     const uint32_t off = swz<256>(i, ch);
@@ -284,7 +290,7 @@ __global__ void __launch_bounds__(256, 2) kda_prepare_mma_kernel(PrepArgs a) {
     *reinterpret_cast<uint4*>(sm + PS_EK + KM_TILE + off) = make_uint4(el[0], el[1], el[2], el[3]);
   }
   if (tid < KM_K) {
-    const float dl = exp2f(sG[(KM_C - 1) * KM_K + tid]);
+    const float dl = ex2_fast(sG[(KM_C - 1) * KM_K + tid]);
 #pragma unroll
     for (int s = 0; s < KM_V / 64; ++s)
       reinterpret_cast<float*>(wsc + KM_OFF_U + s * KM_U_SLICE + 16384)[tid] = dl;

@@ -20,18 +20,27 @@ __device__ __forceinline__ void mma_bf16_16816(float (&d)[4], const uint32_t (&a
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 __device__ __forceinline__ uint32_t pack2_bf16(float lo, float hi) {
-  __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
-  return *reinterpret_cast<uint32_t*>(&h);
+  uint32_t r;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
 }
 // Two-term bf16 split of a pair of fp32 values: x ~= hi + lo with ~16 bits of mantissa in total.
+// One packed conversion per term (cvt.rn.bf16x2.f32 packs {upper = first operand, lower = second}).
+__device__ __forceinline__ uint32_t cvt_bf16x2(float lo_elem, float hi_elem) {
+  uint32_t r;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi_elem), "f"(lo_elem));
+  return r;
+}
 __device__ __forceinline__ void split2_bf16(float x0, float x1, uint32_t& hi, uint32_t& lo) {
-  __nv_bfloat16 h0 = __float2bfloat16_rn(x0), h1 = __float2bfloat16_rn(x1);
-  __nv_bfloat162 hh, ll;
-  hh.x = h0; hh.y = h1;
-  ll.x = __float2bfloat16_rn(x0 - __bfloat162float(h0));
-  ll.y = __float2bfloat16_rn(x1 - __bfloat162float(h1));
-  hi = *reinterpret_cast<uint32_t*>(&hh);
-  lo = *reinterpret_cast<uint32_t*>(&ll);
+  hi = cvt_bf16x2(x0, x1);
+  const float h0 = __uint_as_float(hi << 16), h1 = __uint_as_float(hi & 0xFFFF0000u);
+  lo = cvt_bf16x2(x0 - h0, x1 - h1);
+}
+// 2^x with the hardware approximation (2 ulp), flushing denormals
+__device__ __forceinline__ float ex2_fast(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
 }
 __device__ __forceinline__ void split1_bf16(float x, bf16& hi, bf16& lo) {
   hi = __float2bfloat16_rn(x);

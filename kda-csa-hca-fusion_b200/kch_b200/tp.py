@@ -62,9 +62,10 @@ def gather_heads(o_local, ctx: TPContext):
     lead = o_local.shape[:-1]
     kl = o_local.shape[-1]
     flat = o_local.reshape(-1, kl).contiguous()
-    buf = torch.empty(ctx.world, flat.shape[0], kl, dtype=flat.dtype, device=flat.device)
+    rows = flat.shape[0]
+    buf = torch.empty(ctx.world * rows, kl, dtype=flat.dtype, device=flat.device)    # rank-major concatenation
     dist.all_gather_into_tensor(buf, flat, group=ctx.group)
-    return buf.permute(1, 0, 2).reshape(*lead, ctx.world * kl)
+    return buf.view(ctx.world, rows, kl).permute(1, 0, 2).reshape(*lead, ctx.world * kl)
 
 
 def build_tp_model(cfg, params, total_layers, ctx: TPContext, device, dtype):
