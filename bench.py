@@ -140,14 +140,14 @@ class GemmProbe:
 
 
 def cpu_baseline_sample(seconds_hint=20):
-    """The oracle port of the same stack on the host cores, on a bounded sample: B=1, T=2048 of the
-    same geometry, all host threads."""
+    """The oracle port of the same stack on the host cores, on a bounded sample: B=1, T=8192 of the
+    same geometry, all host threads (about 10-20 s)."""
     from kch_b200 import synthetic as syn
     from oracle import kch_oracle as orc
     spec = orc.HybridSpec(**C4)
     spec.build_layout(LAYERS)
     params = syn.hybrid_params(SEED, spec, LAYERS, dtype=torch.bfloat16)
-    T = 2048
+    T = 8192
     x = syn.hidden_states(SEED, 1, T, C4["d_model"], torch.bfloat16)
     with torch.no_grad():
         t0 = time.perf_counter()
@@ -155,6 +155,57 @@ def cpu_baseline_sample(seconds_hint=20):
         dt = time.perf_counter() - t0
     return {"value": T / dt, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
             "sample": f"oracle port, same stack, B=1 T={T} bf16, one pass, {dt:.1f} s"}
+
+
+def decode_state_bytes(cfg, B, context, kv_bytes):
+    """Bytes one decode step must move at this context (the algorithmic floor of the step): the three KDA
+    states read and written in fp32, the CSA indexer's fp32 scoring rows, the selected CSA rows, every HCA
+    row, both windows, and the weights once."""
+    HV, K, V = cfg["n_heads_v"], cfg["head_dim_k"], cfg["head_dim_v"]
+    kda = cfg["n_kda"] * B * HV * K * V * 4 * 2
+    nb, nb2 = context // cfg["csa_m"], context // cfg["hca_m2"]
+    idx = B * nb * cfg["csa_cI"] * 4
+    sel = B * min(nb, cfg["csa_topk"]) * cfg["csa_c"] * kv_bytes
+    hca = B * nb2 * cfg["hca_c"] * kv_bytes
+    win = B * (cfg["csa_sliding_window"] * cfg["csa_c"] + cfg["hca_sliding_window"] * cfg["hca_c"]) * 2
+    d = cfg["d_model"]
+    w_kda = d * (2 * cfg["n_heads_qk"] * K + HV * V + K + HV) + K * HV * K + HV * V * d
+    w_csa = d * (4 * cfg["csa_c"] + 2 * cfg["csa_cI"] + cfg["csa_dc"] + cfg["csa_nIh"]) + cfg["csa_dc"] * (
+        cfg["csa_nh"] * cfg["csa_c"] + cfg["csa_nIh"] * cfg["csa_cI"]) + cfg["csa_nh"] * cfg["csa_c"] * d
+    w_hca = d * (2 * cfg["hca_c"] + cfg["hca_dc"]) + cfg["hca_dc"] * cfg["hca_nh"] * cfg["hca_c"] + cfg["hca_nh"] * cfg["hca_c"] * d
+    weights = 2 * (cfg["n_kda"] * w_kda + cfg["n_csa"] * w_csa + cfg["n_hca"] * w_hca)
+    return kda + idx + sel + hca + win + weights
+
+
+def decode_bench(model, cfg_dict, B, context, steps, warmup, dev, peak_gbs):
+    """One-token decode steps through `HybridDecoding` at a long context, bf16 and FP8 compressed rows."""
+    import kch_b200
+    from kch_b200.synthetic import fill_decode_state
+    out = {"batch": B, "context": context, "steps": steps, "warmup": warmup}
+    x = torch.randn(B, 1, cfg_dict["d_model"], device=dev).to(torch.bfloat16)
+    for name, quant, kvb in (("bf16", None, 2), ("fp8", "fp8", 1.0625)):
+        dec = kch_b200.HybridDecoding(model=model, kv_quant=quant, use_cuda_graph=True)
+        fill_decode_state(dec, B, context, steps + warmup, dev, 11)
+        for _ in range(warmup):
+            dec(x)
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(steps):
+            y = dec(x)
+        b.record()
+        torch.cuda.synchronize()
+        us = a.elapsed_time(b) * 1e3 / steps
+        nbytes = decode_state_bytes(cfg_dict, B, context, kvb)
+        out[name] = {"us_per_step": us, "us_per_token": us / B, "tokens_per_s": B / (us * 1e-6),
+                     "algorithmic_bytes_per_step": nbytes, "achieved_gbs": nbytes / (us * 1e-6) / 1e9,
+                     "frac_of_hbm_peak": nbytes / (us * 1e-6) / 1e9 / peak_gbs,
+                     "finite": bool(torch.isfinite(y.float()).all()), "cuda_graph": dec._graph is not None}
+        dec.reset()
+        del dec
+        torch.cuda.empty_cache()
+    model.reset_state()
+    return out
 
 
 def run_reference(args):
@@ -168,7 +219,7 @@ def run_reference(args):
     spec = orc.HybridSpec(**C4)
     spec.build_layout(LAYERS)
     params = syn.hybrid_params(SEED, spec, LAYERS, dtype=torch.bfloat16)
-    T = 1024
+    T = 4096
     x = syn.hidden_states(SEED, 1, T, C4["d_model"], torch.bfloat16)
     times = []
     with torch.no_grad():
@@ -311,6 +362,9 @@ def run_b200(args):
                                "frac_of_tensor_peak": value * fpt / 1e12 / peak_tf},
             "clocks": clocks.summary(), "device_status": status,
         }
+        if world == 1 and not args.no_decode:
+            out["decode"] = decode_bench(model, C4, args.decode_batch, args.decode_context, args.decode_steps, 8, dev,
+                                         float(peaks.get("hbm_gbs", 6650.0)))
         if world == 1 and not args.no_cpu_baseline:
             out["cpu_baseline"] = cpu_baseline_sample()
         print(json.dumps(out))
@@ -327,6 +381,10 @@ def main():
     ap.add_argument("--batch", type=int, default=4)
     ap.add_argument("--seq-len", type=int, default=32768)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-decode", action="store_true")
+    ap.add_argument("--decode-batch", type=int, default=64)
+    ap.add_argument("--decode-context", type=int, default=131072)
+    ap.add_argument("--decode-steps", type=int, default=256)
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

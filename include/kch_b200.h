@@ -53,6 +53,10 @@ int kch_layernorm(const void* x, const void* weight, const void* bias, void* y, 
  * x,y [B,T,d]; lookback [B,2,d] or NULL (zeros); weight [d,3]; bias [d]; all in `dtype`. */
 int kch_short_conv(const void* x, const void* lookback, const void* weight, const void* bias, void* y,
                    int B, int T, int d, int dtype, void* stream);
+/* One-token step of the same convolution (x,y [B,1,d]) that also slides `lookback` [B,2,d] by one token in
+ * place: lookback <- [lookback[:,1], x] (the concatenation of ops_fused.py:560-569 without a new tensor). */
+int kch_short_conv_step(const void* x, void* lookback, const void* weight, const void* bias, void* y, int B, int d,
+                        int dtype, void* stream);
 
 /* F.linear at ops_fused.py:571-581,609,713,739 and ops_csa.py:841-878, ops_hca.py:132-141:
  * C[M,N] = A[M,K] . W[N,K]^T, fp32 accumulation, rounded to `dtype`; if `residual` is given the
@@ -198,10 +202,26 @@ int kch_attend(const kch_attend_args* args, void* stream);
 
 /* ---- decode caches ---------------------------------------------------------------------------------- */
 
+/* Device-resident mirror of a decode cache's counters (int32[8]; no counterpart in the reference, whose
+ * counters are Python ints): with it a decode step has no host-side arguments that change from token to
+ * token, so the whole step can be replayed from a CUDA graph.  kch_cache_advance applies the same update
+ * the host makes after an append (ops_decoding_cache.py:764-779). */
+#define KCH_CTR_ACC_LEN 0   /* tokens in the open block */
+#define KCH_CTR_N_BLOCKS 1  /* completed compressed rows */
+#define KCH_CTR_RING_N 2    /* tokens ever written to the window ring */
+#define KCH_CTR_HAS_PREV 3  /* CSA: a previous block's b-branch is held */
+#define KCH_CTR_TOKENS 4    /* tokens seen */
+#define KCH_CTR_WORDS 8
+#define KCH_STATUS_CACHE_CAPACITY 64  /* device status: an append found its counters out of range / storage full */
+int kch_cache_advance(int32_t* counters, int m, void* stream);
+
 /* One appended token for every sequence of the batch: CSADecodingCache.append_step
  * (ops_decoding_cache.py:704-779) when Cb/Zb/K_idx/Z_idx are given, HCADecodingCache.append_step
- * (1238-1264) when they are NULL.  Host-side counters (acc_len, n_blocks, ring_pos, has_prev) are
- * owned by the caller, as in the reference's cache objects. */
+ * (1238-1264) when they are NULL.  The counters (acc_len, n_blocks, ring_pos, has_prev) are host values
+ * owned by the caller, as in the reference's cache objects, unless `counters` points at their device
+ * mirror: then the kernel reads them there (ring_pos = ring_n % win), skips the append and raises
+ * KCH_STATUS_CACHE_CAPACITY if a closing block finds no room, and the caller follows with
+ * kch_cache_advance. */
 typedef struct kch_cache_append_args {
   int B, c, c_I, m, win;
   int dtype;                 /* dtype of projections, accumulators, ring, kcomp (KCH_F32 / KCH_BF16) */
@@ -217,14 +237,63 @@ typedef struct kch_cache_append_args {
   float* comp_scales;        /* [B,capacity,c/64] for 8-bit kinds */
   float* comp_norms;         /* [B,capacity] */
   void* kcomp;               /* [B,capacity,c_I] in dtype */
-  float* kcomp_normalized;   /* [B,capacity,c_I] fp32 scoring copy */
+  float* kcomp_norms;        /* [B,capacity] max(||stored indexer key||, 1e-12) */
   int64_t capacity;
   int n_blocks;
   void* ring;                /* [B,win,c] in dtype */
   int ring_pos;
   int normalize;
+  const int32_t* counters;   /* optional device mirror, see above */
 } kch_cache_append_args;
 int kch_cache_append_token(const kch_cache_append_args* args, void* stream);
+
+/* Lightning indexer of one decode step over a cache's stored indexer keys
+ * (CSADecodingCache.forward_step, ops_decoding_cache.py:903-1000): q_idx [B,HI*DI] rows q_ld apart in
+ * q_dtype (read as fp32, normalised here when `normalize`), keys [B,capacity,DI] in k_dtype with k_norms
+ * [B,capacity] (key_n = key / norm when `normalize`), w [B,HI] rows w_ld apart in w_dtype.  The visible prefix is min(tokens / m, n_blocks) read from `counters`.
+ * Writes idx_out [B,topk] (ascending block index, -1 padded).  workspace: B * round_up(capacity,4) floats. */
+int64_t kch_decode_indexer_workspace_bytes(int B, int64_t capacity);
+int kch_decode_indexer_topk(const void* q_idx, int q_dtype, int64_t q_ld, const void* keys, int k_dtype,
+                            const float* k_norms, const void* w, int w_dtype, int64_t w_ld,
+                            int32_t* idx_out, int B, int64_t capacity, int HI, int DI, int topk, int normalize,
+                            float scale, int m, const int32_t* counters, void* workspace, int64_t workspace_bytes,
+                            void* stream);
+
+/* Attention of one decode step (one query per sequence) straight over a cache's storage, split over the
+ * entries so that a small batch still fills the GPU (CSADecodingCache.forward_step
+ * ops_decoding_cache.py:1001-1070, HCADecodingCache.forward_step 1318-1395).  Same joint softmax as
+ * kch_attend; rows are used as row / norm when comp_norms is given.  Entry counts come from `counters`:
+ * visible rows = min(tokens / m, n_blocks), window rows = min(ring_n, sliding_window).
+ * workspace: B * n_splits * nh * (c + 2) floats, n_splits = kch_attend_decode_splits(B). */
+typedef struct kch_attend_decode_args {
+  const void* q;             /* [B, nh*c] rows q_ld apart */
+  int q_dtype;
+  int64_t q_ld;
+  int q_normalize;
+  int B, nh, c;
+  const void* comp;          /* [B,capacity,c] */
+  int comp_dtype;
+  int64_t capacity;
+  const float* comp_norms;   /* [B,capacity] or NULL */
+  const float* comp_scales;  /* [B,capacity,c/64] for the 8-bit kinds */
+  const int32_t* sel_indices;/* [B,topk] or NULL = every visible row */
+  int topk;
+  int m;
+  const void* win;           /* ring [B,sliding_window,c] or NULL */
+  int win_dtype;
+  int sliding_window;
+  const void* sink;
+  int sink_dtype;
+  float scale;
+  void* out;                 /* [B, nh*c] */
+  int out_dtype;
+  const int32_t* counters;
+  void* workspace;
+  int64_t workspace_bytes;
+} kch_attend_decode_args;
+int kch_attend_decode_splits(int B);
+int64_t kch_attend_decode_workspace_bytes(int B, int nh, int c);
+int kch_attend_decode(const kch_attend_decode_args* args, void* stream);
 
 /* Block-scaled 8-bit encoding of rows (no counterpart in the reference; it stores the cache dtype only):
  * payload [rows,c], scales [rows,c/64], norms [rows] = max(||dequantised row||, 1e-12). */

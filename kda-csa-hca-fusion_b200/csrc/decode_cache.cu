@@ -13,6 +13,8 @@
 
 #include "kch_common.cuh"
 
+unsigned int* kch_status_device_ptr();   // device address of the library's status word
+
 struct AppendArgs {
   const void *Ca, *Cb, *Za, *Zb, *Ki, *Zi;   // new token rows, row b at element offset b*ld
   int64_t ld_c, ld_i;
@@ -22,10 +24,12 @@ struct AppendArgs {
   const void *Ba, *Bb, *Bi;                              // [m,c], [m,c], [m,cI]
   void* comp; float* comp_scales; float* comp_norms;     // [B,cap,c] (+ [B,cap,c/64], [B,cap])
   int comp_kind;                                         // KCH_F32 / KCH_BF16 / KCH_FP8_E4M3 / KCH_INT8
-  void* kcomp; float* kcomp_n;                           // [B,cap,cI] stored rows and fp32 scoring copy
+  void* kcomp; float* kcomp_norms;                       // [B,cap,cI] stored indexer keys, [B,cap] their fp32 norms
   int64_t cap; int n_blocks;
   void* ring; int ring_pos; int win;
   int acc_len, m, c, cI, normalize, overlap;
+  const int32_t* counters;                               // device-resident {acc_len, n_blocks, ring_n, has_prev, ...} or null
+  unsigned int* status;
 };
 
 template <typename T>
@@ -43,6 +47,16 @@ __global__ void __launch_bounds__(128) cache_append_kernel(AppendArgs a) {
   extern __shared__ float srow[];   // [c] compressed row, then [cI]
   __shared__ float red[4];
   const int b = blockIdx.x, tid = threadIdx.x;
+  if (a.counters) {   // the step is replayed from a CUDA graph: the counters live on the device
+    a.acc_len = a.counters[KCH_CTR_ACC_LEN];
+    a.n_blocks = a.counters[KCH_CTR_N_BLOCKS];
+    a.ring_pos = a.win > 0 ? a.counters[KCH_CTR_RING_N] % a.win : 0;
+    a.has_prev = a.counters[KCH_CTR_HAS_PREV];
+    if (a.acc_len < 0 || a.acc_len >= a.m || (a.acc_len + 1 == a.m && (a.n_blocks >= a.cap || !a.comp))) {
+      if (tid == 0) atomicCAS(a.status, 0u, (unsigned)KCH_STATUS_CACHE_CAPACITY);
+      return;
+    }
+  }
   const int c = a.c, cI = a.cI, m = a.m, slot = a.acc_len;
   const int64_t accoff = ((int64_t)b * m + slot) * c;
   // 1. stash the token
@@ -136,7 +150,7 @@ __global__ void __launch_bounds__(128) cache_append_kernel(AppendArgs a) {
   }
   float nrm = fmaxf(sqrtf(block_sum_128<T>(nsq, red)), 1e-12f);
   if (tid == 0) a.comp_norms[orow] = nrm;
-  // 4. indexer key of the block (single branch) and its normalised fp32 copy
+  // 4. indexer key of the block (single branch) and the fp32 norm of the stored key
   if (a.Ki) {
     __syncthreads();
     const int64_t blki = (int64_t)b * m * cI;
@@ -156,8 +170,8 @@ __global__ void __launch_bounds__(128) cache_append_kernel(AppendArgs a) {
       stf((T*)a.kcomp + orow * cI + d, r);
       isq += r * r;
     }
-    float inrm = a.normalize ? fmaxf(sqrtf(block_sum_128<T>(isq, red)), 1e-12f) : 1.f;
-    for (int d = tid; d < cI; d += 128) a.kcomp_n[orow * cI + d] = srow[d] / inrm;
+    float inrm = fmaxf(sqrtf(block_sum_128<T>(isq, red)), 1e-12f);
+    if (tid == 0) a.kcomp_norms[orow] = inrm;
   }
   // 5. this block's b-branch becomes the overlap partner of the next block
   if (a.overlap) {
@@ -173,17 +187,19 @@ extern "C" int kch_cache_append_token(const kch_cache_append_args* p, void* stre
   KCH_REQUIRE(p->B >= 1, "B=%d must be >= 1", p->B);
   KCH_REQUIRE(p->c >= 1, "c=%d must be >= 1", p->c);
   KCH_REQUIRE(p->m >= 1, "m=%d must be >= 1", p->m);
-  KCH_REQUIRE(p->acc_len >= 0 && p->acc_len < p->m, "acc_len=%d out of range for m=%d", p->acc_len, p->m);
+  KCH_REQUIRE(p->counters || (p->acc_len >= 0 && p->acc_len < p->m), "acc_len=%d out of range for m=%d", p->acc_len, p->m);
   KCH_REQUIRE(p->dtype == KCH_F32 || p->dtype == KCH_BF16, "cache dtype tag %d unsupported", p->dtype);
-  const bool closes = p->acc_len + 1 == p->m;
+  // with device counters the host cannot know whether this token closes a block: require the storage up front
+  const bool closes = p->counters ? true : p->acc_len + 1 == p->m;
   if (p->comp_kind == KCH_FP8_E4M3 || p->comp_kind == KCH_INT8)
     KCH_REQUIRE(p->c % 64 == 0 && (!closes || p->comp_scales),
                 "block-scaled 8-bit rows need c %% 64 == 0 (c=%d) and a scale buffer", p->c);
   else
     KCH_REQUIRE(p->comp_kind == p->dtype, "comp_kind=%d must equal the cache dtype or be an 8-bit kind", p->comp_kind);
   if (closes)
-    KCH_REQUIRE(p->comp && p->comp_norms && p->n_blocks < p->capacity, "compressed-row capacity %lld exhausted",
-                (long long)p->capacity);
+    KCH_REQUIRE(p->comp && p->comp_norms && (p->counters || p->n_blocks < p->capacity),
+                "compressed-row capacity %lld exhausted", (long long)p->capacity);
+  if (closes && p->K_idx) KCH_REQUIRE(p->kcomp && p->kcomp_norms, "kch_cache_append_token: indexer key storage missing");
   AppendArgs a;
   a.Ca = p->Ca; a.Cb = p->Cb; a.Za = p->Za; a.Zb = p->Zb; a.Ki = p->K_idx; a.Zi = p->Z_idx;
   a.ld_c = p->ld_c; a.ld_i = p->ld_i;
@@ -191,7 +207,8 @@ extern "C" int kch_cache_append_token(const kch_cache_append_args* p, void* stre
   a.prevCb = p->prev_Cb; a.prevZb = p->prev_Zb; a.has_prev = p->has_prev;
   a.Ba = p->Ba; a.Bb = p->Bb; a.Bi = p->B_idx;
   a.comp = p->comp; a.comp_scales = p->comp_scales; a.comp_norms = p->comp_norms; a.comp_kind = p->comp_kind;
-  a.kcomp = p->kcomp; a.kcomp_n = p->kcomp_normalized; a.cap = p->capacity; a.n_blocks = p->n_blocks;
+  a.kcomp = p->kcomp; a.kcomp_norms = p->kcomp_norms; a.cap = p->capacity; a.n_blocks = p->n_blocks;
+  a.counters = p->counters; a.status = kch_status_device_ptr();
   a.ring = p->win > 0 ? p->ring : nullptr; a.ring_pos = p->ring_pos; a.win = p->win;
   a.acc_len = p->acc_len; a.m = p->m; a.c = p->c; a.cI = p->c_I; a.normalize = p->normalize; a.overlap = p->Cb != nullptr;
   if (!a.Ki) a.cI = 0;
@@ -199,6 +216,27 @@ extern "C" int kch_cache_append_token(const kch_cache_append_args* p, void* stre
   cudaStream_t s = kch_stream(stream);
   if (p->dtype == KCH_BF16) cache_append_kernel<bf16><<<p->B, 128, smem, s>>>(a);
   else cache_append_kernel<float><<<p->B, 128, smem, s>>>(a);
+  KCH_LAUNCH_OK();
+  return KCH_OK;
+}
+
+// One thread advances the device-resident counters after a token has been appended (a separate launch:
+// every CTA of the append kernel reads the old values).
+__global__ void cache_advance_kernel(int32_t* ctr, int m) {
+  int acc = ctr[KCH_CTR_ACC_LEN] + 1;
+  ctr[KCH_CTR_RING_N] += 1;
+  ctr[KCH_CTR_TOKENS] += 1;
+  if (acc >= m) {
+    acc = 0;
+    ctr[KCH_CTR_N_BLOCKS] += 1;
+    ctr[KCH_CTR_HAS_PREV] = 1;
+  }
+  ctr[KCH_CTR_ACC_LEN] = acc;
+}
+
+extern "C" int kch_cache_advance(int32_t* counters, int m, void* stream) {
+  KCH_REQUIRE(counters != nullptr && m >= 1, "kch_cache_advance: counters=%p m=%d", (void*)counters, m);
+  cache_advance_kernel<<<1, 1, 0, kch_stream(stream)>>>(counters, m);
   KCH_LAUNCH_OK();
   return KCH_OK;
 }

@@ -101,9 +101,9 @@ extern "C" int kch_layernorm(const void* x, const void* weight, const void* bias
 // Follows KDAHybridLayer.forward_functional (ops_fused.py:505-527).
 // ---------------------------------------------------------------------------------------
 template <typename T>
-__global__ void short_conv_kernel(const T* __restrict__ x, const T* __restrict__ lb,
+__global__ void short_conv_kernel(const T* __restrict__ x, const T* lb,
                                   const T* __restrict__ w, const T* __restrict__ bias,
-                                  T* __restrict__ y, int B, int T_, int d) {
+                                  T* __restrict__ y, int B, int T_, int d, T* lb_out = nullptr) {
   int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   int64_t total = (int64_t)B * T_ * d;
   if (i >= total) return;
@@ -122,12 +122,16 @@ __global__ void short_conv_kernel(const T* __restrict__ x, const T* __restrict__
   acc = fmaf(ldf(w + ch * 3 + 1), x1, acc);
   acc = fmaf(ldf(w + ch * 3 + 2), x0, acc);
   stf(y + i, acc + ldf(bias + ch));
+  if (lb_out) {   // one-token step: the lookback slides by one token, in place (this thread owns channel ch)
+    stf(lb_out + ((int64_t)b * 2 + 0) * d + ch, x1);
+    stf(lb_out + ((int64_t)b * 2 + 1) * d + ch, x0);
+  }
 }
 
 // bf16 fast path: 8 channels (16 bytes) per thread
-__global__ void short_conv_kernel_bf16x8(const bf16* __restrict__ x, const bf16* __restrict__ lb,
+__global__ void short_conv_kernel_bf16x8(const bf16* __restrict__ x, const bf16* lb,
                                          const bf16* __restrict__ w, const bf16* __restrict__ bias,
-                                         bf16* __restrict__ y, int B, int T_, int d) {
+                                         bf16* __restrict__ y, int B, int T_, int d, bf16* lb_out = nullptr) {
   const int d8 = d >> 3;
   int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= (int64_t)B * T_ * d8) return;
@@ -178,6 +182,15 @@ __global__ void short_conv_kernel_bf16x8(const bf16* __restrict__ x, const bf16*
     out[k] = __float2bfloat16_rn(acc + bb[k]);
   }
   *reinterpret_cast<uint4*>(y + bt * d + c0) = outv;
+  if (lb_out) {   // one-token step (T_ == 1): slide the lookback in place; the values are exact bf16 already
+    uint4 v1, v0;
+    bf16* e1 = reinterpret_cast<bf16*>(&v1);
+    bf16* e0 = reinterpret_cast<bf16*>(&v0);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) { e1[k] = __float2bfloat16_rn(x1[k]); e0[k] = __float2bfloat16_rn(x0[k]); }
+    *reinterpret_cast<uint4*>(lb_out + ((int64_t)b * 2 + 0) * d + c0) = v1;
+    *reinterpret_cast<uint4*>(lb_out + ((int64_t)b * 2 + 1) * d + c0) = v0;
+  }
 }
 
 extern "C" int kch_short_conv(const void* x, const void* lookback, const void* weight,
@@ -195,6 +208,27 @@ extern "C" int kch_short_conv(const void* x, const void* lookback, const void* w
     dim3 grid((unsigned)ceil_div64(total, 256)), block(256);
     KCH_DISPATCH_FLOAT(dtype, T_, (short_conv_kernel<T_><<<grid, block, 0, kch_stream(stream)>>>(
         (const T_*)x, (const T_*)lookback, (const T_*)weight, (const T_*)bias, (T_*)y, B, T, d)));
+  }
+  KCH_LAUNCH_OK();
+  return KCH_OK;
+}
+
+// One-token step of the conv with the lookback [B,2,d] updated where it lies (ops_fused.py:560-569 builds
+// the new lookback by concatenation; here the same two rows are written back by the thread that read them).
+extern "C" int kch_short_conv_step(const void* x, void* lookback, const void* weight, const void* bias, void* y,
+                                   int B, int d, int dtype, void* stream) {
+  KCH_REQUIRE(B >= 1 && d >= 1 && x && lookback && y, "kch_short_conv_step: B=%d d=%d", B, d);
+  int64_t total = (int64_t)B * d;
+  const uintptr_t al = (uintptr_t)x | (uintptr_t)y | (uintptr_t)weight | (uintptr_t)bias | (uintptr_t)lookback;
+  if (dtype == KCH_BF16 && (d % 8) == 0 && (al & 15) == 0) {
+    dim3 grid((unsigned)ceil_div64(total / 8, 256)), block(256);
+    short_conv_kernel_bf16x8<<<grid, block, 0, kch_stream(stream)>>>((const bf16*)x, (const bf16*)lookback,
+                                                                    (const bf16*)weight, (const bf16*)bias, (bf16*)y, B, 1, d,
+                                                                    (bf16*)lookback);
+  } else {
+    dim3 grid((unsigned)ceil_div64(total, 256)), block(256);
+    KCH_DISPATCH_FLOAT(dtype, T_, (short_conv_kernel<T_><<<grid, block, 0, kch_stream(stream)>>>(
+        (const T_*)x, (const T_*)lookback, (const T_*)weight, (const T_*)bias, (T_*)y, B, 1, d, (T_*)lookback)));
   }
   KCH_LAUNCH_OK();
   return KCH_OK;

@@ -5,7 +5,7 @@
 //
 // Structure (one persistent CTA per SM, 320 threads):
 //   warp 0      : TMA producer — cp.async.bulk.tensor tiles of A (128x64) and W (BNx64), 128-byte
-//                 swizzle, into a 4-stage shared-memory ring (no multicast: every CTA fetches its own).
+//                 swizzle, into a 4..10-stage shared-memory ring (no multicast: every CTA fetches its own).
 //   warp 1      : allocates tensor memory, then one elected lane issues tcgen05.mma (M=128, N=BN,
 //                 K=16 per instruction, four per stage) and tcgen05.commit to release stages.
 //   warps 2..9  : epilogue — tcgen05.ld of the fp32 accumulator (each warp its 32-lane quarter and one
@@ -22,7 +22,6 @@
 
 #define TG_BM 128
 #define TG_BK 64
-#define TG_STAGES 4
 #define TG_THREADS 320
 #define TG_SPIN_LIMIT (1u << 24)
 
@@ -109,12 +108,18 @@ __device__ __forceinline__ float bf16r(float v) { return __bfloat162float(__floa
 // Fast intrinsics (ex2.approx, approximate reciprocal): a few fp32 ulp, far below the bf16 rounding
 // that follows every step, so a fused result differs from the unfused chain by at most one bf16 rounding.
 __device__ __forceinline__ float ep_silu(float x) { return __fdividef(x, 1.0f + __expf(-x)); }
+// Ring depth: as many (A tile + W tile) stages as fit in about 200 KB, so that narrow tiles (small BN) keep
+// the same number of bytes in flight per SM as the 256-wide tile does with 4 stages.
+template <int BN>
+struct TgStages { static constexpr int value = BN >= 256 ? 4 : BN >= 128 ? 6 : BN >= 64 ? 8 : 10; };
+
 template <int BN>
 struct TgSmem {
-  alignas(1024) bf16 a[TG_STAGES][TG_BM * TG_BK];
-  alignas(1024) bf16 b[TG_STAGES][BN * TG_BK];
-  alignas(8) uint64_t full[TG_STAGES];
-  uint64_t empty[TG_STAGES];
+  static constexpr int STAGES = TgStages<BN>::value;
+  alignas(1024) bf16 a[STAGES][TG_BM * TG_BK];
+  alignas(1024) bf16 b[STAGES][BN * TG_BK];
+  alignas(8) uint64_t full[STAGES];
+  uint64_t empty[STAGES];
   uint64_t acc_full[2];
   uint64_t acc_empty[2];
   uint32_t tmem_base;
@@ -127,6 +132,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     int64_t ldc, int64_t ldr, int vec_ok, const TgEpilogue ep) {
   extern __shared__ uint8_t smem_raw[];
   TgSmem<BN>& sm = *reinterpret_cast<TgSmem<BN>*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  constexpr int TG_STAGES = TgStages<BN>::value;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n_tiles = (N + BN - 1) / BN;
   const int64_t m_tiles = (M + TG_BM - 1) / TG_BM;
@@ -389,6 +395,14 @@ int kch_linear_tcgen05(const void* A, const void* W, void* C, const void* R, int
   if (e && e->n_segments) {
     ep.nseg = e->n_segments;
     for (int i = 0; i < e->n_segments; ++i) { ep.seg_end[i] = e->seg_end[i]; ep.seg_act[i] = e->seg_act[i]; ep.seg_param[i] = e->seg_param[i]; }
+  }
+  if (M <= TG_BM && N > 128) {
+    // One row of tiles (a decode batch): the launch is a weight stream, so spread it over many SMs with
+    // narrow tiles.  A fused L2-norm needs a whole 128-column head inside the tile.
+    bool l2 = false;
+    for (int i = 0; i < ep.nseg; ++i) l2 = l2 || ep.seg_act[i] == KCH_ACT_SILU_L2NORM;
+    if (l2) return launch_tg<128>(A, W, C, R, M, N, K, lda, ldw, ldc, ldr, ep, s);
+    return launch_tg<32>(A, W, C, R, M, N, K, lda, ldw, ldc, ldr, ep, s);
   }
   if (N > 128) return launch_tg<256>(A, W, C, R, M, N, K, lda, ldw, ldc, ldr, ep, s);
   if (N > 64) return launch_tg<128>(A, W, C, R, M, N, K, lda, ldw, ldc, ldr, ep, s);

@@ -382,7 +382,12 @@ __device__ __forceinline__ int block_excl_scan(int v, int* buf, int* total) {
 
 __global__ void __launch_bounds__(256)
 topk_select_kernel(const float* __restrict__ logits, int32_t* __restrict__ out, int T, int n,
-                   int64_t n_ld, int topk, int m, int64_t t0, int nvis_fixed, int sorted, int cache_cap) {
+                   int64_t n_ld, int topk, int m, int64_t t0, int nvis_fixed, int sorted, int cache_cap,
+                   const int32_t* __restrict__ ctr = nullptr, int ctr_m = 1) {
+  if (ctr) {   // decode step: row count and visible prefix come from the cache's device counters
+    n = ctr[KCH_CTR_N_BLOCKS];
+    nvis_fixed = min(ctr[KCH_CTR_TOKENS] / ctr_m, n);
+  }
   // dynamic shared memory: [cache_cap floats: the row's visible logits] [sort keys, only when sorted]
   extern __shared__ __align__(16) uint8_t sel_smem[];
   float* srow = reinterpret_cast<float*>(sel_smem);
@@ -614,6 +619,252 @@ extern "C" int kch_indexer_topk_static(const float* q_idx, const float* k_idx, c
   KCH_CUDA_OK(cudaFuncSetAttribute(topk_select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, cache_cap * 4));
   topk_select_kernel<<<(unsigned)((int64_t)B * T), 256, (size_t)cache_cap * 4, s>>>(logits, indices, T, n_blocks, n_ld,
                                                                                      topk, m, t0, n_visible, 0, cache_cap);
+  KCH_LAUNCH_OK();
+  return KCH_OK;
+}
+
+// ---------------------------------------------------------------------------------------
+// Decode step: one indexer query per sequence against that sequence's stored keys.
+// A memory-bound matrix-vector product: every visible key row is read once in its storage type
+// (bf16 or fp32; DI*2 bytes per row at bf16) together with its fp32 norm (the reference normalises the
+// stored keys with F.normalize, ops_decoding_cache.py:919-924; here q . key is divided by the norm) and
+// scored against the HI query heads held in shared memory.  The visible prefix comes from the
+// cache's device counters.  VEC path: 16-byte loads, DI/EPL lanes per row; otherwise one warp per row.
+// ---------------------------------------------------------------------------------------
+#define DIX_ROWS 1024   // key rows per CTA
+#define DIX_MAX_HD 1024 // HI*DI floats of query held in shared memory
+
+template <typename T, bool VEC>
+__global__ void __launch_bounds__(256)
+decode_indexer_logits_kernel(const void* __restrict__ q, int q_dtype, int64_t q_ld, const T* __restrict__ keys,
+                             const float* __restrict__ norms, const void* __restrict__ w, int w_dtype, int64_t w_ld,
+                             float* __restrict__ logits, int64_t cap, int64_t n_ld,
+                             int HI, int DI, int normalize, float scale, int m, const int32_t* __restrict__ ctr) {
+  const int b = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int nvis = min(ctr[KCH_CTR_TOKENS] / m, ctr[KCH_CTR_N_BLOCKS]);
+  const int r0 = blockIdx.x * DIX_ROWS;
+  if (r0 >= nvis) return;
+  const int r1 = min(nvis, r0 + DIX_ROWS);
+  __shared__ __align__(16) float sq[DIX_MAX_HD];
+  __shared__ float sw[64];
+  // the query of this sequence, L2-normalised per head when cosine scoring is on (one warp per head)
+  for (int h = warp; h < HI; h += 8) {
+    float ss = 0.f;
+    for (int d = lane; d < DI; d += 32) { float v = ld_any(q, (int64_t)b * q_ld + h * DI + d, q_dtype); sq[h * DI + d] = v; ss += v * v; }
+    if (normalize) {
+      const float nrm = fmaxf(sqrtf(warp_sum(ss)), 1e-12f);
+      for (int d = lane; d < DI; d += 32) sq[h * DI + d] /= nrm;
+    }
+    if (lane == 0) sw[h] = w ? ld_any(w, (int64_t)b * w_ld + h, w_dtype) : 1.f;
+  }
+  __syncthreads();
+  const T* kb = keys + (int64_t)b * cap * DI;
+  const float* nb = norms + (int64_t)b * cap;
+  float* lg = logits + (int64_t)b * n_ld;
+  if (VEC) {
+    constexpr int EPL = 16 / (int)sizeof(T);          // elements per lane
+    const int LPR = DI / EPL;                          // lanes per row (power of two <= 32)
+    const int rpp = 256 / LPR;                         // rows per pass of the CTA
+    const int sub = tid % LPR, rloc = tid / LPR;
+    // uniform trip count keeps the shuffles converged; four rows per thread are loaded before any is scored
+    for (int rb = r0 + rloc; rb < r0 + DIX_ROWS; rb += 4 * rpp) {
+      uint4 raw[4];
+      float dv[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int r = rb + u * rpp;
+        raw[u] = make_uint4(0u, 0u, 0u, 0u);
+        dv[u] = 1.f;
+        if (r < r1) {
+          raw[u] = *reinterpret_cast<const uint4*>(kb + (int64_t)r * DI + sub * EPL);
+          if (normalize) dv[u] = nb[r];
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int r = rb + u * rpp;
+        float kv[EPL];
+        if (sizeof(T) == 2) {
+          const uint32_t w4[4] = {raw[u].x, raw[u].y, raw[u].z, raw[u].w};
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            kv[(2 * i) % EPL] = __uint_as_float(w4[i] << 16);
+            kv[(2 * i + 1) % EPL] = __uint_as_float(w4[i] & 0xFFFF0000u);
+          }
+        } else {
+          kv[0] = __uint_as_float(raw[u].x); kv[1] = __uint_as_float(raw[u].y);
+          kv[2 % EPL] = __uint_as_float(raw[u].z); kv[3 % EPL] = __uint_as_float(raw[u].w);
+        }
+        float out = 0.f;
+        for (int h = 0; h < HI; ++h) {
+          const float* qh = sq + h * DI + sub * EPL;
+          float p = 0.f;
+#pragma unroll
+          for (int i = 0; i < EPL; ++i) p = fmaf(qh[i], kv[i], p);
+          for (int off = LPR >> 1; off > 0; off >>= 1) p += __shfl_xor_sync(0xffffffffu, p, off);
+          // the key's norm divides the finished dot product (the reference divides the key element by element:
+          // the same value up to one rounding of the logit)
+          out = fmaf(fmaxf(p / dv[u] * scale, 0.f), sw[h], out);
+        }
+        if (r < r1 && sub == 0) lg[r] = out;
+      }
+    }
+  } else {
+    for (int r = r0 + warp; r < r1; r += 8) {
+      const float dv = normalize ? nb[r] : 1.f;
+      float out = 0.f;
+      for (int h = 0; h < HI; ++h) {
+        float p = 0.f;
+        for (int d = lane; d < DI; d += 32) p = fmaf(sq[h * DI + d], ldf(kb + (int64_t)r * DI + d) / dv, p);
+        p = warp_sum(p);
+        out = fmaf(fmaxf(p * scale, 0.f), sw[h], out);
+      }
+      if (lane == 0) lg[r] = out;
+    }
+  }
+}
+
+// Tensor-core form of the same product for bf16 keys with DI = 64 and up to 8 indexer heads.  Sixteen key rows
+// are the M rows of mma.sync m16n8k16 and the heads its N columns; the query is split in three bf16 terms
+// (24 bits of mantissa) while the stored keys are exact bf16, so every product is exact and the sum is
+// fp32-grade.  A key row is 128 bytes: four lanes read it with 16-byte loads (fully coalesced, no shared
+// memory); the contraction index is permuted so that those 8 consecutive elements are the A fragments of two
+// k-steps, and the query fragments are built once with the same permutation.
+__global__ void __launch_bounds__(256)
+decode_indexer_logits_mma_kernel(const void* __restrict__ q, int q_dtype, int64_t q_ld, const bf16* __restrict__ keys,
+                                 const float* __restrict__ norms, const void* __restrict__ w, int w_dtype, int64_t w_ld,
+                                 float* __restrict__ logits, int64_t cap, int64_t n_ld, int HI, int normalize,
+                                 float scale, int m, const int32_t* __restrict__ ctr) {
+  constexpr int DI = 64;
+  const int b = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int g = lane >> 2, t = lane & 3;
+  const int nvis = min(ctr[KCH_CTR_TOKENS] / m, ctr[KCH_CTR_N_BLOCKS]);
+  const int r0 = blockIdx.x * DIX_ROWS;
+  if (r0 >= nvis) return;
+  __shared__ float sq[8 * DI];
+  __shared__ float sw[8];
+  {
+    const int h = warp;                                        // 8 warps, 8 head slots
+    float v0 = 0.f, v1 = 0.f;
+    if (h < HI) { v0 = ld_any(q, (int64_t)b * q_ld + h * DI + lane, q_dtype); v1 = ld_any(q, (int64_t)b * q_ld + h * DI + 32 + lane, q_dtype); }
+    if (normalize) {
+      const float nrm = fmaxf(sqrtf(warp_sum(v0 * v0 + v1 * v1)), 1e-12f);
+      v0 /= nrm; v1 /= nrm;
+    }
+    sq[h * DI + lane] = v0; sq[h * DI + 32 + lane] = v1;
+    if (lane == 0) sw[h] = h < HI ? (w ? ld_any(w, (int64_t)b * w_ld + h, w_dtype) : 1.f) : 0.f;
+  }
+  __syncthreads();
+  // B fragments (head g is column g) of the four k-steps, three terms each: logical k-step 2c+s' holds the
+  // query elements 32c + 8t + 4s' + {0,1} (b0) and + {2,3} (b1), matching the key chunk a lane loads
+  uint32_t qb[4][3][2];
+#pragma unroll
+  for (int ks = 0; ks < 4; ++ks) {
+    const int k0 = (ks >> 1) * 32 + 8 * t + 4 * (ks & 1);
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      uint32_t hi, mid, lo;
+      split3_pair(sq[g * DI + k0 + 2 * half], sq[g * DI + k0 + 2 * half + 1], hi, mid, lo);
+      qb[ks][0][half] = hi; qb[ks][1][half] = mid; qb[ks][2][half] = lo;
+    }
+  }
+  const float w0 = sw[2 * t], w1 = sw[2 * t + 1];             // this thread's output columns are heads 2t, 2t+1
+  const bf16* kb = keys + (int64_t)b * cap * DI;
+  const float* nb = norms + (int64_t)b * cap;
+  float* lg = logits + (int64_t)b * n_ld;
+  const int wr0 = r0 + warp * (DIX_ROWS / 8);                 // 128 rows per warp, 8 groups of 16
+#pragma unroll 1
+  for (int gi = 0; gi < 8; gi += 2) {
+    uint4 raw[2][4];                                           // [group][row g chunk 0/1, row g+8 chunk 0/1]
+    float nv[2][2];
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      const int rg = wr0 + (gi + u) * 16;
+#pragma unroll
+      for (int hh = 0; hh < 2; ++hh) {
+        const int row = rg + g + 8 * hh;
+        raw[u][2 * hh] = raw[u][2 * hh + 1] = make_uint4(0u, 0u, 0u, 0u);
+        nv[u][hh] = 1.f;
+        if (row < nvis) {
+          const uint4* rp = reinterpret_cast<const uint4*>(kb + (int64_t)row * DI);
+          raw[u][2 * hh] = rp[t];
+          raw[u][2 * hh + 1] = rp[4 + t];
+          if (normalize) nv[u][hh] = nb[row];
+        }
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      const int rg = wr0 + (gi + u) * 16;
+      if (rg >= nvis) break;                                   // warp-uniform
+      float c[4] = {0.f, 0.f, 0.f, 0.f};
+      // a0 = row g, first pair; a1 = row g+8, first pair; a2 = row g, second pair; a3 = row g+8, second pair
+      const uint32_t lo_row[8] = {raw[u][0].x, raw[u][0].y, raw[u][0].z, raw[u][0].w, raw[u][1].x, raw[u][1].y, raw[u][1].z, raw[u][1].w};
+      const uint32_t hi_row[8] = {raw[u][2].x, raw[u][2].y, raw[u][2].z, raw[u][2].w, raw[u][3].x, raw[u][3].y, raw[u][3].z, raw[u][3].w};
+#pragma unroll
+      for (int ks = 0; ks < 4; ++ks) {
+        const uint32_t af[4] = {lo_row[2 * ks], hi_row[2 * ks], lo_row[2 * ks + 1], hi_row[2 * ks + 1]};
+#pragma unroll
+        for (int term = 0; term < 3; ++term) mma_bf16_16816(c, af, qb[ks][term][0], qb[ks][term][1]);
+      }
+      // c0,c1: row rg+g, heads 2t, 2t+1;  c2,c3: row rg+g+8
+      float o0 = fmaxf(c[0] / nv[u][0] * scale, 0.f) * w0 + fmaxf(c[1] / nv[u][0] * scale, 0.f) * w1;
+      float o1 = fmaxf(c[2] / nv[u][1] * scale, 0.f) * w0 + fmaxf(c[3] / nv[u][1] * scale, 0.f) * w1;
+      o0 += __shfl_xor_sync(0xffffffffu, o0, 1); o0 += __shfl_xor_sync(0xffffffffu, o0, 2);
+      o1 += __shfl_xor_sync(0xffffffffu, o1, 1); o1 += __shfl_xor_sync(0xffffffffu, o1, 2);
+      if (t == 0) {
+        if (rg + g < nvis) lg[rg + g] = o0;
+        if (rg + g + 8 < nvis) lg[rg + g + 8] = o1;
+      }
+    }
+  }
+}
+
+extern "C" int64_t kch_decode_indexer_workspace_bytes(int B, int64_t capacity) {
+  if (B < 1 || capacity < 1) return 0;
+  return (int64_t)B * ((capacity + 3) & ~3LL) * 4;
+}
+
+extern "C" int kch_decode_indexer_topk(const void* q_idx, int q_dtype, int64_t q_ld, const void* keys, int k_dtype,
+                                       const float* k_norms, const void* w, int w_dtype, int64_t w_ld,
+                                       int32_t* idx_out, int B, int64_t capacity, int HI, int DI,
+                                       int topk, int normalize, float scale, int m, const int32_t* counters,
+                                       void* workspace, int64_t workspace_bytes, void* stream) {
+  KCH_REQUIRE(topk >= 1, "kch_decode_indexer_topk: topk=%d must be >= 1", topk);
+  KCH_REQUIRE(DI >= 1 && HI >= 1 && HI <= 64 && (int64_t)HI * DI <= DIX_MAX_HD,
+              "kch_decode_indexer_topk: nIh=%d c_I=%d (needs nIh <= 64, nIh*c_I <= 1024)", HI, DI);
+  KCH_REQUIRE(B >= 1 && capacity >= 1 && m >= 1, "kch_decode_indexer_topk: B=%d capacity=%lld m=%d", B, (long long)capacity, m);
+  KCH_REQUIRE(k_dtype == KCH_F32 || k_dtype == KCH_BF16, "kch_decode_indexer_topk: k_dtype=%d", k_dtype);
+  KCH_REQUIRE((q_dtype == KCH_F32 || q_dtype == KCH_BF16) && (!w || w_dtype == KCH_F32 || w_dtype == KCH_BF16),
+              "kch_decode_indexer_topk: q_dtype=%d w_dtype=%d", q_dtype, w_dtype);
+  KCH_REQUIRE(q_ld >= (int64_t)HI * DI && (!w || w_ld >= HI), "kch_decode_indexer_topk: q_ld=%lld w_ld=%lld",
+              (long long)q_ld, (long long)w_ld);
+  KCH_REQUIRE(q_idx && keys && idx_out && counters && (!normalize || k_norms), "kch_decode_indexer_topk: null operand");
+  KCH_REQUIRE(workspace && workspace_bytes >= kch_decode_indexer_workspace_bytes(B, capacity),
+              "kch_decode_indexer_topk: workspace %lld < %lld bytes", (long long)workspace_bytes,
+              (long long)kch_decode_indexer_workspace_bytes(B, capacity));
+  cudaStream_t s = kch_stream(stream);
+  const int64_t n_ld = (capacity + 3) & ~3LL;
+  float* logits = (float*)workspace;
+  dim3 grid((unsigned)((capacity + DIX_ROWS - 1) / DIX_ROWS), B);
+  const int epl = k_dtype == KCH_BF16 ? 8 : 4;
+  const int lpr = DI % epl == 0 ? DI / epl : 0;
+  const bool vec = lpr >= 1 && lpr <= 32 && (lpr & (lpr - 1)) == 0 && ((uintptr_t)keys & 15) == 0;
+#define GO(T_, V_) decode_indexer_logits_kernel<T_, V_><<<grid, 256, 0, s>>>(q_idx, q_dtype, q_ld, (const T_*)keys, k_norms, \
+      w, w_dtype, w_ld, logits, capacity, n_ld, HI, DI, normalize, scale, m, counters)
+  static const bool force_simt = [] { const char* e = getenv("KCH_INDEXER_DECODE"); return e && e[0] == 's'; }();
+  if (!force_simt && k_dtype == KCH_BF16 && DI == 64 && HI <= 8 && ((uintptr_t)keys & 15) == 0)
+    decode_indexer_logits_mma_kernel<<<grid, 256, 0, s>>>(q_idx, q_dtype, q_ld, (const bf16*)keys, k_norms, w, w_dtype, w_ld,
+                                                          logits, capacity, n_ld, HI, normalize, scale, m, counters);
+  else if (k_dtype == KCH_BF16) { if (vec) GO(bf16, true); else GO(bf16, false); }
+  else { if (vec) GO(float, true); else GO(float, false); }
+#undef GO
+  KCH_LAUNCH_OK();
+  // the whole row of logits is staged in shared memory when it fits (one CTA per SM at the largest size)
+  const int cache_cap = (int)(n_ld <= 49152 ? ((n_ld + 255) & ~255LL) : 0);
+  KCH_CUDA_OK(cudaFuncSetAttribute(topk_select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, cache_cap * 4));
+  topk_select_kernel<<<(unsigned)B, 256, (size_t)cache_cap * 4, s>>>(logits, idx_out, 1, (int)capacity, n_ld, topk, m, 0, -1,
+                                                                     0, cache_cap, counters, m);
   KCH_LAUNCH_OK();
   return KCH_OK;
 }

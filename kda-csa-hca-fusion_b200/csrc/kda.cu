@@ -11,12 +11,14 @@
 // split the K rows of the state, which lives in registers for the whole sequence.
 // Per token: S <- diag(exp g) S ; S <- S + beta k (v - k^T S)^T ; o = (scale q)^T S.
 // Decode (T=1) reads and writes the state exactly once: 2*K*V*4 bytes per (b, hv).
+// S0 and S_out may be the same memory: every thread loads its own state elements before the token loop and
+// stores the same elements after it.
 // =====================================================================================
 template <typename T, int KPT>
 __global__ void __launch_bounds__(128)
 kda_recurrent_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v,
                      const T* __restrict__ g, const T* __restrict__ beta,
-                     const float* __restrict__ S0, T* __restrict__ o, float* __restrict__ S_out,
+                     const float* S0, T* __restrict__ o, float* S_out,
                      int T_, int H, int HV, int K, int V, float scale, float g_min, int64_t ld_qk,
                      int64_t ld_v, int64_t ld_g, int64_t ld_b) {
   const int vb = blockIdx.x, hv = blockIdx.y, b = blockIdx.z;

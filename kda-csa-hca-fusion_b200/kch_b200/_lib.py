@@ -42,8 +42,24 @@ class CacheAppendArgs(C.Structure):
                 ("acc_len", _i), ("prev_Cb", _vp), ("prev_Zb", _vp), ("has_prev", _i),
                 ("Ba", _vp), ("Bb", _vp), ("B_idx", _vp),
                 ("comp", _vp), ("comp_kind", _i), ("comp_scales", _vp), ("comp_norms", _vp),
-                ("kcomp", _vp), ("kcomp_normalized", _vp), ("capacity", _i64), ("n_blocks", _i),
-                ("ring", _vp), ("ring_pos", _i), ("normalize", _i)]
+                ("kcomp", _vp), ("kcomp_norms", _vp), ("capacity", _i64), ("n_blocks", _i),
+                ("ring", _vp), ("ring_pos", _i), ("normalize", _i), ("counters", _vp)]
+
+
+class AttendDecodeArgs(C.Structure):
+    _fields_ = [("q", _vp), ("q_dtype", _i), ("q_ld", _i64), ("q_normalize", _i),
+                ("B", _i), ("nh", _i), ("c", _i),
+                ("comp", _vp), ("comp_dtype", _i), ("capacity", _i64), ("comp_norms", _vp), ("comp_scales", _vp),
+                ("sel_indices", _vp), ("topk", _i), ("m", _i),
+                ("win", _vp), ("win_dtype", _i), ("sliding_window", _i),
+                ("sink", _vp), ("sink_dtype", _i), ("scale", _f),
+                ("out", _vp), ("out_dtype", _i),
+                ("counters", _vp), ("workspace", _vp), ("workspace_bytes", _i64)]
+
+
+# indices into a cache's device counters (include/kch_b200.h KCH_CTR_*)
+CTR_ACC_LEN, CTR_N_BLOCKS, CTR_RING_N, CTR_HAS_PREV, CTR_TOKENS, CTR_WORDS = 0, 1, 2, 3, 4, 8
+STATUS_CACHE_CAPACITY = 64
 
 
 # name -> (restype, argtypes); must list every symbol declared in include/kch_b200.h
@@ -70,6 +86,14 @@ PROTOTYPES = {
     "kch_attend": (_i, [C.POINTER(AttendArgs), _vp]),
     "kch_cache_append_token": (_i, [C.POINTER(CacheAppendArgs), _vp]),
     "kch_quantize_rows": (_i, [_vp, _i64, _vp, _vp, _vp, _i64, _i, _i, _i, _vp]),
+    "kch_cache_advance": (_i, [_vp, _i, _vp]),
+    "kch_decode_indexer_workspace_bytes": (_i64, [_i, _i64]),
+    "kch_decode_indexer_topk": (_i, [_vp, _i, _i64, _vp, _i, _vp, _vp, _i, _i64, _vp, _i, _i64, _i, _i, _i, _i, _f, _i, _vp,
+                                     _vp, _i64, _vp]),
+    "kch_short_conv_step": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
+    "kch_attend_decode_splits": (_i, [_i]),
+    "kch_attend_decode_workspace_bytes": (_i64, [_i, _i, _i]),
+    "kch_attend_decode": (_i, [C.POINTER(AttendDecodeArgs), _vp]),
 }
 
 _lib = None

@@ -67,7 +67,91 @@ class _SlidingWindowRingBuffer:
         self._n += Tn
 
 
+def _row_norms(x):
+    """fp32 ``max(||row||, 1e-12)`` of ``x [B,n,c]`` (the divisor the kernels use for a stored row)."""
+    lib = _lib.load()
+    B, n, c = x.shape
+    x = x.contiguous()
+    out = torch.empty(B, n, dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        _lib.check(lib.kch_rownorm(_lib.ptr(x), c, None, _lib.ptr(out), B * n, c, _lib.dtype_tag(x.dtype), _lib.KCH_F32,
+                                   _lib.stream()))
+    return out
+
+
 class _CacheBase:
+    # The counters live twice: Python ints (the reference's interface) and an int32 vector on the device that
+    # the one-token kernels read, so that a decode step has no host argument that changes between tokens.
+    def _init_counters(self):
+        self._ctr = torch.zeros(_lib.CTR_WORDS, dtype=torch.int32, device=self.device)
+        self._ws_attn = None
+        self._ws_idx = None
+
+    def _sync_counters(self):
+        """Host counters -> device mirror (after reset, a bulk append or any direct edit of the counters)."""
+        vals = [0] * _lib.CTR_WORDS
+        vals[_lib.CTR_ACC_LEN] = self._acc_len
+        vals[_lib.CTR_N_BLOCKS] = self._n_blocks
+        vals[_lib.CTR_RING_N] = 0 if self._sw is None else self._sw._n
+        vals[_lib.CTR_HAS_PREV] = int(getattr(self, "_has_prev", False))
+        vals[_lib.CTR_TOKENS] = self._n_tokens_seen
+        self._ctr.copy_(torch.tensor(vals, dtype=torch.int32))
+
+    def _advance(self, m):
+        """The host half of one appended token (the device half is kch_cache_advance)."""
+        if self._sw is not None:
+            self._sw._n += 1
+        self._n_tokens_seen += 1
+        if self._acc_len + 1 == m:
+            self._n_blocks += 1
+            self._acc_len = 0
+            if hasattr(self, "_has_prev"):
+                self._has_prev = True
+        else:
+            self._acc_len += 1
+
+    def _decode_attend_ok(self, nh):
+        return self.c == 128 and nh <= 16
+
+    def _attend_decode(self, q, sel, topk, m, nh, scale, sink, normalize_qk, q_normalize=False, out_dtype=None):
+        """One-token attention over the cache storage with the split kernel; geometry from the device counters.
+        ``q`` may be a row-strided view (a slice of a fused projection) in fp32 or bf16."""
+        lib = _lib.load()
+        B = self.B
+        q2 = q.reshape(B, nh * self.c) if q.is_contiguous() else q.flatten(1)
+        if q2.dim() != 2 or q2.stride(-1) != 1 or (B > 1 and q2.stride(0) < nh * self.c):
+            q2 = q2.contiguous().view(B, nh * self.c)
+        out_dtype = torch.float32 if out_dtype is None else out_dtype
+        need = int(lib.kch_attend_decode_workspace_bytes(B, nh, self.c))
+        if self._ws_attn is None or self._ws_attn.numel() < need:
+            self._ws_attn = torch.empty(need, dtype=torch.uint8, device=self.device)
+        out = torch.empty(B, nh * self.c, dtype=out_dtype, device=self.device)
+        a = _lib.AttendDecodeArgs()
+        a.q, a.q_dtype, a.q_normalize = q2.data_ptr(), _lib.dtype_tag(q2.dtype), int(q_normalize)
+        a.q_ld = q2.stride(0) if B > 1 else nh * self.c
+        a.B, a.nh, a.c = B, nh, self.c
+        if self._comp is not None:
+            a.comp = self._comp.data_ptr()
+            a.comp_dtype = self._kind if self._kind is not None else _lib.dtype_tag(self.dtype)
+            a.capacity = self._comp.shape[1]
+            a.comp_norms = self._norms.data_ptr() if normalize_qk else None
+            a.comp_scales = None if self._scales is None else self._scales.data_ptr()
+            if sel is not None:
+                a.sel_indices, a.topk = sel.data_ptr(), int(topk)
+        a.m = int(m)
+        if self._sw is not None:
+            a.win, a.win_dtype, a.sliding_window = self._sw._buf.data_ptr(), _lib.dtype_tag(self._sw.dtype), self.win
+        if sink is not None:
+            sk = sink if sink.is_contiguous() else sink.contiguous()
+            a.sink, a.sink_dtype = sk.data_ptr(), _lib.dtype_tag(sk.dtype)
+        a.scale = float(scale)
+        a.out, a.out_dtype = out.data_ptr(), _lib.dtype_tag(out_dtype)
+        a.counters = self._ctr.data_ptr()
+        a.workspace, a.workspace_bytes = self._ws_attn.data_ptr(), self._ws_attn.numel()
+        with torch.cuda.device(self.device):
+            _lib.check(lib.kch_attend_decode(a, _lib.stream()))
+        return out
+
     def _alloc_rows(self, cap):
         B, c, dev = self.B, self.c, self.device
         if self._kind is None:
@@ -179,18 +263,20 @@ class CSADecodingCache(_CacheBase):
         self._prev = [torch.zeros(B, m, c, dtype=dt, device=dev) for _ in range(2)]
         self._has_prev = False
         self._comp = self._scales = self._norms = None
-        self._kcomp = self._kcomp_n = None
+        self._kcomp = self._kcomp_norms = None
         self._sw = _SlidingWindowRingBuffer(B, self.win, c, dev, dt) if self.win > 0 else None
         self._n_tokens_seen = 0
         self._n_blocks = 0
+        self._init_counters()
 
     def _grow_extra(self, cap, nb):
         k = torch.empty(self.B, cap, self.c_I, dtype=self.dtype, device=self.device)
-        kn = torch.empty(self.B, cap, self.c_I, dtype=torch.float32, device=self.device)
+        kn = torch.ones(self.B, cap, dtype=torch.float32, device=self.device)
         if nb:
             k[:, :nb] = self._kcomp[:, :nb]
-            kn[:, :nb] = self._kcomp_n[:, :nb]
-        self._kcomp, self._kcomp_n = k, kn
+            kn[:, :nb] = self._kcomp_norms[:, :nb]
+        self._kcomp, self._kcomp_norms = k, kn
+        self._ws_idx = None
 
     # ---- properties of the reference object --------------------------------------------------------
     @property
@@ -254,9 +340,7 @@ class CSADecodingCache(_CacheBase):
     def _append_one(self, new, biases):
         lib = _lib.load()
         m = self.m
-        closes = self._acc_len + 1 == m
-        if closes:
-            self._grow(self._n_blocks + 1)
+        self._grow(self._n_blocks + 1)      # the kernel learns on the device whether this token closes a block
         a = _lib.CacheAppendArgs()
         a.B, a.c, a.c_I, a.m, a.win, a.dtype = self.B, self.c, self.c_I, m, self.win, _lib.dtype_tag(self.dtype)
         rows = [x[:, 0] for x in new]
@@ -276,24 +360,18 @@ class CSADecodingCache(_CacheBase):
             a.comp = self._comp.data_ptr()
             a.comp_scales = None if self._scales is None else self._scales.data_ptr()
             a.comp_norms = self._norms.data_ptr()
-            a.kcomp, a.kcomp_normalized = self._kcomp.data_ptr(), self._kcomp_n.data_ptr()
+            a.kcomp, a.kcomp_norms = self._kcomp.data_ptr(), self._kcomp_norms.data_ptr()
             a.capacity = self._comp.shape[1]
         a.comp_kind = self._kind if self._kind is not None else _lib.dtype_tag(self.dtype)
         a.n_blocks = self._n_blocks
         if self._sw is not None:
             a.ring, a.ring_pos = self._sw._buf.data_ptr(), self._sw._n % self.win
         a.normalize = int(self._normalize_qk)
+        a.counters = self._ctr.data_ptr()
         with torch.cuda.device(self.device):
             _lib.check(lib.kch_cache_append_token(a, _lib.stream()))
-        if self._sw is not None:
-            self._sw._n += 1
-        self._n_tokens_seen += 1
-        if closes:
-            self._n_blocks += 1
-            self._has_prev = True
-            self._acc_len = 0
-        else:
-            self._acc_len += 1
+            _lib.check(lib.kch_cache_advance(self._ctr.data_ptr(), m, _lib.stream()))
+        self._advance(m)
 
     def _append_many(self, new, biases):
         m, T_new = self.m, new[0].shape[1]
@@ -314,7 +392,7 @@ class CSADecodingCache(_CacheBase):
             self._store_rows(rows, self._n_blocks)
             krows = csa_compress_kv(full[4], full[5], biases[2], m).to(self.dtype)
             self._kcomp[:, self._n_blocks:self._n_blocks + nb] = krows
-            self._kcomp_n[:, self._n_blocks:self._n_blocks + nb] = rownorm(krows, self._normalize_qk)
+            self._kcomp_norms[:, self._n_blocks:self._n_blocks + nb] = _row_norms(krows)
             self._prev[0].copy_(full[1][:, -m:])
             self._prev[1].copy_(full[3][:, -m:])
             self._has_prev = True
@@ -325,10 +403,12 @@ class CSADecodingCache(_CacheBase):
                 a[:, :rest] = s[:, nb * m:]
         self._acc_len = rest
         self._n_tokens_seen += T_new
+        self._sync_counters()
 
     # ---- attend -----------------------------------------------------------------------------------------
     def forward_step(self, q, q_idx, w_idx, *, topk, nh, nIh, scale=None, sink_logits=None, use_ste=True,
-                     ste_mode="topk_columns", normalize_qk=True, _return_indices=False):
+                     ste_mode="topk_columns", normalize_qk=True, _return_indices=False, _q_normalize=False,
+                     _out_dtype=None):
         B, T_new = q.shape[0], q.shape[1]
         if T_new != 1:
             raise ValueError(f"CSADecodingCache.forward_step: T_new={T_new} must be 1. For multi-token chunks, "
@@ -350,47 +430,59 @@ class CSADecodingCache(_CacheBase):
         nb = self._n_blocks
         nvis = min((t + 1) // self.m, nb)
         sel = None
-        if nb > 0 and topk > 0:
-            if normalize_qk == self._normalize_qk:
-                # the fp32 scoring copy was prepared at append time in this mode: read it in place
-                sel = _indexer_on_cache(q_idx, self._kcomp_n, nb, w_idx, topk, nvis, normalize_qk,
-                                        self._kcomp_n.shape[1] * self.c_I)
-            else:
-                sel = indexer_topk(q_idx.float(), self._kcomp[:, :nb].float().contiguous(), w_idx.float(), topk,
-                                   n_visible=nvis, normalize_qk=normalize_qk, sorted_output=False)
+        if topk > 0 and self._kcomp is not None and nIh <= 64 and nIh * self.c_I <= 1024:
+            # stored keys + their norms are scored in place; row count and visible prefix come from the device counters
+            sel = self._indexer_decode(q_idx, w_idx, topk, normalize_qk)
+        elif nb > 0 and topk > 0:
+            sel = indexer_topk(q_idx.float(), self._kcomp[:, :nb].float().contiguous(), w_idx.float(), topk,
+                               n_visible=nvis, normalize_qk=normalize_qk, sorted_output=False)
         elif topk > 0:
             sel = torch.full((B, 1, topk), -1, dtype=torch.int32, device=self.device)
         if topk == 0:
             out = self._attend_no_comp(q, nh, core_scale, sink_logits)
+        elif self._decode_attend_ok(nh) and self._comp is not None:
+            out = self._attend_decode(q, sel, topk, self.m, nh, core_scale, sink_logits, normalize_qk,
+                                      q_normalize=_q_normalize, out_dtype=_out_dtype)
         else:
+            if _q_normalize:
+                q = rownorm(q.contiguous(), True)
             out = self._attend(q.float(), sel, nvis, nh, core_scale, sink_logits, normalize_qk)
+            if _out_dtype is not None:
+                out = out.to(_out_dtype)
         out = out.reshape(B, 1, nh, self.c)
         return (out, sel) if _return_indices else out
+
+    def _indexer_decode(self, q_idx, w_idx, topk, normalize_qk):
+        lib = _lib.load()
+        B, _, HI, DI = q_idx.shape
+        cap = self._kcomp.shape[1]
+        need = int(lib.kch_decode_indexer_workspace_bytes(B, cap))
+        if self._ws_idx is None or self._ws_idx.numel() < need:
+            self._ws_idx = torch.empty(need, dtype=torch.uint8, device=self.device)
+        def rows(x, width):          # [B, width] view with unit inner stride (a projection slice is fine as it is)
+            x2 = x.reshape(B, width) if x.is_contiguous() else x.flatten(1)
+            if x2.dtype not in (torch.float32, torch.bfloat16):
+                x2 = x2.float()
+            if x2.stride(-1) != 1 or (B > 1 and x2.stride(0) < width):
+                x2 = x2.contiguous()
+            return x2, (x2.stride(0) if B > 1 else width)
+        qf, q_ld = rows(q_idx, HI * DI)
+        wf, w_ld = (None, 0) if w_idx is None else rows(w_idx, HI)
+        idx = torch.empty(B, 1, topk, dtype=torch.int32, device=self.device)
+        scale = 1.0 if normalize_qk else DI ** -0.5
+        with torch.cuda.device(self.device):
+            _lib.check(lib.kch_decode_indexer_topk(
+                _lib.ptr(qf), _lib.dtype_tag(qf.dtype), q_ld, _lib.ptr(self._kcomp), _lib.dtype_tag(self.dtype),
+                _lib.ptr(self._kcomp_norms), _lib.ptr(wf), 0 if wf is None else _lib.dtype_tag(wf.dtype), w_ld,
+                _lib.ptr(idx), B, cap, HI, DI, int(topk), int(normalize_qk), scale, self.m, self._ctr.data_ptr(),
+                _lib.ptr(self._ws_idx), self._ws_idx.numel(), _lib.stream()))
+        return idx
 
     def _attend_no_comp(self, q, nh, scale, sink):
         win_len = 0 if self._sw is None else self._sw.n_valid
         return attend(q.float(), None, nh=nh, c=self.c, sel=None, n_visible=0, q_normalize=False,
                       win=None if self._sw is None else self._sw._buf, sliding_window=self.win, win_mode=1,
                       win_len=win_len, sink=sink, scale=scale, out_dtype=torch.float32)
-
-
-def _indexer_on_cache(q_idx, kcomp_n, nb, w_idx, topk, nvis, normalize_qk, kbs):
-    """Indexer over the first ``nb`` rows of the cache's fp32 scoring copy, read in place."""
-    lib = _lib.load()
-    B, T, HI, DI = q_idx.shape
-    dev = q_idx.device
-    qn = rownorm(q_idx.float().contiguous(), normalize_qk).contiguous()
-    wf = None if w_idx is None else w_idx.float().contiguous()
-    idx = torch.empty(B, T, topk, dtype=torch.int32, device=dev)
-    # logits only: a single query row per sequence does not amortise pre-splitting the whole key cache
-    nbytes = B * T * ((nb + 3) // 4 * 4) * 4
-    ws = torch.empty(max(nbytes, 1), dtype=torch.uint8, device=dev)
-    scale = 1.0 if normalize_qk else DI ** -0.5
-    with torch.cuda.device(dev):
-        _lib.check(lib.kch_indexer_topk(_lib.ptr(qn), _lib.ptr(kcomp_n), _lib.ptr(wf), _lib.ptr(idx), B, T, nb, HI, DI,
-                                        int(topk), scale, 0, 0, int(nvis), 0, int(kbs), _lib.ptr(ws), nbytes,
-                                        _lib.stream()))
-    return idx
 
 
 class HCADecodingCache(_CacheBase):
@@ -426,6 +518,7 @@ class HCADecodingCache(_CacheBase):
         self._sw = _SlidingWindowRingBuffer(B, self.win, c, dev, dt) if self.win > 0 else None
         self._n_tokens_seen = 0
         self._n_blocks = 0
+        self._init_counters()
 
     @property
     def n_tokens_seen(self):
@@ -478,9 +571,7 @@ class HCADecodingCache(_CacheBase):
     def _append_one(self, new, bias):
         lib = _lib.load()
         m = self.m2
-        closes = self._acc_len + 1 == m
-        if closes:
-            self._grow(self._n_blocks + 1)
+        self._grow(self._n_blocks + 1)
         a = _lib.CacheAppendArgs()
         a.B, a.c, a.c_I, a.m, a.win, a.dtype = self.B, self.c, 0, m, self.win, _lib.dtype_tag(self.dtype)
         rows = [x[:, 0] for x in new]
@@ -504,16 +595,11 @@ class HCADecodingCache(_CacheBase):
         if self._sw is not None:
             a.ring, a.ring_pos = self._sw._buf.data_ptr(), self._sw._n % self.win
         a.normalize = int(self._normalize_qk)
+        a.counters = self._ctr.data_ptr()
         with torch.cuda.device(self.device):
             _lib.check(lib.kch_cache_append_token(a, _lib.stream()))
-        if self._sw is not None:
-            self._sw._n += 1
-        self._n_tokens_seen += 1
-        if closes:
-            self._n_blocks += 1
-            self._acc_len = 0
-        else:
-            self._acc_len += 1
+            _lib.check(lib.kch_cache_advance(self._ctr.data_ptr(), m, _lib.stream()))
+        self._advance(m)
 
     def _append_many(self, new, bias):
         m, T_new = self.m2, new[0].shape[1]
@@ -536,8 +622,10 @@ class HCADecodingCache(_CacheBase):
                 a[:, :rest] = s[:, nb * m:]
         self._acc_len = rest
         self._n_tokens_seen += T_new
+        self._sync_counters()
 
-    def forward_step(self, q, *, nh, scale=None, sink_logits=None, normalize_qk=True):
+    def forward_step(self, q, *, nh, scale=None, sink_logits=None, normalize_qk=True, _q_normalize=False,
+                     _out_dtype=None):
         B, T_new = q.shape[0], q.shape[1]
         if T_new != 1:
             raise ValueError(f"HCADecodingCache.forward_step: T_new={T_new} must be 1.")
@@ -551,5 +639,13 @@ class HCADecodingCache(_CacheBase):
         core_scale = (1.0 if normalize_qk else self.c ** -0.5) if scale is None else float(scale)
         t = self._n_tokens_seen - 1
         nvis = min((t + 1) // self.m2, self._n_blocks)
-        out = self._attend(q.float(), None, nvis, nh, core_scale, sink_logits, normalize_qk)
+        if self._decode_attend_ok(nh) and self._comp is not None:
+            out = self._attend_decode(q, None, 0, self.m2, nh, core_scale, sink_logits, normalize_qk,
+                                      q_normalize=_q_normalize, out_dtype=_out_dtype)
+        else:
+            if _q_normalize:
+                q = rownorm(q.contiguous(), True)
+            out = self._attend(q.float(), None, nvis, nh, core_scale, sink_logits, normalize_qk)
+            if _out_dtype is not None:
+                out = out.to(_out_dtype)
         return out.reshape(B, 1, nh, self.c)

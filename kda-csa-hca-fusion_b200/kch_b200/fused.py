@@ -121,6 +121,22 @@ def short_conv(x, weight, bias, lookback=None):
     return y
 
 
+def short_conv_step(x, weight, bias, lookback):
+    """One-token conv step: x ``[B,1,d]``; ``lookback [B,2,d]`` (same dtype, contiguous) slides by one token in place."""
+    lib = _lib.load()
+    B, T, d = x.shape
+    if T != 1 or lookback.dtype != x.dtype or not lookback.is_contiguous() or tuple(lookback.shape) != (B, 2, d):
+        raise ValueError("short_conv_step: needs x [B,1,d] and a contiguous lookback [B,2,d] of the same dtype")
+    x = x.contiguous()
+    w = weight.reshape(d, 3).to(x.dtype).contiguous()
+    b = bias.to(x.dtype).contiguous()
+    y = torch.empty_like(x)
+    with torch.cuda.device(x.device):
+        _lib.check(lib.kch_short_conv_step(_lib.ptr(x), _lib.ptr(lookback), _lib.ptr(w), _lib.ptr(b), _lib.ptr(y), B, d,
+                                           _lib.dtype_tag(x.dtype), _lib.stream()))
+    return y
+
+
 def activation(x, act, *, param=0.0, group=1):
     """Activation with the reference's rounding points on a ``[..., cols]`` view (row-strided ok)."""
     lib = _lib.load()
@@ -178,30 +194,46 @@ class KDAHybridLayer(nn.Module):
         self.register_buffer("scale", torch.tensor(K ** -0.5), persistent=False)
         self._conv_lookback = None
         self._fused = _FusedWeights()
+        self._scale_cache = None
         self.tp = None              # TPContext when heads are sharded across GPUs
+
+    def _scale_value(self):
+        """The `scale` buffer as a Python float, read from the device once per dtype / device (the buffer is
+        cast with the module, so the value is the one the reference passes, ops_fused.py:602)."""
+        key = (self.scale.dtype, self.scale.device)
+        if self._scale_cache is None or self._scale_cache[0] != key:
+            self._scale_cache = (key, float(self.scale))
+        return self._scale_cache[1]
 
     def reset_conv_state(self):
         self._conv_lookback = None
 
-    def forward(self, x, state=None, residual=None):
-        o, new_state, lb = self.forward_functional(x, state, self._conv_lookback, residual=residual)
+    def forward(self, x, state=None, residual=None, state_out=None, lookback_in_place=False):
+        o, new_state, lb = self.forward_functional(x, state, self._conv_lookback, residual=residual,
+                                                   state_out=state_out, lookback_in_place=lookback_in_place)
         self._conv_lookback = lb
         return o, new_state
 
-    def project(self, x, conv_lookback):
-        """conv + fused projection + activations -> (q, k, v, g, beta, new_lookback)."""
+    def project(self, x, conv_lookback, lookback_in_place=False):
+        """conv + fused projection + activations -> (q, k, v, g, beta, new_lookback).  With
+        ``lookback_in_place`` a one-token call slides ``conv_lookback`` where it lies and returns it."""
         cfg = self.cfg
         B, T, d = x.shape
         H, HV, K, V = cfg.n_heads_qk, cfg.n_heads_v, cfg.head_dim_k, cfg.head_dim_v
         lb = conv_lookback
         if lb is not None and lb.shape[0] != B:
             lb = None
-        xc = short_conv(x, self.short_conv.weight, self.short_conv.bias, lb)
-        if T >= 2:
-            new_lb = x[:, -2:].clone()
+        if (lookback_in_place and T == 1 and lb is not None and lb.dtype == x.dtype and lb.is_contiguous()
+                and tuple(lb.shape) == (B, 2, d)):
+            xc = short_conv_step(x, self.short_conv.weight, self.short_conv.bias, lb)
+            new_lb = lb
         else:
-            prev = lb if lb is not None else x.new_zeros(B, 2, d)
-            new_lb = torch.cat([prev.to(x.dtype), x], dim=1)[:, -2:].clone()
+            xc = short_conv(x, self.short_conv.weight, self.short_conv.bias, lb)
+            if T >= 2:
+                new_lb = x[:, -2:].clone()
+            else:
+                prev = lb if lb is not None else x.new_zeros(B, 2, d)
+                new_lb = torch.cat([prev.to(x.dtype), x], dim=1)[:, -2:].clone()
         W = self._fused.get(self.q_proj.weight, self.k_proj.weight, self.v_proj.weight, self.g_down.weight,
                             self.beta.weight)
         # one GEMM for q|k|v|g_down|beta with the activations of ops_fused.py:571-581 applied in its epilogue
@@ -215,15 +247,16 @@ class KDAHybridLayer(nn.Module):
         return (q.unflatten(-1, (H, K)), k.unflatten(-1, (H, K)), v.unflatten(-1, (HV, V)),
                 g.view(B, T, HV, K), beta, new_lb)
 
-    def forward_functional(self, x, state, conv_lookback, *, detach_lookback=True, residual=None):
+    def forward_functional(self, x, state, conv_lookback, *, detach_lookback=True, residual=None, state_out=None,
+                           lookback_in_place=False):
         cfg = self.cfg
         B, T, _ = x.shape
         HV, V = cfg.n_heads_v, cfg.head_dim_v
-        q, k, v, g, beta, new_lb = self.project(x, conv_lookback)
+        q, k, v, g, beta, new_lb = self.project(x, conv_lookback, lookback_in_place)
         use_chunk = cfg.kda_chunk_size >= 1 and T >= cfg.kda_chunk_size
-        o, new_state = kda_forward(q, k, v, g, beta, scale=self.scale, initial_state=state,
+        o, new_state = kda_forward(q, k, v, g, beta, scale=self._scale_value(), initial_state=state,
                                    output_final_state=True, chunk_size=cfg.kda_chunk_size, use_chunk=use_chunk,
-                                   backend=cfg.kda_backend)
+                                   backend=cfg.kda_backend, state_out=None if use_chunk else state_out)
         o = gather_heads(o.reshape(B, T, HV * V), self.tp)
         out = linear(o, self.o_proj.weight, residual=residual)
         return out, new_state, new_lb
@@ -395,7 +428,7 @@ class HybridDecoding(nn.Module):
     through them; KDA layers carry their recurrent state and conv lookback."""
 
     def __init__(self, cfg: HybridConfig | None = None, total_layers: int = 5, *, model=None, kv_quant=None,
-                 reserve_tokens: int = 0):
+                 reserve_tokens: int = 0, use_cuda_graph: bool = False):
         super().__init__()
         if model is None:
             model = HybridKCHAttention(cfg, total_layers)
@@ -403,11 +436,17 @@ class HybridDecoding(nn.Module):
         self.cfg = model.cfg
         self.kv_quant = kv_quant
         self.reserve_tokens = reserve_tokens
+        # one-token steps are replayed from a captured CUDA graph once a first step has run eagerly; every
+        # per-token quantity the kernels need is on the device (cache counters), so the launch arguments are static
+        self.use_cuda_graph = use_cuda_graph
         self._caches = {}
+        self._graph = None
+        self._eager_token_steps = 0
 
     def reset(self):
         self.model.reset_state()
         self._caches = {}
+        self._graph = None
 
     def _cache(self, i, layer, h):
         cfg, B = self.cfg, h.shape[0]
@@ -441,10 +480,19 @@ class HybridDecoding(nn.Module):
             qq = linear(cQ, layer.q_weight())
             q, q_idx = qq[..., :nh * c + nIh * cI].split([nh * c, nIh * cI], dim=-1)
             cache.append_step(Ca, Cb, Za, Zb, K_idx, Z_idx, layer.Ba, layer.Bb, layer.B_idx)
-            qn = rownorm(q.contiguous().view(B, 1, nh, c), True)
-            o = cache.forward_step(qn, q_idx.contiguous().view(B, 1, nIh, cI).float(), w_idx.float(), topk=cfg.csa_topk,
-                                   nh=nh, nIh=nIh, scale=1.0, sink_logits=layer.sink, use_ste=False, normalize_qk=True)
-            o_core = o.reshape(B, 1, nh * c).to(h.dtype)
+            if cache._decode_attend_ok(nh):
+                # the decode kernels read the projection slices where they lie, normalise the query themselves
+                # and write the layer dtype: the same arithmetic as the chain below without its glue launches
+                o = cache.forward_step(q.unflatten(-1, (nh, c)), q_idx.unflatten(-1, (nIh, cI)), w_idx, topk=cfg.csa_topk,
+                                       nh=nh, nIh=nIh, scale=1.0, sink_logits=layer.sink, use_ste=False,
+                                       normalize_qk=True, _q_normalize=True, _out_dtype=h.dtype)
+                o_core = o.reshape(B, 1, nh * c)
+            else:
+                qn = rownorm(q.contiguous().view(B, 1, nh, c), True)
+                o = cache.forward_step(qn, q_idx.contiguous().view(B, 1, nIh, cI).float(), w_idx.float(),
+                                       topk=cfg.csa_topk, nh=nh, nIh=nIh, scale=1.0, sink_logits=layer.sink,
+                                       use_ste=False, normalize_qk=True)
+                o_core = o.reshape(B, 1, nh * c).to(h.dtype)
         return linear(gather_heads(o_core, layer.tp), layer.o_proj.weight, residual=residual)
 
     def _hca(self, i, layer, h, residual):
@@ -460,13 +508,89 @@ class HybridDecoding(nn.Module):
             C, Z, cQ = proj[..., :2 * c + dc].split([c, c, dc], dim=-1)
             q = linear(cQ, layer.W_UQ.weight)
             cache.append_step(C, Z, layer.B_pos)
-            qn = rownorm(q.view(B, 1, nh, c), True)
-            o = cache.forward_step(qn, nh=nh, scale=1.0, sink_logits=layer.sink)
-            o_core = o.reshape(B, 1, nh * c).to(h.dtype)
+            if cache._decode_attend_ok(nh):
+                o = cache.forward_step(q.view(B, 1, nh, c), nh=nh, scale=1.0, sink_logits=layer.sink, _q_normalize=True,
+                                       _out_dtype=h.dtype)
+                o_core = o.reshape(B, 1, nh * c)
+            else:
+                qn = rownorm(q.view(B, 1, nh, c), True)
+                o = cache.forward_step(qn, nh=nh, scale=1.0, sink_logits=layer.sink)
+                o_core = o.reshape(B, 1, nh * c).to(h.dtype)
         return linear(gather_heads(o_core, layer.tp), layer.o_proj.weight, residual=residual)
+
+    # ---- CUDA-graph replay of one-token steps ------------------------------------------------------------------
+    def _graph_signature(self, x):
+        """What a captured step depends on besides the data: the addresses of every state tensor it updates in
+        place.  None when a step cannot be replayed (no state yet, or a geometry served by host-counter kernels)."""
+        model, cfg = self.model, self.cfg
+        st = model._kda_state
+        if model.n_kda_layers and (st is None or st.shape[1] != x.shape[0] or st.dtype != torch.float32
+                                   or not st.is_contiguous() or cfg.kda_chunk_size == 1):
+            return None
+        sig = [x.shape[0], x.dtype, 0 if st is None else st.data_ptr()]
+        for i, (layer, kind) in enumerate(zip(model.layers, model.layout)):
+            if layer.tp is not None and layer.tp.world > 1:
+                return None                                    # the head all-gather is launched eagerly
+            if kind == "kda":
+                lb = layer._conv_lookback
+                if lb is None or lb.shape[0] != x.shape[0] or lb.dtype != x.dtype:
+                    return None
+                sig.append(lb.data_ptr())
+                continue
+            cache = self._caches.get(i)
+            nh = cfg.csa_nh if kind == "csa" else cfg.hca_nh
+            if cache is None or cache.B != x.shape[0] or cache._comp is None or not cache._decode_attend_ok(nh):
+                return None
+            if kind == "csa" and (cfg.csa_nIh > 64 or cfg.csa_nIh * cfg.csa_cI > 1024 or cfg.csa_topk < 1):
+                return None
+            if cache._n_blocks + 1 > cache._comp.shape[1]:
+                cache.reserve(2 * cache._comp.shape[1])        # grow outside the graph; forces a re-capture
+            sig.extend([cache._comp.data_ptr(), cache._ctr.data_ptr(), cache._n_blocks >= 0])
+        return tuple(sig)
+
+    def _host_counters(self):
+        return [(c._acc_len, c._n_blocks, c._n_tokens_seen, getattr(c, "_has_prev", None),
+                 None if c._sw is None else c._sw._n) for c in self._caches.values()]
+
+    def _restore_host_counters(self, saved):
+        for c, (acc, nb, nt, hp, rn) in zip(self._caches.values(), saved):
+            c._acc_len, c._n_blocks, c._n_tokens_seen = acc, nb, nt
+            if hp is not None:
+                c._has_prev = hp
+            if rn is not None:
+                c._sw._n = rn
+
+    def _graph_step(self, x, sig):
+        if self._graph is None or self._graph[0] != sig:
+            # capture records the launches without running them: the host counters the Python path advanced
+            # are put back, the device state is untouched, and the first replay below performs the step
+            x_static = x.clone()
+            saved = self._host_counters()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, capture_error_mode="thread_local"):
+                y_static = self._forward_eager(x_static)
+            self._restore_host_counters(saved)
+            self._graph = (sig, graph, x_static, y_static)
+        _, graph, x_static, y_static = self._graph
+        x_static.copy_(x)
+        graph.replay()
+        for i, cache in self._caches.items():
+            cache._advance(cache.m if hasattr(cache, "m") else cache.m2)
+        return y_static.clone()
 
     @torch.no_grad()
     def forward(self, x):
+        B, T, _ = x.shape
+        if T == 1 and self.use_cuda_graph and self._eager_token_steps >= 1:
+            sig = self._graph_signature(x)
+            if sig is not None:
+                return self._graph_step(x, sig)
+        if T == 1:
+            self._eager_token_steps += 1       # every kernel of the step is loaded before a capture is attempted
+        return self._forward_eager(x)
+
+    @torch.no_grad()
+    def _forward_eager(self, x):
         model = self.model
         B, T, _ = x.shape
         stacked = model._kda_state
@@ -474,19 +598,25 @@ class HybridDecoding(nn.Module):
             states = list(stacked.unbind(0))
         else:
             states = [None] * model.n_kda_layers
+            stacked = None
+        # a one-token step on an existing fp32 state updates it where it lies (no copy of the 3 x B x HV x K x V state)
+        in_place = (T == 1 and stacked is not None and stacked.dtype == torch.float32 and stacked.is_contiguous()
+                    and stacked.device == x.device and model.cfg.kda_chunk_size != 1)
         ki = 0
         for i, (layer, norm, kind) in enumerate(zip(model.layers, model.norms, model.layout)):
             if T == 0:
                 continue
             h = norm(x)
             if kind == "kda":
-                x, st = layer(h, states[ki], residual=x)
+                # in place: the state and the conv lookback keep their addresses from token to token
+                x, st = layer(h, states[ki], residual=x, state_out=states[ki] if in_place else None,
+                              lookback_in_place=in_place)
                 states[ki] = st
                 ki += 1
             elif kind == "csa":
                 x = self._csa(i, layer, h, x)
             else:
                 x = self._hca(i, layer, h, x)
-        if T > 0:
+        if T > 0 and not in_place:
             model._kda_state = torch.stack(states, dim=0) if model.n_kda_layers > 0 else None
         return x

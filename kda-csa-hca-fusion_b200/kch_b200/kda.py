@@ -92,7 +92,7 @@ def _scale_value(scale, K):
 
 
 def _run(fn_name, q, k, v, g, beta, scale, initial_state, output_final_state, g_clamp_min, state_dtype,
-         chunk_size):
+         chunk_size, state_out=None):
     _validate_inputs(q, k, v, g, beta, fn_name)
     _validate_shapes(q, k, v, g, beta, fn_name, chunk_size)
     _lib.require_cuda(q, fn=fn_name)
@@ -111,7 +111,17 @@ def _run(fn_name, q, k, v, g, beta, scale, initial_state, output_final_state, g_
             raise ValueError(f"{fn_name}: initial_state.shape={tuple(S0.shape)} must be (B, HV, K, V)="
                              f"({B}, {HV}, {K}, {V})")
     o = torch.empty(B, T, HV, V, dtype=v.dtype, device=q.device)
-    S = torch.empty(B, HV, K, V, dtype=torch.float32, device=q.device) if output_final_state else None
+    S = None
+    if output_final_state:
+        if state_out is not None:
+            # caller-owned fp32 state buffer; may be the same memory as `initial_state` (decode updates in place)
+            if (state_out.dtype != torch.float32 or tuple(state_out.shape) != (B, HV, K, V)
+                    or not state_out.is_contiguous() or state_out.device != q.device):
+                raise ValueError(f"{fn_name}: state_out must be a contiguous fp32 ({B}, {HV}, {K}, {V}) tensor on "
+                                 f"{q.device}")
+            S = state_out
+        else:
+            S = torch.empty(B, HV, K, V, dtype=torch.float32, device=q.device)
     gmin = float(g_clamp_min) if g_clamp_min > -math.inf else -math.inf
     sc = _scale_value(scale, K)
     with torch.cuda.device(q.device):
@@ -132,11 +142,13 @@ def _run(fn_name, q, k, v, g, beta, scale, initial_state, output_final_state, g_
 
 
 def naive_recurrent_kda(q, k, v, g, beta, scale=None, initial_state=None, output_final_state=False, *,
-                        g_clamp_min: float = -10.0, state_dtype=None):
+                        g_clamp_min: float = -10.0, state_dtype=None, state_out=None):
     """Token-by-token KDA.  q,k ``[B,T,H,K]``; v ``[B,T,HV,V]``; g ``[B,T,HV,K]``; beta ``[B,T,HV]``;
-    ``initial_state [B,HV,K,V]``.  Returns ``(o [B,T,HV,V] in v.dtype, final state or None)``."""
+    ``initial_state [B,HV,K,V]``.  Returns ``(o [B,T,HV,V] in v.dtype, final state or None)``.
+    ``state_out`` (not in the reference) names an fp32 buffer to receive the final state; it may be the
+    ``initial_state`` tensor itself, which makes a decode step update its state in place."""
     return _run("naive_recurrent_kda", q, k, v, g, beta, scale, initial_state, output_final_state,
-                g_clamp_min, state_dtype, None)
+                g_clamp_min, state_dtype, None, state_out)
 
 
 def naive_chunk_kda(q, k, v, g, beta, scale=None, initial_state=None, output_final_state=False,
@@ -156,7 +168,7 @@ def validate_kda_backend(backend: str) -> str:
 
 def kda_forward(q, k, v, g, beta, *, scale=None, initial_state=None, output_final_state=False,
                 chunk_size: int = 64, use_chunk: bool = False, g_clamp_min: float = -10.0,
-                backend: str = "b200"):
+                backend: str = "b200", state_out=None):
     """Dispatcher with the keyword contract of ``ops_kda_backend.kda_forward``; only ``backend='b200'``
     exists here (no Triton, no FLA, no CPU path)."""
     validate_kda_backend(backend)
@@ -172,7 +184,7 @@ def kda_forward(q, k, v, g, beta, *, scale=None, initial_state=None, output_fina
                                output_final_state=output_final_state, chunk_size=chunk_size,
                                g_clamp_min=g_clamp_min)
     return naive_recurrent_kda(q, k, v, g, beta, scale=scale, initial_state=initial_state,
-                               output_final_state=output_final_state, g_clamp_min=g_clamp_min)
+                               output_final_state=output_final_state, g_clamp_min=g_clamp_min, state_out=state_out)
 
 
 def warn_if_nonfinite(o, fn_name):

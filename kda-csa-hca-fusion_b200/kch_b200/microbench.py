@@ -5,6 +5,7 @@
     python -m kch_b200.microbench csa_attend --B 1 --T 4096 --topk 1024
     python -m kch_b200.microbench compress --B 4 --T 32768
     python -m kch_b200.microbench indexer --B 1 --T 4096
+    python -m kch_b200.microbench decode --B 64 --T 131072 --iters 4 [--kv-quant fp8]
 
 Each prints one JSON line with the average launch time and the achieved algorithmic rate.  Inputs are
 seeded synthetic tensors of the benchmark geometry (K=V=c=128, 16 heads, m=4, 4x64 indexer).
@@ -23,16 +24,23 @@ if _HERE not in sys.path:
     sys.path.insert(0, _HERE)
 
 
+_PROFILE = False
+
+
 def _time(fn, iters, warmup):
     for _ in range(warmup):
         fn()
     torch.cuda.synchronize()
+    if _PROFILE:        # `ncu --profile-from-start off` then sees the timed iterations only
+        torch.cuda.profiler.start()
     a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     a.record()
     for _ in range(iters):
         fn()
     b.record()
     torch.cuda.synchronize()
+    if _PROFILE:
+        torch.cuda.profiler.stop()
     return a.elapsed_time(b) / iters
 
 
@@ -42,7 +50,7 @@ def main():
 
     ap = argparse.ArgumentParser()
     ap.add_argument("kernel", choices=["linear", "kda_chunk", "kda_recurrent", "csa_attend", "hca_attend", "compress",
-                                       "indexer"])
+                                       "indexer", "decode"])
     ap.add_argument("--M", type=int, default=16384)
     ap.add_argument("--N", type=int, default=2048)
     ap.add_argument("--K", type=int, default=2048)
@@ -52,7 +60,12 @@ def main():
     ap.add_argument("--topk", type=int, default=1024)
     ap.add_argument("--iters", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=2)
+    ap.add_argument("--kv-quant", default=None, choices=[None, "fp8", "int8"])
+    ap.add_argument("--graph", action="store_true", help="decode: replay the step from a CUDA graph")
+    ap.add_argument("--profile", action="store_true", help="bracket the timed iterations with cudaProfilerStart/Stop")
     a = ap.parse_args()
+    global _PROFILE
+    _PROFILE = a.profile
     dev = "cuda:0"
     g = torch.Generator().manual_seed(1)
     out = {"kernel": a.kernel}
@@ -109,6 +122,21 @@ def main():
                    a.iters, a.warmup)
         vis = float(((torch.arange(a.T, dtype=torch.float64) + 1) // m).sum()) * a.B
         out.update(B=a.B, T=a.T, ms=ms, tflops=vis * 2 * HI * DI / ms / 1e9)
+    elif a.kernel == "decode":
+        # one-token steps of the 5-layer stack (d_model 2048) on caches filled as after --T tokens
+        cfg = kch_b200.HybridConfig(d_model=2048, n_heads_qk=16, n_heads_v=16, head_dim_k=128, head_dim_v=128,
+                                    kda_chunk_size=64, csa_m=4, csa_topk=a.topk, csa_nh=16, csa_c=128, csa_dc=128,
+                                    csa_nIh=4, csa_cI=64, csa_sliding_window=128, hca_m2=128, hca_nh=16, hca_c=128,
+                                    hca_dc=128, hca_sliding_window=128)
+        model = kch_b200.HybridKCHAttention(cfg, 5)
+        model.load_state_dict(syn.hybrid_params(3, cfg, 5, dtype=torch.bfloat16), strict=True)
+        model = model.bfloat16().to(dev).eval()
+        dec = kch_b200.HybridDecoding(model=model, kv_quant=a.kv_quant, use_cuda_graph=a.graph)
+        syn.fill_decode_state(dec, a.B, a.T, a.iters + a.warmup, torch.device(dev), 11)
+        x = torch.randn(a.B, 1, 2048, generator=g).bfloat16().to(dev)
+        ms = _time(lambda: dec(x), a.iters, a.warmup)
+        out.update(B=a.B, context=a.T, kv_quant=a.kv_quant, graph=dec._graph is not None, us_per_step=ms * 1e3,
+                   us_per_token=ms * 1e3 / a.B)
     print(json.dumps(out))
 
 

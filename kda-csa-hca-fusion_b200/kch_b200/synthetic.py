@@ -135,3 +135,46 @@ def hybrid_params(seed, cfg, total_layers=5, dtype=torch.bfloat16, std=0.02, ran
 
 def hidden_states(seed, B, T, d, dtype=torch.bfloat16):
     return torch.randn(B, T, d, generator=_gen(seed)).to(dtype)
+
+
+def fill_decode_state(dec, B, context, extra_tokens, dev, seed):
+    """Put the decode wrapper in the state it has after `context` tokens without running a prefill:
+    compressed rows, scoring copies, norms, accumulators, rings and KDA states filled with seeded random
+    values of the right scale, counters set.  The step cost does not depend on the values."""
+    from .fused import CSAHybridLayer, HCAHybridLayer
+    g = torch.Generator(device=dev).manual_seed(seed)
+    model, cfg = dec.model, dec.cfg
+    dec.reset()
+    h = torch.empty(B, 1, cfg.d_model, dtype=torch.bfloat16, device=dev)
+    for i, layer in enumerate(model.layers):
+        if not isinstance(layer, (CSAHybridLayer, HCAHybridLayer)):
+            continue
+        cache = dec._cache(i, layer, h)
+        m = cache.m if isinstance(layer, CSAHybridLayer) else cache.m2
+        nb = context // m
+        cache.reserve(nb + extra_tokens // m + 2)
+        for s0 in range(0, nb, 4096):                 # bounded temporaries
+            n = min(4096, nb - s0)
+            cache._store_rows(torch.randn(B, n, cache.c, device=dev, generator=g), s0)
+        if isinstance(layer, CSAHybridLayer):
+            k = torch.randn(B, nb, cache.c_I, device=dev, generator=g).to(cache.dtype)
+            cache._kcomp[:, :nb] = k
+            cache._kcomp_norms[:, :nb] = k.float().norm(dim=-1).clamp_min(1e-12)
+            for p in cache._prev:
+                p.copy_(torch.randn(p.shape, device=dev, generator=g))
+            cache._has_prev = True
+        for a in cache._acc:
+            a.copy_(torch.randn(a.shape, device=dev, generator=g))
+        cache._acc_len = context % m
+        cache._n_blocks = nb
+        cache._n_tokens_seen = context
+        if cache._sw is not None:
+            w = torch.randn(cache._sw._buf.shape, device=dev, generator=g)
+            cache._sw._buf.copy_(w / w.norm(dim=-1, keepdim=True))
+            cache._sw._n = context
+        cache._sync_counters()
+    HV, K, V = cfg.n_heads_v, cfg.head_dim_k, cfg.head_dim_v
+    model._kda_state = 0.02 * torch.randn(model.n_kda_layers, B, HV, K, V, device=dev, generator=g)
+    for layer in model.layers:
+        if hasattr(layer, "_conv_lookback"):
+            layer._conv_lookback = torch.randn(B, 2, cfg.d_model, device=dev, generator=g).to(torch.bfloat16)

@@ -473,9 +473,10 @@ class CSACacheOracle:
             self.prev_Zb = blk[3][:, -m:].clone()
 
     def step(self, q, q_idx, w_idx, *, topk, sink_logits=None, scale=None, normalize_qk=True,
-             return_indices=False):
+             return_indices=False, indices_override=None):
         """q ``[B,1,nh,c]`` fp32 (already normalised when normalize_qk), q_idx ``[B,1,nIh,c_I]``,
-        w_idx ``[B,1,nIh]``  ->  fp32 ``[B,1,nh,c]``."""
+        w_idx ``[B,1,nIh]``  ->  fp32 ``[B,1,nh,c]``.  ``indices_override [B,1,k]`` replaces the indexer's
+        selection (to check the attention on a selection that differs only by a near-tie)."""
         B, _, nh, c = q.shape
         t = self.tokens - 1
         nvis = min((t + 1) // self.m, self.C_comp.shape[1])
@@ -485,7 +486,9 @@ class CSACacheOracle:
         Cn = self.C_comp.float()
         if normalize_qk:
             Cn = l2_normalize(Cn)
-        if Cn.shape[1] > 0 and topk > 0:
+        if indices_override is not None:
+            idx = indices_override.long()
+        elif Cn.shape[1] > 0 and topk > 0:
             idx = lightning_indexer(q_idx.float(), self.K_IComp.float(), w_idx.float(), topk,
                                     n_visible=nvis, normalize_qk=normalize_qk)
         else:

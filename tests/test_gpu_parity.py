@@ -403,6 +403,80 @@ def test_quantised_cache_against_oracle(kch, kind):
         assert md(a, ra) <= 1e-4 and md(b, rb) <= 1e-4, t
     assert md(cc.C_comp.float(), oc.C_comp.float()) <= 1e-2
 
+@pytest.mark.parametrize("kind", [None, "fp8", "int8"])
+def test_split_decode_attention_against_oracle(kch, kind):
+    """Production geometry (c = 128, 16 heads): the one-token path runs the split-softmax decode kernel and the
+    matrix-vector indexer, both driven by the cache's device counters; top-k is smaller than the visible prefix."""
+    c = dict(seed=73, B=3, T=150, c=128, c_I=64, m=4, m2=8, win=16, nh=16, nIh=4, topk=12, dtype=torch.bfloat16)
+    stc = make_cache_stream(c)
+    st = {k: v.to(DEV) for k, v in stc.items()}
+    cc = kch.CSADecodingCache(c["B"], c["c"], c["c_I"], c["m"], c["win"], DEV, c["dtype"], kv_quant=kind)
+    hc = kch.HCADecodingCache(c["B"], c["c"], c["m2"], c["win"], DEV, c["dtype"], kv_quant=kind)
+    oc = orc.CSACacheOracle(c["B"], c["c"], c["c_I"], c["m"], c["win"], c["dtype"], kv_quant=kind)
+    oh = orc.HCACacheOracle(c["B"], c["c"], c["m2"], c["win"], c["dtype"], kv_quant=kind)
+    names = ("Ca", "Cb", "Za", "Zb", "K_idx", "Z_idx")
+    bulk = 37                                          # a bulk prefix first: the counters must be mirrored to the device
+    cc.append_step(*[st[n][:, :bulk] for n in names], st["Ba"], st["Bb"], st["B_idx"])
+    hc.append_step(st["Ca"][:, :bulk], st["Za"][:, :bulk], st["B_pos"])
+    for t in range(bulk):
+        sl = slice(t, t + 1)
+        oc.append(*[stc[n][:, sl] for n in names], stc["Ba"], stc["Bb"], stc["B_idx"])
+        oh.append(stc["Ca"][:, sl], stc["Za"][:, sl], stc["B_pos"])
+    worst = 0.0
+    for t in range(bulk, c["T"]):
+        sl = slice(t, t + 1)
+        cc.append_step(*[st[n][:, sl] for n in names], st["Ba"], st["Bb"], st["B_idx"])
+        hc.append_step(st["Ca"][:, sl], st["Za"][:, sl], st["B_pos"])
+        oc.append(*[stc[n][:, sl] for n in names], stc["Ba"], stc["Bb"], stc["B_idx"])
+        oh.append(stc["Ca"][:, sl], stc["Za"][:, sl], stc["B_pos"])
+        qn = torch.nn.functional.normalize(st["q"][:, sl].float(), dim=-1)
+        a, sel = cc.forward_step(qn, st["q_idx"][:, sl].float(), st["w_idx"][:, sl].float(), topk=c["topk"], nh=c["nh"],
+                                 nIh=c["nIh"], scale=1.0, sink_logits=st["sink"], use_ste=False, _return_indices=True)
+        b = hc.forward_step(qn, nh=c["nh"], scale=1.0, sink_logits=st["sink"])
+        ra, rsel = oc.step(qn.cpu(), stc["q_idx"][:, sl].float(), stc["w_idx"][:, sl].float(), topk=c["topk"],
+                           sink_logits=stc["sink"], scale=1.0, return_indices=True)
+        rb = oh.step(qn.cpu(), sink_logits=stc["sink"], scale=1.0)
+        assert md(b, rb) <= 1e-4, t
+        same = all(set(sel[i, 0].tolist()) - {-1} == set(rsel[i, 0].tolist()) - {-1} for i in range(c["B"]))
+        if same:
+            worst = max(worst, md(a, ra))
+        else:                                          # a near-tie at the selection boundary: rerun the oracle on our set
+            ra2 = oc.step(qn.cpu(), stc["q_idx"][:, sl].float(), stc["w_idx"][:, sl].float(), topk=c["topk"],
+                          sink_logits=stc["sink"], scale=1.0, indices_override=sel.cpu())
+            worst = max(worst, md(a, ra2))
+    assert worst <= 1e-4
+    assert cc.n_tokens_seen == c["T"] and cc.n_blocks == c["T"] // c["m"]
+    ctr = cc._ctr.cpu().tolist()
+    assert ctr[:5] == [c["T"] % c["m"], c["T"] // c["m"], c["T"], 1, c["T"]]
+    assert kch._lib.device_status() == 0
+
+
+def test_hybrid_decode_graph_replay_matches_eager(kch):
+    """One-token steps replayed from a captured CUDA graph give the same bits as the same kernels launched from
+    Python, across block closings of both caches and one growth of the cache storage."""
+    cfgd = dict(d_model=256, n_heads_qk=2, n_heads_v=2, head_dim_k=128, head_dim_v=128, kda_chunk_size=64, csa_m=4,
+                csa_topk=8, csa_nh=4, csa_c=128, csa_dc=64, csa_nIh=2, csa_cI=64, csa_sliding_window=16, hca_m2=16,
+                hca_nh=4, hca_c=128, hca_dc=64, hca_sliding_window=16)
+    cfg, model, _ = _load_model(kch, cfgd, 5, 91, torch.bfloat16)
+    B, prefill, steps = 2, 70, 45
+    x = syn.hidden_states(92, B, prefill + steps, cfg.d_model, torch.bfloat16).to(DEV)
+    outs = {}
+    for mode in (False, True):
+        dec = kch.HybridDecoding(model=model, use_cuda_graph=mode)
+        dec.reset()
+        ys = [dec(x[:, :prefill])]
+        for t in range(steps):
+            ys.append(dec(x[:, prefill + t:prefill + t + 1]))
+        outs[mode] = torch.cat(ys, 1).float()
+        if mode:
+            assert dec._graph is not None
+        caches = list(dec._caches.values())
+        assert all(cch.n_tokens_seen == prefill + steps for cch in caches)
+        assert all(cch._ctr.cpu().tolist()[4] == prefill + steps for cch in caches)
+    assert torch.isfinite(outs[True]).all()
+    assert torch.equal(outs[True], outs[False])
+    assert kch._lib.device_status() == 0
+
 
 # ---------------------------------------------------------------------------------------------- stack
 def _load_model(kch, cfgd, layers, seed, dtype):
