@@ -149,6 +149,16 @@ int kch_indexer_topk(const float* q_idx, const float* k_idx, const float* w_idx,
                      int T, int n_blocks, int HI, int DI, int topk, float scale, int m, int64_t t0,
                      int n_visible, int sorted, int64_t k_batch_stride, void* workspace,
                      int64_t workspace_bytes, void* stream);
+/* Same selection with the queries read as the projection wrote them: q_idx [B,T,HI*DI] in q_dtype, tokens q_ld
+ * elements apart.  KCH_BF16 (needs DI == 64): the un-normalised bf16 queries are exact tensor-core operands and,
+ * with q_normalize, each head's dot products are divided by max(||q_h||, 1e-12) (the reference normalises the
+ * query first, ops_csa.py:531-536: the same value up to one rounding).  KCH_F32: identical to kch_indexer_topk.
+ * Workspace: kch_indexer_workspace_bytes_ex(B, T, n_blocks, q_dtype). */
+int64_t kch_indexer_workspace_bytes_ex(int B, int T, int n_blocks, int q_dtype);
+int kch_indexer_topk_ex(const void* q_idx, int q_dtype, int64_t q_ld, int q_normalize, const float* k_idx,
+                        const float* w_idx, int32_t* indices, int B, int T, int n_blocks, int HI, int DI, int topk,
+                        float scale, int m, int64_t t0, int n_visible, int sorted, int64_t k_batch_stride,
+                        void* workspace, int64_t workspace_bytes, void* stream);
 
 /* No counterpart in the reference (it allocates freely through PyTorch).  Same selection as
  * kch_indexer_topk (unsorted picks), for callers that must not allocate device memory while serving:

@@ -122,11 +122,17 @@ __device__ __forceinline__ void cpa16(uint32_t dst, const void* src, int bytes) 
 struct IdxSplit {            // pre-split operands (PRE = true); rows are 64 bf16
   const bf16 *qh, *qm, *ql;  // [B*T*HI][64]
   const bf16 *kh, *km, *kl;  // [B*n][64]
+  const bf16* qraw;          // QRAW: un-normalised bf16 queries, token t of batch b at qraw + (b*T+t)*q_ld, head h at +64h
+  int64_t q_ld;
+  int q_normalize;           // QRAW: divide each head's dot products by max(||q_h||, 1e-12)
 };
 
 // PRE = false: operands are split inside the kernel (no extra workspace); PRE = true: the three bf16 terms
 // were prepared once by split3_rows_kernel and are streamed in with cp.async (query tiles double-buffered).
-template <bool PRE>
+// QRAW (with PRE): the queries are bf16 as the projection wrote them, so they are exact single-term operands;
+// their L2 norm is taken from the fragments and divides the finished dot product.  Three products per k-step
+// (q x key hi/mid/lo) instead of six, and no split pass over the queries.
+template <bool PRE, bool QRAW = false>
 __global__ void __launch_bounds__(128)
 indexer_logits_mma_kernel(const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ w,
                           IdxSplit sp, float* __restrict__ logits, int T, int n, int HI, int64_t n_ld, float scale,
@@ -137,8 +143,8 @@ indexer_logits_mma_kernel(const float* __restrict__ q, const float* __restrict__
   const int64_t vis_last = nvis_fixed >= 0 ? nvis_fixed : (m > 0 ? (t0 + tlast + 1) / m : n);
   if (nt0 >= vis_last) return;
   uint8_t* kt = sm;                        // 3 x [128][64] bf16 (hi, mid, lo), 128-byte rows, swizzled
-  uint8_t* qt = sm + 3 * IM_TN * 128;      // (PRE: 2 x) 3 x [64][64] bf16
-  constexpr int QT_BYTES = 3 * IM_TQ * 128;
+  uint8_t* qt = sm + 3 * IM_TN * 128;      // (PRE: 2 x) 3 x [64][64] bf16; QRAW: 2 x [64][64] bf16
+  constexpr int QT_BYTES = (QRAW ? 1 : 3) * IM_TQ * 128;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g4 = lane >> 2, j4 = lane & 3;
 
   auto stage_q = [&](int h, int buf) {
@@ -147,7 +153,10 @@ indexer_logits_mma_kernel(const float* __restrict__ q, const float* __restrict__
       const int r = idx >> 3, ch = idx & 7;
       const int t = tq0 + r;
       const uint32_t off = swz<128>(r, ch);
-      if constexpr (PRE) {
+      if constexpr (QRAW) {
+        const int64_t src = ((int64_t)b * T + (t < T ? t : 0)) * sp.q_ld + h * IM_D + 8 * ch;
+        cpa16(smem_addr_u32(dstb + off), sp.qraw + src, t < T ? 16 : 0);
+      } else if constexpr (PRE) {
         const int64_t src = ((((int64_t)b * T + (t < T ? t : 0)) * HI + h) * IM_D + 8 * ch);
         const int bytes = t < T ? 16 : 0;
         cpa16(smem_addr_u32(dstb + off), sp.qh + src, bytes);
@@ -219,14 +228,35 @@ indexer_logits_mma_kernel(const float* __restrict__ q, const float* __restrict__
     }
     const uint32_t qth = smem_addr_u32(qt + buf * QT_BYTES), qtm = qth + IM_TQ * 128, qtl = qtm + IM_TQ * 128;
     uint32_t ah[4][4], am[4][4], al[4][4];
+    float qs0 = scale, qs1 = scale;        // scale / ||q|| of rows r0, r1 (QRAW)
     {
       const int arow = 16 * warp + (lane & 7) + ((lane >> 3) & 1) * 8;
 #pragma unroll
       for (int ks = 0; ks < 4; ++ks) {
         const uint32_t o = swz<128>(arow, 2 * ks + (lane >> 4));
         ldmatrix_x4(qth + o, ah[ks][0], ah[ks][1], ah[ks][2], ah[ks][3]);
-        ldmatrix_x4(qtm + o, am[ks][0], am[ks][1], am[ks][2], am[ks][3]);
-        ldmatrix_x4(qtl + o, al[ks][0], al[ks][1], al[ks][2], al[ks][3]);
+        if constexpr (!QRAW) {
+          ldmatrix_x4(qtm + o, am[ks][0], am[ks][1], am[ks][2], am[ks][3]);
+          ldmatrix_x4(qtl + o, al[ks][0], al[ks][1], al[ks][2], al[ks][3]);
+        }
+      }
+      if constexpr (QRAW) {
+        if (sp.q_normalize) {
+          // registers 0,2 of a fragment hold row g4 (r0), registers 1,3 row g4+8 (r1); a quad covers a row
+          float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+          for (int ks = 0; ks < 4; ++ks) {
+#pragma unroll
+            for (int rr = 0; rr < 4; ++rr) {
+              const float x = __uint_as_float(ah[ks][rr] << 16), y = __uint_as_float(ah[ks][rr] & 0xFFFF0000u);
+              if (rr & 1) s1 = fmaf(x, x, fmaf(y, y, s1)); else s0 = fmaf(x, x, fmaf(y, y, s0));
+            }
+          }
+          s0 += __shfl_xor_sync(0xffffffffu, s0, 1); s0 += __shfl_xor_sync(0xffffffffu, s0, 2);
+          s1 += __shfl_xor_sync(0xffffffffu, s1, 1); s1 += __shfl_xor_sync(0xffffffffu, s1, 2);
+          qs0 = scale / fmaxf(sqrtf(s0), 1e-12f);
+          qs1 = scale / fmaxf(sqrtf(s1), 1e-12f);
+        }
       }
     }
     float w0 = 1.f, w1 = 1.f;
@@ -251,6 +281,15 @@ indexer_logits_mma_kernel(const float* __restrict__ q, const float* __restrict__
 #pragma unroll
         for (int kk = 0; kk < 2; ++kk) {
           const int ks = 2 * qd + kk;
+          if constexpr (QRAW) {
+            mma_bf16_16816(acc[0], ah[ks], bl[0][2 * kk], bl[0][2 * kk + 1]);
+            mma_bf16_16816(acc[1], ah[ks], bl[1][2 * kk], bl[1][2 * kk + 1]);
+            mma_bf16_16816(acc[0], ah[ks], bm[0][2 * kk], bm[0][2 * kk + 1]);
+            mma_bf16_16816(acc[1], ah[ks], bm[1][2 * kk], bm[1][2 * kk + 1]);
+            mma_bf16_16816(acc[0], ah[ks], bh[0][2 * kk], bh[0][2 * kk + 1]);
+            mma_bf16_16816(acc[1], ah[ks], bh[1][2 * kk], bh[1][2 * kk + 1]);
+            continue;
+          }
           // smallest terms first; the two column tiles alternate so consecutive MMAs are independent
           mma_bf16_16816(acc[0], al[ks], bh[0][2 * kk], bh[0][2 * kk + 1]);
           mma_bf16_16816(acc[1], al[ks], bh[1][2 * kk], bh[1][2 * kk + 1]);
@@ -269,10 +308,10 @@ indexer_logits_mma_kernel(const float* __restrict__ q, const float* __restrict__
 #pragma unroll
       for (int u = 0; u < 2; ++u) {
         const int nt = 2 * np + u;
-        out[nt][0] = fmaf(fmaxf(acc[u][0] * scale, 0.f), w0, out[nt][0]);
-        out[nt][1] = fmaf(fmaxf(acc[u][1] * scale, 0.f), w0, out[nt][1]);
-        out[nt][2] = fmaf(fmaxf(acc[u][2] * scale, 0.f), w1, out[nt][2]);
-        out[nt][3] = fmaf(fmaxf(acc[u][3] * scale, 0.f), w1, out[nt][3]);
+        out[nt][0] = fmaf(fmaxf(acc[u][0] * qs0, 0.f), w0, out[nt][0]);
+        out[nt][1] = fmaf(fmaxf(acc[u][1] * qs0, 0.f), w0, out[nt][1]);
+        out[nt][2] = fmaf(fmaxf(acc[u][2] * qs1, 0.f), w1, out[nt][2]);
+        out[nt][3] = fmaf(fmaxf(acc[u][3] * qs1, 0.f), w1, out[nt][3]);
       }
     }
     if constexpr (PRE) __syncthreads();   // every warp is done with this head's query buffer
@@ -302,12 +341,35 @@ static int64_t indexer_split_bytes(int B, int T, int n_blocks, int HI, int DI) {
   return 3 * (align256((int64_t)B * T * HI * IM_D * 2) + align256((int64_t)B * n_blocks * IM_D * 2));
 }
 
+static int64_t indexer_ksplit_bytes(int B, int n_blocks) { return 3 * align256((int64_t)B * n_blocks * IM_D * 2); }
+
+// `qraw` (optional): un-normalised bf16 queries read in place (token stride q_ld); then q_idx is not used.
 static int launch_indexer_logits(const float* q_idx, const float* k_idx, const float* w_idx, float* logits, int B,
                                  int T, int n_blocks, int HI, int DI, int64_t n_ld, float scale, int m, int64_t t0,
                                  int n_visible, int64_t k_batch_stride, void* split_ws, int64_t split_bytes,
-                                 cudaStream_t s) {
+                                 cudaStream_t s, const bf16* qraw = nullptr, int64_t q_ld = 0, int q_normalize = 0) {
   const int64_t kbs = k_batch_stride > 0 ? k_batch_stride : (int64_t)n_blocks * DI;
   static const bool force_simt = [] { const char* e = getenv("KCH_INDEXER"); return e && e[0] == 's'; }();
+  if (qraw) {
+    KCH_REQUIRE(DI == IM_D && (((uintptr_t)qraw | (uintptr_t)k_idx) & 15) == 0 && (q_ld % 8) == 0 && (kbs % 4) == 0,
+                "kch_indexer_topk_ex: bf16 queries need c_I == 64, 16-byte aligned operands and q_ld %% 8 == 0");
+    KCH_REQUIRE(split_ws && split_bytes >= indexer_ksplit_bytes(B, n_blocks) && (((uintptr_t)split_ws) & 15) == 0,
+                "kch_indexer_topk_ex: workspace too small for the split keys");
+    dim3 g((n_blocks + IM_TN - 1) / IM_TN, (T + IM_TQ - 1) / IM_TQ, B);
+    const int64_t krows = (int64_t)B * n_blocks, kb = align256(krows * IM_D * 2);
+    uint8_t* p = (uint8_t*)split_ws;
+    bf16* kh = (bf16*)p; bf16* km = (bf16*)(p + kb); bf16* kl = (bf16*)(p + 2 * kb);
+    split3_rows_kernel<<<(unsigned)ceil_div64(krows * 8, 256), 256, 0, s>>>(k_idx, n_blocks, kbs, krows, kh, km, kl);
+    KCH_LAUNCH_OK();
+    IdxSplit sp = {};
+    sp.kh = kh; sp.km = km; sp.kl = kl; sp.qraw = qraw; sp.q_ld = q_ld; sp.q_normalize = q_normalize;
+    const int smem = 3 * IM_TN * 128 + 2 * IM_TQ * 128;
+    KCH_CUDA_OK(cudaFuncSetAttribute(indexer_logits_mma_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    indexer_logits_mma_kernel<true, true><<<g, 128, smem, s>>>(nullptr, k_idx, w_idx, sp, logits, T, n_blocks, HI, n_ld, scale,
+                                                               m, t0, n_visible, kbs);
+    KCH_LAUNCH_OK();
+    return KCH_OK;
+  }
   const bool aligned = (((uintptr_t)q_idx | (uintptr_t)k_idx) & 15) == 0 && (kbs % 4) == 0;
   if (!force_simt && DI == IM_D && aligned) {
     dim3 g((n_blocks + IM_TN - 1) / IM_TN, (T + IM_TQ - 1) / IM_TQ, B);
@@ -427,9 +489,22 @@ topk_select_kernel(const float* __restrict__ logits, int32_t* __restrict__ out, 
       const int shift = 24 - 8 * pass;
       hist[tid] = 0;
       __syncthreads();
-      for (int k = 0; k < cnt_mine; ++k) {
-        uint32_t u = f2ord(val(k));
-        if ((u & pmask) == prefix) atomicAdd(&hist[(u >> shift) & 255], 1);
+      // long rows (decode over a whole cache): the logits crowd into a few bins of the leading bytes, so lanes
+      // that hit the same bin are counted with one atomic (match.any) instead of serialising on one word
+      if (E >= 64) {
+        for (int k = 0; k < E; ++k) {
+          const uint32_t u = k < cnt_mine ? f2ord(val(k)) : 0u;
+          if (k < cnt_mine && (u & pmask) == prefix) {
+            const int bin2 = (u >> shift) & 255;
+            const unsigned peers = __match_any_sync(__activemask(), bin2);
+            if ((threadIdx.x & 31) == __ffs(peers) - 1) atomicAdd(&hist[bin2], __popc(peers));
+          }
+        }
+      } else {
+        for (int k = 0; k < cnt_mine; ++k) {
+          const uint32_t u = f2ord(val(k));
+          if ((u & pmask) == prefix) atomicAdd(&hist[(u >> shift) & 255], 1);
+        }
       }
       __syncthreads();
       // thread t looks at bin 255-t: an exclusive scan gives the population of all higher bins
@@ -505,11 +580,35 @@ extern "C" int64_t kch_indexer_workspace_bytes(int B, int T, int n, int HI, int 
   return indexer_logits_bytes(B, T, n) + indexer_split_bytes(B, T, n, HI, DI);
 }
 
+extern "C" int64_t kch_indexer_workspace_bytes_ex(int B, int T, int n, int q_dtype) {
+  if (B <= 0 || T <= 0 || n <= 0) return 0;
+  if (q_dtype == KCH_BF16) return indexer_logits_bytes(B, T, n) + indexer_ksplit_bytes(B, n);
+  return indexer_logits_bytes(B, T, n);
+}
+
+extern "C" int kch_indexer_topk_ex(const void* q_idx, int q_dtype, int64_t q_ld, int q_normalize, const float* k_idx,
+                                   const float* w_idx, int32_t* indices, int B, int T, int n_blocks, int HI, int DI,
+                                   int topk, float scale, int m, int64_t t0, int n_visible, int sorted,
+                                   int64_t k_batch_stride, void* workspace, int64_t workspace_bytes, void* stream);
+
 extern "C" int kch_indexer_topk(const float* q_idx, const float* k_idx, const float* w_idx,
                                 int32_t* indices, int B, int T, int n_blocks, int HI, int DI, int topk,
                                 float scale, int m, int64_t t0, int n_visible, int sorted,
                                 int64_t k_batch_stride, void* workspace, int64_t workspace_bytes,
                                 void* stream) {
+  return kch_indexer_topk_ex(q_idx, KCH_F32, (int64_t)HI * DI, 0, k_idx, w_idx, indices, B, T, n_blocks, HI, DI, topk, scale,
+                             m, t0, n_visible, sorted, k_batch_stride, workspace, workspace_bytes, stream);
+}
+
+extern "C" int kch_indexer_topk_ex(const void* q_idx_any, int q_dtype, int64_t q_ld, int q_normalize, const float* k_idx,
+                                   const float* w_idx, int32_t* indices, int B, int T, int n_blocks, int HI, int DI,
+                                   int topk, float scale, int m, int64_t t0, int n_visible, int sorted,
+                                   int64_t k_batch_stride, void* workspace, int64_t workspace_bytes, void* stream) {
+  KCH_REQUIRE(q_dtype == KCH_F32 || q_dtype == KCH_BF16, "kch_indexer_topk_ex: q_dtype=%d", q_dtype);
+  KCH_REQUIRE(q_dtype == KCH_BF16 || (q_ld == (int64_t)HI * DI && !q_normalize),
+              "kch_indexer_topk_ex: fp32 queries must be dense and already normalised");
+  const float* q_idx = q_dtype == KCH_F32 ? (const float*)q_idx_any : nullptr;
+  const bf16* q_raw = q_dtype == KCH_BF16 ? (const bf16*)q_idx_any : nullptr;
   KCH_REQUIRE(topk >= 0, "topk=%d must be >= 0 (0 selects zero blocks)", topk);
   KCH_REQUIRE(DI >= 1, "q_idx.shape[-1]=%d must be >= 1 (indexer key dimension c_I must be positive)", DI);
   KCH_REQUIRE(HI >= 1, "nIh=%d must be >= 1 (indexer head count)", HI);
@@ -530,7 +629,7 @@ extern "C" int kch_indexer_topk(const float* q_idx, const float* k_idx, const fl
   {
     void* split_ws = workspace_bytes > need ? (void*)((uint8_t*)workspace + need) : nullptr;
     int rc = launch_indexer_logits(q_idx, k_idx, w_idx, logits, B, T, n_blocks, HI, DI, n_ld, scale, m, t0, n_visible,
-                                   k_batch_stride, split_ws, workspace_bytes - need, s);
+                                   k_batch_stride, split_ws, workspace_bytes - need, s, q_raw, q_ld, q_normalize);
     if (rc != KCH_OK) return rc;
   }
   size_t smem = 0;

@@ -81,6 +81,9 @@ PROTOTYPES = {
     "kch_compress_kv_overlapped": (_i, [_vp] * 8 + [_i64, _vp, _i, _i64, _i, _i, _i64, _i64, _i64, _i, _i, _vp]),
     "kch_indexer_workspace_bytes": (_i64, [_i, _i, _i, _i, _i]),
     "kch_indexer_topk": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _i64, _i, _i, _i64, _vp, _i64, _vp]),
+    "kch_indexer_workspace_bytes_ex": (_i64, [_i, _i, _i, _i]),
+    "kch_indexer_topk_ex": (_i, [_vp, _i, _i64, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _i64, _i, _i, _i64, _vp,
+                                 _i64, _vp]),
     "kch_indexer_topk_static_capacity": (_i64, []),
     "kch_indexer_topk_static": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _i64, _i, _i64, _vp]),
     "kch_attend": (_i, [C.POINTER(AttendArgs), _vp]),

@@ -171,7 +171,23 @@ def indexer_topk(q_idx, k_idx, w_idx, topk, *, m=0, t0=0, n_visible=-1, normaliz
     idx = torch.empty(B, T, topk, dtype=torch.int32, device=dev)
     if B == 0 or T == 0 or topk == 0:
         return idx
-    qn = rownorm(q_idx, normalize_qk).contiguous()
+    # bf16 queries of the production width are scored as they lie (a strided slice of the fused projection is
+    # fine): exact tensor-core operands, their norm divides the dot product inside the kernel
+    raw_q = (q_idx.dtype == torch.bfloat16 and DI == 64 and normalize_qk and n > 0 and q_idx.stride(-1) == 1
+             and q_idx.stride(2) == DI and q_idx.stride(1) % 8 == 0 and q_idx.data_ptr() % 16 == 0
+             and (B == 1 or q_idx.stride(0) == T * q_idx.stride(1)))
+    if raw_q:
+        kn = k_idx if k_prenormalized else rownorm(k_idx, True).contiguous()
+        wf = None if w_idx is None else w_idx.float().contiguous()
+        nbytes = int(lib.kch_indexer_workspace_bytes_ex(B, T, n, _lib.KCH_BF16))
+        ws = torch.empty(max(nbytes, 1), dtype=torch.uint8, device=dev)
+        with torch.cuda.device(dev):
+            _lib.check(lib.kch_indexer_topk_ex(_lib.ptr(q_idx), _lib.KCH_BF16, q_idx.stride(1), 1, _lib.ptr(kn),
+                                               _lib.ptr(wf), _lib.ptr(idx), B, T, n, HI, DI, int(topk), float(scale),
+                                               int(m), int(t0), int(n_visible), 1 if sorted_output else 0,
+                                               int(k_batch_stride), _lib.ptr(ws), nbytes, _lib.stream()))
+        return idx
+    qn = rownorm(q_idx.contiguous(), normalize_qk).contiguous()
     if k_prenormalized:
         kn = k_idx                      # fp32, rows dense, batch entries k_batch_stride elements apart
     elif normalize_qk:
@@ -365,7 +381,7 @@ def naive_csa(H, W_aKV, W_bKV, W_aZ, W_bZ, Ba, Bb, W_DQ, W_UQ, W_IUQ, W_w, W_KV_
     W_q = _fused_q_weight if _fused_q_weight is not None else torch.cat([W_UQ, W_IUQ], dim=0)
     qq = linear(cQ, W_q)                                                # [B,T,nh*c + nIh*cI]
     q, q_idx = qq[..., :nh * c + nIh * c_I].split([nh * c, nIh * c_I], dim=-1)
-    q_idx = q_idx.reshape(B_, T, nIh, c_I) if q_idx.is_contiguous() else q_idx.contiguous().reshape(B_, T, nIh, c_I)
+    q_idx = q_idx.unflatten(-1, (nIh, c_I))                             # a view of the fused projection
     indices = None
     if topk > 0:
         indices = indexer_topk(q_idx, K_IComp, w_idx, topk, m=m, normalize_qk=normalize_qk, sorted_output=False)

@@ -1,0 +1,65 @@
+"""Host-resident batches through the stack with the PCIe copies hidden behind the kernels.
+
+The reference keeps its tensors wherever the caller put them and has no notion of streams.  A caller whose
+hidden states live in host memory pays one host->device copy before and one device->host copy after every
+forward pass; at the benchmark size those copies (2 x 537 MB) cost about a third of the pass itself.
+``HostPipeline`` runs a sequence of passes with three CUDA streams: while pass ``i`` computes, the input of
+pass ``i+1`` is uploaded into the other of two device buffers and the output of pass ``i-1`` is downloaded.
+Every copy still happens, once per pass; only the first upload and the last download are exposed.
+"""
+from __future__ import annotations
+
+import torch
+
+
+class HostPipeline:
+    def __init__(self, model, device=None):
+        self.model = model
+        self.device = torch.device(device) if device is not None else next(model.parameters()).device
+        if self.device.type != "cuda":
+            raise RuntimeError("HostPipeline requires a CUDA device; there is no CPU path")
+        self._up = torch.cuda.Stream(self.device)
+        self._down = torch.cuda.Stream(self.device)
+        self._xd = [None, None]
+
+    @torch.no_grad()
+    def run(self, inputs, outputs, *, reset_state=True):
+        """``inputs[i]`` (pinned host ``[B,T,d]``) -> ``outputs[i]`` (pinned host, same shape).  Passes are
+        independent prefill passes when ``reset_state`` (the KDA state is cleared before each)."""
+        if len(inputs) != len(outputs):
+            raise ValueError(f"HostPipeline.run: {len(inputs)} inputs but {len(outputs)} outputs")
+        dev = self.device
+        compute = torch.cuda.current_stream(dev)
+        n = len(inputs)
+        uploaded = [torch.cuda.Event() for _ in range(n)]
+        computed = [torch.cuda.Event() for _ in range(n)]
+        self._up.wait_stream(compute)
+        self._down.wait_stream(compute)
+
+        def upload(i):
+            x = inputs[i]
+            slot = i % 2
+            if self._xd[slot] is None or self._xd[slot].shape != x.shape or self._xd[slot].dtype != x.dtype:
+                self._xd[slot] = torch.empty(x.shape, dtype=x.dtype, device=dev)
+            with torch.cuda.stream(self._up):
+                if i >= 2:
+                    self._up.wait_event(computed[i - 2])        # the pass that read this buffer has finished
+                self._xd[slot].copy_(x, non_blocking=True)
+                uploaded[i].record(self._up)
+
+        if n:
+            upload(0)
+        for i in range(n):
+            if i + 1 < n:
+                upload(i + 1)
+            compute.wait_event(uploaded[i])
+            if reset_state:
+                self.model.reset_state()
+            y = self.model(self._xd[i % 2])
+            computed[i].record(compute)
+            with torch.cuda.stream(self._down):
+                self._down.wait_event(computed[i])
+                outputs[i].copy_(y, non_blocking=True)
+            y.record_stream(self._down)
+        compute.wait_stream(self._down)
+        return outputs

@@ -516,3 +516,20 @@ def test_hybrid_decode(kch, golden):
     for t in range(c["steps"]):
         ys.append(dec(x[:, c["prefill"] + t:c["prefill"] + t + 1]))
     assert md(torch.cat(ys, 1), golden["decode/y"]) <= 5e-5
+
+
+def test_host_pipeline_matches_direct_passes(kch):
+    """Overlapped upload / compute / download of several host batches gives exactly the passes run one by one."""
+    cfgd = dict(d_model=256, n_heads_qk=2, n_heads_v=2, head_dim_k=128, head_dim_v=128, kda_chunk_size=64, csa_m=4,
+                csa_topk=8, csa_nh=4, csa_c=128, csa_dc=64, csa_nIh=2, csa_cI=64, csa_sliding_window=16, hca_m2=16,
+                hca_nh=4, hca_c=128, hca_dc=64, hca_sliding_window=16)
+    cfg, model, _ = _load_model(kch, cfgd, 5, 95, torch.bfloat16)
+    xs = [syn.hidden_states(96 + i, 2, 300, cfg.d_model, torch.bfloat16).pin_memory() for i in range(4)]
+    ys = [torch.empty_like(x).pin_memory() for x in xs]
+    kch.HostPipeline(model, DEV).run(xs, ys)
+    torch.cuda.synchronize()
+    for x, y in zip(xs, ys):
+        model.reset_state()
+        ref = model(x.to(DEV)).cpu()
+        assert torch.equal(ref, y)
+
