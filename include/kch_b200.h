@@ -53,6 +53,14 @@ int kch_layernorm(const void* x, const void* weight, const void* bias, void* y, 
  * x,y [B,T,d]; lookback [B,2,d] or NULL (zeros); weight [d,3]; bias [d]; all in `dtype`. */
 int kch_short_conv(const void* x, const void* lookback, const void* weight, const void* bias, void* y,
                    int B, int T, int d, int dtype, void* stream);
+/* LayerNorm (fp32 arithmetic, rounded to bf16) followed by the short convolution in one pass; bf16 only,
+ * d a multiple of 256 up to 2048, T >= 2.  Same values as kch_layernorm then kch_short_conv.  `lookback` /
+ * `lookback_out` [B,2,d] hold NORMALISED rows (what the convolution consumes); lookback_out receives the last
+ * two normalised rows of the sequence.  ln_weight / ln_bias in wdtype, conv operands in bf16. */
+int kch_layernorm_short_conv(const void* x, const void* ln_weight, const void* ln_bias, float eps,
+                             const void* lookback, const void* conv_weight, const void* conv_bias, void* y,
+                             void* lookback_out, int B, int T, int d, int dtype, int wdtype, void* stream);
+
 /* One-token step of the same convolution (x,y [B,1,d]) that also slides `lookback` [B,2,d] by one token in
  * place: lookback <- [lookback[:,1], x] (the concatenation of ops_fused.py:560-569 without a new tensor). */
 int kch_short_conv_step(const void* x, void* lookback, const void* weight, const void* bias, void* y, int B, int d,

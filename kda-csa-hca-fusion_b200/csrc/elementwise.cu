@@ -213,6 +213,136 @@ extern "C" int kch_short_conv(const void* x, const void* lookback, const void* w
   return KCH_OK;
 }
 
+// ---------------------------------------------------------------------------------------
+// LayerNorm + short convolution in one pass (the KDA sub-layer reads LayerNorm(x) only through the
+// convolution, ops_fused.py:505-527 after :52-60): a CTA normalises a tile of LC_TT tokens plus the two
+// tokens before it into shared memory (bf16, exactly what the separate LayerNorm kernel would have stored)
+// and convolves from there, so the normalised activations never travel to HBM and back.  The two
+// normalised rows that end the sequence are written out as the next call's lookback.
+// HBM traffic per token: d*2 bytes in, d*2 bytes out (+ 2/LC_TT re-read of the halo rows, L2 hits).
+// ---------------------------------------------------------------------------------------
+#define LC_TT 14
+#define LC_ROWS (LC_TT + 2)
+
+template <typename TW, int NV>
+__global__ void __launch_bounds__(256)
+ln_conv_kernel_bf16(const bf16* __restrict__ x, const TW* __restrict__ lw, const TW* __restrict__ lb2, float eps,
+                    const bf16* __restrict__ lookback, const bf16* __restrict__ cw, const bf16* __restrict__ cb,
+                    bf16* __restrict__ y, bf16* __restrict__ lb_out, int T_, int d) {
+  extern __shared__ __align__(16) uint8_t lc_smem[];
+  bf16* sh = reinterpret_cast<bf16*>(lc_smem);               // [LC_ROWS][d] normalised rows t0-2 .. t0+LC_TT-1
+  const int b = blockIdx.y, t0 = blockIdx.x * LC_TT;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int r = warp; r < LC_ROWS; r += 8) {
+    const int t = t0 - 2 + r;
+    bf16* dst = sh + (size_t)r * d;
+    if (t >= T_) continue;
+    if (t < 0) {                                             // before the sequence: lookback row t+2, or zeros
+#pragma unroll
+      for (int i = 0; i < NV; ++i) {
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (lookback) v = *reinterpret_cast<const uint4*>(lookback + ((int64_t)b * 2 + (t + 2)) * d + i * 256 + lane * 8);
+        *reinterpret_cast<uint4*>(dst + i * 256 + lane * 8) = v;
+      }
+      continue;
+    }
+    const bf16* xr = x + ((int64_t)b * T_ + t) * d;
+    float v[NV][8];
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      uint4 raw = *reinterpret_cast<const uint4*>(xr + i * 256 + lane * 8);
+      const bf16* e = reinterpret_cast<const bf16*>(&raw);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) { v[i][k] = __bfloat162float(e[k]); s += v[i][k]; }
+    }
+    const float mean = warp_sum(s) / (float)d;
+    float q = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i)
+#pragma unroll
+      for (int k = 0; k < 8; ++k) { float tt = v[i][k] - mean; q += tt * tt; }
+    const float rstd = 1.0f / sqrtf(warp_sum(q) / (float)d + eps);
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      uint4 outv;
+      bf16* out = reinterpret_cast<bf16*>(&outv);
+      const int c0 = i * 256 + lane * 8;
+#pragma unroll
+      for (int k = 0; k < 8; ++k) out[k] = __float2bfloat16_rn((v[i][k] - mean) * rstd * ldf(lw + c0 + k) + ldf(lb2 + c0 + k));
+      *reinterpret_cast<uint4*>(dst + c0) = outv;
+      if (lb_out && t >= T_ - 2) *reinterpret_cast<uint4*>(lb_out + ((int64_t)b * 2 + (t - (T_ - 2))) * d + c0) = outv;
+    }
+  }
+  __syncthreads();
+  auto ld8 = [&](const bf16* p, float (&o)[8]) {
+    uint4 raw = *reinterpret_cast<const uint4*>(p);
+    const bf16* e = reinterpret_cast<const bf16*>(&raw);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) o[k] = __bfloat162float(e[k]);
+  };
+  for (int ch = threadIdx.x; ch < d / 8; ch += 256) {
+    const int c0 = ch * 8;
+    float wt[24], bb[8], x2[8], x1[8], x0[8];
+    {
+      const uint4* wp = reinterpret_cast<const uint4*>(cw + c0 * 3);
+#pragma unroll
+      for (int v3 = 0; v3 < 3; ++v3) {
+        uint4 raw = wp[v3];
+        const bf16* e = reinterpret_cast<const bf16*>(&raw);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) wt[8 * v3 + k] = __bfloat162float(e[k]);
+      }
+    }
+    ld8(cb + c0, bb);
+    ld8(sh + c0, x2);
+    ld8(sh + (size_t)d + c0, x1);
+    const int tmax = min(LC_TT, T_ - t0);
+    for (int tt = 0; tt < tmax; ++tt) {
+      ld8(sh + (size_t)(tt + 2) * d + c0, x0);
+      uint4 outv;
+      bf16* out = reinterpret_cast<bf16*>(&outv);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        float acc = wt[3 * k] * x2[k];
+        acc = fmaf(wt[3 * k + 1], x1[k], acc);
+        acc = fmaf(wt[3 * k + 2], x0[k], acc);
+        out[k] = __float2bfloat16_rn(acc + bb[k]);
+        x2[k] = x1[k];
+        x1[k] = x0[k];
+      }
+      *reinterpret_cast<uint4*>(y + ((int64_t)b * T_ + t0 + tt) * d + c0) = outv;
+    }
+  }
+}
+
+extern "C" int kch_layernorm_short_conv(const void* x, const void* ln_weight, const void* ln_bias, float eps,
+                                        const void* lookback, const void* conv_weight, const void* conv_bias, void* y,
+                                        void* lookback_out, int B, int T, int d, int dtype, int wdtype, void* stream) {
+  KCH_REQUIRE(dtype == KCH_BF16 && (d % 256) == 0 && d >= 256 && d <= 2048,
+              "kch_layernorm_short_conv: bf16 with d %% 256 == 0 and d <= 2048 only (dtype tag %d, d=%d)", dtype, d);
+  KCH_REQUIRE(B >= 1 && T >= 2, "kch_layernorm_short_conv: B=%d T=%d (needs T >= 2)", B, T);
+  const uintptr_t al = (uintptr_t)x | (uintptr_t)y | (uintptr_t)conv_weight | (uintptr_t)conv_bias | (uintptr_t)lookback |
+                       (uintptr_t)lookback_out;
+  KCH_REQUIRE((al & 15) == 0, "kch_layernorm_short_conv: operands must be 16-byte aligned");
+  const size_t smem = (size_t)LC_ROWS * d * 2;
+  dim3 grid((unsigned)((T + LC_TT - 1) / LC_TT), B);
+  cudaStream_t s = kch_stream(stream);
+#define LCV(NV)                                                                                                   \
+  KCH_DISPATCH_FLOAT(wdtype, TW, {                                                                                 \
+    KCH_CUDA_OK(cudaFuncSetAttribute(ln_conv_kernel_bf16<TW, NV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+    ln_conv_kernel_bf16<TW, NV><<<grid, 256, smem, s>>>((const bf16*)x, (const TW*)ln_weight, (const TW*)ln_bias, eps, \
+        (const bf16*)lookback, (const bf16*)conv_weight, (const bf16*)conv_bias, (bf16*)y, (bf16*)lookback_out, T, d); \
+  })
+  switch (d / 256) {
+    case 1: LCV(1); break; case 2: LCV(2); break; case 3: LCV(3); break; case 4: LCV(4); break;
+    case 5: LCV(5); break; case 6: LCV(6); break; case 7: LCV(7); break; default: LCV(8); break;
+  }
+#undef LCV
+  KCH_LAUNCH_OK();
+  return KCH_OK;
+}
+
 // One-token step of the conv with the lookback [B,2,d] updated where it lies (ops_fused.py:560-569 builds
 // the new lookback by concatenation; here the same two rows are written back by the thread that read them).
 extern "C" int kch_short_conv_step(const void* x, void* lookback, const void* weight, const void* bias, void* y,

@@ -489,22 +489,9 @@ topk_select_kernel(const float* __restrict__ logits, int32_t* __restrict__ out, 
       const int shift = 24 - 8 * pass;
       hist[tid] = 0;
       __syncthreads();
-      // long rows (decode over a whole cache): the logits crowd into a few bins of the leading bytes, so lanes
-      // that hit the same bin are counted with one atomic (match.any) instead of serialising on one word
-      if (E >= 64) {
-        for (int k = 0; k < E; ++k) {
-          const uint32_t u = k < cnt_mine ? f2ord(val(k)) : 0u;
-          if (k < cnt_mine && (u & pmask) == prefix) {
-            const int bin2 = (u >> shift) & 255;
-            const unsigned peers = __match_any_sync(__activemask(), bin2);
-            if ((threadIdx.x & 31) == __ffs(peers) - 1) atomicAdd(&hist[bin2], __popc(peers));
-          }
-        }
-      } else {
-        for (int k = 0; k < cnt_mine; ++k) {
-          const uint32_t u = f2ord(val(k));
-          if ((u & pmask) == prefix) atomicAdd(&hist[(u >> shift) & 255], 1);
-        }
+      for (int k = 0; k < cnt_mine; ++k) {
+        uint32_t u = f2ord(val(k));
+        if ((u & pmask) == prefix) atomicAdd(&hist[(u >> shift) & 255], 1);
       }
       __syncthreads();
       // thread t looks at bin 255-t: an exclusive scan gives the population of all higher bins

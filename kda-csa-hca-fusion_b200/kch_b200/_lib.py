@@ -94,6 +94,7 @@ PROTOTYPES = {
     "kch_decode_indexer_topk": (_i, [_vp, _i, _i64, _vp, _i, _vp, _vp, _i, _i64, _vp, _i, _i64, _i, _i, _i, _i, _f, _i, _vp,
                                      _vp, _i64, _vp]),
     "kch_short_conv_step": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
+    "kch_layernorm_short_conv": (_i, [_vp, _vp, _vp, _f, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp]),
     "kch_attend_decode_splits": (_i, [_i]),
     "kch_attend_decode_workspace_bytes": (_i64, [_i, _i, _i]),
     "kch_attend_decode": (_i, [C.POINTER(AttendDecodeArgs), _vp]),

@@ -121,6 +121,30 @@ def short_conv(x, weight, bias, lookback=None):
     return y
 
 
+def layernorm_short_conv_ok(x, lookback):
+    B, T, d = x.shape
+    return (x.is_cuda and x.dtype == torch.bfloat16 and T >= 2 and d % 256 == 0 and d <= 2048
+            and (lookback is None or (lookback.dtype == x.dtype and tuple(lookback.shape) == (B, 2, d))))
+
+
+def layernorm_short_conv(x, ln_weight, ln_bias, eps, weight, bias, lookback=None):
+    """``short_conv(layernorm(x))`` in one pass; returns ``(y, last two normalised rows [B,2,d])``."""
+    lib = _lib.load()
+    B, T, d = x.shape
+    x = x.contiguous()
+    w = weight.reshape(d, 3).to(x.dtype).contiguous()
+    b = bias.to(x.dtype).contiguous()
+    lb = None if lookback is None else lookback.contiguous()
+    lw, lbias = ln_weight.contiguous(), ln_bias.contiguous()
+    y = torch.empty_like(x)
+    new_lb = torch.empty(B, 2, d, dtype=x.dtype, device=x.device)
+    with torch.cuda.device(x.device):
+        _lib.check(lib.kch_layernorm_short_conv(_lib.ptr(x), _lib.ptr(lw), _lib.ptr(lbias), float(eps), _lib.ptr(lb),
+                                                _lib.ptr(w), _lib.ptr(b), _lib.ptr(y), _lib.ptr(new_lb), B, T, d,
+                                                _lib.dtype_tag(x.dtype), _lib.dtype_tag(lw.dtype), _lib.stream()))
+    return y, new_lb
+
+
 def short_conv_step(x, weight, bias, lookback):
     """One-token conv step: x ``[B,1,d]``; ``lookback [B,2,d]`` (same dtype, contiguous) slides by one token in place."""
     lib = _lib.load()
@@ -208,22 +232,30 @@ class KDAHybridLayer(nn.Module):
     def reset_conv_state(self):
         self._conv_lookback = None
 
-    def forward(self, x, state=None, residual=None, state_out=None, lookback_in_place=False):
+    def forward(self, x, state=None, residual=None, state_out=None, lookback_in_place=False, norm=None):
         o, new_state, lb = self.forward_functional(x, state, self._conv_lookback, residual=residual,
-                                                   state_out=state_out, lookback_in_place=lookback_in_place)
+                                                   state_out=state_out, lookback_in_place=lookback_in_place, norm=norm)
         self._conv_lookback = lb
         return o, new_state
 
-    def project(self, x, conv_lookback, lookback_in_place=False):
+    def project(self, x, conv_lookback, lookback_in_place=False, norm=None):
         """conv + fused projection + activations -> (q, k, v, g, beta, new_lookback).  With
-        ``lookback_in_place`` a one-token call slides ``conv_lookback`` where it lies and returns it."""
+        ``lookback_in_place`` a one-token call slides ``conv_lookback`` where it lies and returns it.
+        ``norm``: the sub-layer's pre-norm when ``x`` is the un-normalised residual stream; LayerNorm and the
+        convolution then run as one kernel where the shape allows."""
         cfg = self.cfg
         B, T, d = x.shape
         H, HV, K, V = cfg.n_heads_qk, cfg.n_heads_v, cfg.head_dim_k, cfg.head_dim_v
         lb = conv_lookback
         if lb is not None and lb.shape[0] != B:
             lb = None
-        if (lookback_in_place and T == 1 and lb is not None and lb.dtype == x.dtype and lb.is_contiguous()
+        fused_norm = norm is not None and layernorm_short_conv_ok(x, lb)
+        if norm is not None and not fused_norm:
+            x = norm(x)
+        if fused_norm:
+            xc, new_lb = layernorm_short_conv(x, norm.weight, norm.bias, norm.eps, self.short_conv.weight,
+                                              self.short_conv.bias, lb)
+        elif (lookback_in_place and T == 1 and lb is not None and lb.dtype == x.dtype and lb.is_contiguous()
                 and tuple(lb.shape) == (B, 2, d)):
             xc = short_conv_step(x, self.short_conv.weight, self.short_conv.bias, lb)
             new_lb = lb
@@ -248,11 +280,11 @@ class KDAHybridLayer(nn.Module):
                 g.view(B, T, HV, K), beta, new_lb)
 
     def forward_functional(self, x, state, conv_lookback, *, detach_lookback=True, residual=None, state_out=None,
-                           lookback_in_place=False):
+                           lookback_in_place=False, norm=None):
         cfg = self.cfg
         B, T, _ = x.shape
         HV, V = cfg.n_heads_v, cfg.head_dim_v
-        q, k, v, g, beta, new_lb = self.project(x, conv_lookback, lookback_in_place)
+        q, k, v, g, beta, new_lb = self.project(x, conv_lookback, lookback_in_place, norm)
         use_chunk = cfg.kda_chunk_size >= 1 and T >= cfg.kda_chunk_size
         o, new_state = kda_forward(q, k, v, g, beta, scale=self._scale_value(), initial_state=state,
                                    output_final_state=True, chunk_size=cfg.kda_chunk_size, use_chunk=use_chunk,
@@ -410,14 +442,14 @@ class HybridKCHAttention(nn.Module):
         ki = 0
         new_lbs = []
         for layer, norm, kind in zip(self.layers, self.norms, self.layout):
-            h = norm(x)
             if kind == "kda":
-                x, st, lb = layer.forward_functional(h, states[ki], lookbacks[ki], residual=x)
+                # the pre-norm goes into the layer: LayerNorm + short conv are one kernel there
+                x, st, lb = layer.forward_functional(x, states[ki], lookbacks[ki], residual=x, norm=norm)
                 states[ki] = st
                 new_lbs.append(lb)
                 ki += 1
             else:
-                x, _ = layer(h, None, residual=x)
+                x, _ = layer(norm(x), None, residual=x)
         new_state = torch.stack(states, dim=0) if self.n_kda_layers > 0 else None
         return x, new_state, new_lbs
 
@@ -606,17 +638,16 @@ class HybridDecoding(nn.Module):
         for i, (layer, norm, kind) in enumerate(zip(model.layers, model.norms, model.layout)):
             if T == 0:
                 continue
-            h = norm(x)
             if kind == "kda":
                 # in place: the state and the conv lookback keep their addresses from token to token
-                x, st = layer(h, states[ki], residual=x, state_out=states[ki] if in_place else None,
-                              lookback_in_place=in_place)
+                x, st = layer(x, states[ki], residual=x, state_out=states[ki] if in_place else None,
+                              lookback_in_place=in_place, norm=norm)
                 states[ki] = st
                 ki += 1
             elif kind == "csa":
-                x = self._csa(i, layer, h, x)
+                x = self._csa(i, layer, norm(x), x)
             else:
-                x = self._hca(i, layer, h, x)
+                x = self._hca(i, layer, norm(x), x)
         if T > 0 and not in_place:
             model._kda_state = torch.stack(states, dim=0) if model.n_kda_layers > 0 else None
         return x
