@@ -8,8 +8,9 @@
 Workload ("hybrid_prefill_c4"): the 5-layer KDA-KDA-KDA-CSA-HCA stack, d_model 2048, 16 heads x 128,
 KDA chunk 64, CSA m=4 / top-k 1024 / 4x64 indexer / window 128 / sink, HCA ratio 128 / window 128 / sink,
 bf16, batch 4 x T=32768 of synthetic N(0,1) hidden states, random-init N(0,0.02) weights.  One step is
-one forward pass over the whole batch.  With N > 1 the heads are tensor-parallel across the GPUs (total
-work fixed: strong scaling) with one all-gather of head outputs per layer.
+one forward pass over the whole batch.  With N > 1 the total work stays fixed (strong scaling): the sequences of
+the batch are dealt out to the GPUs first (no exchange on the data path), and GPUs beyond the batch size split the
+heads of their sequences (tensor parallel, one all-gather of head outputs per layer); `--tp-only` shards heads only.
 
 The JSON line carries: the device-timed value, `e2e` (host buffers, H2D + D2H inside the timed region,
 through the public module API), `roofline` for the dominant kernel (the tcgen05 GEMM) measured with CUDA
@@ -41,6 +42,7 @@ C4 = dict(d_model=2048, n_heads_qk=16, n_heads_v=16, head_dim_k=128, head_dim_v=
           hca_nh=16, hca_c=128, hca_dc=128, hca_sliding_window=128, n_kda=3, n_csa=1, n_hca=1)
 LAYERS = 5
 SEED = 3
+NCU_GEMM_DRAM_BYTES_M16384 = 101.9e6    # dram__bytes_read.sum + dram__bytes_write.sum, one o_proj-shaped launch
 
 
 def algorithmic_flops_per_token(cfg, T):
@@ -274,14 +276,30 @@ def run_b200(args):
     B, T = args.batch, args.seq_len
     cfg = kch_b200.HybridConfig(**C4)
     params = syn.hybrid_params(SEED, cfg, LAYERS, dtype=torch.bfloat16)
-    if world > 1:
-        model = build_tp_model(cfg, params, LAYERS, TPContext(rank, world, None), dev, torch.bfloat16)
+    # N GPUs: the sequences of the batch are independent, so they are dealt out first (dp ranks, no exchange on
+    # the data path); GPUs beyond the batch size split the heads of their sequences (tp ranks, one all-gather
+    # of head outputs per layer inside each tp group).  The total work stays that of one B x T batch.
+    dp = 1
+    while dp * 2 <= world and B % (dp * 2) == 0 and world % (dp * 2) == 0 and not args.tp_only:
+        dp *= 2
+    tp = world // dp
+    dp_rank, tp_rank = rank // tp, rank % tp
+    tp_group = None
+    if tp > 1 and dp > 1:
+        for g in range(dp):                                   # every rank creates every group, in the same order
+            grp = dist.new_group(list(range(g * tp, (g + 1) * tp)))
+            if g == dp_rank:
+                tp_group = grp
+    if tp > 1:
+        model = build_tp_model(cfg, params, LAYERS, TPContext(tp_rank, tp, tp_group), dev, torch.bfloat16)
     else:
         model = kch_b200.HybridKCHAttention(cfg, LAYERS)
         model.load_state_dict(params, strict=True)
         model = model.bfloat16().to(dev).eval()
     del params
-    x_host = syn.hidden_states(SEED, B, T, cfg.d_model, torch.bfloat16).pin_memory()
+    B_local = B // dp
+    x_host = syn.hidden_states(SEED, B, T, cfg.d_model, torch.bfloat16)[dp_rank * B_local:(dp_rank + 1) * B_local]
+    x_host = x_host.contiguous().pin_memory()
     x = x_host.to(dev)
 
     probe = GemmProbe()
@@ -325,7 +343,7 @@ def run_b200(args):
 
     # end to end through the public host-buffer API: every step uploads its input from pinned host memory and
     # downloads its output; HostPipeline overlaps those copies with the neighbouring steps' kernels
-    y_host = torch.empty(B, T, cfg.d_model, dtype=torch.bfloat16).pin_memory()
+    y_host = torch.empty(B_local, T, cfg.d_model, dtype=torch.bfloat16).pin_memory()
     e2e_steps = max(1, args.steps)
     pipe = kch_b200.HostPipeline(model, dev)
     pipe.run([x_host], [y_host])
@@ -366,15 +384,20 @@ def run_b200(args):
             "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic",
             "config": {"workload": "hybrid_prefill_c4", "B": B, "T": T, "layers": LAYERS, "layout": model.layout_str(),
-                       "parallelism": f"tp{world}_by_heads", "l2": "inputs larger than L2 (537 MB hidden states)", **C4},
-            "e2e": {"value": tokens / (e2e_ms / 1e3), "unit": UNIT, "h2d_bytes_per_step": x_host.numel() * 2,
-                    "d2h_bytes_per_step": y_host.numel() * 2, "steps": e2e_steps, "ms_per_step": e2e_ms,
+                       "parallelism": ("single_gpu" if world == 1 else (f"dp{dp}_sequences" if tp == 1 else (
+                           f"tp{tp}_heads" if dp == 1 else f"dp{dp}_sequences_x_tp{tp}_heads"))), "l2": "inputs larger than L2 (537 MB hidden states)", **C4},
+            "e2e": {"value": tokens / (e2e_ms / 1e3), "unit": UNIT, "h2d_bytes_per_step": x_host.numel() * 2 * dp,
+                    "d2h_bytes_per_step": y_host.numel() * 2 * dp, "steps": e2e_steps, "ms_per_step": e2e_ms,
                     "api": "kch_b200.HostPipeline.run (pinned host in / out, copies overlapped with the passes)",
                     "ms_per_step_without_overlap": e2e_serial_ms},
             "gpu_launches": launches,
             "roofline": {"bound": "tensor", "kernel": "gemm_tcgen05_kernel (all dense projections)",
                          "achieved": achieved, "peak": peak_tf, "unit": "TFLOP/s", "frac": achieved / peak_tf,
-                         "peak_source": peak_src, "traffic": None, "launches": gemm_calls,
+                         "peak_source": peak_src, "traffic": NCU_GEMM_DRAM_BYTES_M16384 * (B * T / 16384.0),
+                         "traffic_note": "DRAM bytes (read + write) of one N=2048 K=2048 launch: ncu capture at M=16384 "
+                                         "(profiles/gemm_tcgen05_M16384_N2048_K2048.md), scaled by M to this batch; the "
+                                         "algorithmic bytes of that launch are 2(MK + NK + MN)",
+                         "launches": gemm_calls,
                          "flops_per_step": gemm_flops / max(1, args.steps), "ms_per_step": gemm_ms / max(1, args.steps),
                          "shapes": probe.by_shape()},
             "layer_roofline": {"flops_per_token": fpt, "achieved_tflops": value * fpt / 1e12,
@@ -401,6 +424,7 @@ def main():
     ap.add_argument("--seq-len", type=int, default=32768)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-decode", action="store_true")
+    ap.add_argument("--tp-only", action="store_true", help="N > 1: shard heads only (no sequence sharding)")
     ap.add_argument("--decode-batch", type=int, default=64)
     ap.add_argument("--decode-context", type=int, default=131072)
     ap.add_argument("--decode-steps", type=int, default=256)

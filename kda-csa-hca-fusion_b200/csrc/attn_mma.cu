@@ -5,18 +5,18 @@
 //   S[16 heads x 8 keys]  = Q[16 x 128] . X^T        (8 k-steps per 8 keys)
 //   O[16 heads x 128]    += P[16 x 16 keys] . X      (values are the keys)
 // The gathered key rows (selected compressed entries, or the dense visible prefix, then the window
-// rows) are streamed L2 -> shared memory with 16-byte cp.async in a 3-stage ring of 32-row tiles, XOR
+// rows) are streamed L2 -> shared memory with 16-byte cp.async in a 2-stage ring of 32-row tiles, XOR
 // swizzled so ldmatrix (plain for S, .trans for P.X) is conflict-free.  Because q and the keys are unit
 // vectors, |s| <= |scale|, so the softmax uses the fixed shift max(|scale|, sink_h) instead of a running
 // maximum; invalid slots get p = 0 and their rows are zero-filled.
 // Bound: the gather, 256 B per (query, entry) out of L2; tensor work is 4*16*128 flop per entry.
 #include <math.h>
+#include <stdlib.h>
 
 #include "kch_common.cuh"
 
 #define AM_WARPS 4
 #define AM_TILE 32
-#define AM_STAGES 3
 #define AM_C 128
 #define AM_QLD 136   // padded row of the per-warp query tile (bf16 elements)
 
@@ -60,7 +60,8 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&h);
 }
 
-__global__ void __launch_bounds__(AM_WARPS * 32) attn_mma_kernel(AttnMmaArgs a) {
+template <int AM_STAGES, int MINB>
+__global__ void __launch_bounds__(AM_WARPS * 32, MINB) attn_mma_kernel(AttnMmaArgs a) {
   extern __shared__ __align__(128) uint8_t smem_raw[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int64_t bt = (int64_t)blockIdx.x * AM_WARPS + warp;
@@ -251,11 +252,22 @@ int kch_attend_mma(const kch_attend_args* p, void* stream) {
   a.win_size = has_win ? p->sliding_window : 0;
   a.sink = p->sink; a.sink_dtype = p->sink_dtype; a.scale = p->scale; a.out = (bf16*)p->out;
   static_assert(16 * AM_QLD * 2 <= AM_TILE * AM_C * 2, "query staging tile must fit one ring stage");
-  size_t smem = (size_t)AM_WARPS * (AM_STAGES * AM_TILE * AM_C * 2);
-  KCH_CUDA_OK(cudaFuncSetAttribute(attn_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   int64_t nq = (int64_t)p->B * p->T;
   unsigned grid = (unsigned)((nq + AM_WARPS - 1) / AM_WARPS);
-  attn_mma_kernel<<<grid, AM_WARPS * 32, smem, kch_stream(stream)>>>(a);
+  // ring depth / resident CTAs per SM: two stages and three CTAs per SM (168 registers) measured fastest on
+  // B200 (7.1 ms vs 8.0 ms for three stages / two CTAs at the benchmark size); KCH_ATTN_CFG = 0 | 2 selects
+  // (3 stages, 2 CTAs) | (2 stages, 4 CTAs) for experiments
+  static const int cfg = [] { const char* e = getenv("KCH_ATTN_CFG"); return e ? atoi(e) : 1; }();
+#define AM_GO(ST, MB)                                                                                          \
+  do {                                                                                                         \
+    size_t smem = (size_t)AM_WARPS * (ST * AM_TILE * AM_C * 2);                                                \
+    KCH_CUDA_OK(cudaFuncSetAttribute(attn_mma_kernel<ST, MB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+    attn_mma_kernel<ST, MB><<<grid, AM_WARPS * 32, smem, kch_stream(stream)>>>(a);                             \
+  } while (0)
+  if (cfg == 1) AM_GO(2, 3);
+  else if (cfg == 2) AM_GO(2, 4);
+  else AM_GO(3, 2);
+#undef AM_GO
   KCH_LAUNCH_OK();
   return KCH_OK;
 }
