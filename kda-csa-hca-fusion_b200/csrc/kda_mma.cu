@@ -51,14 +51,17 @@ struct PrepArgs {
 };
 
 // shared-memory map of the prepare kernel (bytes)
-#define PS_G 0                                  // gamma fp32 [64][128]            32768
-#define PS_A (PS_G + 32768)                     // A fp32 [64][68]                 17408
+#define PS_GLD 136                              // gamma row stride (floats): fragment-pattern reads are conflict-free
+#define PS_G 0                                  // gamma fp32 [64][136]            34816
+#define PS_A (PS_G + 34816)                     // A fp32 [64][68]                 17408
 #define PS_T (PS_A + 17408)                     // (I+A)^-1 fp32 [64][68]          17408
-#define PS_ST (PS_T + 17408)                    // 6 staging tiles [16][128] bf16  24576
+#define PS_ST (PS_T + 17408)                    // first 24576 bytes of the e^gamma k tiles (see PS_EK)
 #define PS_Q (PS_ST + 24576)                    // Aqk fp32 [64][68]               17408
 #define PS_BETA (PS_Q + 17408)                  // beta [64], scratch P [3][16][17]
 #define PS_TOTAL (PS_BETA + 256 + 3 * 16 * 17 * 4)
 #define PS_LD 68
+#define PS_KLD 136                              // row stride of the bf16 k / q tiles (elements)
+#define PS_KQ PS_T                              // k then q tile [64][136] bf16, 2 x 17408 bytes (over T + ST)
 // aliases (valid after the producers of the aliased regions are dead)
 #define PS_EK PS_ST                             // e^gamma k hi [64][128] bf16 then lo   (over ST + Q)
 #define PS_V PS_G                               // v bf16 [64][128]                     (over gamma, first half)
@@ -100,12 +103,12 @@ __global__ void __launch_bounds__(256, 2) kda_prepare_mma_kernel(PrepArgs a) {
     load8(a.g + g_off(i) + 8 * ch, t0 + i < a.T, gv);
 #pragma unroll
     for (int x = 0; x < 8; ++x) gv[x] = (t0 + i < a.T) ? fmaxf(gv[x], a.g_min) * KM_LOG2E : 0.f;
-    float4* dst = reinterpret_cast<float4*>(sG + i * KM_K + 8 * ch);
+    float4* dst = reinterpret_cast<float4*>(sG + i * PS_GLD + 8 * ch);
     dst[0] = make_float4(gv[0], gv[1], gv[2], gv[3]);
     dst[1] = make_float4(gv[4], gv[5], gv[6], gv[7]);
   }
   if (tid < KM_C) sbeta[tid] = (t0 + tid < a.T) ? __bfloat162float(a.beta[((int64_t)b * a.T + t0 + tid) * a.ld_b + hv]) : 0.f;
-  for (int idx = tid; idx < KM_C * PS_LD; idx += 256) { sA[idx] = 0.f; sQ[idx] = 0.f; sT[idx] = 0.f; }
+  for (int idx = tid; idx < KM_C * PS_LD; idx += 256) { sA[idx] = 0.f; sQ[idx] = 0.f; }
   // Every elementwise stage below maps thread -> (row r0 + 16*s, 8-channel chunk c8) with r0 = tid/16 and
   // c8 = tid%16, so the k and q values a thread ever needs are these 4 x 8: keep them in registers.
   const int r0 = tid >> 4, c8 = tid & 15;
@@ -120,6 +123,16 @@ __global__ void __launch_bounds__(256, 2) kda_prepare_mma_kernel(PrepArgs a) {
       qreg[s4] = *reinterpret_cast<const uint4*>(a.q + qk_off(i) + 8 * c8);
     }
   }
+  // the same rows as bf16 tiles in shared memory for the fragment-pattern reads of the A / Aqk stage (row stride
+  // 136 elements: conflict-free); they live over T and the e^gamma k area, both unused until that stage is over
+  bf16* sKt = reinterpret_cast<bf16*>(sm + PS_KQ);
+  bf16* sQt = sKt + KM_C * PS_KLD;
+#pragma unroll
+  for (int s4 = 0; s4 < 4; ++s4) {
+    const int i = r0 + 16 * s4;
+    *reinterpret_cast<uint4*>(sKt + i * PS_KLD + 8 * c8) = kreg[s4];
+    *reinterpret_cast<uint4*>(sQt + i * PS_KLD + 8 * c8) = qreg[s4];
+  }
   auto unpack8 = [](const uint4& raw, float (&out)[8]) {
     const bf16* e = reinterpret_cast<const bf16*>(&raw);
 #pragma unroll
@@ -130,121 +143,82 @@ __global__ void __launch_bounds__(256, 2) kda_prepare_mma_kernel(PrepArgs a) {
     float acc = 0.f;
 #pragma unroll 8
     for (int i = 0; i < KM_C; ++i) {
-      acc += sG[i * KM_K + tid];
-      sG[i * KM_K + tid] = acc;
+      acc += sG[i * PS_GLD + tid];
+      sG[i * PS_GLD + tid] = acc;
     }
   }
   __syncthreads();
 
   // ---- A and Aqk, block by block ------------------------------------------------------------------
-  // staging tiles: 0 Krow hi, 1 Krow lo, 2 Qrow hi, 3 Qrow lo, 4 Kcol hi, 5 Kcol lo ([16][128] bf16, swizzled)
-  uint8_t* st = sm + PS_ST;
-  const int pa[10] = {0, 1, 2, 3, 1, 2, 3, 2, 3, 3};
-  const int pb[10] = {0, 1, 2, 3, 0, 1, 2, 0, 1, 0};
-  for (int p = 0; p < 10; ++p) {
-    const int ba = pa[p], bb = pb[p];
-    {
-      const int r = tid >> 4, ch = tid & 15;
+  // 40 independent warp tasks (block pair, 8-column half, contraction half): a warp builds its operand fragments in
+  // registers, straight in the mma.sync layout, from gamma (shared memory) and the bf16 rows of k / q (L1), so
+  // the whole stage needs no staging tiles and no block barrier.  Row operand: x_i e^{gamma_i - gamma_ref};
+  // column operand: k_j e^{gamma_ref - gamma_j}; ref is the middle row of a diagonal block, else the last row of
+  // the column block, which keeps both factors representable for every log-decay down to -10 per token.
+  {
+    const int pa[10] = {0, 1, 2, 3, 1, 2, 3, 2, 3, 3};
+    const int pb[10] = {0, 1, 2, 3, 0, 1, 2, 0, 1, 0};
+    auto lo16 = [](uint32_t u) { return __uint_as_float(u << 16); };
+    auto hi16 = [](uint32_t u) { return __uint_as_float(u & 0xFFFF0000u); };
+    for (int task = warp; task < 40; task += 8) {
+      // task = (block pair, 8-column half, half of the contraction): A and Aqk together, since they share the
+      // column operand and every decay factor; the two contraction halves meet through shared-memory adds
+      const int p = task >> 2, nt = (task >> 1) & 1, khalf = task & 1;
+      const int ba = pa[p], bb = pb[p];
       const int refrow = (ba == bb) ? (16 * ba + 8) : (16 * bb + 15);
-      const int i = 16 * ba + r, jr = 16 * bb + r;
-      float ref[8], gi[8], kv[8], qv[8];
-      {
-        const float4* p4 = reinterpret_cast<const float4*>(sG + refrow * KM_K + 8 * ch);
-        float4 x = p4[0], y = p4[1];
-        ref[0] = x.x; ref[1] = x.y; ref[2] = x.z; ref[3] = x.w; ref[4] = y.x; ref[5] = y.y; ref[6] = y.z; ref[7] = y.w;
-        p4 = reinterpret_cast<const float4*>(sG + i * KM_K + 8 * ch);
-        x = p4[0]; y = p4[1];
-        gi[0] = x.x; gi[1] = x.y; gi[2] = x.z; gi[3] = x.w; gi[4] = y.x; gi[5] = y.y; gi[6] = y.z; gi[7] = y.w;
+      const int i0 = 16 * ba + g4, i1 = i0 + 8;          // accumulator / row-operand rows of this thread
+      const int jn = 16 * bb + 8 * nt + g4;              // the k row that is column g4 of the column operand
+      const bf16* k0p = sKt + i0 * PS_KLD;
+      const bf16* k1p = sKt + i1 * PS_KLD;
+      const bf16* q0p = sQt + i0 * PS_KLD;
+      const bf16* q1p = sQt + i1 * PS_KLD;
+      const bf16* cjp = sKt + jn * PS_KLD;
+      const float* gref = sG + refrow * PS_GLD;
+      const float* gi0 = sG + i0 * PS_GLD;
+      const float* gi1 = sG + i1 * PS_GLD;
+      const float* gj = sG + jn * PS_GLD;
+      float c0[4] = {0.f, 0.f, 0.f, 0.f}, c1[4] = {0.f, 0.f, 0.f, 0.f}, c2[4] = {0.f, 0.f, 0.f, 0.f};
+      float d0[4] = {0.f, 0.f, 0.f, 0.f}, d1[4] = {0.f, 0.f, 0.f, 0.f}, d2[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 2
+      for (int ks = 4 * khalf; ks < 4 * khalf + 4; ++ks) {
+        uint32_t ah[4], al[4], qh[4], ql[4], bh[2], bl[2];
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {             // k index pairs 16ks + 2j4 (+8)
+          const int kk = 16 * ks + 8 * half + 2 * j4;
+          const float2 gr = *reinterpret_cast<const float2*>(gref + kk);
+          const float2 g0 = *reinterpret_cast<const float2*>(gi0 + kk);
+          const float2 g1 = *reinterpret_cast<const float2*>(gi1 + kk);
+          const float2 gc = *reinterpret_cast<const float2*>(gj + kk);
+          const uint32_t x0 = *reinterpret_cast<const uint32_t*>(k0p + kk);
+          const uint32_t x1 = *reinterpret_cast<const uint32_t*>(k1p + kk);
+          const uint32_t y0 = *reinterpret_cast<const uint32_t*>(q0p + kk);
+          const uint32_t y1 = *reinterpret_cast<const uint32_t*>(q1p + kk);
+          const uint32_t xc = *reinterpret_cast<const uint32_t*>(cjp + kk);
+          const float e0x = ex2_fast(g0.x - gr.x), e0y = ex2_fast(g0.y - gr.y);
+          const float e1x = ex2_fast(g1.x - gr.x), e1y = ex2_fast(g1.y - gr.y);
+          split2_bf16(lo16(x0) * e0x, hi16(x0) * e0y, ah[2 * half], al[2 * half]);
+          split2_bf16(lo16(x1) * e1x, hi16(x1) * e1y, ah[2 * half + 1], al[2 * half + 1]);
+          split2_bf16(lo16(y0) * a.scale * e0x, hi16(y0) * a.scale * e0y, qh[2 * half], ql[2 * half]);
+          split2_bf16(lo16(y1) * a.scale * e1x, hi16(y1) * a.scale * e1y, qh[2 * half + 1], ql[2 * half + 1]);
+          split2_bf16(lo16(xc) * ex2_fast(gr.x - gc.x), hi16(xc) * ex2_fast(gr.y - gc.y), bh[half], bl[half]);
+        }
+        mma_bf16_16816(c0, ah, bh[0], bh[1]);
+        mma_bf16_16816(d0, qh, bh[0], bh[1]);
+        mma_bf16_16816(c1, al, bh[0], bh[1]);
+        mma_bf16_16816(d1, ql, bh[0], bh[1]);
+        mma_bf16_16816(c2, ah, bl[0], bl[1]);
+        mma_bf16_16816(d2, qh, bl[0], bl[1]);
       }
-      // (compile-time register selection: ba, bb are uniform, the switch keeps kreg/qreg in registers)
-      switch (ba) {
-        case 0: unpack8(kreg[0], kv); unpack8(qreg[0], qv); break;
-        case 1: unpack8(kreg[1], kv); unpack8(qreg[1], qv); break;
-        case 2: unpack8(kreg[2], kv); unpack8(qreg[2], qv); break;
-        default: unpack8(kreg[3], kv); unpack8(qreg[3], qv); break;
-      }
-      uint32_t kh[4], kl[4], qh[4], ql[4], ch_[4], cl_[4];
+      const int jc = 16 * bb + 8 * nt + 2 * j4;
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
-        const float e0 = ex2_fast(gi[2 * e] - ref[2 * e]), e1 = ex2_fast(gi[2 * e + 1] - ref[2 * e + 1]);
-        split2_bf16(kv[2 * e] * e0, kv[2 * e + 1] * e1, kh[e], kl[e]);
-        split2_bf16(qv[2 * e] * a.scale * e0, qv[2 * e + 1] * a.scale * e1, qh[e], ql[e]);
-      }
-      float gj[8], kc[8];
-      if (ba == bb) {
-#pragma unroll
-        for (int x = 0; x < 8; ++x) { gj[x] = gi[x]; kc[x] = kv[x]; }
-      } else {
-        const float4* p4 = reinterpret_cast<const float4*>(sG + jr * KM_K + 8 * ch);
-        float4 x = p4[0], y = p4[1];
-        gj[0] = x.x; gj[1] = x.y; gj[2] = x.z; gj[3] = x.w; gj[4] = y.x; gj[5] = y.y; gj[6] = y.z; gj[7] = y.w;
-        switch (bb) {
-          case 0: unpack8(kreg[0], kc); break;
-          case 1: unpack8(kreg[1], kc); break;
-          default: unpack8(kreg[2], kc); break;
-        }
-      }
-#pragma unroll
-      for (int e = 0; e < 4; ++e)
-        split2_bf16(kc[2 * e] * ex2_fast(ref[2 * e] - gj[2 * e]), kc[2 * e + 1] * ex2_fast(ref[2 * e + 1] - gj[2 * e + 1]),
-                    ch_[e], cl_[e]);
-      const uint32_t off = swz<256>(r, ch);
-      *reinterpret_cast<uint4*>(st + 0 * 4096 + off) = make_uint4(kh[0], kh[1], kh[2], kh[3]);
-      *reinterpret_cast<uint4*>(st + 1 * 4096 + off) = make_uint4(kl[0], kl[1], kl[2], kl[3]);
-      *reinterpret_cast<uint4*>(st + 2 * 4096 + off) = make_uint4(qh[0], qh[1], qh[2], qh[3]);
-      *reinterpret_cast<uint4*>(st + 3 * 4096 + off) = make_uint4(ql[0], ql[1], ql[2], ql[3]);
-      *reinterpret_cast<uint4*>(st + 4 * 4096 + off) = make_uint4(ch_[0], ch_[1], ch_[2], ch_[3]);
-      *reinterpret_cast<uint4*>(st + 5 * 4096 + off) = make_uint4(cl_[0], cl_[1], cl_[2], cl_[3]);
-    }
-    __syncthreads();
-    {
-      // 8 warps: (A | Aqk) x (column tile) x (half of the 8 k-steps); three independent accumulator chains
-      // per warp (hi.hi, lo.hi, hi.lo); the two k-halves meet in shared memory through atomic adds.
-      const int nt = warp & 1, which = (warp >> 1) & 1, khalf = warp >> 2;
-      const uint32_t rhi = smem_addr_u32(st + (which ? 2 : 0) * 4096), rlo = rhi + 4096;
-      const uint32_t chi = smem_addr_u32(st + 4 * 4096), clo = chi + 4096;
-      float a0[4] = {0.f, 0.f, 0.f, 0.f}, a1[4] = {0.f, 0.f, 0.f, 0.f}, a2[4] = {0.f, 0.f, 0.f, 0.f};
-      const int arow = (lane & 7) + ((lane >> 3) & 1) * 8;
-      const int brow = 8 * nt + (lane & 7);
-#pragma unroll
-      for (int q2 = 0; q2 < 2; ++q2) {
-        const int qd = 2 * khalf + q2;
-        uint32_t ah[2][4], al[2][4], bh_[4], bl_[4];
-#pragma unroll
-        for (int kk = 0; kk < 2; ++kk) {
-          const uint32_t o = swz<256>(arow, 2 * (2 * qd + kk) + (lane >> 4));
-          ldmatrix_x4(rhi + o, ah[kk][0], ah[kk][1], ah[kk][2], ah[kk][3]);
-          ldmatrix_x4(rlo + o, al[kk][0], al[kk][1], al[kk][2], al[kk][3]);
-        }
-        const uint32_t ob = swz<256>(brow, 4 * qd + (lane >> 3));
-        ldmatrix_x4(chi + ob, bh_[0], bh_[1], bh_[2], bh_[3]);
-        ldmatrix_x4(clo + ob, bl_[0], bl_[1], bl_[2], bl_[3]);
-#pragma unroll
-        for (int kk = 0; kk < 2; ++kk) {
-          mma_bf16_16816(a0, ah[kk], bh_[2 * kk], bh_[2 * kk + 1]);
-          mma_bf16_16816(a1, al[kk], bh_[2 * kk], bh_[2 * kk + 1]);
-          mma_bf16_16816(a2, ah[kk], bl_[2 * kk], bl_[2 * kk + 1]);
-        }
-      }
-      float acc[4];
-#pragma unroll
-      for (int e = 0; e < 4; ++e) acc[e] = a0[e] + (a1[e] + a2[e]);
-      const int i0 = 16 * ba + g4, i1 = i0 + 8;
-      const int jc = 16 * bb + 8 * nt + 2 * j4;
-      if (which == 0) {
-        if (jc < i0) atomicAdd(&sA[i0 * PS_LD + jc], acc[0] * sbeta[i0]);
-        if (jc + 1 < i0) atomicAdd(&sA[i0 * PS_LD + jc + 1], acc[1] * sbeta[i0]);
-        if (jc < i1) atomicAdd(&sA[i1 * PS_LD + jc], acc[2] * sbeta[i1]);
-        if (jc + 1 < i1) atomicAdd(&sA[i1 * PS_LD + jc + 1], acc[3] * sbeta[i1]);
-      } else {
-        if (jc <= i0) atomicAdd(&sQ[i0 * PS_LD + jc], acc[0]);
-        if (jc + 1 <= i0) atomicAdd(&sQ[i0 * PS_LD + jc + 1], acc[1]);
-        if (jc <= i1) atomicAdd(&sQ[i1 * PS_LD + jc], acc[2]);
-        if (jc + 1 <= i1) atomicAdd(&sQ[i1 * PS_LD + jc + 1], acc[3]);
+        const int i = (e & 2) ? i1 : i0, jj = jc + (e & 1);
+        if (jj < i) atomicAdd(&sA[i * PS_LD + jj], (c0[e] + (c1[e] + c2[e])) * sbeta[i]);
+        if (jj <= i) atomicAdd(&sQ[i * PS_LD + jj], d0[e] + (d1[e] + d2[e]));
       }
     }
-    __syncthreads();
   }
+  __syncthreads();
 
   // ---- Aqk -> workspace as swizzled bf16 hi/lo tiles [64][64] --------------------------------------
   for (int idx = tid; idx < KM_C * 8; idx += 256) {
@@ -266,10 +240,10 @@ __global__ void __launch_bounds__(256, 2) kda_prepare_mma_kernel(PrepArgs a) {
     unpack8(kreg[it], kf);
     unpack8(qreg[it], qf);
     {
-      const float4* p4 = reinterpret_cast<const float4*>(sG + i * KM_K + 8 * ch);
+      const float4* p4 = reinterpret_cast<const float4*>(sG + i * PS_GLD + 8 * ch);
       float4 x = p4[0], y = p4[1];
       gm[0] = x.x; gm[1] = x.y; gm[2] = x.z; gm[3] = x.w; gm[4] = y.x; gm[5] = y.y; gm[6] = y.z; gm[7] = y.w;
-      p4 = reinterpret_cast<const float4*>(sG + (KM_C - 1) * KM_K + 8 * ch);
+      p4 = reinterpret_cast<const float4*>(sG + (KM_C - 1) * PS_GLD + 8 * ch);
       x = p4[0]; y = p4[1];
       gl[0] = x.x; gl[1] = x.y; gl[2] = x.z; gl[3] = x.w; gl[4] = y.x; gl[5] = y.y; gl[6] = y.z; gl[7] = y.w;
     }
@@ -290,13 +264,19 @@ __global__ void __launch_bounds__(256, 2) kda_prepare_mma_kernel(PrepArgs a) {
     *reinterpret_cast<uint4*>(sm + PS_EK + KM_TILE + off) = make_uint4(el[0], el[1], el[2], el[3]);
   }
   if (tid < KM_K) {
-    const float dl = ex2_fast(sG[(KM_C - 1) * KM_K + tid]);
+    const float dl = ex2_fast(sG[(KM_C - 1) * PS_GLD + tid]);
 #pragma unroll
     for (int s = 0; s < KM_V / 64; ++s)
       reinterpret_cast<float*>(wsc + KM_OFF_U + s * KM_U_SLICE + 16384)[tid] = dl;
   }
 
   // ---- (I + A)^-1 by block forward substitution (fp32, CUDA cores) ------------------------------------
+  // blocks above the diagonal are zero (the area held the k / q tiles until now); nothing else writes them
+  for (int idx = tid; idx < 6 * 256; idx += 256) {
+    const int bi = idx >> 8, r = (idx >> 4) & 15, cc = idx & 15;
+    const int ub_a[6] = {0, 0, 0, 1, 1, 2}, ub_b[6] = {1, 2, 3, 2, 3, 3};
+    sT[(16 * ub_a[bi] + r) * PS_LD + 16 * ub_b[bi] + cc] = 0.f;
+  }
   // diagonal 16x16 blocks: one thread per (block, column)
   if (tid < 64) {
     const int blk = tid >> 4, cc = tid & 15, base = 16 * blk;
