@@ -557,6 +557,139 @@ topk_select_kernel(const float* __restrict__ logits, int32_t* __restrict__ out, 
   for (int i = tid; i < nsel; i += 256) orow[i] = 0x7FFFFFFF - (int)(uint32_t)(ssort[i] & 0xFFFFFFFFu);
 }
 
+// Register variant for rows of up to 256*EPT logits (the prefill case: n_blocks <= 8192): thread t owns the
+// contiguous index range [t*E, (t+1)*E), E = ceil(nv/256) rounded up to 4, and keeps the order-preserving keys of
+// its logits in registers for all four radix passes, the counting and the ordered compaction: one 16-byte-vector
+// read of the row, no shared-memory staging.  Same selection rule and output as topk_select_kernel.
+template <int EPT>
+__global__ void __launch_bounds__(256)
+topk_select_reg_kernel(const float* __restrict__ logits, int32_t* __restrict__ out, int T, int n, int64_t n_ld,
+                       int topk, int m, int64_t t0, int nvis_fixed, int sorted) {
+  extern __shared__ __align__(16) uint8_t sel_smem[];
+  unsigned long long* ssort = reinterpret_cast<unsigned long long*>(sel_smem);
+  const int64_t row = blockIdx.x;
+  const int t = (int)(row % T);
+  const float* lg = logits + row * n_ld;
+  int32_t* orow = out + row * topk;
+  int64_t nv64 = nvis_fixed >= 0 ? nvis_fixed : (m > 0 ? (t0 + t + 1) / m : n);
+  const int nv = (int)(nv64 < n ? nv64 : n);
+  const int ksel = topk < n ? topk : n;
+  const int tid = threadIdx.x;
+  __shared__ int hist[256];
+  __shared__ int sbuf[9];
+  __shared__ uint32_t s_prefix;
+  __shared__ int s_need;
+  int nsel;
+  if (nv <= ksel) {
+    for (int i = tid; i < topk; i += 256) orow[i] = i < nv ? i : -1;
+    nsel = nv;
+  } else {
+    const int E = (((nv + 255) >> 8) + 3) & ~3;          // <= EPT by the host's choice of EPT
+    const int i0 = tid * E;
+    const int cnt_mine = max(0, min(E, nv - i0));
+    uint32_t u[EPT];
+#pragma unroll
+    for (int k4 = 0; k4 < EPT / 4; ++k4) {
+      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (4 * k4 < E && i0 + 4 * k4 < n_ld) v = *reinterpret_cast<const float4*>(lg + i0 + 4 * k4);   // row pad is readable
+      u[4 * k4] = f2ord(v.x); u[4 * k4 + 1] = f2ord(v.y); u[4 * k4 + 2] = f2ord(v.z); u[4 * k4 + 3] = f2ord(v.w);
+    }
+    uint32_t prefix = 0, pmask = 0;
+    int need = ksel;
+    for (int pass = 0; pass < 4; ++pass) {
+      const int shift = 24 - 8 * pass;
+      hist[tid] = 0;
+      __syncthreads();
+#pragma unroll
+      for (int k = 0; k < EPT; ++k)
+        if (k < cnt_mine && (u[k] & pmask) == prefix) atomicAdd(&hist[(u[k] >> shift) & 255], 1);
+      __syncthreads();
+      const int bin = 255 - tid;
+      const int cnt = hist[bin];
+      int tot;
+      const int cum = block_excl_scan(cnt, sbuf, &tot);
+      if (cum < need && cum + cnt >= need) {
+        s_prefix = prefix | ((uint32_t)bin << shift);
+        s_need = need - cum;
+      }
+      __syncthreads();
+      prefix = s_prefix;
+      need = s_need;
+      pmask |= 0xFFu << shift;
+    }
+    const int n_gt = ksel - need;
+    int c_gt = 0, c_eq = 0;
+#pragma unroll
+    for (int k = 0; k < EPT; ++k)
+      if (k < cnt_mine) { c_gt += (u[k] > prefix); c_eq += (u[k] == prefix); }
+    int tot_gt, tot_eq;
+    int p_gt = block_excl_scan(c_gt, sbuf, &tot_gt);
+    int p_eq = block_excl_scan(c_eq, sbuf, &tot_eq);
+#pragma unroll
+    for (int k = 0; k < EPT; ++k)
+      if (k < cnt_mine) {
+        if (u[k] > prefix) orow[p_gt++] = i0 + k;
+        else if (u[k] == prefix) { if (p_eq < need) orow[n_gt + p_eq] = i0 + k; ++p_eq; }
+      }
+    for (int i = ksel + tid; i < topk; i += 256) orow[i] = -1;
+    nsel = ksel;
+  }
+  if (!sorted) return;
+  __syncthreads();
+  int P = 1;
+  while (P < nsel) P <<= 1;
+  for (int i = tid; i < P; i += 256) {
+    unsigned long long key = 0ull;
+    if (i < nsel) {
+      int id = orow[i];
+      key = ((unsigned long long)f2ord(lg[id]) << 32) | (uint32_t)(0x7FFFFFFF - id);
+    }
+    ssort[i] = key;
+  }
+  __syncthreads();
+  for (int size = 2; size <= P; size <<= 1)
+    for (int stride = size >> 1; stride > 0; stride >>= 1) {
+      for (int i = tid; i < P; i += 256) {
+        int j = i ^ stride;
+        if (j > i) {
+          unsigned long long a = ssort[i], c = ssort[j];
+          bool desc = (i & size) == 0;
+          if (desc ? (a < c) : (a > c)) { ssort[i] = c; ssort[j] = a; }
+        }
+      }
+      __syncthreads();
+    }
+  for (int i = tid; i < nsel; i += 256) orow[i] = 0x7FFFFFFF - (int)(uint32_t)(ssort[i] & 0xFFFFFFFFu);
+}
+
+// shared launcher of the selection: register variant when a row fits 256 x 32 logits, else the staged one
+static int launch_topk_select(const float* logits, int32_t* indices, int B, int T, int n_blocks, int64_t n_ld, int topk,
+                              int m, int64_t t0, int n_visible, int sorted, size_t sort_smem, cudaStream_t s) {
+  const unsigned grid = (unsigned)((int64_t)B * T);
+  static const bool force_staged = [] { const char* e = getenv("KCH_SELECT"); return e && e[0] == 's'; }();
+  const int e_needed = (((n_blocks + 255) >> 8) + 3) & ~3;
+  if (!force_staged && e_needed <= 32 && (((uintptr_t)logits) & 15) == 0 && (n_ld % 4) == 0) {
+#define SEL_GO(EPT_)                                                                                              \
+    do {                                                                                                          \
+      if (sort_smem > 48 * 1024)                                                                                  \
+        KCH_CUDA_OK(cudaFuncSetAttribute(topk_select_reg_kernel<EPT_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sort_smem)); \
+      topk_select_reg_kernel<EPT_><<<grid, 256, sort_smem, s>>>(logits, indices, T, n_blocks, n_ld, topk, m, t0, n_visible, sorted); \
+    } while (0)
+    if (e_needed <= 8) SEL_GO(8);
+    else if (e_needed <= 16) SEL_GO(16);
+    else SEL_GO(32);
+#undef SEL_GO
+    KCH_LAUNCH_OK();
+    return KCH_OK;
+  }
+  const int cache_cap = (int)(n_ld <= 16384 ? ((n_ld + 255) & ~255LL) : 0);
+  const size_t smem = sort_smem + (size_t)cache_cap * 4;
+  KCH_CUDA_OK(cudaFuncSetAttribute(topk_select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  topk_select_kernel<<<grid, 256, smem, s>>>(logits, indices, T, n_blocks, n_ld, topk, m, t0, n_visible, sorted, cache_cap);
+  KCH_LAUNCH_OK();
+  return KCH_OK;
+}
+
 static int64_t indexer_logits_bytes(int B, int T, int n) {
   int64_t n_ld = ((int64_t)n + 3) & ~3LL;
   return align256((int64_t)B * T * n_ld * 4);
@@ -627,14 +760,7 @@ extern "C" int kch_indexer_topk_ex(const void* q_idx_any, int q_dtype, int64_t q
     KCH_REQUIRE(P <= 8192, "kch_indexer_topk: sorted output supports topk <= 8192 (got %d)", ks);
     smem = (size_t)P * 8;
   }
-  // row cache: up to 16384 logits (64 KiB); n_ld is a multiple of 4 so the float4 read stays in the row
-  const int cache_cap = (int)(n_ld <= 16384 ? ((n_ld + 255) & ~255LL) : 0);
-  smem += (size_t)cache_cap * 4;
-  KCH_CUDA_OK(cudaFuncSetAttribute(topk_select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  topk_select_kernel<<<(unsigned)((int64_t)B * T), 256, smem, s>>>(logits, indices, T, n_blocks, n_ld, topk, m,
-                                                                    t0, n_visible, sorted, cache_cap);
-  KCH_LAUNCH_OK();
-  return KCH_OK;
+  return launch_topk_select(logits, indices, B, T, n_blocks, n_ld, topk, m, t0, n_visible, sorted, smem, s);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -701,12 +827,7 @@ extern "C" int kch_indexer_topk_static(const float* q_idx, const float* k_idx, c
   rc = launch_indexer_logits(q_idx, k_idx, w_idx, logits, B, T, n_blocks, HI, DI, n_ld, scale, m, t0, n_visible,
                              k_batch_stride, nullptr, 0, s);
   if (rc != KCH_OK) return rc;
-  const int cache_cap = (int)(n_ld <= 16384 ? ((n_ld + 255) & ~255LL) : 0);
-  KCH_CUDA_OK(cudaFuncSetAttribute(topk_select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, cache_cap * 4));
-  topk_select_kernel<<<(unsigned)((int64_t)B * T), 256, (size_t)cache_cap * 4, s>>>(logits, indices, T, n_blocks, n_ld,
-                                                                                     topk, m, t0, n_visible, 0, cache_cap);
-  KCH_LAUNCH_OK();
-  return KCH_OK;
+  return launch_topk_select(logits, indices, B, T, n_blocks, n_ld, topk, m, t0, n_visible, 0, 0, s);
 }
 
 // ---------------------------------------------------------------------------------------

@@ -139,12 +139,21 @@ __global__ void __launch_bounds__(256, 2) kda_prepare_mma_kernel(PrepArgs a) {
     for (int x = 0; x < 8; ++x) out[x] = __bfloat162float(e[x]);
   };
   __syncthreads();
-  if (tid < KM_K) {
+  {
+    // running sum over the 64 rows: two 32-row segments per channel in parallel, then the second segment adds
+    // the first one's total (independent adds)
+    const int cch = tid & (KM_K - 1), seg = tid >> 7;
     float acc = 0.f;
 #pragma unroll 8
-    for (int i = 0; i < KM_C; ++i) {
-      acc += sG[i * PS_GLD + tid];
-      sG[i * PS_GLD + tid] = acc;
+    for (int i = 32 * seg; i < 32 * seg + 32; ++i) {
+      acc += sG[i * PS_GLD + cch];
+      sG[i * PS_GLD + cch] = acc;
+    }
+    __syncthreads();
+    if (seg == 1) {
+      const float base = sG[31 * PS_GLD + cch];
+#pragma unroll 8
+      for (int i = 32; i < 64; ++i) sG[i * PS_GLD + cch] += base;
     }
   }
   __syncthreads();
@@ -277,17 +286,25 @@ __global__ void __launch_bounds__(256, 2) kda_prepare_mma_kernel(PrepArgs a) {
     const int ub_a[6] = {0, 0, 0, 1, 1, 2}, ub_b[6] = {1, 2, 3, 2, 3, 3};
     sT[(16 * ub_a[bi] + r) * PS_LD + 16 * ub_b[bi] + cc] = 0.f;
   }
-  // diagonal 16x16 blocks: one thread per (block, column)
-  if (tid < 64) {
-    const int blk = tid >> 4, cc = tid & 15, base = 16 * blk;
+  // diagonal 16x16 blocks: four lanes per (block, column); lane q keeps the solved entries x_s with s = q (mod 4)
+  // in registers and contributes their part of each row's dot product, two shuffles complete it
+  {
+    const int col = tid >> 2, q4 = tid & 3;
+    const int blk = col >> 4, cc = col & 15, base = 16 * blk;
+    float xs[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
     for (int r = 0; r < 16; ++r) {
-      float x = (r == cc) ? 1.f : 0.f;
-      if (r > cc) {
-        float acc = 0.f;
-        for (int s = cc; s < r; ++s) acc = fmaf(sA[(base + r) * PS_LD + base + s], sT[(base + s) * PS_LD + base + cc], acc);
-        x = -acc;
+      float acc = 0.f;
+#pragma unroll
+      for (int m4 = 0; m4 < 4; ++m4) {
+        const int sidx = 4 * m4 + q4;
+        if (sidx < r && sidx >= cc) acc = fmaf(sA[(base + r) * PS_LD + base + sidx], xs[m4], acc);
       }
-      sT[(base + r) * PS_LD + base + cc] = x;
+      acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+      acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+      const float x = (r == cc) ? 1.f : (r > cc ? -acc : 0.f);
+      if ((r & 3) == q4) xs[r >> 2] = x;
+      if (q4 == 0) sT[(base + r) * PS_LD + base + cc] = x;
     }
   }
   __syncthreads();
