@@ -9,7 +9,8 @@
 //   warp 1      : allocates tensor memory, then one elected lane issues tcgen05.mma (M=128, N=BN,
 //                 K=16 per instruction, four per stage) and tcgen05.commit to release stages.
 //   warps 2..9  : epilogue — tcgen05.ld of the fp32 accumulator (each warp its 32-lane quarter and one
-//                 half of the tile's columns), bf16 rounding, optional activations / residual, 64-byte stores.
+//                 half of the tile's columns), bf16 rounding, optional activations / residual, a 32x32 transpose
+//                 through shared memory and stores of whole 64-byte row segments.
 // Two accumulator buffers in tensor memory let the epilogue of tile i overlap the main loop of
 // tile i+1.  Every wait on an mbarrier is bounded; on expiry the kernel records a status word,
 // leaves its loops, frees tensor memory and returns.
@@ -23,6 +24,7 @@
 #define TG_BM 128
 #define TG_BK 64
 #define TG_THREADS 320
+#define TG_EPI_LD 80
 #define TG_SPIN_LIMIT (1u << 24)
 
 __device__ unsigned int g_kch_status = 0;  // nonzero: a bounded wait expired (see kch_device_status)
@@ -118,6 +120,7 @@ struct TgSmem {
   static constexpr int STAGES = TgStages<BN>::value;
   alignas(1024) bf16 a[STAGES][TG_BM * TG_BK];
   alignas(1024) bf16 b[STAGES][BN * TG_BK];
+  alignas(16) uint8_t epi[8][32 * TG_EPI_LD];   // per epilogue warp: a 32 x 32 bf16 chunk, rows padded to 80 bytes
   alignas(8) uint64_t full[STAGES];
   uint64_t empty[STAGES];
   uint64_t acc_full[2];
@@ -262,35 +265,53 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             r[j] = __float_as_uint(-bf16r(v > 20.f ? v : __logf(1.0f + __expf(v))) * prm);
           }
         }
-        if (row < M && col < N) {
+        if (vec_ok && col + 32 <= N) {
+          // Transpose the 32 x 32 chunk through shared memory so that a store instruction writes 8 row segments
+          // of 64 contiguous bytes (full 32-byte sectors) instead of 16 bytes in each of 32 rows.
+          uint8_t* stg = sm.epi[warp - 2];
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            uint32_t o[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(r[8 * v + 2 * j]), __uint_as_float(r[8 * v + 2 * j + 1]));
+              o[j] = *reinterpret_cast<uint32_t*>(&h);
+            }
+            *reinterpret_cast<uint4*>(stg + lane * TG_EPI_LD + v * 16) = make_uint4(o[0], o[1], o[2], o[3]);
+          }
+          __syncwarp();
+          const int64_t row0 = mb * TG_BM + quarter * 32;
+          const int piece = lane & 3;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const int rr = (lane >> 2) + 8 * j;
+            const int64_t grow = row0 + rr;
+            uint4 cv = *reinterpret_cast<const uint4*>(stg + rr * TG_EPI_LD + piece * 16);
+            if (grow < M) {
+              if (R) {
+                const uint4 resv = *reinterpret_cast<const uint4*>(R + grow * ldr + col + piece * 8);
+                uint32_t* cw = &cv.x;
+                const uint32_t* rw = &resv.x;
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  const __nv_bfloat162 hc = *reinterpret_cast<const __nv_bfloat162*>(&cw[e]);
+                  const __nv_bfloat162 hr = *reinterpret_cast<const __nv_bfloat162*>(&rw[e]);
+                  __nv_bfloat162 hs = __floats2bfloat162_rn(__bfloat162float(hc.x) + __bfloat162float(hr.x),
+                                                            __bfloat162float(hc.y) + __bfloat162float(hr.y));
+                  cw[e] = *reinterpret_cast<uint32_t*>(&hs);
+                }
+              }
+              *reinterpret_cast<uint4*>(C + grow * ldc + col + piece * 8) = cv;
+            }
+          }
+          __syncwarp();
+        } else if (row < M && col < N) {
           bf16* cp = C + row * ldc + col;
           const bf16* rp = R ? R + row * ldr + col : nullptr;
-          if (vec_ok && col + 32 <= N) {
-#pragma unroll
-            for (int v = 0; v < 4; ++v) {
-              uint4 resv;
-              if (rp) resv = *reinterpret_cast<const uint4*>(rp + 8 * v);
-              uint32_t o[4];
-#pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                float f0 = __uint_as_float(r[8 * v + 2 * j]), f1 = __uint_as_float(r[8 * v + 2 * j + 1]);
-                __nv_bfloat162 h = __floats2bfloat162_rn(f0, f1);
-                if (rp) {
-                  uint32_t rw = (&resv.x)[j];
-                  __nv_bfloat162 rr = *reinterpret_cast<__nv_bfloat162*>(&rw);
-                  h = __floats2bfloat162_rn(__bfloat162float(h.x) + __bfloat162float(rr.x),
-                                            __bfloat162float(h.y) + __bfloat162float(rr.y));
-                }
-                o[j] = *reinterpret_cast<uint32_t*>(&h);
-              }
-              *reinterpret_cast<uint4*>(cp + 8 * v) = make_uint4(o[0], o[1], o[2], o[3]);
-            }
-          } else {
-            for (int j = 0; j < 32 && col + j < N; ++j) {
-              float f = __bfloat162float(__float2bfloat16_rn(__uint_as_float(r[j])));
-              if (rp) f += __bfloat162float(rp[j]);
-              cp[j] = __float2bfloat16_rn(f);
-            }
+          for (int j = 0; j < 32 && col + j < N; ++j) {
+            float f = __bfloat162float(__float2bfloat16_rn(__uint_as_float(r[j])));
+            if (rp) f += __bfloat162float(rp[j]);
+            cp[j] = __float2bfloat16_rn(f);
           }
         }
       }
