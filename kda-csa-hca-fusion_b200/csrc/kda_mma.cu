@@ -524,17 +524,19 @@ __global__ void __launch_bounds__(160, 1) kda_scan_mma_kernel(ScanArgs a) {
 #pragma unroll
       for (int nt = 0; nt < 8; ++nt) {
         const uint32_t off = swz<256>(8 * nt + (lane & 7), 4 * qd + (lane >> 3));
-        uint32_t h0, h1, h2, h3, l0, l1, l2, l3;
+        // the w and q products are independent accumulator chains: alternate them so that consecutive MMAs
+        // never wait on each other's result
+        uint32_t h0, h1, h2, h3, l0, l1, l2, l3, g0, g1, g2, g3, m0, m1, m2, m3;
         ldmatrix_x4(whi + off, h0, h1, h2, h3);
+        ldmatrix_x4(qhi + off, g0, g1, g2, g3);
         ldmatrix_x4(wlo + off, l0, l1, l2, l3);
-        mma_bf16_16816(accw[nt], ah[0], h0, h1); mma_bf16_16816(accw[nt], ah[1], h2, h3);
-        mma_bf16_16816(accw[nt], al[0], h0, h1); mma_bf16_16816(accw[nt], al[1], h2, h3);
-        mma_bf16_16816(accw[nt], ah[0], l0, l1); mma_bf16_16816(accw[nt], ah[1], l2, l3);
-        ldmatrix_x4(qhi + off, h0, h1, h2, h3);
-        ldmatrix_x4(qlo + off, l0, l1, l2, l3);
-        mma_bf16_16816(accq[nt], ah[0], h0, h1); mma_bf16_16816(accq[nt], ah[1], h2, h3);
-        mma_bf16_16816(accq[nt], al[0], h0, h1); mma_bf16_16816(accq[nt], al[1], h2, h3);
-        mma_bf16_16816(accq[nt], ah[0], l0, l1); mma_bf16_16816(accq[nt], ah[1], l2, l3);
+        ldmatrix_x4(qlo + off, m0, m1, m2, m3);
+        mma_bf16_16816(accw[nt], ah[0], h0, h1); mma_bf16_16816(accq[nt], ah[0], g0, g1);
+        mma_bf16_16816(accw[nt], ah[1], h2, h3); mma_bf16_16816(accq[nt], ah[1], g2, g3);
+        mma_bf16_16816(accw[nt], al[0], h0, h1); mma_bf16_16816(accq[nt], al[0], g0, g1);
+        mma_bf16_16816(accw[nt], al[1], h2, h3); mma_bf16_16816(accq[nt], al[1], g2, g3);
+        mma_bf16_16816(accw[nt], ah[0], l0, l1); mma_bf16_16816(accq[nt], ah[0], m0, m1);
+        mma_bf16_16816(accw[nt], ah[1], l2, l3); mma_bf16_16816(accq[nt], ah[1], m2, m3);
       }
     }
     release_tile(it0 + 0); release_tile(it0 + 1); release_tile(it0 + 2); release_tile(it0 + 3);
