@@ -126,6 +126,17 @@ int kch_kda_chunk(const void* q, const void* k, const void* v, const void* g, co
                   int64_t ld_v, int64_t ld_g, int64_t ld_beta, void* workspace, int64_t workspace_bytes,
                   void* stream);
 
+/* The same operator fed with the PRE-activation of the gate: g_pre is the output of g_up, and the decay is
+ * g = round(-round(softplus(g_pre)) * gate_scale) evaluated on load with the layer's bf16 rounding points
+ * (KDAHybridLayer, ops_fused.py:575-578), which saves the activation pass over [B,T,HV,K].  Tensor-core path only:
+ * bf16, K = V = 128, chunk_size 64, g_clamp_min >= -10 (kch_kda_chunk_gate_supported tells). */
+int kch_kda_chunk_gate_supported(int K, int V, int chunk_size, float g_clamp_min, int dtype);
+int kch_kda_chunk_gate(const void* q, const void* k, const void* v, const void* g_pre, const void* beta,
+                       const float* initial_state, void* o, float* final_state, int B, int T, int H, int HV,
+                       int K, int V, int chunk_size, float scale, float g_clamp_min, float gate_scale, int dtype,
+                       int64_t ld_qk, int64_t ld_v, int64_t ld_g, int64_t ld_beta, void* workspace,
+                       int64_t workspace_bytes, void* stream);
+
 /* ---- compression ------------------------------------------------------------------------------ */
 
 /* csa_compress_kv, ops_csa.py:198-234.  C,Z: rows of c elements, `ld` apart, batch b starts at row

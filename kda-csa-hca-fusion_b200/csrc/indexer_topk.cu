@@ -557,34 +557,14 @@ topk_select_kernel(const float* __restrict__ logits, int32_t* __restrict__ out, 
   for (int i = tid; i < nsel; i += 256) orow[i] = 0x7FFFFFFF - (int)(uint32_t)(ssort[i] & 0xFFFFFFFFu);
 }
 
-// Register variant for rows of up to 256*EPT logits (the prefill case: n_blocks <= 8192): thread t owns the
-// contiguous index range [t*E, (t+1)*E), E = ceil(nv/256) rounded up to 4, and keeps the order-preserving keys of
-// its logits in registers for all four radix passes, the counting and the ordered compaction: one 16-byte-vector
-// read of the row, no shared-memory staging.  Same selection rule and output as topk_select_kernel.
+// Radix select of one row with SLOTS keys per thread in registers (E <= SLOTS elements owned by each thread).
 template <int EPT>
-__global__ void __launch_bounds__(256)
-topk_select_reg_kernel(const float* __restrict__ logits, int32_t* __restrict__ out, int T, int n, int64_t n_ld,
-                       int topk, int m, int64_t t0, int nvis_fixed, int sorted) {
-  extern __shared__ __align__(16) uint8_t sel_smem[];
-  unsigned long long* ssort = reinterpret_cast<unsigned long long*>(sel_smem);
-  const int64_t row = blockIdx.x;
-  const int t = (int)(row % T);
-  const float* lg = logits + row * n_ld;
-  int32_t* orow = out + row * topk;
-  int64_t nv64 = nvis_fixed >= 0 ? nvis_fixed : (m > 0 ? (t0 + t + 1) / m : n);
-  const int nv = (int)(nv64 < n ? nv64 : n);
-  const int ksel = topk < n ? topk : n;
+__device__ __forceinline__ void select_row_regs(const float* __restrict__ lg, int32_t* __restrict__ orow, int nv, int ksel,
+                                                int E, int64_t n_ld, int* hist, int* sbuf, uint32_t* s_prefix_p,
+                                                int* s_need_p) {
   const int tid = threadIdx.x;
-  __shared__ int hist[256];
-  __shared__ int sbuf[9];
-  __shared__ uint32_t s_prefix;
-  __shared__ int s_need;
-  int nsel;
-  if (nv <= ksel) {
-    for (int i = tid; i < topk; i += 256) orow[i] = i < nv ? i : -1;
-    nsel = nv;
-  } else {
-    const int E = (((nv + 255) >> 8) + 3) & ~3;          // <= EPT by the host's choice of EPT
+  uint32_t& s_prefix = *s_prefix_p;
+  int& s_need = *s_need_p;
     const int i0 = tid * E;
     const int cnt_mine = max(0, min(E, nv - i0));
     uint32_t u[EPT];
@@ -631,6 +611,40 @@ topk_select_reg_kernel(const float* __restrict__ logits, int32_t* __restrict__ o
         if (u[k] > prefix) orow[p_gt++] = i0 + k;
         else if (u[k] == prefix) { if (p_eq < need) orow[n_gt + p_eq] = i0 + k; ++p_eq; }
       }
+}
+
+// Register variant for rows of up to 256*EPT logits (the prefill case: n_blocks <= 8192): thread t owns the
+// contiguous index range [t*E, (t+1)*E), E = ceil(nv/256) rounded up to 4, and keeps the order-preserving keys of
+// its logits in registers for all four radix passes, the counting and the ordered compaction: one 16-byte-vector
+// read of the row, no shared-memory staging.  Same selection rule and output as topk_select_kernel.
+template <int EPT>
+__global__ void __launch_bounds__(256)
+topk_select_reg_kernel(const float* __restrict__ logits, int32_t* __restrict__ out, int T, int n, int64_t n_ld,
+                       int topk, int m, int64_t t0, int nvis_fixed, int sorted) {
+  extern __shared__ __align__(16) uint8_t sel_smem[];
+  unsigned long long* ssort = reinterpret_cast<unsigned long long*>(sel_smem);
+  const int64_t row = blockIdx.x;
+  const int t = (int)(row % T);
+  const float* lg = logits + row * n_ld;
+  int32_t* orow = out + row * topk;
+  int64_t nv64 = nvis_fixed >= 0 ? nvis_fixed : (m > 0 ? (t0 + t + 1) / m : n);
+  const int nv = (int)(nv64 < n ? nv64 : n);
+  const int ksel = topk < n ? topk : n;
+  const int tid = threadIdx.x;
+  __shared__ int hist[256];
+  __shared__ int sbuf[9];
+  __shared__ uint32_t s_prefix;
+  __shared__ int s_need;
+  int nsel;
+  if (nv <= ksel) {
+    for (int i = tid; i < topk; i += 256) orow[i] = i < nv ? i : -1;
+    nsel = nv;
+  } else {
+    // slots per thread follow this row's visible length, not the longest row of the launch
+    const int E = (((nv + 255) >> 8) + 3) & ~3;          // <= EPT by the host's choice of EPT
+    if (EPT > 8 && E <= 8) select_row_regs<8>(lg, orow, nv, ksel, E, n_ld, hist, sbuf, &s_prefix, &s_need);
+    else if (EPT > 16 && E <= 16) select_row_regs<(EPT > 16 ? 16 : EPT)>(lg, orow, nv, ksel, E, n_ld, hist, sbuf, &s_prefix, &s_need);
+    else select_row_regs<EPT>(lg, orow, nv, ksel, E, n_ld, hist, sbuf, &s_prefix, &s_need);
     for (int i = ksel + tid; i < topk; i += 256) orow[i] = -1;
     nsel = ksel;
   }

@@ -418,7 +418,7 @@ int64_t kch_kda_mma_workspace_bytes(int B, int T, int HV);
 int kch_kda_chunk_mma(const void* q, const void* k, const void* v, const void* g, const void* beta,
                       const float* initial_state, void* o, float* final_state, int B, int T, int H, int HV,
                       float scale, float g_clamp_min, int64_t ld_qk, int64_t ld_v, int64_t ld_g, int64_t ld_beta,
-                      void* workspace, int64_t workspace_bytes, void* stream);
+                      void* workspace, int64_t workspace_bytes, void* stream, float gate_scale);
 
 extern "C" int64_t kch_kda_chunk_workspace_bytes(int B, int T, int HV, int K, int V, int chunk_size) {
   if (B <= 0 || T <= 0 || HV <= 0 || K <= 0 || V <= 0 || chunk_size < 1) return 0;
@@ -433,12 +433,12 @@ extern "C" int64_t kch_kda_chunk_workspace_bytes(int B, int T, int HV, int K, in
   return need;
 }
 
-extern "C" int kch_kda_chunk(const void* q, const void* k, const void* v, const void* g,
-                             const void* beta, const float* initial_state, void* o,
-                             float* final_state, int B, int T, int H, int HV, int K, int V,
-                             int chunk_size, float scale, float g_clamp_min, int dtype, int64_t ld_qk,
-                             int64_t ld_v, int64_t ld_g, int64_t ld_beta, void* workspace,
-                             int64_t workspace_bytes, void* stream) {
+static int kda_chunk_impl(const void* q, const void* k, const void* v, const void* g,
+                          const void* beta, const float* initial_state, void* o,
+                          float* final_state, int B, int T, int H, int HV, int K, int V,
+                          int chunk_size, float scale, float g_clamp_min, int dtype, int64_t ld_qk,
+                          int64_t ld_v, int64_t ld_g, int64_t ld_beta, void* workspace,
+                          int64_t workspace_bytes, void* stream, float gate_scale) {
   if (ld_qk <= 0) ld_qk = (int64_t)H * K;
   if (ld_v <= 0) ld_v = (int64_t)HV * V;
   if (ld_g <= 0) ld_g = (int64_t)HV * K;
@@ -449,13 +449,17 @@ extern "C" int kch_kda_chunk(const void* q, const void* k, const void* v, const 
   KCH_REQUIRE(chunk_size >= 1, "chunk_size=%d must be >= 1", chunk_size);
   KCH_REQUIRE(HV >= 1 && HV % H == 0, "HV=%d must be divisible by H=%d (GVA factor)", HV, H);
   KCH_REQUIRE(B >= 0 && T >= 0, "B=%d T=%d", B, T);
+  if (gate_scale != 0.f)
+    KCH_REQUIRE(T > 0 && K <= 128 && kch_kda_mma_supported(K, V, chunk_size, g_clamp_min, dtype),
+                "kch_kda_chunk_gate: the fused gate activation needs bf16, K = V = 128, chunk_size = 64 (K=%d V=%d chunk=%d)",
+                K, V, chunk_size);
   if (K > 128)  // state slice + staging tiles exceed shared memory: same maths, token form
     return kch_kda_recurrent(q, k, v, g, beta, initial_state, o, final_state, B, T, H, HV, K, V, scale,
                              g_clamp_min, dtype, ld_qk, ld_v, ld_g, ld_beta, stream);
   if (B == 0) return KCH_OK;
   if (T > 0 && kch_kda_mma_supported(K, V, chunk_size, g_clamp_min, dtype))
     return kch_kda_chunk_mma(q, k, v, g, beta, initial_state, o, final_state, B, T, H, HV, scale, g_clamp_min,
-                             ld_qk, ld_v, ld_g, ld_beta, workspace, workspace_bytes, stream);
+                             ld_qk, ld_v, ld_g, ld_beta, workspace, workspace_bytes, stream, gate_scale);
   if (T == 0) {
     if (final_state) {
       size_t nb = (size_t)B * HV * K * V * sizeof(float);
@@ -492,4 +496,29 @@ extern "C" int kch_kda_chunk(const void* q, const void* k, const void* v, const 
   kch_note_launch(1);  // two kernels per call
   KCH_LAUNCH_OK();
   return KCH_OK;
+}
+
+extern "C" int kch_kda_chunk(const void* q, const void* k, const void* v, const void* g,
+                             const void* beta, const float* initial_state, void* o,
+                             float* final_state, int B, int T, int H, int HV, int K, int V,
+                             int chunk_size, float scale, float g_clamp_min, int dtype, int64_t ld_qk,
+                             int64_t ld_v, int64_t ld_g, int64_t ld_beta, void* workspace,
+                             int64_t workspace_bytes, void* stream) {
+  return kda_chunk_impl(q, k, v, g, beta, initial_state, o, final_state, B, T, H, HV, K, V, chunk_size, scale,
+                        g_clamp_min, dtype, ld_qk, ld_v, ld_g, ld_beta, workspace, workspace_bytes, stream, 0.f);
+}
+
+extern "C" int kch_kda_chunk_gate_supported(int K, int V, int chunk_size, float g_clamp_min, int dtype) {
+  return K <= 128 && kch_kda_mma_supported(K, V, chunk_size, g_clamp_min, dtype) ? 1 : 0;
+}
+
+extern "C" int kch_kda_chunk_gate(const void* q, const void* k, const void* v, const void* g_pre,
+                                  const void* beta, const float* initial_state, void* o,
+                                  float* final_state, int B, int T, int H, int HV, int K, int V,
+                                  int chunk_size, float scale, float g_clamp_min, float gate_scale, int dtype,
+                                  int64_t ld_qk, int64_t ld_v, int64_t ld_g, int64_t ld_beta, void* workspace,
+                                  int64_t workspace_bytes, void* stream) {
+  KCH_REQUIRE(gate_scale > 0.f, "kch_kda_chunk_gate: gate_scale=%g must be > 0", (double)gate_scale);
+  return kda_chunk_impl(q, k, v, g_pre, beta, initial_state, o, final_state, B, T, H, HV, K, V, chunk_size, scale,
+                        g_clamp_min, dtype, ld_qk, ld_v, ld_g, ld_beta, workspace, workspace_bytes, stream, gate_scale);
 }

@@ -47,6 +47,7 @@ struct PrepArgs {
   uint8_t* ws;
   int T, H, HV, NT;
   float scale, g_min;
+  float gate_scale;                  // != 0: g holds the gate's pre-activation x; the decay is -softplus(x) * gate_scale
   int64_t ld_qk, ld_v, ld_g, ld_b;   // elements between consecutive tokens
 };
 
@@ -102,7 +103,16 @@ __global__ void __launch_bounds__(256, 2) kda_prepare_mma_kernel(PrepArgs a) {
     float gv[8];
     load8(a.g + g_off(i) + 8 * ch, t0 + i < a.T, gv);
 #pragma unroll
-    for (int x = 0; x < 8; ++x) gv[x] = (t0 + i < a.T) ? fmaxf(gv[x], a.g_min) * KM_LOG2E : 0.f;
+    for (int x = 0; x < 8; ++x) {
+      float gx = gv[x];
+      if (a.gate_scale != 0.f) {
+        // the gate activation of the layer (ops_fused.py:575-578) with its bf16 rounding points, as the GEMM
+        // epilogue would have applied it: round(-round(softplus(x)) * scale)
+        const float sp = __bfloat162float(__float2bfloat16_rn(gx > 20.f ? gx : __logf(1.0f + __expf(gx))));
+        gx = __bfloat162float(__float2bfloat16_rn(-sp * a.gate_scale));
+      }
+      gv[x] = (t0 + i < a.T) ? fmaxf(gx, a.g_min) * KM_LOG2E : 0.f;
+    }
     float4* dst = reinterpret_cast<float4*>(sG + i * PS_GLD + 8 * ch);
     dst[0] = make_float4(gv[0], gv[1], gv[2], gv[3]);
     dst[1] = make_float4(gv[4], gv[5], gv[6], gv[7]);
@@ -653,7 +663,7 @@ int64_t kch_kda_mma_workspace_bytes(int B, int T, int HV) {
 int kch_kda_chunk_mma(const void* q, const void* k, const void* v, const void* g, const void* beta,
                       const float* initial_state, void* o, float* final_state, int B, int T, int H, int HV,
                       float scale, float g_clamp_min, int64_t ld_qk, int64_t ld_v, int64_t ld_g, int64_t ld_beta,
-                      void* workspace, int64_t workspace_bytes, void* stream) {
+                      void* workspace, int64_t workspace_bytes, void* stream, float gate_scale) {
   const int NT = (T + KM_C - 1) / KM_C;
   KCH_REQUIRE(workspace && workspace_bytes >= kch_kda_mma_workspace_bytes(B, T, HV),
               "kch_kda_chunk: workspace %lld < %lld bytes", (long long)workspace_bytes,
@@ -664,7 +674,7 @@ int kch_kda_chunk_mma(const void* q, const void* k, const void* v, const void* g
   cudaStream_t s = kch_stream(stream);
   PrepArgs pa;
   pa.q = (const bf16*)q; pa.k = (const bf16*)k; pa.v = (const bf16*)v; pa.g = (const bf16*)g; pa.beta = (const bf16*)beta;
-  pa.ws = (uint8_t*)workspace; pa.T = T; pa.H = H; pa.HV = HV; pa.NT = NT; pa.scale = scale; pa.g_min = g_clamp_min;
+  pa.ws = (uint8_t*)workspace; pa.T = T; pa.H = H; pa.HV = HV; pa.NT = NT; pa.scale = scale; pa.g_min = g_clamp_min; pa.gate_scale = gate_scale;
   pa.ld_qk = ld_qk; pa.ld_v = ld_v; pa.ld_g = ld_g; pa.ld_b = ld_beta;
   // 16-byte vector loads: token strides and base pointers must be multiples of 8 elements / 16 bytes
   KCH_REQUIRE((ld_qk % 8) == 0 && (ld_v % 8) == 0 && (ld_g % 8) == 0 &&

@@ -77,6 +77,8 @@ PROTOTYPES = {
     "kch_kda_recurrent": (_i, [_vp] * 8 + [_i] * 6 + [_f, _f, _i, _i64, _i64, _i64, _i64, _vp]),
     "kch_kda_chunk_workspace_bytes": (_i64, [_i] * 6),
     "kch_kda_chunk": (_i, [_vp] * 8 + [_i] * 7 + [_f, _f, _i, _i64, _i64, _i64, _i64, _vp, _i64, _vp]),
+    "kch_kda_chunk_gate_supported": (_i, [_i, _i, _i, _f, _i]),
+    "kch_kda_chunk_gate": (_i, [_vp] * 8 + [_i] * 7 + [_f, _f, _f, _i, _i64, _i64, _i64, _i64, _vp, _i64, _vp]),
     "kch_compress_kv": (_i, [_vp, _vp, _vp, _vp, _i, _i64, _i, _i, _i64, _i64, _i64, _i, _i, _vp]),
     "kch_compress_kv_overlapped": (_i, [_vp] * 8 + [_i64, _vp, _i, _i64, _i, _i, _i64, _i64, _i64, _i, _i, _vp]),
     "kch_indexer_workspace_bytes": (_i64, [_i, _i, _i, _i, _i]),

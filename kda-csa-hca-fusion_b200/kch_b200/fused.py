@@ -21,7 +21,7 @@ from . import _lib
 from .csa import attend, fuse_rows, linear, naive_csa, rownorm
 from .decoding_cache import CSADecodingCache, HCADecodingCache
 from .hca import naive_hca
-from .kda import kda_forward, validate_kda_backend
+from .kda import chunk_gate_supported, kda_forward, validate_kda_backend
 from .tp import gather_heads
 
 
@@ -238,7 +238,7 @@ class KDAHybridLayer(nn.Module):
         self._conv_lookback = lb
         return o, new_state
 
-    def project(self, x, conv_lookback, lookback_in_place=False, norm=None):
+    def project(self, x, conv_lookback, lookback_in_place=False, norm=None, raw_gate=False):
         """conv + fused projection + activations -> (q, k, v, g, beta, new_lookback).  With
         ``lookback_in_place`` a one-token call slides ``conv_lookback`` where it lies and returns it.
         ``norm``: the sub-layer's pre-norm when ``x`` is the un-normalised residual stream; LayerNorm and the
@@ -275,7 +275,10 @@ class KDAHybridLayer(nn.Module):
                 (K, 0, 0.0), (HV + (W.shape[0] - n_used), _lib.ACT_SIGMOID, 0.0)]
         proj = linear(xc, W, epilogue=segs, group=K)
         q, k, v, gd, beta = proj[..., :n_used].split([H * K, H * K, HV * V, K, HV], dim=-1)
-        g = linear(gd, self.g_up.weight, epilogue=[(HV * K, _lib.ACT_NEG_SOFTPLUS, cfg.kda_decay_scale)])
+        if raw_gate:     # the chunk kernel applies -softplus(.) * decay_scale when it loads the gate
+            g = linear(gd, self.g_up.weight)
+        else:
+            g = linear(gd, self.g_up.weight, epilogue=[(HV * K, _lib.ACT_NEG_SOFTPLUS, cfg.kda_decay_scale)])
         return (q.unflatten(-1, (H, K)), k.unflatten(-1, (H, K)), v.unflatten(-1, (HV, V)),
                 g.view(B, T, HV, K), beta, new_lb)
 
@@ -284,11 +287,14 @@ class KDAHybridLayer(nn.Module):
         cfg = self.cfg
         B, T, _ = x.shape
         HV, V = cfg.n_heads_v, cfg.head_dim_v
-        q, k, v, g, beta, new_lb = self.project(x, conv_lookback, lookback_in_place, norm)
         use_chunk = cfg.kda_chunk_size >= 1 and T >= cfg.kda_chunk_size
+        raw_gate = use_chunk and cfg.kda_decay_scale > 0 and chunk_gate_supported(
+            cfg.head_dim_k, cfg.head_dim_v, cfg.kda_chunk_size, -10.0, x.dtype)
+        q, k, v, g, beta, new_lb = self.project(x, conv_lookback, lookback_in_place, norm, raw_gate)
         o, new_state = kda_forward(q, k, v, g, beta, scale=self._scale_value(), initial_state=state,
                                    output_final_state=True, chunk_size=cfg.kda_chunk_size, use_chunk=use_chunk,
-                                   backend=cfg.kda_backend, state_out=None if use_chunk else state_out)
+                                   backend=cfg.kda_backend, state_out=None if use_chunk else state_out,
+                                   gate_scale=cfg.kda_decay_scale if raw_gate else None)
         o = gather_heads(o.reshape(B, T, HV * V), self.tp)
         out = linear(o, self.o_proj.weight, residual=residual)
         return out, new_state, new_lb

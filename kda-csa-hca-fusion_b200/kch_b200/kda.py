@@ -92,7 +92,7 @@ def _scale_value(scale, K):
 
 
 def _run(fn_name, q, k, v, g, beta, scale, initial_state, output_final_state, g_clamp_min, state_dtype,
-         chunk_size, state_out=None):
+         chunk_size, state_out=None, gate_scale=None):
     _validate_inputs(q, k, v, g, beta, fn_name)
     _validate_shapes(q, k, v, g, beta, fn_name, chunk_size)
     _lib.require_cuda(q, fn=fn_name)
@@ -132,10 +132,16 @@ def _run(fn_name, q, k, v, g, beta, scale, initial_state, output_final_state, g_
         else:
             nbytes = lib.kch_kda_chunk_workspace_bytes(B, T, HV, K, V, int(chunk_size))
             ws = torch.empty(max(int(nbytes), 1), dtype=torch.uint8, device=q.device)
-            _lib.check(lib.kch_kda_chunk(_lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(g), _lib.ptr(beta),
-                                         _lib.ptr(S0), _lib.ptr(o), _lib.ptr(S), B, T, H, HV, K, V, int(chunk_size),
-                                         sc, gmin, tag, ld_q, ld_v, ld_g, ld_b, _lib.ptr(ws), int(nbytes),
-                                         _lib.stream()))
+            if gate_scale is not None:
+                _lib.check(lib.kch_kda_chunk_gate(_lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(g), _lib.ptr(beta),
+                                                  _lib.ptr(S0), _lib.ptr(o), _lib.ptr(S), B, T, H, HV, K, V,
+                                                  int(chunk_size), sc, gmin, float(gate_scale), tag, ld_q, ld_v, ld_g,
+                                                  ld_b, _lib.ptr(ws), int(nbytes), _lib.stream()))
+            else:
+                _lib.check(lib.kch_kda_chunk(_lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(g), _lib.ptr(beta),
+                                             _lib.ptr(S0), _lib.ptr(o), _lib.ptr(S), B, T, H, HV, K, V, int(chunk_size),
+                                             sc, gmin, tag, ld_q, ld_v, ld_g, ld_b, _lib.ptr(ws), int(nbytes),
+                                             _lib.stream()))
     if S is not None and state_dtype is not None:
         S = S.to(state_dtype)
     return o, S
@@ -151,13 +157,22 @@ def naive_recurrent_kda(q, k, v, g, beta, scale=None, initial_state=None, output
                 g_clamp_min, state_dtype, None, state_out)
 
 
+def chunk_gate_supported(K, V, chunk_size, g_clamp_min, dtype):
+    """Can ``naive_chunk_kda`` take the gate's pre-activation (``_gate_scale``) for this geometry?"""
+    if dtype != torch.bfloat16:
+        return False
+    gmin = float(g_clamp_min) if g_clamp_min > -math.inf else -math.inf
+    return bool(_lib.load().kch_kda_chunk_gate_supported(int(K), int(V), int(chunk_size), gmin, _lib.KCH_BF16))
+
+
 def naive_chunk_kda(q, k, v, g, beta, scale=None, initial_state=None, output_final_state=False,
-                    chunk_size: int = 64, *, g_clamp_min: float = -10.0, state_dtype=None):
+                    chunk_size: int = 64, *, g_clamp_min: float = -10.0, state_dtype=None, _gate_scale=None):
     """Chunk-parallel KDA; equals :func:`naive_recurrent_kda` up to fp32 round-off.  Chunks larger
     than 64 tokens (or than K) are processed as smaller chunks: the same mathematics in a different
-    summation order."""
+    summation order.  ``_gate_scale`` (not in the reference): ``g`` is the pre-activation of the layer's gate and
+    the kernel applies ``-softplus(g) * _gate_scale`` itself (see :func:`chunk_gate_supported`)."""
     return _run("naive_chunk_kda", q, k, v, g, beta, scale, initial_state, output_final_state,
-                g_clamp_min, state_dtype, int(chunk_size))
+                g_clamp_min, state_dtype, int(chunk_size), gate_scale=_gate_scale)
 
 
 def validate_kda_backend(backend: str) -> str:
@@ -168,7 +183,7 @@ def validate_kda_backend(backend: str) -> str:
 
 def kda_forward(q, k, v, g, beta, *, scale=None, initial_state=None, output_final_state=False,
                 chunk_size: int = 64, use_chunk: bool = False, g_clamp_min: float = -10.0,
-                backend: str = "b200", state_out=None):
+                backend: str = "b200", state_out=None, gate_scale=None):
     """Dispatcher with the keyword contract of ``ops_kda_backend.kda_forward``; only ``backend='b200'``
     exists here (no Triton, no FLA, no CPU path)."""
     validate_kda_backend(backend)
@@ -182,7 +197,9 @@ def kda_forward(q, k, v, g, beta, *, scale=None, initial_state=None, output_fina
     if use_chunk:
         return naive_chunk_kda(q, k, v, g, beta, scale=scale, initial_state=initial_state,
                                output_final_state=output_final_state, chunk_size=chunk_size,
-                               g_clamp_min=g_clamp_min)
+                               g_clamp_min=g_clamp_min, _gate_scale=gate_scale)
+    if gate_scale is not None:
+        raise ValueError("kda_forward: gate_scale is only meaningful with use_chunk=True")
     return naive_recurrent_kda(q, k, v, g, beta, scale=scale, initial_state=initial_state,
                                output_final_state=output_final_state, g_clamp_min=g_clamp_min, state_out=state_out)
 
