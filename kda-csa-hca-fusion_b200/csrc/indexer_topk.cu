@@ -442,7 +442,40 @@ __device__ __forceinline__ int block_excl_scan(int v, int* buf, int* total) {
   return res;
 }
 
-__global__ void __launch_bounds__(256)
+// the same scan over NT threads (NT / 32 <= 32 warps); `buf` has 34 words
+template <int NT>
+__device__ __forceinline__ int block_excl_scan_n(int v, int* buf, int* total) {
+  constexpr int NW = NT / 32;
+  int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  int inc = v;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    int y = __shfl_up_sync(0xffffffffu, inc, o);
+    if (lane >= o) inc += y;
+  }
+  if (lane == 31) buf[warp] = inc;
+  __syncthreads();
+  if (warp == 0) {
+    int x = lane < NW ? buf[lane] : 0;
+    int xi = x;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      int y = __shfl_up_sync(0xffffffffu, xi, o);
+      if (lane >= o) xi += y;
+    }
+    if (lane < NW) buf[lane] = xi - x;
+    if (lane == 31) buf[33] = xi;
+  }
+  __syncthreads();
+  int res = buf[warp] + inc - v;
+  *total = buf[33];
+  __syncthreads();
+  return res;
+}
+
+// NT threads per row: 256 for the rows of a prefill, 1024 for the few long rows of a decode step
+template <int NT>
+__global__ void __launch_bounds__(NT)
 topk_select_kernel(const float* __restrict__ logits, int32_t* __restrict__ out, int T, int n,
                    int64_t n_ld, int topk, int m, int64_t t0, int nvis_fixed, int sorted, int cache_cap,
                    const int32_t* __restrict__ ctr = nullptr, int ctr_m = 1) {
@@ -463,31 +496,31 @@ topk_select_kernel(const float* __restrict__ logits, int32_t* __restrict__ out, 
   const int ksel = topk < n ? topk : n;
   const int tid = threadIdx.x;
   __shared__ int hist[256];
-  __shared__ int sbuf[9];
+  __shared__ int sbuf[34];
   __shared__ uint32_t s_prefix;
   __shared__ int s_need;
   int nsel;
   if (nv <= ksel) {
-    for (int i = tid; i < topk; i += 256) orow[i] = i < nv ? i : -1;
+    for (int i = tid; i < topk; i += NT) orow[i] = i < nv ? i : -1;
     nsel = nv;
   } else {
     // Thread t owns the contiguous index range [t*E, (t+1)*E): ordered compaction then needs one
     // block scan in total.  The row is staged in shared memory transposed (element k of thread t at
-    // k*256 + t) so that those strided-by-E reads are bank-conflict free.
-    const int E = (nv + 255) >> 8;
-    const bool cached = E * 256 <= cache_cap;
+    // k*NT + t) so that those strided-by-E reads are bank-conflict free.
+    const int E = (nv + NT - 1) / NT;
+    const bool cached = E * NT <= cache_cap;
     if (cached) {
-      for (int i = tid; i < nv; i += 256) srow[(i % E) * 256 + i / E] = lg[i];
+      for (int i = tid; i < nv; i += NT) srow[(i % E) * NT + i / E] = lg[i];
       __syncthreads();
     }
     const int i0 = tid * E;
     const int cnt_mine = max(0, min(E, nv - i0));
-    auto val = [&](int k) -> float { return cached ? srow[k * 256 + tid] : lg[i0 + k]; };
+    auto val = [&](int k) -> float { return cached ? srow[k * NT + tid] : lg[i0 + k]; };
     uint32_t prefix = 0, pmask = 0;
     int need = ksel;  // how many still to take from the current prefix class
     for (int pass = 0; pass < 4; ++pass) {
       const int shift = 24 - 8 * pass;
-      hist[tid] = 0;
+      if (tid < 256) hist[tid] = 0;
       __syncthreads();
       for (int k = 0; k < cnt_mine; ++k) {
         uint32_t u = f2ord(val(k));
@@ -496,10 +529,10 @@ topk_select_kernel(const float* __restrict__ logits, int32_t* __restrict__ out, 
       __syncthreads();
       // thread t looks at bin 255-t: an exclusive scan gives the population of all higher bins
       const int bin = 255 - tid;
-      const int cnt = hist[bin];
+      const int cnt = tid < 256 ? hist[bin] : 0;
       int tot;
-      const int cum = block_excl_scan(cnt, sbuf, &tot);
-      if (cum < need && cum + cnt >= need) {
+      const int cum = block_excl_scan_n<NT>(cnt, sbuf, &tot);
+      if (tid < 256 && cum < need && cum + cnt >= need) {
         s_prefix = prefix | ((uint32_t)bin << shift);
         s_need = need - cum;
       }
@@ -518,14 +551,14 @@ topk_select_kernel(const float* __restrict__ logits, int32_t* __restrict__ out, 
       c_eq += (u == prefix);
     }
     int tot_gt, tot_eq;
-    int p_gt = block_excl_scan(c_gt, sbuf, &tot_gt);
-    int p_eq = block_excl_scan(c_eq, sbuf, &tot_eq);
+    int p_gt = block_excl_scan_n<NT>(c_gt, sbuf, &tot_gt);
+    int p_eq = block_excl_scan_n<NT>(c_eq, sbuf, &tot_eq);
     for (int k = 0; k < cnt_mine; ++k) {
       uint32_t u = f2ord(val(k));
       if (u > prefix) orow[p_gt++] = i0 + k;
       else if (u == prefix) { if (p_eq < need) orow[n_gt + p_eq] = i0 + k; ++p_eq; }
     }
-    for (int i = ksel + tid; i < topk; i += 256) orow[i] = -1;
+    for (int i = ksel + tid; i < topk; i += NT) orow[i] = -1;
     nsel = ksel;
   }
   if (!sorted) return;
@@ -533,7 +566,7 @@ topk_select_kernel(const float* __restrict__ logits, int32_t* __restrict__ out, 
   __syncthreads();
   int P = 1;
   while (P < nsel) P <<= 1;
-  for (int i = tid; i < P; i += 256) {
+  for (int i = tid; i < P; i += NT) {
     unsigned long long key = 0ull;
     if (i < nsel) {
       int id = orow[i];
@@ -544,7 +577,7 @@ topk_select_kernel(const float* __restrict__ logits, int32_t* __restrict__ out, 
   __syncthreads();
   for (int size = 2; size <= P; size <<= 1)
     for (int stride = size >> 1; stride > 0; stride >>= 1) {
-      for (int i = tid; i < P; i += 256) {
+      for (int i = tid; i < P; i += NT) {
         int j = i ^ stride;
         if (j > i) {
           unsigned long long a = ssort[i], c = ssort[j];
@@ -554,7 +587,7 @@ topk_select_kernel(const float* __restrict__ logits, int32_t* __restrict__ out, 
       }
       __syncthreads();
     }
-  for (int i = tid; i < nsel; i += 256) orow[i] = 0x7FFFFFFF - (int)(uint32_t)(ssort[i] & 0xFFFFFFFFu);
+  for (int i = tid; i < nsel; i += NT) orow[i] = 0x7FFFFFFF - (int)(uint32_t)(ssort[i] & 0xFFFFFFFFu);
 }
 
 // Radix select of one row with SLOTS keys per thread in registers (E <= SLOTS elements owned by each thread).
@@ -698,8 +731,8 @@ static int launch_topk_select(const float* logits, int32_t* indices, int B, int 
   }
   const int cache_cap = (int)(n_ld <= 16384 ? ((n_ld + 255) & ~255LL) : 0);
   const size_t smem = sort_smem + (size_t)cache_cap * 4;
-  KCH_CUDA_OK(cudaFuncSetAttribute(topk_select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  topk_select_kernel<<<grid, 256, smem, s>>>(logits, indices, T, n_blocks, n_ld, topk, m, t0, n_visible, sorted, cache_cap);
+  KCH_CUDA_OK(cudaFuncSetAttribute(topk_select_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  topk_select_kernel<256><<<grid, 256, smem, s>>>(logits, indices, T, n_blocks, n_ld, topk, m, t0, n_visible, sorted, cache_cap);
   KCH_LAUNCH_OK();
   return KCH_OK;
 }
@@ -1082,10 +1115,10 @@ extern "C" int kch_decode_indexer_topk(const void* q_idx, int q_dtype, int64_t q
 #undef GO
   KCH_LAUNCH_OK();
   // the whole row of logits is staged in shared memory when it fits (one CTA per SM at the largest size)
-  const int cache_cap = (int)(n_ld <= 49152 ? ((n_ld + 255) & ~255LL) : 0);
-  KCH_CUDA_OK(cudaFuncSetAttribute(topk_select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, cache_cap * 4));
-  topk_select_kernel<<<(unsigned)B, 256, (size_t)cache_cap * 4, s>>>(logits, idx_out, 1, (int)capacity, n_ld, topk, m, 0, -1,
-                                                                     0, cache_cap, counters, m);
+  const int cache_cap = (int)(n_ld <= 49152 ? ((n_ld + 1023) & ~1023LL) : 0);
+  KCH_CUDA_OK(cudaFuncSetAttribute(topk_select_kernel<1024>, cudaFuncAttributeMaxDynamicSharedMemorySize, cache_cap * 4));
+  topk_select_kernel<1024><<<(unsigned)B, 1024, (size_t)cache_cap * 4, s>>>(logits, idx_out, 1, (int)capacity, n_ld, topk, m, 0,
+                                                                            -1, 0, cache_cap, counters, m);
   KCH_LAUNCH_OK();
   return KCH_OK;
 }

@@ -76,7 +76,8 @@ def _token_stride(x):
         inner *= x.shape[d]
     B, T = x.shape[0], x.shape[1]
     if ok and T > 0 and B > 0:
-        ld = x.stride(1) if T > 1 else max(inner, x.stride(1))
+        # one token per sequence: the token stride is whatever separates the batch entries
+        ld = x.stride(1) if T > 1 else (x.stride(0) if B > 1 else inner)
         if ld >= inner and (B == 1 or x.stride(0) == T * ld) and ld % 8 == 0 and x.data_ptr() % 16 == 0:
             return x, ld
     x = x.contiguous()
