@@ -132,3 +132,54 @@ def test_install_is_reversible_when_reference_is_importable():
             ops_kda_backend.validate_kda_backend("b200")
     finally:
         sys.path.remove(ref)
+
+
+def test_projection_slices_are_read_in_place():
+    """Column slices of a fused projection reach the KDA kernels without a copy, also for a single token per
+    sequence (where PyTorch reports an arbitrary stride for the size-1 time axis)."""
+    from kch_b200.kda import _token_stride
+    for B, T in ((64, 1), (1, 1), (2, 5), (1, 7)):
+        proj = torch.zeros(B, T, 6288, dtype=torch.bfloat16)
+        q, k, v, gd, beta = proj.split([2048, 2048, 2048, 128, 16], dim=-1)
+        for t, inner in ((q.unflatten(-1, (16, 128)), 2048), (v.unflatten(-1, (16, 128)), 2048), (beta, 16)):
+            t2, ld = _token_stride(t)
+            assert t2.data_ptr() == t.data_ptr()
+            assert ld == (6288 if B * T > 1 else inner)
+    odd = torch.zeros(2, 3, 100, dtype=torch.bfloat16)[..., 1:65].unflatten(-1, (2, 32))   # misaligned start
+    t2, ld = _token_stride(odd)
+    assert t2.is_contiguous() and ld == 64
+
+
+def test_new_entry_points_validate_on_the_host():
+    from kch_b200 import _lib
+    lib = _lib.load()
+    rc = lib.kch_cache_advance(None, 4, None)
+    assert rc < 0 and b"counters" in lib.kch_last_error()
+    assert lib.kch_attend_decode_splits(64) >= 1 and lib.kch_attend_decode_splits(1) <= 32
+    assert lib.kch_attend_decode_workspace_bytes(64, 16, 128) == 64 * lib.kch_attend_decode_splits(64) * 16 * 130 * 4
+    assert lib.kch_decode_indexer_workspace_bytes(64, 32770) == 64 * 32772 * 4
+    a = _lib.AttendDecodeArgs()
+    a.B, a.nh, a.c = 4, 16, 64
+    rc = lib.kch_attend_decode(a, None)
+    assert rc < 0 and b"c == 128" in lib.kch_last_error()
+    rc = lib.kch_decode_indexer_topk(None, 0, 0, None, 1, None, None, 0, 0, None, 2, 16, 4, 64, 0, 1, 1.0, 4, None, None, 0, None)
+    assert rc < 0 and b"topk" in lib.kch_last_error()
+    rc = lib.kch_layernorm_short_conv(None, None, None, 1e-5, None, None, None, None, None, 1, 8, 100, 1, 1, None)
+    assert rc < 0 and b"d=100" in lib.kch_last_error()
+    rc = lib.kch_indexer_topk_ex(None, 2, 64, 0, None, None, None, 1, 4, 4, 1, 64, 4, 1.0, 4, 0, -1, 0, 0, None, 0, None)
+    assert rc < 0 and b"q_dtype" in lib.kch_last_error()
+    assert lib.kch_kda_chunk_gate_supported(128, 128, 64, -10.0, _lib.KCH_BF16) == 1
+    assert lib.kch_kda_chunk_gate_supported(64, 128, 64, -10.0, _lib.KCH_BF16) == 0
+    assert lib.kch_kda_chunk_gate_supported(128, 128, 64, -10.0, _lib.KCH_F32) == 0
+
+
+def test_bench_accounting():
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("kch_bench", os.path.join(ROOT, "bench.py"))
+    bench = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bench)
+    fpt = bench.algorithmic_flops_per_token(bench.C4, 32768)
+    assert abs(fpt - 145.86e6) / 145.86e6 < 1e-3
+    nbytes = bench.decode_state_bytes(bench.C4, 64, 131072, 2)
+    assert 1.0e9 < nbytes < 1.2e9
+    assert bench.decode_state_bytes(bench.C4, 64, 131072, 1.0625) < nbytes
