@@ -15,6 +15,7 @@
 // tile i+1.  Every wait on an mbarrier is bounded; on expiry the kernel records a status word,
 // leaves its loops, frees tensor memory and returns.
 #include <cuda.h>
+#include <stdlib.h>
 #include <cudaTypedefs.h>
 #include <mutex>
 #include <unordered_map>
@@ -429,6 +430,265 @@ int kch_linear_tcgen05(const void* A, const void* W, void* C, const void* R, int
   if (N > 64) return launch_tg<128>(A, W, C, R, M, N, K, lda, ldw, ldc, ldr, ep, s);
   if (N > 32) return launch_tg<64>(A, W, C, R, M, N, K, lda, ldw, ldc, ldr, ep, s);
   return launch_tg<32>(A, W, C, R, M, N, K, lda, ldw, ldc, ldr, ep, s);
+}
+
+// =====================================================================================================
+// Lightning-indexer logits on the same machinery (csa_lightning_indexer, ops_csa.py:503-554):
+//   logits[t, n] = sum_h w[t,h] relu(scale q_h[t] . k[n] / ||q_h[t]||)  =  sum_h c[t,h] relu(q_h[t] . k[n]),
+//   c[t,h] = w[t,h] scale / max(||q_h[t]||, 1e-12)  (the positive factor commutes with the ReLU).
+// Queries are the bf16 rows the projection wrote (exact operands, read in place through a tensor map);
+// the normalised fp32 keys arrive as three bf16 terms (hi + mid + lo, 24 bits of mantissa), so per head a
+// 128-query x 256-block tile is 12 tcgen05.mma (3 terms x K = 64) into one tensor-memory accumulator.
+// Epilogue warps apply c relu(.) and sum the heads in registers; the two accumulator buffers let the
+// epilogue of head h overlap the MMAs of head h+1.  Tiles are the causally visible ones only, taken in
+// strips of one key tile (the key operand stays in shared memory for a whole strip) and dealt out to the
+// persistent CTAs in equal contiguous runs.
+// =====================================================================================================
+#define IX_BM 128
+#define IX_BN 256
+#define IX_D 64
+#define IX_ASTAGES 4
+#define IX_MAX_STRIPS 256
+
+struct IxSched {
+  int n_strips;                        // B * ceil(n / IX_BN)
+  int total_tiles;
+  int prefix[IX_MAX_STRIPS + 1];       // visible tiles before strip s
+  short qt_first[IX_MAX_STRIPS];       // first query tile that sees strip s
+};
+
+struct IxSmem {
+  alignas(1024) bf16 kb[3][IX_BN * IX_D];          // key tile, three terms
+  alignas(1024) bf16 qa[IX_ASTAGES][IX_BM * IX_D]; // query tiles (one head each)
+  alignas(8) uint64_t a_full[IX_ASTAGES];
+  uint64_t a_empty[IX_ASTAGES];
+  uint64_t b_full, b_empty;
+  uint64_t acc_full[2], acc_empty[2];
+  uint32_t tmem_base;
+};
+
+__global__ void indexer_coef_kernel(const bf16* __restrict__ q, int64_t q_ld, const float* __restrict__ w,
+                                    float* __restrict__ coef, int64_t rows, int HI, float scale, int normalize) {
+  const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  for (int h = 0; h < HI; ++h) {
+    const uint32_t raw = *reinterpret_cast<const uint32_t*>(q + row * q_ld + h * IX_D + 2 * lane);
+    const float x = __uint_as_float(raw << 16), y = __uint_as_float(raw & 0xFFFF0000u);
+    float ss = x * x + y * y;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if (lane == 0) {
+      const float nrm = normalize ? fmaxf(sqrtf(ss), 1e-12f) : 1.f;
+      coef[row * HI + h] = (w ? w[row * HI + h] : 1.f) * scale / nrm;
+    }
+  }
+}
+
+__global__ void __launch_bounds__(TG_THREADS, 1)
+indexer_logits_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kh,
+                              const __grid_constant__ CUtensorMap map_km, const __grid_constant__ CUtensorMap map_kl,
+                              const __grid_constant__ IxSched sched, const float* __restrict__ coef,
+                              float* __restrict__ logits, int T, int n, int HI, int64_t n_ld, int strips_per_batch) {
+  extern __shared__ uint8_t smem_raw[];
+  IxSmem& sm = *reinterpret_cast<IxSmem*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  constexpr uint32_t TMEM_COLS = 2 * IX_BN;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < IX_ASTAGES; ++s) { mbar_init(&sm.a_full[s], 1); mbar_init(&sm.a_empty[s], 1); }
+    mbar_init(&sm.b_full, 1); mbar_init(&sm.b_empty, 1);
+    for (int i = 0; i < 2; ++i) { mbar_init(&sm.acc_full[i], 1); mbar_init(&sm.acc_empty[i], 8); }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm.tmem_base)), "r"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = sm.tmem_base;
+  // this CTA's run of visible tiles
+  const int per = (sched.total_tiles + (int)gridDim.x - 1) / (int)gridDim.x;
+  const int tile_lo = min(sched.total_tiles, (int)blockIdx.x * per), tile_hi = min(sched.total_tiles, tile_lo + per);
+  auto strip_of = [&](int tile, int hint) {          // strips are visited in order: a short forward scan finds it
+    int s = hint;
+    while (s + 1 < sched.n_strips && sched.prefix[s + 1] <= tile) ++s;
+    return s;
+  };
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0) {
+      uint32_t ait = 0, bit = 0;
+      int strip = 0, cur = -1;
+      bool ok = true;
+      for (int tile = tile_lo; tile < tile_hi && ok; ++tile) {
+        strip = strip_of(tile, strip);
+        const int b = strip / strips_per_batch, nt = strip % strips_per_batch;
+        const int qt = sched.qt_first[strip] + (tile - sched.prefix[strip]);
+        if (strip != cur) {
+          if (!mbar_wait(&sm.b_empty, (bit & 1) ^ 1, 31)) { ok = false; break; }
+          mbar_expect_tx(&sm.b_full, 3 * IX_BN * IX_D * 2);
+          const int row = b * n + nt * IX_BN;
+          tma_load_2d(sm.kb[0], &map_kh, 0, row, &sm.b_full);
+          tma_load_2d(sm.kb[1], &map_km, 0, row, &sm.b_full);
+          tma_load_2d(sm.kb[2], &map_kl, 0, row, &sm.b_full);
+          ++bit;
+          cur = strip;
+        }
+        for (int h = 0; h < HI; ++h, ++ait) {
+          const uint32_t s = ait % IX_ASTAGES, ph = (ait / IX_ASTAGES) & 1;
+          if (!mbar_wait(&sm.a_empty[s], ph ^ 1, 32)) { ok = false; break; }
+          mbar_expect_tx(&sm.a_full[s], IX_BM * IX_D * 2);
+          tma_load_2d(sm.qa[s], &map_q, h * IX_D, b * T + qt * IX_BM, &sm.a_full[s]);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer ---------------------------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(IX_BN >> 3) << 17) | ((uint32_t)(IX_BM >> 4) << 24);
+      uint32_t ait = 0, bit = 0, hcount = 0;
+      int strip = 0, cur = -1;
+      bool ok = true;
+      for (int tile = tile_lo; tile < tile_hi && ok; ++tile) {
+        strip = strip_of(tile, strip);
+        if (strip != cur) {
+          if (cur >= 0) tc_commit(&sm.b_empty);         // every MMA that read the previous key tile has completed
+          if (!mbar_wait(&sm.b_full, bit & 1, 33)) { ok = false; break; }
+          tc_fence_after();
+          ++bit;
+          cur = strip;
+        }
+        for (int h = 0; h < HI; ++h, ++ait, ++hcount) {
+          const uint32_t acc = hcount & 1, aph = (hcount >> 1) & 1;
+          const uint32_t s = ait % IX_ASTAGES, ph = (ait / IX_ASTAGES) & 1;
+          if (!mbar_wait(&sm.acc_empty[acc], aph ^ 1, 34)) { ok = false; break; }
+          if (!mbar_wait(&sm.a_full[s], ph, 35)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t d_tmem = tmem_base + acc * IX_BN;
+          const uint64_t adesc = make_smem_desc(smem_u32(sm.qa[s]));
+#pragma unroll
+          for (int term = 0; term < 3; ++term) {
+            const uint64_t bdesc = make_smem_desc(smem_u32(sm.kb[term]));
+#pragma unroll
+            for (int k = 0; k < IX_D / 16; ++k)
+              tc_mma_bf16(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (term | k) ? 1u : 0u);
+          }
+          tc_commit(&sm.a_empty[s]);
+          tc_commit(&sm.acc_full[acc]);
+        }
+      }
+    }
+  } else {
+    // ------------------------------ epilogue warps ------------------------------
+    const int quarter = warp & 3;            // tensor-memory lanes 32*quarter .. +31 = query rows of the tile
+    const int half = (warp - 2) >> 2;        // columns half*128 .. +127
+    uint32_t hcount = 0;
+    int strip = 0;
+    bool ok = true;
+    for (int tile = tile_lo; tile < tile_hi && ok; ++tile) {
+      strip = strip_of(tile, strip);
+      const int b = strip / strips_per_batch, nt = strip % strips_per_batch;
+      const int qt = sched.qt_first[strip] + (tile - sched.prefix[strip]);
+      const int64_t row = (int64_t)b * T + qt * IX_BM + quarter * 32 + lane;
+      float out[128];
+#pragma unroll
+      for (int j = 0; j < 128; ++j) out[j] = 0.f;
+      for (int h = 0; h < HI; ++h, ++hcount) {
+        const uint32_t acc = hcount & 1, aph = (hcount >> 1) & 1;
+        if (!mbar_wait(&sm.acc_full[acc], aph, 36)) { ok = false; break; }
+        tc_fence_after();
+        const float c = coef[row * HI + h];
+        const uint32_t tbase = tmem_base + acc * IX_BN + half * 128 + ((uint32_t)(quarter * 32) << 16);
+#pragma unroll
+        for (int c0 = 0; c0 < 128; c0 += 32) {
+          uint32_t r[32];
+          tc_ld32(tbase + c0, r);
+          tc_wait_ld();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) out[c0 + j] = fmaf(c, fmaxf(__uint_as_float(r[j]), 0.f), out[c0 + j]);
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&sm.acc_empty[acc]);
+      }
+      if (!ok) break;
+      const int col0 = nt * IX_BN + half * 128;
+      float* dst = logits + row * n_ld + col0;
+#pragma unroll
+      for (int j = 0; j < 128; j += 4)
+        if (col0 + j + 4 <= n_ld) *reinterpret_cast<float4*>(dst + j) = make_float4(out[j], out[j + 1], out[j + 2], out[j + 3]);
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+}
+
+// Host side.  `coef` is caller workspace of B*T*HI floats; kh/km/kl are the three key terms, [B*n][64] bf16 each.
+bool kch_indexer_logits_tcgen05_ok(int B, int T, int n, int HI, int64_t q_ld, const void* q) {
+  static const bool off = [] { const char* e = getenv("KCH_INDEXER"); return e && e[0] == 'm'; }();   // "mma": legacy path
+  const int strips = (n + IX_BN - 1) / IX_BN;
+  return !off && T % IX_BM == 0 && HI >= 1 && HI <= 16 && (int64_t)B * strips <= IX_MAX_STRIPS && (q_ld % 8) == 0 &&
+         (((uintptr_t)q) & 15) == 0 && T / IX_BM < 32768;
+}
+
+int kch_indexer_logits_tcgen05(const void* q, int64_t q_ld, int q_normalize, const void* kh, const void* km,
+                               const void* kl, const float* w, float* coef, float* logits, int B, int T, int n, int HI,
+                               int64_t n_ld, float scale, int m, int64_t t0, int n_visible, cudaStream_t s) {
+  const int64_t rows = (int64_t)B * T;
+  indexer_coef_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, s>>>((const bf16*)q, q_ld, w, coef, rows, HI, scale, q_normalize);
+  KCH_LAUNCH_OK();
+  CUtensorMap mq, mkh, mkm, mkl;
+  int rc = make_map_2d(&mq, q, (uint64_t)rows, (uint64_t)HI * IX_D, (uint64_t)q_ld, IX_BM, IX_D);
+  if (rc) return rc;
+  const uint64_t krows = (uint64_t)B * n;
+  if ((rc = make_map_2d(&mkh, kh, krows, IX_D, IX_D, IX_BN, IX_D))) return rc;
+  if ((rc = make_map_2d(&mkm, km, krows, IX_D, IX_D, IX_BN, IX_D))) return rc;
+  if ((rc = make_map_2d(&mkl, kl, krows, IX_D, IX_D, IX_BN, IX_D))) return rc;
+  // visible tiles per strip: query tile qt sees key tile nt iff nt*256 < min(n, visible blocks of its last query)
+  IxSched sch;
+  const int strips = (n + IX_BN - 1) / IX_BN, QT = T / IX_BM;
+  sch.n_strips = B * strips;
+  int total = 0;
+  for (int b = 0; b < B; ++b)
+    for (int nt = 0; nt < strips; ++nt) {
+      int first = QT;
+      // visibility is monotone in qt: binary search the first visible query tile
+      int lo = 0, hi = QT;
+      while (lo < hi) {
+        const int mid = (lo + hi) / 2;
+        const int64_t tlast = (int64_t)mid * IX_BM + IX_BM - 1;
+        int64_t vis = n_visible >= 0 ? n_visible : (m > 0 ? (t0 + tlast + 1) / m : n);
+        if (vis > n) vis = n;
+        if ((int64_t)nt * IX_BN < vis) hi = mid; else lo = mid + 1;
+      }
+      first = lo;
+      const int sidx = b * strips + nt;
+      sch.prefix[sidx] = total;
+      sch.qt_first[sidx] = (short)first;
+      total += QT - first;
+    }
+  sch.prefix[sch.n_strips] = total;
+  sch.total_tiles = total;
+  if (total == 0) return KCH_OK;
+  static int sms = 0;
+  if (!sms) {
+    int dev = 0;
+    KCH_CUDA_OK(cudaGetDevice(&dev));
+    KCH_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  }
+  const size_t smem = sizeof(IxSmem) + 1024;
+  KCH_CUDA_OK(cudaFuncSetAttribute(indexer_logits_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  const int grid = total < sms ? total : sms;
+  indexer_logits_tcgen05_kernel<<<grid, TG_THREADS, smem, s>>>(mq, mkh, mkm, mkl, sch, coef, logits, T, n, HI, n_ld, strips);
+  KCH_LAUNCH_OK();
+  return KCH_OK;
 }
 
 unsigned int* kch_status_device_ptr() {

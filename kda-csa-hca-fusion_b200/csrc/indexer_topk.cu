@@ -343,6 +343,12 @@ static int64_t indexer_split_bytes(int B, int T, int n_blocks, int HI, int DI) {
 
 static int64_t indexer_ksplit_bytes(int B, int n_blocks) { return 3 * align256((int64_t)B * n_blocks * IM_D * 2); }
 
+// tcgen05 form of the logits (gemm_tcgen05.cu)
+bool kch_indexer_logits_tcgen05_ok(int B, int T, int n, int HI, int64_t q_ld, const void* q);
+int kch_indexer_logits_tcgen05(const void* q, int64_t q_ld, int q_normalize, const void* kh, const void* km,
+                               const void* kl, const float* w, float* coef, float* logits, int B, int T, int n, int HI,
+                               int64_t n_ld, float scale, int m, int64_t t0, int n_visible, cudaStream_t s);
+
 // `qraw` (optional): un-normalised bf16 queries read in place (token stride q_ld); then q_idx is not used.
 static int launch_indexer_logits(const float* q_idx, const float* k_idx, const float* w_idx, float* logits, int B,
                                  int T, int n_blocks, int HI, int DI, int64_t n_ld, float scale, int m, int64_t t0,
@@ -361,6 +367,12 @@ static int launch_indexer_logits(const float* q_idx, const float* k_idx, const f
     bf16* kh = (bf16*)p; bf16* km = (bf16*)(p + kb); bf16* kl = (bf16*)(p + 2 * kb);
     split3_rows_kernel<<<(unsigned)ceil_div64(krows * 8, 256), 256, 0, s>>>(k_idx, n_blocks, kbs, krows, kh, km, kl);
     KCH_LAUNCH_OK();
+    // tcgen05 path (query tiles of 128 rows, tensor-memory accumulators) when the shape allows and the workspace
+    // also holds the per-(query, head) coefficients; else the mma.sync kernel below
+    const int64_t coef_off = 3 * kb, coef_bytes = (int64_t)B * T * HI * 4;
+    if (kch_indexer_logits_tcgen05_ok(B, T, n_blocks, HI, q_ld, qraw) && split_bytes >= coef_off + coef_bytes)
+      return kch_indexer_logits_tcgen05(qraw, q_ld, q_normalize, kh, km, kl, w_idx, (float*)(p + coef_off), logits, B, T,
+                                        n_blocks, HI, n_ld, scale, m, t0, n_visible, s);
     IdxSplit sp = {};
     sp.kh = kh; sp.km = km; sp.kl = kl; sp.qraw = qraw; sp.q_ld = q_ld; sp.q_normalize = q_normalize;
     const int smem = 3 * IM_TN * 128 + 2 * IM_TQ * 128;
@@ -749,7 +761,8 @@ extern "C" int64_t kch_indexer_workspace_bytes(int B, int T, int n, int HI, int 
 
 extern "C" int64_t kch_indexer_workspace_bytes_ex(int B, int T, int n, int q_dtype) {
   if (B <= 0 || T <= 0 || n <= 0) return 0;
-  if (q_dtype == KCH_BF16) return indexer_logits_bytes(B, T, n) + indexer_ksplit_bytes(B, n);
+  if (q_dtype == KCH_BF16)   // logits + three key terms + one coefficient per (query, head), up to 16 heads
+    return indexer_logits_bytes(B, T, n) + indexer_ksplit_bytes(B, n) + align256((int64_t)B * T * 16 * 4);
   return indexer_logits_bytes(B, T, n);
 }
 

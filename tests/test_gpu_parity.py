@@ -332,6 +332,35 @@ def test_hca_errors(kch):
     assert kch.naive_hca(H[:, :0].to(DEV), *a, **kw).shape == (1, 0, c["nh"] * c["c"])
 
 
+@pytest.mark.parametrize("T", [200, 512])
+def test_csa_stage_topk_exact_with_bf16_queries(kch, T):
+    """bf16 queries are scored in place as exact tensor-core operands (T = 512: the tcgen05 kernel with 128-query
+    tiles; T = 200: the mma.sync kernel), keys as three bf16 terms: the picks must still be exact wherever the
+    boundary gap exceeds 1e-6 relative.  The queries are a strided column slice, as in the layer."""
+    g = torch.Generator().manual_seed(79)
+    B, HI, DI, m, topk = 2, 4, 64, 4, 24
+    n = T // m
+    wide = torch.randn(B, T, 40 + HI * DI, generator=g).to(torch.bfloat16)
+    q = wide[..., 40:].unflatten(-1, (HI, DI))
+    k = torch.randn(B, n, DI, generator=g)
+    w = torch.randn(B, T, HI, generator=g) * 0.1
+    ref, lg = orc.lightning_indexer(q.float(), k, w, topk, m=m, normalize_qk=True, return_logits=True)
+    from kch_b200 import csa as csa_mod
+    wide_d = wide.to(DEV)
+    qd = wide_d[..., 40:].unflatten(-1, (HI, DI))
+    mine = csa_mod.indexer_topk(qd, k.to(DEV), w.to(DEV), topk, m=m, normalize_qk=True, sorted_output=True).cpu().long()
+    sv = lg.sort(-1, descending=True).values
+    nvis = ((torch.arange(T) + 1) // m).clamp(max=n)
+    clear = torch.ones(B, T, dtype=torch.bool)
+    rows = nvis > topk
+    a, b = sv[:, :, topk - 1], sv[:, :, topk]
+    clear[:, rows] = ((a - b).abs() > 1e-6 * a.abs().clamp_min(1e-30))[:, rows]
+    same = (mine.sort(-1).values == ref.sort(-1).values).all(-1)
+    assert same[clear].all(), (~same[clear]).sum()
+    assert _multiset_equal(lg, mine, ref).all()
+    assert kch._lib.device_status() == 0
+
+
 # ---------------------------------------------------------------------------------------------- caches
 @pytest.mark.parametrize("name", list(CACHE_CASES))
 @pytest.mark.parametrize("bulk_prefix", [0, 13])
