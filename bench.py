@@ -72,39 +72,57 @@ def algorithmic_flops_per_token(cfg, T):
 
 
 class ClockSampler:
-    """Samples nvidia-smi clocks / throttle reasons while the timed region runs."""
+    """Samples nvidia-smi clocks / throttle reasons while the timed region runs (one streaming nvidia-smi
+    process, a line every 50 ms, started before and terminated after the region)."""
 
     Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
          "clocks_event_reasons.sw_power_cap")
 
     def __init__(self, index):
-        self.index, self.samples, self._stop, self._t = index, [], threading.Event(), None
+        self.index, self.samples, self._proc, self._t, self._mark = index, [], None, None, 0
+
+    def mark(self):
+        """Call when the timed region starts: earlier samples (idle clocks) are left out of the summary."""
+        self._mark = len(self.samples)
 
     def _run(self):
-        while not self._stop.is_set():
-            try:
-                out = subprocess.run(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                                      "-i", str(self.index)], capture_output=True, text=True, timeout=5).stdout
-                f = [s.strip() for s in out.strip().split(",")]
+        try:
+            for line in self._proc.stdout:
+                f = [x.strip() for x in line.strip().split(",")]
                 if len(f) >= 7:
                     self.samples.append(f)
-            except Exception:
-                pass
-            self._stop.wait(0.2)
+        except Exception:
+            pass
 
     def __enter__(self):
-        self._t = threading.Thread(target=self._run, daemon=True)
-        self._t.start()
+        try:
+            self._proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                           "-i", str(self.index), "-lms", "50"], stdout=subprocess.PIPE,
+                                          stderr=subprocess.DEVNULL, text=True)
+            self._t = threading.Thread(target=self._run, daemon=True)
+            self._t.start()
+            time.sleep(0.15)          # first sample lands before the region starts
+        except Exception:
+            self._proc = None
         return self
 
     def __exit__(self, *a):
-        self._stop.set()
-        self._t.join(timeout=6)
+        if self._proc is not None:
+            self._proc.terminate()
+            try:
+                self._proc.wait(timeout=5)
+            except Exception:
+                self._proc.kill()
+            if self._t is not None:
+                self._t.join(timeout=5)
 
     def summary(self):
         if not self.samples:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        if len(self.samples) > self._mark:
+            self.samples = self.samples[self._mark:]
+            self._mark = 0
         sm = sorted(float(s[0]) for s in self.samples if s[0].replace(".", "").isdigit())
         reasons = []
         for i, name in ((3, "hw_slowdown"), (4, "hw_thermal_slowdown"), (5, "sw_thermal_slowdown"), (6, "sw_power_cap")):
@@ -325,6 +343,7 @@ def run_b200(args):
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with ClockSampler(local_rank) as clocks:
         barrier()
+        clocks.mark()
         ev0.record()
         for _ in range(args.steps):
             y = step()
