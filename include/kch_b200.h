@@ -226,6 +226,8 @@ typedef struct kch_attend_args {
   float scale;
   void* out;                /* [B,T,nh*c] */
   int out_dtype;
+  int win_t0;               /* win_mode 0: query t sits at row t + win_t0 of `win` (rows before it: earlier tokens,
+                             * e.g. the tail of a cache's ring when a later chunk of a sequence is attended) */
 } kch_attend_args;
 int kch_attend(const kch_attend_args* args, void* stream);
 

@@ -21,6 +21,7 @@ struct AttnArgs {
   const int32_t* sel; int topk;
   int m; int64_t t0; int nvis_fixed;
   const void* win_ptr; int win_dtype; int64_t win_ld; int64_t win_batch_rows; int win_size; int win_mode; int win_len;
+  int win_t0;
   const void* sink; int sink_dtype;
   float scale;
   void* out; int out_dtype;
@@ -56,7 +57,7 @@ __global__ void __launch_bounds__(256) attn_generic_kernel(AttnArgs a) {
   int nw, wrow0;                                     // window entries and their first row
   if (a.win_size <= 0 || !a.win_ptr) { nw = 0; wrow0 = 0; }
   else if (a.win_mode == 1) { nw = a.win_len; wrow0 = 0; }
-  else { int lo = t - a.win_size + 1; if (lo < 0) lo = 0; nw = t - lo + 1; wrow0 = lo; }
+  else { const int tw = t + a.win_t0; int lo = tw - a.win_size + 1; if (lo < 0) lo = 0; nw = tw - lo + 1; wrow0 = lo; }
   const int E = ns + nw;
   float* sq = smem;                 // [nh][c]
   float* ss = sq + nh * c;          // [E][nh]   scores, then probabilities
@@ -198,6 +199,7 @@ extern "C" int kch_attend(const kch_attend_args* p, void* stream) {
   KCH_REQUIRE(p->sliding_window >= 0, "sliding_window=%d must be >= 0 (0 disables the branch)", p->sliding_window);
   KCH_REQUIRE(p->B >= 0 && p->T >= 0, "kch_attend: B=%d T=%d", p->B, p->T);
   KCH_REQUIRE(p->topk >= 0, "topk=%d must be >= 0", p->topk);
+  KCH_REQUIRE(p->win_t0 >= 0, "win_t0=%d must be >= 0", p->win_t0);
   if ((p->comp_dtype == KCH_FP8_E4M3 || p->comp_dtype == KCH_INT8))
     KCH_REQUIRE(p->comp_scales && p->c % 64 == 0, "block-scaled 8-bit rows need scales and c %% 64 == 0 (c=%d)", p->c);
   if (p->B == 0 || p->T == 0) return KCH_OK;
@@ -214,6 +216,7 @@ extern "C" int kch_attend(const kch_attend_args* p, void* stream) {
   a.m = p->m; a.t0 = p->t0; a.nvis_fixed = p->n_visible;
   a.win_ptr = p->win; a.win_dtype = p->win_dtype; a.win_ld = p->win_ld; a.win_batch_rows = p->win_batch_rows;
   a.win_size = p->win ? p->sliding_window : 0; a.win_mode = p->win_mode; a.win_len = p->win_len;
+  a.win_t0 = p->win_t0;
   a.sink = p->sink; a.sink_dtype = p->sink_dtype; a.scale = p->scale; a.out = p->out; a.out_dtype = p->out_dtype;
   int nw_max = !p->win ? 0 : (p->win_mode == 1 ? p->win_len : p->sliding_window);
   // maximum entry count over all queries bounds the shared-memory need

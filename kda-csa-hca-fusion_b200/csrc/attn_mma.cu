@@ -26,7 +26,7 @@ struct AttnMmaArgs {
   const bf16* comp; int64_t comp_batch_rows; int n_comp;
   const int32_t* sel; int topk;
   int m; int64_t t0; int nvis_fixed;
-  const bf16* win; int64_t win_ld; int64_t win_batch_rows; int win_size;
+  const bf16* win; int64_t win_ld; int64_t win_batch_rows; int win_size; int win_t0;
   const void* sink; int sink_dtype;
   float scale;
   bf16* out;
@@ -78,7 +78,7 @@ __global__ void __launch_bounds__(AM_WARPS * 32, MINB) attn_mma_kernel(AttnMmaAr
   const int nvis = (int)(nv64 < a.n_comp ? nv64 : a.n_comp);
   const int ns = a.sel ? a.topk : nvis;
   int nw = 0, wrow0 = 0;
-  if (a.win_size > 0 && a.win) { int lo = t - a.win_size + 1; if (lo < 0) lo = 0; nw = t - lo + 1; wrow0 = lo; }
+  if (a.win_size > 0 && a.win) { const int tw = t + a.win_t0; int lo = tw - a.win_size + 1; if (lo < 0) lo = 0; nw = tw - lo + 1; wrow0 = lo; }
   const int E = ns + nw;
   const int ntiles = (E + AM_TILE - 1) / AM_TILE;
   const int32_t* selrow = a.sel ? a.sel + bt * a.topk : nullptr;
@@ -249,7 +249,7 @@ int kch_attend_mma(const kch_attend_args* p, void* stream) {
   a.m = p->m; a.t0 = p->t0; a.nvis_fixed = p->n_visible;
   const bool has_win = p->win && p->sliding_window > 0;
   a.win = has_win ? (const bf16*)p->win : nullptr; a.win_ld = p->win_ld; a.win_batch_rows = p->win_batch_rows;
-  a.win_size = has_win ? p->sliding_window : 0;
+  a.win_size = has_win ? p->sliding_window : 0; a.win_t0 = p->win_t0;
   a.sink = p->sink; a.sink_dtype = p->sink_dtype; a.scale = p->scale; a.out = (bf16*)p->out;
   static_assert(16 * AM_QLD * 2 <= AM_TILE * AM_C * 2, "query staging tile must fit one ring stage");
   int64_t nq = (int64_t)p->B * p->T;

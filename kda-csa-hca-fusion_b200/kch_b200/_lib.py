@@ -27,7 +27,7 @@ class AttendArgs(C.Structure):
                 ("sel_indices", _vp), ("topk", _i), ("m", _i), ("t0", _i64), ("n_visible", _i),
                 ("win", _vp), ("win_dtype", _i), ("win_ld", _i64), ("win_batch_rows", _i64),
                 ("sliding_window", _i), ("win_mode", _i), ("win_len", _i),
-                ("sink", _vp), ("sink_dtype", _i), ("scale", _f), ("out", _vp), ("out_dtype", _i)]
+                ("sink", _vp), ("sink_dtype", _i), ("scale", _f), ("out", _vp), ("out_dtype", _i), ("win_t0", _i)]
 
 
 class Epilogue(C.Structure):

@@ -267,7 +267,7 @@ def mma_attention_eligible(dtype, c, nh, normalize_qk, scale):
 
 def attend(q, comp, *, nh, c, sel=None, m=0, t0=0, n_visible=-1, q_normalize=False, comp_norms=None,
            comp_scales=None, comp_kind=None, win=None, sliding_window=0, win_mode=0, win_len=0, sink=None,
-           scale=1.0, out_dtype=torch.float32):
+           scale=1.0, out_dtype=torch.float32, win_t0=0):
     """Kernel-level joint-softmax attention.  q ``[B,T,nh*c]`` view (row-strided ok); comp ``[B,n,c]``
     contiguous or None; win ``[B,Tw,c]`` (row-strided ok) or None."""
     lib = _lib.load()
@@ -304,6 +304,7 @@ def attend(q, comp, *, nh, c, sel=None, m=0, t0=0, n_visible=-1, q_normalize=Fal
         keep.append(w3)
         a.win, a.win_dtype, a.win_ld, a.win_batch_rows = w3.data_ptr(), _lib.dtype_tag(w3.dtype), wld, wbsr
         a.sliding_window, a.win_mode, a.win_len = int(sliding_window), int(win_mode), int(win_len)
+        a.win_t0 = int(win_t0)
     if sink is not None:
         sink = sink.contiguous()
         keep.append(sink)

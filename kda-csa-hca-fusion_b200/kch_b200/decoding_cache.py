@@ -110,6 +110,57 @@ class _CacheBase:
         else:
             self._acc_len += 1
 
+    # ---- state export / import (not in the reference: checkpoint / resume of a long decode session) ----------
+    def export_state(self):
+        """Everything needed to continue decoding elsewhere: a dict of tensors (clones, trimmed to the rows in
+        use) and Python counters.  ``import_state`` of a cache built with the same constructor arguments
+        restores it exactly."""
+        nb = self._n_blocks
+        st = {
+            "kind": type(self).__name__, "B": self.B, "c": self.c, "win": self.win, "dtype": str(self.dtype),
+            "kv_quant": self.kv_quant, "n_blocks": nb, "acc_len": self._acc_len, "n_tokens_seen": self._n_tokens_seen,
+            "acc": [a.clone() for a in self._acc],
+            "comp": None if self._comp is None else self._comp[:, :nb].clone(),
+            "scales": None if self._scales is None else self._scales[:, :nb].clone(),
+            "norms": None if self._norms is None else self._norms[:, :nb].clone(),
+            "ring": None if self._sw is None else self._sw._buf.clone(),
+            "ring_n": 0 if self._sw is None else self._sw._n,
+        }
+        if hasattr(self, "_prev"):
+            st.update(prev=[p.clone() for p in self._prev], has_prev=self._has_prev,
+                      kcomp=None if self._kcomp is None else self._kcomp[:, :nb].clone(),
+                      kcomp_norms=None if self._kcomp_norms is None else self._kcomp_norms[:, :nb].clone())
+        return st
+
+    def import_state(self, st):
+        if st["kind"] != type(self).__name__ or st["B"] != self.B or st["c"] != self.c or st["win"] != self.win \
+                or st["dtype"] != str(self.dtype) or st["kv_quant"] != self.kv_quant:
+            raise ValueError(f"{type(self).__name__}.import_state: the state was exported from a cache with a "
+                             f"different geometry ({st['kind']}, B={st['B']}, c={st['c']}, win={st['win']}, "
+                             f"{st['dtype']}, kv_quant={st['kv_quant']})")
+        self.reset()
+        nb = int(st["n_blocks"])
+        if nb:
+            self._grow(nb)
+            self._comp[:, :nb] = st["comp"].to(self.device)
+            self._norms[:, :nb] = st["norms"].to(self.device)
+            if self._scales is not None:
+                self._scales[:, :nb] = st["scales"].to(self.device)
+            if hasattr(self, "_prev"):
+                self._kcomp[:, :nb] = st["kcomp"].to(self.device)
+                self._kcomp_norms[:, :nb] = st["kcomp_norms"].to(self.device)
+        for a, src in zip(self._acc, st["acc"]):
+            a.copy_(src)
+        if hasattr(self, "_prev"):
+            for p_, src in zip(self._prev, st["prev"]):
+                p_.copy_(src)
+            self._has_prev = bool(st["has_prev"])
+        if self._sw is not None:
+            self._sw._buf.copy_(st["ring"])
+            self._sw._n = int(st["ring_n"])
+        self._n_blocks, self._acc_len, self._n_tokens_seen = nb, int(st["acc_len"]), int(st["n_tokens_seen"])
+        self._sync_counters()
+
     def _decode_attend_ok(self, nh):
         return self.c == 128 and nh <= 16
 

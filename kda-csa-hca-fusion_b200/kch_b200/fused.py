@@ -18,7 +18,7 @@ import torch
 import torch.nn as nn
 
 from . import _lib
-from .csa import attend, fuse_rows, linear, naive_csa, rownorm
+from .csa import attend, fuse_rows, indexer_topk, linear, mma_attention_eligible, naive_csa, rownorm
 from .decoding_cache import CSADecodingCache, HCADecodingCache
 from .hca import naive_hca
 from .kda import chunk_gate_supported, kda_forward, validate_kda_backend
@@ -462,8 +462,9 @@ class HybridKCHAttention(nn.Module):
 
 class HybridDecoding(nn.Module):
     """Decode-time wiring of the stack: a multi-token call runs the full-sequence operators and fills the
-    per-layer caches from the same projections; a one-token call appends to the caches and attends
-    through them; KDA layers carry their recurrent state and conv lookback."""
+    per-layer caches from the same projections (a later multi-token call continues the sequence: chunked
+    prefill); a one-token call appends to the caches and attends through them; KDA layers carry their
+    recurrent state and conv lookback."""
 
     def __init__(self, cfg: HybridConfig | None = None, total_layers: int = 5, *, model=None, kv_quant=None,
                  reserve_tokens: int = 0, use_cuda_graph: bool = False):
@@ -486,6 +487,43 @@ class HybridDecoding(nn.Module):
         self._caches = {}
         self._graph = None
 
+    def export_state(self):
+        """The whole decode session as a dict: stacked KDA state, conv lookbacks and every layer cache
+        (``CSADecodingCache.export_state`` / ``HCADecodingCache.export_state``).  Tensors stay on their device;
+        move them with ``torch.save`` / ``.cpu()`` as needed."""
+        model = self.model
+        return {
+            "layout": list(model.layout),
+            "kda_state": None if model._kda_state is None else model._kda_state.clone(),
+            "conv_lookbacks": [None if l._conv_lookback is None else l._conv_lookback.clone()
+                               for l in model.layers if isinstance(l, KDAHybridLayer)],
+            "caches": {i: c.export_state() for i, c in self._caches.items()},
+        }
+
+    def import_state(self, st):
+        model, cfg = self.model, self.cfg
+        if list(st["layout"]) != list(model.layout):
+            raise ValueError(f"HybridDecoding.import_state: layout {st['layout']} does not match {list(model.layout)}")
+        self.reset()
+        dev = next(model.parameters()).device
+        if st["kda_state"] is not None:
+            model._kda_state = st["kda_state"].to(dev).clone()
+        kda_layers = [l for l in model.layers if isinstance(l, KDAHybridLayer)]
+        for layer, lb in zip(kda_layers, st["conv_lookbacks"]):
+            layer._conv_lookback = None if lb is None else lb.to(dev).clone()
+        for i, cst in st["caches"].items():
+            layer = model.layers[i]
+            dtype = getattr(torch, cst["dtype"].split(".")[-1])
+            if isinstance(layer, CSAHybridLayer):
+                cache = CSADecodingCache(cst["B"], cfg.csa_c, cfg.csa_cI, cfg.csa_m, cfg.csa_sliding_window, dev, dtype,
+                                         kv_quant=cst["kv_quant"])
+            else:
+                cache = HCADecodingCache(cst["B"], cfg.hca_c, cfg.hca_m2, cfg.hca_sliding_window, dev, dtype,
+                                         kv_quant=cst["kv_quant"])
+            cache.import_state(cst)
+            self._caches[i] = cache
+        self.kv_quant = next((c["kv_quant"] for c in st["caches"].values()), self.kv_quant)
+
     def _cache(self, i, layer, h):
         cfg, B = self.cfg, h.shape[0]
         cache = self._caches.get(i)
@@ -503,11 +541,75 @@ class HybridDecoding(nn.Module):
             self._caches[i] = cache
         return cache
 
+    # ---- a later chunk of a sequence (multi-token call on caches that already hold tokens) -----------------------
+    # Not in the reference, whose caches only attend one token at a time (ops_decoding_cache.py:831-836).  The
+    # chunk's rows are appended first, then its queries run through the full-sequence kernels against everything
+    # the cache holds: visibility n < (t0 + t + 1) // m with t0 = tokens before the chunk, window keys = the tail
+    # of the ring followed by the chunk's own keys.  Same values as feeding the chunk token by token.
+    @staticmethod
+    def _ring_tail(cache, win):
+        if cache._sw is None or win <= 1 or cache._sw.n_valid == 0:
+            return None
+        return cache._sw.get()[:, -(win - 1):]
+
+    def _csa_chunk(self, layer, cache, h):
+        cfg = self.cfg
+        B, T, _ = h.shape
+        c, cI, dc, nIh, nh, m, win = (cfg.csa_c, cfg.csa_cI, cfg.csa_dc, cfg.csa_nIh, cfg.csa_nh, cfg.csa_m,
+                                      cfg.csa_sliding_window)
+        t0 = cache.n_tokens_seen
+        proj = linear(h, layer.fused_weight())
+        Ca, Cb, Za, Zb, K_idx, Z_idx, cQ, w_idx = proj[..., :4 * c + 2 * cI + dc + nIh].split(
+            [c, c, c, c, cI, cI, dc, nIh], dim=-1)
+        qq = linear(cQ, layer.q_weight())
+        q, q_idx = qq[..., :nh * c + nIh * cI].split([nh * c, nIh * cI], dim=-1)
+        prev = self._ring_tail(cache, win)
+        cache.append_step(Ca, Cb, Za, Zb, K_idx, Z_idx, layer.Ba, layer.Bb, layer.B_idx)
+        nb = cache.n_blocks
+        indices = None
+        if cfg.csa_topk > 0 and nb > 0:
+            kn = (cache._kcomp[:, :nb].float() / cache._kcomp_norms[:, :nb].unsqueeze(-1)).contiguous()
+            indices = indexer_topk(q_idx.unflatten(-1, (nIh, cI)), kn, w_idx, cfg.csa_topk, m=m, t0=t0,
+                                   normalize_qk=True, sorted_output=False, k_prenormalized=True)
+        kdt = torch.bfloat16 if mma_attention_eligible(h.dtype, c, nh, True, 1.0) else torch.float32
+        comp_n = rownorm(cache.C_comp, True, kdt) if (cfg.csa_topk > 0 and nb > 0) else None
+        local, P = None, 0
+        if win > 0:
+            local = rownorm(Ca, True, kdt)
+            if prev is not None:
+                P = prev.shape[1]
+                local = torch.cat([prev.to(kdt), local], dim=1)
+        return attend(q, comp_n, nh=nh, c=c, sel=indices, m=m, t0=t0, q_normalize=True, win=local, sliding_window=win,
+                      sink=layer.sink, scale=1.0, out_dtype=h.dtype, win_t0=P)
+
+    def _hca_chunk(self, layer, cache, h):
+        cfg = self.cfg
+        c, dc, nh, m2, win = cfg.hca_c, cfg.hca_dc, cfg.hca_nh, cfg.hca_m2, cfg.hca_sliding_window
+        t0 = cache.n_tokens_seen
+        proj = linear(h, layer.fused_weight())
+        C, Z, cQ = proj[..., :2 * c + dc].split([c, c, dc], dim=-1)
+        q = linear(cQ, layer.W_UQ.weight)
+        prev = self._ring_tail(cache, win)
+        cache.append_step(C, Z, layer.B_pos)
+        nb = cache.n_blocks
+        kdt = torch.bfloat16 if mma_attention_eligible(h.dtype, c, nh, True, 1.0) else torch.float32
+        comp_n = rownorm(cache.C_comp, True, kdt) if nb > 0 else None
+        local, P = None, 0
+        if win > 0:
+            local = rownorm(C, True, kdt)
+            if prev is not None:
+                P = prev.shape[1]
+                local = torch.cat([prev.to(kdt), local], dim=1)
+        return attend(q, comp_n, nh=nh, c=c, sel=None, m=m2, t0=t0, q_normalize=True, win=local, sliding_window=win,
+                      sink=layer.sink, scale=1.0, out_dtype=h.dtype, win_t0=P)
+
     def _csa(self, i, layer, h, residual):
         cfg = self.cfg
         B, T, _ = h.shape
         cache = self._cache(i, layer, h)
-        if T > 1:
+        if T > 1 and cache.n_tokens_seen > 0:
+            o_core = self._csa_chunk(layer, cache, h)
+        elif T > 1:
             o_core, proj = layer.core(h, return_projections=True)
             cache.append_step(*proj, layer.Ba, layer.Bb, layer.B_idx)
         else:
@@ -537,7 +639,9 @@ class HybridDecoding(nn.Module):
         cfg = self.cfg
         B, T, _ = h.shape
         cache = self._cache(i, layer, h)
-        if T > 1:
+        if T > 1 and cache.n_tokens_seen > 0:
+            o_core = self._hca_chunk(layer, cache, h)
+        elif T > 1:
             o_core, (C, Z) = layer.core(h, return_projections=True)
             cache.append_step(C, Z, layer.B_pos)
         else:

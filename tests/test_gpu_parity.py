@@ -562,3 +562,54 @@ def test_host_pipeline_matches_direct_passes(kch):
         ref = model(x.to(DEV)).cpu()
         assert torch.equal(ref, y)
 
+
+@pytest.mark.parametrize("quant", [None, "fp8"])
+def test_decode_state_export_import_round_trip(kch, quant):
+    """A session exported after some steps and imported into a fresh wrapper continues bit for bit."""
+    cfgd = dict(d_model=256, n_heads_qk=2, n_heads_v=2, head_dim_k=128, head_dim_v=128, kda_chunk_size=64, csa_m=4,
+                csa_topk=8, csa_nh=4, csa_c=128, csa_dc=64, csa_nIh=2, csa_cI=64, csa_sliding_window=16, hca_m2=16,
+                hca_nh=4, hca_c=128, hca_dc=64, hca_sliding_window=16)
+    cfg, model, _ = _load_model(kch, cfgd, 5, 97, torch.bfloat16)
+    x = syn.hidden_states(98, 2, 130, cfg.d_model, torch.bfloat16).to(DEV)
+    a = kch.HybridDecoding(model=model, kv_quant=quant)
+    a.reset()
+    a(x[:, :90])
+    for t in range(90, 110):
+        a(x[:, t:t + 1])
+    st = a.export_state()
+    st = {k: (v.cpu() if torch.is_tensor(v) else v) for k, v in st.items()}          # e.g. through host memory
+    ref = [a(x[:, t:t + 1]).float() for t in range(110, 130)]
+    b = kch.HybridDecoding(model=model, kv_quant=quant)
+    b.import_state(st)
+    got = [b(x[:, t:t + 1]).float() for t in range(110, 130)]
+    assert all(torch.equal(r, g) for r, g in zip(ref, got))
+    assert all(c.n_tokens_seen == 130 for c in b._caches.values())
+
+
+@pytest.mark.parametrize("quant", [None, "int8"])
+def test_chunked_prefill_matches_token_by_token(kch, quant):
+    """Later multi-token calls continue a sequence through the caches (chunked prefill): same outputs as feeding
+    the same tokens one at a time, and the same state afterwards."""
+    cfgd = dict(d_model=256, n_heads_qk=2, n_heads_v=2, head_dim_k=128, head_dim_v=128, kda_chunk_size=64, csa_m=4,
+                csa_topk=64, csa_nh=4, csa_c=128, csa_dc=64, csa_nIh=2, csa_cI=64, csa_sliding_window=16, hca_m2=16,
+                hca_nh=4, hca_c=128, hca_dc=64, hca_sliding_window=16)
+    cfg, model, _ = _load_model(kch, cfgd, 5, 101, torch.bfloat16)
+    x = syn.hidden_states(102, 2, 230, cfg.d_model, torch.bfloat16).to(DEV)
+    cuts = [40, 97, 225]                                   # chunks of 57 (recurrent KDA) and 128 (chunked KDA) tokens
+    a = kch.HybridDecoding(model=model, kv_quant=quant)
+    a.reset()
+    ya = [a(x[:, :cuts[0]])] + [a(x[:, t:t + 1]) for t in range(cuts[0], 230)]
+    ya = torch.cat(ya, 1).float()
+    b = kch.HybridDecoding(model=model, kv_quant=quant)
+    b.reset()
+    yb = [b(x[:, :cuts[0]]), b(x[:, cuts[0]:cuts[1]]), b(x[:, cuts[1]:cuts[2]])]
+    assert all(c.n_tokens_seen == cuts[2] for c in b._caches.values())
+    yb += [b(x[:, t:t + 1]) for t in range(cuts[2], 230)]  # and decoding goes on from the chunk-filled caches
+    yb = torch.cat(yb, 1).float()
+    d = (ya - yb).abs()
+    assert float(d.max()) <= 6.3e-2 and float(d.mean()) <= 2e-3, (float(d.max()), float(d.mean()))   # bf16 residual stream
+    for ca, cb in zip(a._caches.values(), b._caches.values()):
+        assert ca.n_blocks == cb.n_blocks and ca.accumulator_len == cb.accumulator_len
+        assert md(ca.C_comp.float(), cb.C_comp.float()) <= 2e-2
+    assert kch._lib.device_status() == 0
+
