@@ -16,8 +16,9 @@ from .fused import (CSAHybridLayer, HCAHybridLayer, HybridConfig, HybridDecoding
                     HybridKCHAttention, KDAHybridLayer)
 from .backend import install, uninstall  # noqa: F401
 from .host_pipeline import HostPipeline  # noqa: F401
+from .decoding_modules import CSAAttnDecoding, HCAAttnDecoding, KDAAttnDecoding  # noqa: F401
 
-__all__ = ["HostPipeline", "kda_forward", "naive_chunk_kda", "naive_recurrent_kda", "validate_kda_backend", "csa_compress_kv",
+__all__ = ["HostPipeline", "CSAAttnDecoding", "HCAAttnDecoding", "KDAAttnDecoding", "kda_forward", "naive_chunk_kda", "naive_recurrent_kda", "validate_kda_backend", "csa_compress_kv",
            "csa_compress_kv_overlapped", "csa_lightning_indexer", "naive_csa", "naive_hca", "CSADecodingCache",
            "HCADecodingCache", "HybridConfig", "HybridKCHAttention", "HybridDecoding", "KDAHybridLayer",
            "CSAHybridLayer", "HCAHybridLayer", "install", "uninstall"]

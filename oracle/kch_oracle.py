@@ -750,3 +750,62 @@ class HybridDecodeOracle:
                     o = oo.reshape(B, 1, -1).to(x.dtype)
             x = x + F.linear(o, p["o_proj.weight"])
         return x
+
+
+class StandaloneDecodeOracle:
+    """The single-operator decode modules ``KDAAttnDecoding`` / ``CSAAttnDecoding`` / ``HCAAttnDecoding``
+    (``run_decoding.py:234-598``): operator + output projection, no pre-norm, no residual.  ``p`` holds the
+    module's ``state_dict``; ``cfg`` its constructor arguments."""
+
+    def __init__(self, kind, p, **cfg):
+        self.kind, self.p, self.cfg = kind, p, cfg
+        self.state = self.lookback = self.cache = None
+
+    def forward(self, x):
+        p, c = self.p, self.cfg
+        B, T, _ = x.shape
+        if self.kind == "kda":
+            H, K, V = c["H"], c["K"], c["V"]
+            xc, self.lookback = short_conv(x, p["short_conv.weight"], p["short_conv.bias"], self.lookback)
+            pp = {"q_proj.weight": p["q.weight"], "k_proj.weight": p["k.weight"], "v_proj.weight": p["v.weight"],
+                  "g_down.weight": p["g_down.weight"], "g_up.weight": p["g_up.weight"], "beta.weight": p["beta.weight"]}
+            q, k, v, g, beta = kda_layer_inputs(pp, xc, H, H, K, V, 0.1)
+            o, self.state = recurrent_kda(q, k, v, g, beta, K ** -0.5, self.state)
+            return F.linear(o.reshape(B, T, H * V), p["o.weight"])
+        if self.kind == "csa":
+            if self.cache is None:
+                self.cache = CSACacheOracle(B, c["c"], c["c_I"], c["m"], c["sliding_window"], x.dtype)
+            W = [p[n] for n in ("W_aKV.weight", "W_bKV.weight", "W_aZ.weight", "W_bZ.weight", "Ba", "Bb", "W_DQ.weight",
+                                "W_UQ.weight", "W_IUQ.weight", "W_w.weight", "W_KV_idx.weight", "W_Z_idx.weight", "B_idx")]
+            if T > 1:
+                o, aux = csa_forward(x, *W, m=c["m"], topk=c["topk"], nh=c["nh"], nIh=c["nIh"], c=c["c"], c_I=c["c_I"],
+                                     dc=c["dc"], sliding_window=c["sliding_window"], sink_logits=p["sink"],
+                                     normalize_qk=True, return_aux=True)
+                self.cache.append(aux["Ca"], aux["Cb"], aux["Za"], aux["Zb"], aux["K_idx"], aux["Z_idx"], p["Ba"], p["Bb"],
+                                  p["B_idx"])
+            else:
+                Wcat = torch.cat([W[0], W[1], W[2], W[3], W[10], W[11]], dim=0)
+                Ca, Cb, Za, Zb, K_idx, Z_idx = F.linear(x, Wcat).split([c["c"]] * 4 + [c["c_I"]] * 2, dim=-1)
+                cQ = F.linear(x, W[6])
+                q = F.linear(cQ, W[7]).reshape(B, 1, c["nh"], c["c"])
+                q_idx = F.linear(cQ, W[8]).reshape(B, 1, c["nIh"], c["c_I"])
+                w_idx = F.linear(x, W[9])
+                self.cache.append(Ca, Cb, Za, Zb, K_idx, Z_idx, p["Ba"], p["Bb"], p["B_idx"])
+                o = self.cache.step(l2_normalize(q.float()), q_idx.float(), w_idx.float(), topk=c["topk"],
+                                    sink_logits=p["sink"], scale=1.0).reshape(B, 1, -1).to(x.dtype)
+            return F.linear(o, p["o_proj.weight"])
+        if self.cache is None:
+            self.cache = HCACacheOracle(B, c["c"], c["m2"], c["sliding_window"], x.dtype)
+        if T > 1:
+            o, aux = hca_forward(x, p["W_KV.weight"], p["W_Z.weight"], p["B_pos"], p["W_DQ.weight"], p["W_UQ.weight"],
+                                 m2=c["m2"], nh=c["nh"], c=c["c"], dc=c["dc"], sliding_window=c["sliding_window"],
+                                 sink_logits=p["sink"], return_aux=True)
+            self.cache.append(aux["C"], aux["Z"], p["B_pos"])
+        else:
+            C = F.linear(x, p["W_KV.weight"])
+            Z = F.linear(x, p["W_Z.weight"])
+            q = F.linear(F.linear(x, p["W_DQ.weight"]), p["W_UQ.weight"]).reshape(B, 1, c["nh"], c["c"])
+            self.cache.append(C, Z, p["B_pos"])
+            o = self.cache.step(l2_normalize(q.float()), sink_logits=p["sink"], scale=1.0).reshape(B, 1, -1).to(x.dtype)
+        return F.linear(o, p["o_proj.weight"])
+

@@ -24,7 +24,7 @@ sys.path.insert(0, os.path.join(ROOT, "kda-csa-hca-fusion_b200"))
 sys.path.insert(0, os.path.join(ROOT, "tests"))
 
 from golden_cases import (CACHE_CASES, CSA_CASES, DECODE_CASE, HCA_CASES, HYBRID_CASES,  # noqa: E402
-                          KDA_CASES, checksum, make_cache_stream, np32)
+                          KDA_CASES, STANDALONE_CASE, checksum, make_cache_stream, np32)
 from kch_b200 import synthetic as syn  # noqa: E402
 
 
@@ -150,6 +150,23 @@ def main():
                                   cfg.csa_m, cfg.csa_topk, cfg.csa_nh, cfg.csa_c, cfg.csa_dc, cfg.csa_nIh,
                                   cfg.csa_cI, cfg.csa_sliding_window, cfg.hca_m2, cfg.hca_nh, cfg.hca_c,
                                   cfg.hca_dc, cfg.hca_sliding_window], dtype=np.int64)
+
+    # ---- single-operator decode modules: parameters as the reference's constructors drew them ----------
+    c = STANDALONE_CASE
+    x = syn.hidden_states(c["seed"] + 100, c["B"], c["prefill"] + c["steps"], c["d_model"], c["dtype"])
+    os.environ["KDA_BACKEND"] = "reference"
+    for kind, cls in (("kda", run_decoding.KDAAttnDecoding), ("csa", run_decoding.CSAAttnDecoding),
+                      ("hca", run_decoding.HCAAttnDecoding)):
+        torch.manual_seed(c["seed"])
+        mod = cls(c["d_model"], **c[kind]).to(c["dtype"]).eval()
+        if kind != "kda":
+            mod.sink.data = torch.randn(mod.sink.shape, generator=torch.Generator().manual_seed(c["seed"] + 1))
+        for k_, v_ in mod.state_dict().items():
+            out[f"standalone/{kind}/param/{k_}"] = np32(v_)
+        ys = [mod(x[:, :c["prefill"]])]
+        for t in range(c["steps"]):
+            ys.append(mod(x[:, c["prefill"] + t:c["prefill"] + t + 1]))
+        out[f"standalone/{kind}/y"] = np32(torch.cat(ys, 1))
 
     path = os.path.join(HERE, "reference_outputs.npz")
     np.savez_compressed(path, **out)

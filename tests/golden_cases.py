@@ -58,6 +58,12 @@ HYBRID_CASES = {
 
 DECODE_CASE = dict(seed=61, B=2, d_model=64, prefill=21, steps=7, csa_topk=100, dtype=F32)
 
+# single-operator decode modules (run_decoding.py:234-598): constructor arguments per kind
+STANDALONE_CASE = dict(seed=83, B=2, d_model=32, prefill=13, steps=9, dtype=F32,
+                       kda=dict(H=2, K=8, V=8),
+                       csa=dict(m=4, topk=100, nh=2, c=8, dc=8, nIh=1, c_I=4, sliding_window=4),
+                       hca=dict(m2=4, nh=2, c=8, dc=8, sliding_window=4))
+
 
 def np32(t: torch.Tensor) -> np.ndarray:
     return t.detach().to(torch.float32).cpu().numpy()

@@ -6,7 +6,7 @@ import numpy as np
 import pytest
 import torch
 
-from golden_cases import (CACHE_CASES, CSA_CASES, DECODE_CASE, HCA_CASES, HYBRID_CASES, KDA_CASES,
+from golden_cases import (CACHE_CASES, CSA_CASES, DECODE_CASE, STANDALONE_CASE, HCA_CASES, HYBRID_CASES, KDA_CASES,
                           make_cache_stream, np32)
 from kch_b200 import synthetic as syn
 from oracle import kch_oracle as orc
@@ -612,4 +612,23 @@ def test_chunked_prefill_matches_token_by_token(kch, quant):
         assert ca.n_blocks == cb.n_blocks and ca.accumulator_len == cb.accumulator_len
         assert md(ca.C_comp.float(), cb.C_comp.float()) <= 2e-2
     assert kch._lib.device_status() == 0
+
+
+@pytest.mark.parametrize("kind", ["kda", "csa", "hca"])
+def test_standalone_decode_modules_against_reference(kch, golden, kind):
+    """The single-operator decode modules load the reference modules' state_dict unchanged and reproduce their
+    outputs (prefill of 13 tokens, then 9 one-token steps)."""
+    from golden_cases import STANDALONE_CASE as c
+    from kch_b200 import decoding_modules as dm
+    cls = {"kda": dm.KDAAttnDecoding, "csa": dm.CSAAttnDecoding, "hca": dm.HCAAttnDecoding}[kind]
+    mod = cls(c["d_model"], **c[kind])
+    pre = f"standalone/{kind}/param/"
+    sd = {k[len(pre):]: torch.from_numpy(golden[k]) for k in golden.files if k.startswith(pre)}
+    mod.load_state_dict(sd, strict=True)
+    mod = mod.to(DEV).eval()
+    x = syn.hidden_states(c["seed"] + 100, c["B"], c["prefill"] + c["steps"], c["d_model"], c["dtype"]).to(DEV)
+    ys = [mod(x[:, :c["prefill"]])]
+    for t in range(c["steps"]):
+        ys.append(mod(x[:, c["prefill"] + t:c["prefill"] + t + 1]))
+    assert md(torch.cat(ys, 1), golden[f"standalone/{kind}/y"]) <= 5e-5
 

@@ -4,7 +4,7 @@ import pytest
 import torch
 
 from golden_cases import (CACHE_CASES, CSA_CASES, DECODE_CASE, HCA_CASES, HYBRID_CASES, KDA_CASES,
-                          checksum, make_cache_stream, np32)
+                          STANDALONE_CASE, checksum, make_cache_stream, np32)
 from kch_b200 import synthetic as syn
 from oracle import kch_oracle as orc
 
@@ -146,3 +146,19 @@ def test_hybrid_decode(golden):
     # csa_topk >= number of blocks (select-all), as in the reference's own cache tests, so that
     # tie order in top-k cannot matter
     assert maxdiff(y, golden["decode/y"]) <= 5e-5
+
+
+@pytest.mark.parametrize("kind", ["kda", "csa", "hca"])
+def test_standalone_decode_modules(golden, kind):
+    """KDAAttnDecoding / CSAAttnDecoding / HCAAttnDecoding of the reference (run_decoding.py:234-598), parameters as
+    its constructors drew them (stored next to the outputs)."""
+    c = STANDALONE_CASE
+    pre = f"standalone/{kind}/param/"
+    p = {k[len(pre):]: torch.from_numpy(golden[k]) for k in golden.files if k.startswith(pre)}
+    x = syn.hidden_states(c["seed"] + 100, c["B"], c["prefill"] + c["steps"], c["d_model"], c["dtype"])
+    dec = orc.StandaloneDecodeOracle(kind, p, **c[kind])
+    ys = [dec.forward(x[:, :c["prefill"]])]
+    for t in range(c["steps"]):
+        ys.append(dec.forward(x[:, c["prefill"] + t:c["prefill"] + t + 1]))
+    assert maxdiff(torch.cat(ys, 1), golden[f"standalone/{kind}/y"]) <= 5e-5
+
