@@ -480,7 +480,8 @@ def test_split_decode_attention_against_oracle(kch, kind):
     assert kch._lib.device_status() == 0
 
 
-def test_hybrid_decode_graph_replay_matches_eager(kch):
+@pytest.mark.parametrize("quant", [None, "fp8"])
+def test_hybrid_decode_graph_replay_matches_eager(kch, quant):
     """One-token steps replayed from a captured CUDA graph give the same bits as the same kernels launched from
     Python, across block closings of both caches and one growth of the cache storage."""
     cfgd = dict(d_model=256, n_heads_qk=2, n_heads_v=2, head_dim_k=128, head_dim_v=128, kda_chunk_size=64, csa_m=4,
@@ -491,7 +492,7 @@ def test_hybrid_decode_graph_replay_matches_eager(kch):
     x = syn.hidden_states(92, B, prefill + steps, cfg.d_model, torch.bfloat16).to(DEV)
     outs = {}
     for mode in (False, True):
-        dec = kch.HybridDecoding(model=model, use_cuda_graph=mode)
+        dec = kch.HybridDecoding(model=model, use_cuda_graph=mode, kv_quant=quant)
         dec.reset()
         ys = [dec(x[:, :prefill])]
         for t in range(steps):
