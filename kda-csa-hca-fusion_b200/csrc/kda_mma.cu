@@ -48,6 +48,7 @@ struct PrepArgs {
   int T, H, HV, NT;
   float scale, g_min;
   float gate_scale;                  // != 0: g holds the gate's pre-activation x; the decay is -softplus(x) * gate_scale
+  int umma;                          // 1: operand tiles in the tcgen05 layout (see kda_scan_tc5.cu) instead of the ldmatrix one
   int64_t ld_qk, ld_v, ld_g, ld_b;   // elements between consecutive tokens
 };
 
@@ -275,18 +276,33 @@ __global__ void __launch_bounds__(256, 2) kda_prepare_mma_kernel(PrepArgs a) {
       split2_bf16(kf[2 * e] * e0, kf[2 * e + 1] * e1, eh[e], el[e]);
     }
     const uint32_t off = swz<256>(i, ch);
-    *reinterpret_cast<uint4*>(wsc + KM_OFF_QHI + off) = make_uint4(qh[0], qh[1], qh[2], qh[3]);
-    *reinterpret_cast<uint4*>(wsc + KM_OFF_QLO + off) = make_uint4(ql[0], ql[1], ql[2], ql[3]);
-    *reinterpret_cast<uint4*>(wsc + KM_OFF_KHI + off) = make_uint4(kh[0], kh[1], kh[2], kh[3]);
-    *reinterpret_cast<uint4*>(wsc + KM_OFF_KLO + off) = make_uint4(kl[0], kl[1], kl[2], kl[3]);
+    if (a.umma) {
+      // tcgen05 operand layout: 64-channel panels of 128-byte rows under the 128-byte swizzle.  Rows 0..63 of a
+      // [w; qg] panel hold w, rows 64..127 hold qg (hi panels at 0, lo panels at 32768); kg keeps tokens as rows
+      // (the state update reads it as an MN-major operand).
+      const uint32_t pan = (uint32_t)(ch >> 3), inner = swz<128>(i, ch & 7);
+      *reinterpret_cast<uint4*>(wsc + pan * 16384u + 8192u + inner) = make_uint4(qh[0], qh[1], qh[2], qh[3]);
+      *reinterpret_cast<uint4*>(wsc + 32768u + pan * 16384u + 8192u + inner) = make_uint4(ql[0], ql[1], ql[2], ql[3]);
+      *reinterpret_cast<uint4*>(wsc + KM_OFF_KHI + pan * 8192u + inner) = make_uint4(kh[0], kh[1], kh[2], kh[3]);
+      *reinterpret_cast<uint4*>(wsc + KM_OFF_KLO + pan * 8192u + inner) = make_uint4(kl[0], kl[1], kl[2], kl[3]);
+    } else {
+      *reinterpret_cast<uint4*>(wsc + KM_OFF_QHI + off) = make_uint4(qh[0], qh[1], qh[2], qh[3]);
+      *reinterpret_cast<uint4*>(wsc + KM_OFF_QLO + off) = make_uint4(ql[0], ql[1], ql[2], ql[3]);
+      *reinterpret_cast<uint4*>(wsc + KM_OFF_KHI + off) = make_uint4(kh[0], kh[1], kh[2], kh[3]);
+      *reinterpret_cast<uint4*>(wsc + KM_OFF_KLO + off) = make_uint4(kl[0], kl[1], kl[2], kl[3]);
+    }
     *reinterpret_cast<uint4*>(sm + PS_EK + off) = make_uint4(eh[0], eh[1], eh[2], eh[3]);
     *reinterpret_cast<uint4*>(sm + PS_EK + KM_TILE + off) = make_uint4(el[0], el[1], el[2], el[3]);
   }
   if (tid < KM_K) {
     const float dl = ex2_fast(sG[(KM_C - 1) * PS_GLD + tid]);
+    if (a.umma) {
+      reinterpret_cast<float*>(wsc + KM_OFF_U + 32768)[tid] = dl;
+    } else {
 #pragma unroll
-    for (int s = 0; s < KM_V / 64; ++s)
-      reinterpret_cast<float*>(wsc + KM_OFF_U + s * KM_U_SLICE + 16384)[tid] = dl;
+      for (int s = 0; s < KM_V / 64; ++s)
+        reinterpret_cast<float*>(wsc + KM_OFF_U + s * KM_U_SLICE + 16384)[tid] = dl;
+    }
   }
 
   // ---- (I + A)^-1 by block forward substitution (fp32, CUDA cores) ------------------------------------
@@ -403,17 +419,30 @@ __global__ void __launch_bounds__(256, 2) kda_prepare_mma_kernel(PrepArgs a) {
       const int nt = 8 * nh + ntl;
       uint32_t hi, lo;
       split2_bf16(wacc[ntl][0], wacc[ntl][1], hi, lo);
-      *reinterpret_cast<uint32_t*>(wsc + KM_OFF_WHI + swz<256>(i0, nt) + 4 * j4) = hi;
-      *reinterpret_cast<uint32_t*>(wsc + KM_OFF_WLO + swz<256>(i0, nt) + 4 * j4) = lo;
+      const uint32_t ow0 = a.umma ? (uint32_t)(nt >> 3) * 16384u + swz<128>(i0, nt & 7) : swz<256>(i0, nt);
+      const uint32_t ow1 = a.umma ? (uint32_t)(nt >> 3) * 16384u + swz<128>(i1, nt & 7) : swz<256>(i1, nt);
+      const uint32_t wlo = a.umma ? 32768u : (uint32_t)KM_OFF_WLO;
+      *reinterpret_cast<uint32_t*>(wsc + KM_OFF_WHI + ow0 + 4 * j4) = hi;
+      *reinterpret_cast<uint32_t*>(wsc + wlo + ow0 + 4 * j4) = lo;
       split2_bf16(wacc[ntl][2], wacc[ntl][3], hi, lo);
-      *reinterpret_cast<uint32_t*>(wsc + KM_OFF_WHI + swz<256>(i1, nt) + 4 * j4) = hi;
-      *reinterpret_cast<uint32_t*>(wsc + KM_OFF_WLO + swz<256>(i1, nt) + 4 * j4) = lo;
+      *reinterpret_cast<uint32_t*>(wsc + KM_OFF_WHI + ow1 + 4 * j4) = hi;
+      *reinterpret_cast<uint32_t*>(wsc + wlo + ow1 + 4 * j4) = lo;
       const int c0 = 8 * nt + 2 * j4;            // value column
-      float* s0 = us + (c0 >> 6) * 4096 + (c0 & 63) * 64;
-      s0[i0] = uacc[ntl][0];
-      s0[64 + i0] = uacc[ntl][1];
-      s0[i1] = uacc[ntl][2];
-      s0[64 + i1] = uacc[ntl][3];
+      if (a.umma) {
+        // u^T as [token / 32][token / 4 % 8][value column][token % 4]: a warp of the scan reads 512 contiguous bytes
+        float* s0 = us + ((i0 >> 5) * 8 + ((i0 >> 2) & 7)) * 512 + (i0 & 3) + 4 * c0;
+        float* s1 = us + ((i1 >> 5) * 8 + ((i1 >> 2) & 7)) * 512 + (i1 & 3) + 4 * c0;
+        s0[0] = uacc[ntl][0];
+        s0[4] = uacc[ntl][1];
+        s1[0] = uacc[ntl][2];
+        s1[4] = uacc[ntl][3];
+      } else {
+        float* s0 = us + (c0 >> 6) * 4096 + (c0 & 63) * 64;
+        s0[i0] = uacc[ntl][0];
+        s0[64 + i0] = uacc[ntl][1];
+        s0[i1] = uacc[ntl][2];
+        s0[64 + i1] = uacc[ntl][3];
+      }
     }
   }
   __syncthreads();
@@ -421,7 +450,7 @@ __global__ void __launch_bounds__(256, 2) kda_prepare_mma_kernel(PrepArgs a) {
     const float4* us4 = reinterpret_cast<const float4*>(sm + PS_U);
 #pragma unroll
     for (int s = 0; s < KM_V / 64; ++s) {
-      float4* dst = reinterpret_cast<float4*>(wsc + KM_OFF_U + s * KM_U_SLICE);
+      float4* dst = reinterpret_cast<float4*>(wsc + KM_OFF_U + s * (a.umma ? 16384 : KM_U_SLICE));
       for (int idx = tid; idx < 1024; idx += 256) dst[idx] = us4[s * 1024 + idx];
     }
   }
@@ -650,6 +679,10 @@ __global__ void __launch_bounds__(160, 1) kda_scan_mma_kernel(ScanArgs a) {
 }
 
 // ---- host -------------------------------------------------------------------------------------------
+bool kch_kda_scan_tc5_enabled();      // kda_scan_tc5.cu
+int kch_kda_scan_tc5(const void* workspace, const float* initial_state, void* o, float* final_state, int B, int T,
+                     int HV, int NT, unsigned int* status, cudaStream_t s);
+
 bool kch_kda_mma_supported(int K, int V, int chunk_size, float g_clamp_min, int dtype) {
   static const bool force_generic = [] { const char* e = getenv("KCH_KDA"); return e && e[0] == 'g'; }();
   return !force_generic && dtype == KCH_BF16 && K == KM_K && V == KM_V && chunk_size == KM_C && g_clamp_min >= -10.0f;
@@ -675,6 +708,7 @@ int kch_kda_chunk_mma(const void* q, const void* k, const void* v, const void* g
   PrepArgs pa;
   pa.q = (const bf16*)q; pa.k = (const bf16*)k; pa.v = (const bf16*)v; pa.g = (const bf16*)g; pa.beta = (const bf16*)beta;
   pa.ws = (uint8_t*)workspace; pa.T = T; pa.H = H; pa.HV = HV; pa.NT = NT; pa.scale = scale; pa.g_min = g_clamp_min; pa.gate_scale = gate_scale;
+  pa.umma = kch_kda_scan_tc5_enabled() ? 1 : 0;
   pa.ld_qk = ld_qk; pa.ld_v = ld_v; pa.ld_g = ld_g; pa.ld_b = ld_beta;
   // 16-byte vector loads: token strides and base pointers must be multiples of 8 elements / 16 bytes
   KCH_REQUIRE((ld_qk % 8) == 0 && (ld_v % 8) == 0 && (ld_g % 8) == 0 &&
@@ -683,6 +717,7 @@ int kch_kda_chunk_mma(const void* q, const void* k, const void* v, const void* g
   KCH_CUDA_OK(cudaFuncSetAttribute(kda_prepare_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PS_TOTAL));
   kda_prepare_mma_kernel<<<dim3(NT, HV, B), 256, PS_TOTAL, s>>>(pa);
   KCH_LAUNCH_OK();
+  if (pa.umma) return kch_kda_scan_tc5(workspace, initial_state, o, final_state, B, T, HV, NT, status, s);
   ScanArgs sa;
   sa.ws = (const uint8_t*)workspace; sa.S0 = initial_state; sa.o = (bf16*)o; sa.S_out = final_state; sa.status = status;
   sa.T = T; sa.HV = HV; sa.NT = NT;
