@@ -14,7 +14,15 @@
 // Two accumulator buffers in tensor memory let the epilogue of tile i overlap the main loop of
 // tile i+1.  Every wait on an mbarrier is bounded; on expiry the kernel records a status word,
 // leaves its loops, frees tensor memory and returns.
+//
+// Large products (M >= 512, N > 128) run on CTA pairs: clusters of two CTAs share a 256 x 256 tile through
+// tcgen05.mma.cta_group::2 (M = 256).  Each CTA loads its own 128 rows of A and half of the W tile
+// (cp.async.bulk.tensor.cta_group::2, bytes counted on the even CTA's barrier), the even CTA's MMA lane issues
+// one instruction for both and commits to the barriers of both CTAs (two unicast commits), each CTA's epilogue
+// warps drain their own 128 x 256 accumulator.  A CTA then moves 32 KB per k-block instead of 48 KB and the
+// ring holds six stages; measured 1.26-1.31 PFLOP/s against 1.20-1.22 with one CTA per tile at M = 131072.
 #include <cuda.h>
+#include <stdio.h>
 #include <stdlib.h>
 #include <cudaTypedefs.h>
 #include <mutex>
@@ -86,6 +94,40 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
 }
 __device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
+// ---- CTA-pair (cta_group::2) forms: two CTAs of a cluster work on one 256-row tile, the even CTA issues the MMAs
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// shared::cluster address of the same shared-memory location in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t mapa_u32(uint32_t addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// tile into this CTA's shared memory, bytes counted on a barrier that may live in the other CTA of the pair
+__device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* map, int c0, int c1, uint32_t bar_cluster_addr) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(map), "r"(bar_cluster_addr), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void tc_commit_pair(uint32_t bar_cluster_addr) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_cluster_addr) : "memory");
+}
+__device__ __forceinline__ void tc_mma_bf16_pair(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+
 // K-major operand tile, rows of 64 bf16 (128 bytes) under the 128-byte swizzle: 8-row groups are
 // 1024 bytes apart (stride byte offset); the leading byte offset is not used for this layout.
 __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr) {
@@ -116,11 +158,13 @@ __device__ __forceinline__ float ep_silu(float x) { return __fdividef(x, 1.0f + 
 template <int BN>
 struct TgStages { static constexpr int value = BN >= 256 ? 4 : BN >= 128 ? 6 : BN >= 64 ? 8 : 10; };
 
-template <int BN>
+template <int BN, bool TWO = false>
 struct TgSmem {
-  static constexpr int STAGES = TgStages<BN>::value;
+  // a CTA of a pair holds half of the W tile, which buys two more stages
+  static constexpr int STAGES = TWO ? 6 : TgStages<BN>::value;
+  static constexpr int B_ROWS = TWO ? BN / 2 : BN;
   alignas(1024) bf16 a[STAGES][TG_BM * TG_BK];
-  alignas(1024) bf16 b[STAGES][BN * TG_BK];
+  alignas(1024) bf16 b[STAGES][B_ROWS * TG_BK];
   alignas(16) uint8_t epi[8][32 * TG_EPI_LD];   // per epilogue warp: a 32 x 32 bf16 chunk, rows padded to 80 bytes
   alignas(8) uint64_t full[STAGES];
   uint64_t empty[STAGES];
@@ -129,33 +173,43 @@ struct TgSmem {
   uint32_t tmem_base;
 };
 
-template <int BN>
+template <int BN, bool TWO>
 __global__ void __launch_bounds__(TG_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                     bf16* __restrict__ C, const bf16* __restrict__ R, int64_t M, int N, int K,
                     int64_t ldc, int64_t ldr, int vec_ok, const TgEpilogue ep) {
   extern __shared__ uint8_t smem_raw[];
-  TgSmem<BN>& sm = *reinterpret_cast<TgSmem<BN>*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  constexpr int TG_STAGES = TgStages<BN>::value;
+  TgSmem<BN, TWO>& sm = *reinterpret_cast<TgSmem<BN, TWO>*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  constexpr int TG_STAGES = TgSmem<BN, TWO>::STAGES;
+  constexpr int BM_T = TWO ? 2 * TG_BM : TG_BM;       // rows of a tile: a CTA pair takes 256, each CTA its 128
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = TWO ? cluster_ctarank() : 0u;
+  const int64_t unit = TWO ? (blockIdx.x >> 1) : blockIdx.x, nunits = TWO ? (gridDim.x >> 1) : gridDim.x;
   const int n_tiles = (N + BN - 1) / BN;
-  const int64_t m_tiles = (M + TG_BM - 1) / TG_BM;
+  const int64_t m_tiles = (M + BM_T - 1) / BM_T;
   const int64_t total_tiles = m_tiles * n_tiles;
   const int kblocks = (K + TG_BK - 1) / TG_BK;
   constexpr uint32_t ACC_COLS = BN;                 // fp32 accumulator columns per buffer
   constexpr uint32_t TMEM_COLS = (2 * ACC_COLS) < 32 ? 32 : 2 * ACC_COLS;  // power of two >= 32
 
   if (threadIdx.x == 0) {
+    // pair: the even CTA's `full` counts the bytes of both producers, its `acc_empty` the epilogue warps of both CTAs
     for (int s = 0; s < TG_STAGES; ++s) { mbar_init(&sm.full[s], 1); mbar_init(&sm.empty[s], 1); }
-    for (int i = 0; i < 2; ++i) { mbar_init(&sm.acc_full[i], 1); mbar_init(&sm.acc_empty[i], 8); }
+    for (int i = 0; i < 2; ++i) { mbar_init(&sm.acc_full[i], 1); mbar_init(&sm.acc_empty[i], TWO ? 16 : 8); }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm.tmem_base)), "r"(TMEM_COLS) : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    if constexpr (TWO) {
+      asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm.tmem_base)), "r"(TMEM_COLS) : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    } else {
+      asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm.tmem_base)), "r"(TMEM_COLS) : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
   }
   tc_fence_before();
   __syncthreads();
+  if constexpr (TWO) cluster_sync_all();     // both CTAs' barriers exist before either signals the other's
   tc_fence_after();
   const uint32_t tmem_base = sm.tmem_base;
 
@@ -164,25 +218,34 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     if (lane == 0) {
       uint32_t it = 0;
       bool ok = true;
-      for (int64_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+      for (int64_t tile = unit; tile < total_tiles && ok; tile += nunits) {
         const int64_t mb = tile / n_tiles;
         const int nb = (int)(tile % n_tiles);
         for (int kb = 0; kb < kblocks; ++kb, ++it) {
           const uint32_t s = it % TG_STAGES, ph = (it / TG_STAGES) & 1;
           if (!mbar_wait(&sm.empty[s], ph ^ 1, 1)) { ok = false; break; }
-          mbar_expect_tx(&sm.full[s], (TG_BM + BN) * TG_BK * 2);
-          tma_load_2d(sm.a[s], &map_a, kb * TG_BK, (int)(mb * TG_BM), &sm.full[s]);
-          tma_load_2d(sm.b[s], &map_w, kb * TG_BK, nb * BN, &sm.full[s]);
+          if constexpr (TWO) {
+            // this CTA's 128 rows of A and its half of the W tile; the bytes count on the even CTA's barrier, which
+            // that CTA's producer arms for both (the odd CTA's bytes may land first: the count is signed)
+            const uint32_t full_addr = mapa_u32(smem_u32(&sm.full[s]), 0);
+            if (rank == 0) mbar_expect_tx(&sm.full[s], 2 * (TG_BM + BN / 2) * TG_BK * 2);
+            tma_load_2d_pair(sm.a[s], &map_a, kb * TG_BK, (int)(mb * BM_T + rank * TG_BM), full_addr);
+            tma_load_2d_pair(sm.b[s], &map_w, kb * TG_BK, nb * BN + (int)rank * (BN / 2), full_addr);
+          } else {
+            mbar_expect_tx(&sm.full[s], (TG_BM + BN) * TG_BK * 2);
+            tma_load_2d(sm.a[s], &map_a, kb * TG_BK, (int)(mb * TG_BM), &sm.full[s]);
+            tma_load_2d(sm.b[s], &map_w, kb * TG_BK, nb * BN, &sm.full[s]);
+          }
         }
       }
     }
   } else if (warp == 1) {
     // ------------------------------ MMA issuer ---------------------------------
-    if (lane == 0) {
-      constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(TG_BM >> 4) << 24);
+    if (lane == 0 && rank == 0) {
+      constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM_T >> 4) << 24);
       uint32_t it = 0, tcount = 0;
       bool ok = true;
-      for (int64_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++tcount) {
+      for (int64_t tile = unit; tile < total_tiles && ok; tile += nunits, ++tcount) {
         const uint32_t acc = tcount & 1, aph = (tcount >> 1) & 1;
         if (!mbar_wait(&sm.acc_empty[acc], aph ^ 1, 2)) { ok = false; break; }
         tc_fence_after();
@@ -193,12 +256,29 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           tc_fence_after();
           const uint64_t adesc = make_smem_desc(smem_u32(sm.a[s]));
           const uint64_t bdesc = make_smem_desc(smem_u32(sm.b[s]));
+          if constexpr (TWO) {
+            // one instruction covers both CTAs: A rows and W-tile halves are read from both shared memories
+            // at these offsets, each CTA's 128 x BN result lands in its own tensor memory
 #pragma unroll
-          for (int k = 0; k < TG_BK / 16; ++k)
-            tc_mma_bf16(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) ? 1u : 0u);
-          tc_commit(&sm.empty[s]);  // stage reusable once these MMAs have read it
+            for (int k = 0; k < TG_BK / 16; ++k)
+              tc_mma_bf16_pair(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) ? 1u : 0u);
+            tc_commit_pair(smem_u32(&sm.empty[s]));
+            tc_commit_pair(mapa_u32(smem_u32(&sm.empty[s]), 1));
+          } else {
+#pragma unroll
+            for (int k = 0; k < TG_BK / 16; ++k)
+              tc_mma_bf16(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) ? 1u : 0u);
+            tc_commit(&sm.empty[s]);  // stage reusable once these MMAs have read it
+          }
         }
-        if (ok) tc_commit(&sm.acc_full[acc]);
+        if (ok) {
+          if constexpr (TWO) {
+            tc_commit_pair(smem_u32(&sm.acc_full[acc]));
+            tc_commit_pair(mapa_u32(smem_u32(&sm.acc_full[acc]), 1));
+          } else {
+            tc_commit(&sm.acc_full[acc]);
+          }
+        }
       }
     }
   } else {
@@ -211,13 +291,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     const int c_end = (BN == 256) ? c_begin + 128 : (half == 0 ? BN : 0);
     uint32_t tcount = 0;
     bool ok = true;
-    for (int64_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++tcount) {
+    for (int64_t tile = unit; tile < total_tiles && ok; tile += nunits, ++tcount) {
       const int64_t mb = tile / n_tiles;
       const int nb = (int)(tile % n_tiles);
       const uint32_t acc = tcount & 1, aph = (tcount >> 1) & 1;
       if (!mbar_wait(&sm.acc_full[acc], aph, 4)) { ok = false; break; }
       tc_fence_after();
-      const int64_t row = mb * TG_BM + quarter * 32 + lane;
+      const int64_t row = mb * BM_T + rank * TG_BM + quarter * 32 + lane;
       const uint32_t tbase = tmem_base + acc * ACC_COLS + ((uint32_t)(quarter * 32) << 16);
       float nrm = 1.f;
 #pragma unroll 1
@@ -281,7 +361,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             *reinterpret_cast<uint4*>(stg + lane * TG_EPI_LD + v * 16) = make_uint4(o[0], o[1], o[2], o[3]);
           }
           __syncwarp();
-          const int64_t row0 = mb * TG_BM + quarter * 32;
+          const int64_t row0 = mb * BM_T + rank * TG_BM + quarter * 32;
           const int piece = lane & 3;
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
@@ -318,14 +398,21 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       }
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&sm.acc_empty[acc]);
+      if (lane == 0) {
+        if constexpr (TWO) mbar_arrive_cluster(mapa_u32(smem_u32(&sm.acc_empty[acc]), 0));
+        else mbar_arrive(&sm.acc_empty[acc]);
+      }
     }
   }
   tc_fence_before();
   __syncthreads();
+  if constexpr (TWO) cluster_sync_all();     // neither CTA leaves while the other may still touch its memory
   if (warp == 1) {
     tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    if constexpr (TWO)
+      asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    else
+      asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
   }
 }
 
@@ -384,12 +471,46 @@ static int launch_tg(const void* A, const void* W, void* C, const void* R, int64
     KCH_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
   }
   size_t smem = sizeof(TgSmem<BN>) + 1024;
-  KCH_CUDA_OK(cudaFuncSetAttribute(gemm_tcgen05_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  KCH_CUDA_OK(cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   int64_t tiles = ((M + TG_BM - 1) / TG_BM) * ((N + BN - 1) / BN);
   int grid = (int)(tiles < sms ? tiles : sms);
   int vec_ok = (ldc % 8 == 0) && (((uintptr_t)C & 15) == 0) && (!R || ((ldr % 8 == 0) && (((uintptr_t)R & 15) == 0)));
-  gemm_tcgen05_kernel<BN><<<grid, TG_THREADS, smem, s>>>(ma, mw, (bf16*)C, (const bf16*)R, M, N, K, ldc, ldr, vec_ok, ep);
+  gemm_tcgen05_kernel<BN, false><<<grid, TG_THREADS, smem, s>>>(ma, mw, (bf16*)C, (const bf16*)R, M, N, K, ldc, ldr, vec_ok, ep);
   KCH_LAUNCH_OK();
+  return KCH_OK;
+}
+
+// 256 x 256 tiles on CTA pairs (clusters of two, tcgen05 cta_group::2): each CTA loads its 128 rows of A and half
+// of the W tile, so a CTA moves 32 KB per k-block instead of 48 KB and the ring holds six stages.
+static int launch_tg_pair(const void* A, const void* W, void* C, const void* R, int64_t M, int N, int K, int64_t lda,
+                          int64_t ldw, int64_t ldc, int64_t ldr, const TgEpilogue& ep, cudaStream_t s) {
+  constexpr int BN = 256;
+  CUtensorMap ma, mw;
+  int rc = make_map_2d(&ma, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, TG_BM, TG_BK);
+  if (rc) return rc;
+  rc = make_map_2d(&mw, W, (uint64_t)N, (uint64_t)K, (uint64_t)ldw, BN / 2, TG_BK);
+  if (rc) return rc;
+  size_t smem = sizeof(TgSmem<BN, true>) + 1024;
+  KCH_CUDA_OK(cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  cudaLaunchConfig_t cfg = {};
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+  cfg.blockDim = dim3(TG_THREADS); cfg.dynamicSmemBytes = smem; cfg.stream = s; cfg.attrs = attr; cfg.numAttrs = 1;
+  static int max_pairs = 0;
+  if (!max_pairs) {
+    cfg.gridDim = dim3(2);
+    int nc = 0;
+    KCH_CUDA_OK(cudaOccupancyMaxActiveClusters(&nc, gemm_tcgen05_kernel<BN, true>, &cfg));
+    KCH_REQUIRE(nc > 0, "kch_linear: no CTA pair of the tcgen05 GEMM fits on this device");
+    max_pairs = nc;
+  }
+  int64_t tiles = ((M + 2 * TG_BM - 1) / (2 * TG_BM)) * ((N + BN - 1) / BN);
+  int pairs = (int)(tiles < max_pairs ? tiles : max_pairs);
+  cfg.gridDim = dim3(2 * pairs);
+  int vec_ok = (ldc % 8 == 0) && (((uintptr_t)C & 15) == 0) && (!R || ((ldr % 8 == 0) && (((uintptr_t)R & 15) == 0)));
+  KCH_CUDA_OK(cudaLaunchKernelEx(&cfg, gemm_tcgen05_kernel<BN, true>, ma, mw, (bf16*)C, (const bf16*)R, M, N, K, ldc, ldr,
+                                 vec_ok, ep));
   return KCH_OK;
 }
 
@@ -426,6 +547,9 @@ int kch_linear_tcgen05(const void* A, const void* W, void* C, const void* R, int
     if (l2) return launch_tg<128>(A, W, C, R, M, N, K, lda, ldw, ldc, ldr, ep, s);
     return launch_tg<32>(A, W, C, R, M, N, K, lda, ldw, ldc, ldr, ep, s);
   }
+  // large products: 256 x 256 tiles on CTA pairs (KCH_GEMM=1 keeps one CTA per tile, for comparison)
+  static const bool pair_on = [] { const char* e = getenv("KCH_GEMM"); return !(e && e[0] == '1'); }();
+  if (pair_on && N > 128 && M >= 4 * TG_BM) return launch_tg_pair(A, W, C, R, M, N, K, lda, ldw, ldc, ldr, ep, s);
   if (N > 128) return launch_tg<256>(A, W, C, R, M, N, K, lda, ldw, ldc, ldr, ep, s);
   if (N > 64) return launch_tg<128>(A, W, C, R, M, N, K, lda, ldw, ldc, ldr, ep, s);
   if (N > 32) return launch_tg<64>(A, W, C, R, M, N, K, lda, ldw, ldc, ldr, ep, s);
