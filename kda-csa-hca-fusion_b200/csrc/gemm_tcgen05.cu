@@ -110,7 +110,9 @@ __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
-  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+  // relaxed: the arrival orders nothing but itself (tensor-memory reads are ordered by tcgen05.fence); a release at
+  // cluster scope would wait for every global store of the tile
+  asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
 // tile into this CTA's shared memory, bytes counted on a barrier that may live in the other CTA of the pair
 __device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* map, int c0, int c1, uint32_t bar_cluster_addr) {
@@ -300,6 +302,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       const int64_t row = mb * BM_T + rank * TG_BM + quarter * 32 + lane;
       const uint32_t tbase = tmem_base + acc * ACC_COLS + ((uint32_t)(quarter * 32) << 16);
       float nrm = 1.f;
+      // the accumulator chunk after the current one is already on its way from tensor memory
+      uint32_t rn[32];
+      if (c_begin < c_end) tc_ld32(tbase + c_begin, rn);
 #pragma unroll 1
       for (int c0 = c_begin; c0 < c_end; c0 += 32) {
         uint32_t r[32];
@@ -326,8 +331,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             nrm = __fdividef(1.0f, fmaxf(bf16r(sqrtf(ss)), 1e-12f));
           }
         }
-        tc_ld32(tbase + c0, r);
         tc_wait_ld();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) r[j] = rn[j];
+        if (c0 + 32 < c_end) tc_ld32(tbase + c0 + 32, rn);
         // the activation is uniform over the chunk: branch once, then 32 independent element pipelines
         if (act == KCH_ACT_SILU_L2NORM) {
 #pragma unroll
@@ -511,6 +518,7 @@ static int launch_tg_pair(const void* A, const void* W, void* C, const void* R, 
   int vec_ok = (ldc % 8 == 0) && (((uintptr_t)C & 15) == 0) && (!R || ((ldr % 8 == 0) && (((uintptr_t)R & 15) == 0)));
   KCH_CUDA_OK(cudaLaunchKernelEx(&cfg, gemm_tcgen05_kernel<BN, true>, ma, mw, (bf16*)C, (const bf16*)R, M, N, K, ldc, ldr,
                                  vec_ok, ep));
+  kch_note_launch(1);
   return KCH_OK;
 }
 
