@@ -191,6 +191,8 @@ __global__ void __launch_bounds__(256) attn_generic_kernel(AttnArgs a) {
 
 bool kch_attend_mma_supported(const kch_attend_args* p);
 int kch_attend_mma(const kch_attend_args* p, void* stream);
+bool kch_attend_tc5_enabled();
+int kch_attend_tc5(const kch_attend_args* p, void* stream);
 
 extern "C" int kch_attend(const kch_attend_args* p, void* stream) {
   KCH_REQUIRE(p != nullptr, "kch_attend: null args");
@@ -205,7 +207,8 @@ extern "C" int kch_attend(const kch_attend_args* p, void* stream) {
   if (p->B == 0 || p->T == 0) return KCH_OK;
   // tensor-core kernel for the production geometry; KCH_ATTEND=generic forces the fp32 CUDA-core kernel
   static const bool force_generic = [] { const char* e = getenv("KCH_ATTEND"); return e && e[0] == 'g'; }();
-  if (!force_generic && kch_attend_mma_supported(p)) return kch_attend_mma(p, stream);
+  if (!force_generic && kch_attend_mma_supported(p))
+    return kch_attend_tc5_enabled() ? kch_attend_tc5(p, stream) : kch_attend_mma(p, stream);
   AttnArgs a;
   a.q = p->q; a.q_dtype = p->q_dtype; a.q_ld = p->q_ld; a.q_normalize = p->q_normalize;
   a.B = p->B; a.T = p->T; a.nh = p->nh; a.c = p->c;
