@@ -633,3 +633,21 @@ def test_standalone_decode_modules_against_reference(kch, golden, kind):
         ys.append(mod(x[:, c["prefill"] + t:c["prefill"] + t + 1]))
     assert md(torch.cat(ys, 1), golden[f"standalone/{kind}/y"]) <= 5e-5
 
+
+
+@pytest.mark.parametrize("kind,env,atol", [("attend", {"KCH_ATTEND": "t"}, 1e-3), ("kda", {"KCH_KDA_SCAN": "m"}, 2e-3),
+                                           ("linear", {"KCH_GEMM": "1"}, 0.0)])
+def test_alternate_kernels_agree_with_defaults(kch, tmp_path, kind, env, atol):
+    """The kernels behind an environment switch (tcgen05 attention core, mma.sync KDA scan, one-CTA-per-tile GEMM)
+    compute the same case as the default ones: the library reads the switch once, so the alternate runs in a child."""
+    import os
+    import subprocess
+    import sys
+    import alt_kernel_case
+    ref = alt_kernel_case.run(kind)
+    out = tmp_path / f"{kind}.pt"
+    child_env = dict(os.environ, **env)
+    subprocess.run([sys.executable, alt_kernel_case.__file__, kind, str(out)], check=True, env=child_env, timeout=300)
+    alt = torch.load(out)
+    assert alt.shape == ref.shape and bool(torch.isfinite(alt).all())
+    assert md(alt, ref) <= atol, md(alt, ref)
