@@ -18,14 +18,20 @@
 //                  (two 64-channel panels, 128-byte swizzle), zero fill and a validity mask for invalid entries
 // A ring stage owns its S^T columns and its P^T tile, so one barrier (the P.X commit) frees all three.
 //
-// Status: opt-in (KCH_ATTEND=t).  Results match attn_mma_kernel to one bf16 rounding, but at the benchmark size the
-// kernel measures 9.7 ms (CSA, 1024 + 128 entries per query) and 5.5 ms (HCA) against 7.0 / 2.3 ms for the
-// mma.sync kernel: the tensor products take about 430 cycles per 128-key tile, the 16-byte cp.async gather of the
-// tile 1300-2500 cycles on four warps, and the per-query epilogue about 2000.  The core is bound by the LSU gather
-// path (about 25 bytes per clock and SM in both kernels), not by the tensor pipe.
+// Status: opt-in.  KCH_ATTEND=l uses the cp.async gather described above, KCH_ATTEND=t replaces warps 11..14 by one
+// warp that issues copy-engine row gathers (cp.async.bulk.tensor ... tile::gather4: four 128-byte row pieces per
+// instruction, swizzled by the engine, zero fill for invalid rows).  Results match attn_mma_kernel to one bf16
+// rounding.  At the benchmark size (B=4, T=32768) the mma.sync kernel measures 7.0 ms (CSA, 1024 + 128 entries per
+// query) and 2.3 ms (HCA); this kernel 9.5 / 5.4 ms with the cp.async gather and 24.9 / 6.9 ms with the row gather.
+// The tensor products take about 430 cycles per 128-key tile; the cp.async gather of the tile takes 1300-2500 cycles
+// on four warps (the LSU path moves about 25 bytes per clock and SM in both kernels), the copy engine about 90
+// cycles per four-row instruction (5800 per tile), and the per-query epilogue about 2000.  The core is bound by the
+// gather, not by the tensor pipe.
 // Every mbarrier wait is bounded, records a status code and leaves the loops.
+#include <cuda.h>
 #include <math.h>
 #include <stdlib.h>
+#include <string.h>
 
 #include "mma_utils.cuh"
 
@@ -95,10 +101,14 @@ __device__ __forceinline__ void at_cp_async16(uint32_t dst, const void* src, int
 // entry-list geometry of query bt (as in attn_mma_kernel)
 struct AtQuery {
   int nvis, ns, nw, E, ntiles;
+  int b, wrow0, nsp;          // batch, first window row, ns rounded up to the gather granularity
   const int32_t* selrow;
   const bf16* comp_b;
   const bf16* win_b;
 };
+// PAD = 4: the TMA row gather moves four entries per instruction, so the selected region is padded with invalid
+// entries to a multiple of four and the window region starts on a four-entry boundary
+template <int PAD>
 __device__ __forceinline__ AtQuery at_query(const AttnTcArgs& a, int64_t bt) {
   AtQuery qy;
   const int t = (int)(bt % a.T), b = (int)(bt / a.T);
@@ -108,13 +118,16 @@ __device__ __forceinline__ AtQuery at_query(const AttnTcArgs& a, int64_t bt) {
   qy.nw = 0;
   int wrow0 = 0;
   if (a.win_size > 0 && a.win) { const int tw = t + a.win_t0; int lo = tw - a.win_size + 1; if (lo < 0) lo = 0; qy.nw = tw - lo + 1; wrow0 = lo; }
-  qy.E = qy.ns + qy.nw;
+  qy.b = b; qy.wrow0 = wrow0;
+  qy.nsp = (qy.ns + PAD - 1) / PAD * PAD;
+  qy.E = qy.nsp + qy.nw;
   qy.ntiles = qy.E > 0 ? (qy.E + AT_KT - 1) / AT_KT : 1;     // a query without entries still runs one (empty) tile
   qy.selrow = a.sel ? a.sel + bt * a.topk : nullptr;
   qy.comp_b = a.comp ? a.comp + (int64_t)b * a.comp_batch_rows * 128 : nullptr;
   qy.win_b = a.win ? a.win + ((int64_t)b * a.win_batch_rows + wrow0) * a.win_ld : nullptr;
   return qy;
 }
+template <int PAD>
 __device__ __forceinline__ int at_ntiles(const AttnTcArgs& a, int64_t bt) {
   const int t = (int)(bt % a.T);
   int64_t nv64 = a.nvis_fixed >= 0 ? a.nvis_fixed : (a.m > 0 ? (a.t0 + t + 1) / a.m : a.n_comp);
@@ -122,11 +135,23 @@ __device__ __forceinline__ int at_ntiles(const AttnTcArgs& a, int64_t bt) {
   const int ns = a.sel ? a.topk : nvis;
   int nw = 0;
   if (a.win_size > 0 && a.win) { const int tw = t + a.win_t0; int lo = tw - a.win_size + 1; if (lo < 0) lo = 0; nw = tw - lo + 1; }
-  const int E = ns + nw;
+  const int E = (ns + PAD - 1) / PAD * PAD + nw;
   return E > 0 ? (E + AT_KT - 1) / AT_KT : 1;
 }
 
-__global__ void __launch_bounds__(AT_THREADS, 1) attn_tc5_kernel(AttnTcArgs a) {
+// row gather by the copy engine: rows r0..r3 of a [rows][128] bf16 tensor, 64 columns from `col`, land as four
+// consecutive 128-byte rows at `dst` (swizzled by the engine); rows outside the tensor read as zeros
+__device__ __forceinline__ void at_gather4(uint32_t dst, const CUtensorMap* map, int col, int r0, int r1, int r2, int r3,
+                                           uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile::gather4.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
+      ::"r"(dst), "l"(map), "r"(smem_addr_u32(bar)), "r"(col), "r"(r0), "r"(r1), "r"(r2), "r"(r3) : "memory");
+}
+
+template <bool TMAG>
+__global__ void __launch_bounds__(AT_THREADS, 1) attn_tc5_kernel(AttnTcArgs a, const __grid_constant__ CUtensorMap map_comp,
+                                                                  const __grid_constant__ CUtensorMap map_win) {
+  constexpr int PAD = TMAG ? 4 : 1;
   extern __shared__ uint8_t at_raw[];
   uint8_t* sm = reinterpret_cast<uint8_t*>(((uintptr_t)at_raw + 1023) & ~(uintptr_t)1023);
   uint64_t* bars = reinterpret_cast<uint64_t*>(sm + AT_OFF_BARS);
@@ -147,7 +172,7 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attn_tc5_kernel(AttnTcArgs a) {
   constexpr uint32_t TMEM_COLS = 128;            // S^T stages 6 x 16 | O^T 2 x 16
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < AT_NSTG; ++s) { mbarrier_init(&kfull[s], 4); mbarrier_init(&sfull[s], 1); mbarrier_init(&pready[s], 8); mbarrier_init(&done[s], 1); }
+    for (int s = 0; s < AT_NSTG; ++s) { mbarrier_init(&kfull[s], TMAG ? 1 : 4); mbarrier_init(&sfull[s], 1); mbarrier_init(&pready[s], 8); mbarrier_init(&done[s], 1); }
     for (int i = 0; i < 2; ++i) { mbarrier_init(&qfull[i], 1); mbarrier_init(&qempty[i], 1); mbarrier_init(&ofull[i], 1); mbarrier_init(&oempty[i], 8); }
     mbarrier_init(redbar, 8);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -163,6 +188,75 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attn_tc5_kernel(AttnTcArgs a) {
   const uint32_t tS = tmem, tO = tmem + AT_NSTG * 16;
 
   if (warp >= 11) {
+   if constexpr (TMAG) {
+    // ------------------------------ gather by the copy engine (one warp) ------------------------------
+    // A lane owns four consecutive entries of every tile: it turns them into row numbers of the compressed-row
+    // tensor or of the window tensor and issues one four-row gather per 64-channel panel.  Invalid entries name
+    // a row outside the tensor, which the engine fills with zeros.
+    if (warp == 11) {
+      constexpr int OOB = 0x3FFFFFF0;
+      int64_t bt = blockIdx.x;
+      int tile = 0;
+      bool have = bt < nq;
+      AtQuery qy = {};
+      auto load_raw4 = [&](const AtQuery& q_, int tile_) -> int4 {
+        const int e0 = tile_ * AT_KT + 4 * lane;
+        if (q_.selrow && e0 < q_.ns) return *reinterpret_cast<const int4*>(q_.selrow + e0);
+        return make_int4(e0, e0 + 1, e0 + 2, e0 + 3);
+      };
+      int4 raw = make_int4(0, 0, 0, 0);
+      if (have) { qy = at_query<PAD>(a, bt); raw = load_raw4(qy, 0); }
+      uint32_t g = 0;
+      while (have) {
+        // successor position and its index load first: the load's latency hides behind the wait below
+        int64_t bt2 = bt;
+        int tile2 = tile + 1;
+        AtQuery qy2 = qy;
+        bool have2 = true;
+        if (tile2 == qy.ntiles) {
+          tile2 = 0; bt2 = bt + gridDim.x; have2 = bt2 < nq;
+          if (have2) qy2 = at_query<PAD>(a, bt2);
+        }
+        const int4 raw2 = have2 ? load_raw4(qy2, tile2) : make_int4(0, 0, 0, 0);
+        const uint32_t s = g % AT_NSTG, kph = (g / AT_NSTG) & 1;
+        const int e0 = tile * AT_KT + 4 * lane;
+        const bool in_sel = e0 < qy.nsp;
+        int rows[4];
+        uint32_t vbits = 0;
+        const int rr[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int e = e0 + j;
+          int row = OOB;
+          if (in_sel) {
+            if (e < qy.ns && rr[j] >= 0 && rr[j] < qy.nvis) row = (int)((int64_t)qy.b * a.comp_batch_rows + rr[j]);
+          } else {
+            const int w = e - qy.nsp;
+            if (w < qy.nw) row = (int)((int64_t)qy.b * a.win_batch_rows + qy.wrow0 + w);
+          }
+          rows[j] = row;
+          vbits |= (row != OOB ? 1u : 0u) << j;
+        }
+        // validity mask of the tile's 128 rows: word w covers rows 32 w .. 32 w + 31 = lanes 8 w .. 8 w + 7
+        uint32_t mw[4];
+#pragma unroll
+        for (int w = 0; w < 4; ++w) mw[w] = __reduce_or_sync(0xffffffffu, (lane >> 3) == w ? vbits << (4 * (lane & 7)) : 0u);
+        if (!mbarrier_wait_bounded(&done[s], kph ^ 1, 61, AT_SPIN, a.status)) break;
+        if (lane == 0) {
+#pragma unroll
+          for (int w = 0; w < 4; ++w) maskbuf[s * 4 + w] = mw[w];
+          mbarrier_expect_tx(&kfull[s], AT_TILE_BYTES);
+        }
+        __syncwarp();
+        const uint32_t dst = smem_addr_u32(sm + AT_OFF_RING + (size_t)s * AT_TILE_BYTES) + (uint32_t)lane * 512u;
+        const CUtensorMap* mp = in_sel ? &map_comp : &map_win;
+        at_gather4(dst, mp, 0, rows[0], rows[1], rows[2], rows[3], &kfull[s]);
+        at_gather4(dst + 16384u, mp, 64, rows[0], rows[1], rows[2], rows[3], &kfull[s]);
+        ++g;
+        bt = bt2; tile = tile2; qy = qy2; have = have2; raw = raw2;
+      }
+    }
+   } else {
     // ------------------------------ gather producers ------------------------------
     // A tile is announced (kfull) when its copies have landed, which this warp learns from cp.async.wait_group.
     // The warp never blocks on a free ring stage while it has unannounced tiles in flight: it issues while stages
@@ -182,10 +276,10 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attn_tc5_kernel(AttnTcArgs a) {
       const int e = tile_ * AT_KT + 32 * pw + lane;
       if (e >= q_.E) return nullptr;
       if (e < q_.ns) return (raw_ >= 0 && raw_ < q_.nvis) ? q_.comp_b + (int64_t)raw_ * 128 : nullptr;
-      return q_.win_b + (int64_t)(e - q_.ns) * a.win_ld;
+      return q_.win_b + (int64_t)(e - q_.nsp) * a.win_ld;
     };
     int raw = 0;
-    if (have) { qy = at_query(a, bt); raw = load_raw(qy, 0); }
+    if (have) { qy = at_query<PAD>(a, bt); raw = load_raw(qy, 0); }
     uint32_t issued = 0, announced = 0;
     while (have || announced < issued) {
       const uint32_t s = issued % AT_NSTG, kph = (issued / AT_NSTG) & 1;
@@ -207,7 +301,7 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attn_tc5_kernel(AttnTcArgs a) {
         bool have2 = true;
         if (tile2 == qy.ntiles) {
           tile2 = 0; bt2 = bt + gridDim.x; have2 = bt2 < nq;
-          if (have2) qy2 = at_query(a, bt2);
+          if (have2) qy2 = at_query<PAD>(a, bt2);
         }
         const int raw2 = have2 ? load_raw(qy2, tile2) : 0;
         const bf16* p = entry_ptr(qy, tile, raw);
@@ -243,6 +337,7 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attn_tc5_kernel(AttnTcArgs a) {
       }
     }
     asm volatile("cp.async.wait_group 0;" ::: "memory");
+   }
   } else if (warp == 10) {
     // ------------------------------ query loader ------------------------------
     // the rows of the next query are in flight while the current one is normalised
@@ -297,7 +392,7 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attn_tc5_kernel(AttnTcArgs a) {
       uint32_t g = 0, qi = 0;
       bool ok = true;
       for (int64_t bt = blockIdx.x; bt < nq && ok; bt += gridDim.x, ++qi) {
-        const int ntiles = at_ntiles(a, bt);
+        const int ntiles = at_ntiles<PAD>(a, bt);
         const uint32_t qb = qi & 1;
         if (!mbarrier_wait_bounded(&qfull[qb], (qi >> 1) & 1, 63, AT_SPIN, a.status)) break;
         const uint64_t qd = qd0 + (uint64_t)(qb * (4096 >> 4));
@@ -325,7 +420,7 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attn_tc5_kernel(AttnTcArgs a) {
       uint32_t g = 0, qi = 0;
       bool ok = true;
       for (int64_t bt = blockIdx.x; bt < nq && ok; bt += gridDim.x, ++qi) {
-        const int ntiles = at_ntiles(a, bt);
+        const int ntiles = at_ntiles<PAD>(a, bt);
         const uint32_t ob = qi & 1;
         if (!mbarrier_wait_bounded(&oempty[ob], ((qi >> 1) & 1) ^ 1, 66, AT_SPIN, a.status)) break;
         for (int tile = 0; tile < ntiles; ++tile, ++g) {
@@ -387,7 +482,7 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attn_tc5_kernel(AttnTcArgs a) {
       return true;
     };
     for (int64_t bt = blockIdx.x; bt < nq && ok; bt += gridDim.x, ++qi) {
-      const int ntiles = at_ntiles(a, bt);
+      const int ntiles = at_ntiles<PAD>(a, bt);
       float l[8];
 #pragma unroll
       for (int j = 0; j < 8; ++j) l[j] = 0.f;
@@ -439,10 +534,15 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attn_tc5_kernel(AttnTcArgs a) {
 }
 
 // ---- host ----------------------------------------------------------------------------------------------------
-bool kch_attend_tc5_enabled() {
-  static const bool on = [] { const char* e = getenv("KCH_ATTEND"); return e && e[0] == 't'; }();
-  return on;
+int kch_make_tensor_map_2d_bf16(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint64_t ld_elems,
+                                uint32_t box_rows, uint32_t box_cols);   // gemm_tcgen05.cu
+
+// KCH_ATTEND=t: tcgen05 core with the copy-engine row gather; KCH_ATTEND=l: the same core with the cp.async gather
+static int attend_tc5_mode() {
+  static const int mode = [] { const char* e = getenv("KCH_ATTEND"); return (e && e[0] == 't') ? 2 : (e && e[0] == 'l') ? 1 : 0; }();
+  return mode;
 }
+bool kch_attend_tc5_enabled() { return attend_tc5_mode() != 0; }
 
 int kch_attend_tc5(const kch_attend_args* p, void* stream) {
   AttnTcArgs a;
@@ -467,8 +567,28 @@ int kch_attend_tc5(const kch_attend_args* p, void* stream) {
   if (nq == 0) return KCH_OK;
   const int grid = (int)(nq < sms ? nq : sms);
   const int smem = AT_TOTAL + 1024;
-  KCH_CUDA_OK(cudaFuncSetAttribute(attn_tc5_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-  attn_tc5_kernel<<<grid, AT_THREADS, smem, kch_stream(stream)>>>(a);
+  // the row gather needs four-entry groups of the selection list to be 16-byte aligned and row numbers within int32
+  const bool sel_ok = !a.sel || ((a.topk % 4) == 0 && (((uintptr_t)a.sel & 15) == 0));
+  const bool rows_ok = (int64_t)a.B * a.comp_batch_rows < 0x3FFFFFF0LL && (int64_t)a.B * a.win_batch_rows < 0x3FFFFFF0LL;
+  CUtensorMap mc, mw;
+  if (attend_tc5_mode() == 2 && sel_ok && rows_ok && (a.comp || a.win)) {
+    // one [rows][128] tensor per source, box 1 x 64: a gather moves four such boxes
+    const bf16* cb = a.comp ? a.comp : a.win;
+    const uint64_t crows = a.comp ? (uint64_t)a.B * a.comp_batch_rows : 1, cld = a.comp ? 128 : (uint64_t)a.win_ld;
+    const bf16* wb = a.win ? a.win : a.comp;
+    const uint64_t wrows = a.win ? (uint64_t)a.B * a.win_batch_rows : 1, wld = a.win ? (uint64_t)a.win_ld : 128;
+    int rc = kch_make_tensor_map_2d_bf16(&mc, cb, crows, 128, cld, 1, 64);
+    if (rc) return rc;
+    rc = kch_make_tensor_map_2d_bf16(&mw, wb, wrows, 128, wld, 1, 64);
+    if (rc) return rc;
+    KCH_CUDA_OK(cudaFuncSetAttribute(attn_tc5_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    attn_tc5_kernel<true><<<grid, AT_THREADS, smem, kch_stream(stream)>>>(a, mc, mw);
+  } else {
+    memset(&mc, 0, sizeof(mc));
+    memset(&mw, 0, sizeof(mw));
+    KCH_CUDA_OK(cudaFuncSetAttribute(attn_tc5_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    attn_tc5_kernel<false><<<grid, AT_THREADS, smem, kch_stream(stream)>>>(a, mc, mw);
+  }
   KCH_LAUNCH_OK();
   return KCH_OK;
 }

@@ -452,6 +452,12 @@ static int make_map_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64
   return KCH_OK;
 }
 
+// bf16 [rows][cols] tensor map with the 128-byte swizzle for other translation units (box = box_rows x box_cols)
+int kch_make_tensor_map_2d_bf16(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint64_t ld_elems,
+                                uint32_t box_rows, uint32_t box_cols) {
+  return make_map_2d(map, base, rows, cols, ld_elems, box_rows, box_cols);
+}
+
 bool kch_linear_tcgen05_supported(const void* A, const void* W, const void* C, const void* R, int64_t M, int N,
                                   int K, int64_t lda, int64_t ldw, int64_t ldc, int64_t ldr, int dtype) {
   if (dtype != KCH_BF16) return false;
