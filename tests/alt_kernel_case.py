@@ -36,6 +36,12 @@ def run(kind, dev="cuda:0"):
         o, s = kch_b200.naive_chunk_kda(*(x.to(dev) for x in (q, k, v, gg, beta)), initial_state=S0.to(dev),
                                         output_final_state=True, chunk_size=64)
         return torch.cat([o.float().cpu().flatten(), s.float().cpu().flatten()])
+    if kind == "kda_long":      # 256 chunks: the chain length of the benchmark's order, slow-decay gate
+        q, k, v, gg, beta, S0 = syn.kda_inputs(302, 1, 16384, 4, 128, 128, 4, torch.bfloat16, with_state=True)
+        gg = (gg.float() * 0.1).bfloat16()
+        o, s = kch_b200.naive_chunk_kda(*(x.to(dev) for x in (q, k, v, gg, beta)), initial_state=S0.to(dev),
+                                        output_final_state=True, chunk_size=64)
+        return torch.cat([o.float().cpu().flatten(), s.float().cpu().flatten()])
     if kind == "linear":
         x = torch.randn(1000, 2048, generator=g).bfloat16().to(dev)
         w = (torch.randn(772, 2048, generator=g) * 0.05).bfloat16().to(dev)

@@ -636,7 +636,7 @@ def test_standalone_decode_modules_against_reference(kch, golden, kind):
 
 
 @pytest.mark.parametrize("kind,env,atol", [("attend", {"KCH_ATTEND": "t"}, 1e-3), ("attend", {"KCH_ATTEND": "l"}, 1e-3),
-                                           ("kda", {"KCH_KDA_SCAN": "m"}, 2e-3),
+                                           ("kda", {"KCH_KDA_SCAN": "m"}, 2e-3), ("kda_long", {"KCH_KDA_SCAN": "m"}, 4e-3),
                                            ("linear", {"KCH_GEMM": "1"}, 0.0)])
 def test_alternate_kernels_agree_with_defaults(kch, tmp_path, kind, env, atol):
     """The kernels behind an environment switch (tcgen05 attention core, mma.sync KDA scan, one-CTA-per-tile GEMM)
