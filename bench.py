@@ -192,12 +192,12 @@ def cpu_baseline_sample(seconds_hint=20):
 
 def decode_state_bytes(cfg, B, context, kv_bytes):
     """Bytes one decode step must move at this context (the algorithmic floor of the step): the three KDA
-    states read and written in fp32, the CSA indexer's fp32 scoring rows, the selected CSA rows, every HCA
-    row, both windows, and the weights once."""
+    states read and written in fp32, the CSA indexer keys as stored (bf16 row + one fp32 norm per row), the
+    selected CSA rows, every HCA row, both windows, and the weights once."""
     HV, K, V = cfg["n_heads_v"], cfg["head_dim_k"], cfg["head_dim_v"]
     kda = cfg["n_kda"] * B * HV * K * V * 4 * 2
     nb, nb2 = context // cfg["csa_m"], context // cfg["hca_m2"]
-    idx = B * nb * cfg["csa_cI"] * 4
+    idx = B * nb * (cfg["csa_cI"] * 2 + 4)
     sel = B * min(nb, cfg["csa_topk"]) * cfg["csa_c"] * kv_bytes
     hca = B * nb2 * cfg["hca_c"] * kv_bytes
     win = B * (cfg["csa_sliding_window"] * cfg["csa_c"] + cfg["hca_sliding_window"] * cfg["hca_c"]) * 2

@@ -43,6 +43,15 @@ const char* kch_last_error(void);           /* host string, thread-local, valid 
 unsigned int kch_device_status(int reset);  /* synchronising read of the device status word (0 = clean) */
 long long kch_launch_count(int reset);      /* kernels launched by this library in this process so far */
 
+/* Self-test of the failure path that replaces a hang: one CTA waits with the library's bounded mbarrier wait on a
+ * barrier nothing arrives at, gives up after `limit_polls` (1 .. 2^20) polls, records KCH_STATUS_SELFTEST_WAIT in the
+ * status word and returns; `polls_out` (device, optional) receives the number of polls spent.  Afterwards
+ * kch_device_status(1) reports and clears the code.  While the word is set every other bounded wait of the library
+ * returns at its first poll, so read and clear it before launching real work.  No counterpart in the reference
+ * (it has no device code): its nearest relative is the non-finite-output warning, ops_kda.py:151-172. */
+#define KCH_STATUS_SELFTEST_WAIT 0x5E1F
+int kch_selftest_bounded_wait(unsigned int limit_polls, unsigned int* polls_out, void* stream);
+
 /* ---- layer glue ---------------------------------------------------------------------------- */
 
 /* _Fp32LayerNorm.forward, ops_fused.py:52-60: LayerNorm in fp32, stored in `dtype`. x,y [rows,d]. */

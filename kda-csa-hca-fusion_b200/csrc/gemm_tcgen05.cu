@@ -50,10 +50,10 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
-// bounded wait; returns false (and records `code`) if the phase never completes
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, unsigned code) {
+// bounded wait; returns false (and records `code`) if the phase never completes within `limit` polls
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, unsigned code, uint32_t limit = TG_SPIN_LIMIT) {
   uint32_t addr = smem_u32(bar);
-  for (uint32_t it = 0; it < TG_SPIN_LIMIT; ++it) {
+  for (uint32_t it = 0; it < limit; ++it) {
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
@@ -839,6 +839,27 @@ unsigned int* kch_status_device_ptr() {
     cached[dev] = p;
   }
   return cached[dev];
+}
+
+// One CTA waits, with the kernels' own bounded wait, on an mbarrier that nothing ever arrives at.  The wait must
+// give up after `limit` polls, record its code in the status word and return: the path every tcgen05 kernel of this
+// library takes when a copy or an MMA it waits for never completes.  Nothing traps and the context stays usable.
+__global__ void selftest_bounded_wait_kernel(uint32_t limit, unsigned int* polls_out) {
+  __shared__ __align__(8) uint64_t bar;
+  if (threadIdx.x == 0) {
+    mbar_init(&bar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    const bool ok = mbar_wait(&bar, 0, KCH_STATUS_SELFTEST_WAIT, limit);
+    if (polls_out) *polls_out = ok ? 0u : limit;
+  }
+}
+
+extern "C" int kch_selftest_bounded_wait(unsigned int limit_polls, unsigned int* polls_out, void* stream) {
+  KCH_REQUIRE(limit_polls >= 1 && limit_polls <= (1u << 20),
+              "kch_selftest_bounded_wait: limit_polls=%u must be in [1, 2^20]", limit_polls);
+  selftest_bounded_wait_kernel<<<1, 32, 0, kch_stream(stream)>>>(limit_polls, polls_out);
+  KCH_LAUNCH_OK();
+  return KCH_OK;
 }
 
 extern "C" unsigned int kch_device_status(int reset) {

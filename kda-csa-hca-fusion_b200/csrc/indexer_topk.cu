@@ -8,6 +8,8 @@
 #include <math.h>
 #include <stdlib.h>
 
+#include <atomic>
+
 #include "mma_utils.cuh"
 
 // ---------------------------------------------------------------------------------------
@@ -370,7 +372,10 @@ static int launch_indexer_logits(const float* q_idx, const float* k_idx, const f
     // tcgen05 path (query tiles of 128 rows, tensor-memory accumulators) when the shape allows and the workspace
     // also holds the per-(query, head) coefficients; else the mma.sync kernel below
     const int64_t coef_off = 3 * kb, coef_bytes = (int64_t)B * T * HI * 4;
-    if (kch_indexer_logits_tcgen05_ok(B, T, n_blocks, HI, q_ld, qraw) && split_bytes >= coef_off + coef_bytes)
+    // (that kernel folds `scale` into the coefficient outside the relu, which equals relu(scale * q.k) only for
+    // scale >= 0; a negative scale takes the mma.sync kernel, which applies it inside)
+    if (scale >= 0.f && kch_indexer_logits_tcgen05_ok(B, T, n_blocks, HI, q_ld, qraw) &&
+        split_bytes >= coef_off + coef_bytes)
       return kch_indexer_logits_tcgen05(qraw, q_ld, q_normalize, kh, km, kl, w_idx, (float*)(p + coef_off), logits, B, T,
                                         n_blocks, HI, n_ld, scale, m, t0, n_visible, s);
     IdxSplit sp = {};
@@ -846,16 +851,18 @@ extern "C" int kch_indexer_topk_ex(const void* q_idx_any, int q_dtype, int64_t q
 static __device__ __align__(256) float g_indexer_static_logits[KCH_INDEXER_STATIC_FLOATS];
 
 static int indexer_static_address(float** out) {
-  static float* cached[64] = {nullptr};
+  // one slot per device ordinal; host threads that make their first call on a device at the same time all look
+  // the address up and store the same value, so relaxed atomics are enough
+  static std::atomic<float*> cached[64];
   int dev = 0;
   KCH_CUDA_OK(cudaGetDevice(&dev));
   KCH_REQUIRE(dev >= 0 && dev < 64, "kch_indexer_topk_static: device ordinal %d out of range", dev);
-  if (!cached[dev]) {
-    float* p = nullptr;
+  float* p = cached[dev].load(std::memory_order_relaxed);
+  if (!p) {
     KCH_CUDA_OK(cudaGetSymbolAddress((void**)&p, g_indexer_static_logits));
-    cached[dev] = p;
+    cached[dev].store(p, std::memory_order_relaxed);
   }
-  *out = cached[dev];
+  *out = p;
   return KCH_OK;
 }
 

@@ -60,6 +60,7 @@ class AttendDecodeArgs(C.Structure):
 # indices into a cache's device counters (include/kch_b200.h KCH_CTR_*)
 CTR_ACC_LEN, CTR_N_BLOCKS, CTR_RING_N, CTR_HAS_PREV, CTR_TOKENS, CTR_WORDS = 0, 1, 2, 3, 4, 8
 STATUS_CACHE_CAPACITY = 64
+STATUS_SELFTEST_WAIT = 0x5E1F
 
 
 # name -> (restype, argtypes); must list every symbol declared in include/kch_b200.h
@@ -68,6 +69,7 @@ PROTOTYPES = {
     "kch_last_error": (C.c_char_p, []),
     "kch_device_status": (C.c_uint, [_i]),
     "kch_launch_count": (C.c_longlong, [_i]),
+    "kch_selftest_bounded_wait": (_i, [C.c_uint, _vp, _vp]),
     "kch_layernorm": (_i, [_vp, _vp, _vp, _vp, _i64, _i, _f, _i, _i, _vp]),
     "kch_short_conv": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp]),
     "kch_linear": (_i, [_vp, _vp, _vp, _vp, _i64, _i, _i, _i64, _i64, _i64, _i64, _i, _vp]),
@@ -156,3 +158,19 @@ def require_cuda(*tensors, fn="kch_b200"):
 
 def device_status(reset=False) -> int:
     return int(load().kch_device_status(1 if reset else 0))
+
+
+def raise_on_device_status(where: str) -> None:
+    """Synchronise the current device and raise if a bounded device-side wait has expired since the last check.
+
+    The status word is sticky on purpose: after one wait gives up, every later wait returns at its first poll, so
+    kernels drain instead of spinning, but they also leave their outputs unwritten.  Callers that keep a process
+    alive across requests should call this (or `device_status(reset=True)`) at their own synchronisation points;
+    the package does so in `HostPipeline.run` and `HybridDecoding.export_state`."""
+    import torch
+    torch.cuda.synchronize()
+    st = device_status(reset=True)
+    if st:
+        raise RuntimeError(f"kch_b200 ({where}): a device-side bounded wait expired (status 0x{st:x}); results since "
+                           f"the previous check are not valid.  The status word has been cleared.")
+

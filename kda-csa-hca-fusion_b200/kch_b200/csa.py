@@ -321,11 +321,13 @@ def naive_csa(H, W_aKV, W_bKV, W_aZ, W_bZ, Ba, Bb, W_DQ, W_UQ, W_IUQ, W_w, W_KV_
               m: int, topk: int, nh: int, nIh: int, c: int, c_I: int, dc: int, scale=None,
               sliding_window: int = 0, sink_logits=None, use_ste: bool = True, ste_mode: str = "topk_columns",
               normalize_qk: bool = False, fuse_projections: bool = True, return_projections: bool = False,
-              _fused_weight=None, _fused_q_weight=None, _return_indices: bool = False):
+              _fused_weight=None, _fused_q_weight=None, _return_indices: bool = False, _aux: dict | None = None):
     """Full CSA forward: ``[B,T,d] -> [B,T,nh*c]`` in ``H.dtype``; weights in ``nn.Linear`` layout.
 
     ``_fused_weight`` (optional) is the row-concatenation ``[W_aKV;W_bKV;W_aZ;W_bZ;W_KV_idx;W_Z_idx;
     W_DQ;W_w]`` prepared once by the layer object so the eight input projections run as one GEMM.
+    ``_aux`` (a dict, for stage-by-stage checks) receives the intermediate tensors exactly as the kernels saw
+    them: ``q_idx``, ``w_idx``, ``K_IComp``, ``C_comp``, ``q`` (padded length).
     """
     B_, T, d = H.shape
     if m < 1:
@@ -386,6 +388,8 @@ def naive_csa(H, W_aKV, W_bKV, W_aZ, W_bZ, Ba, Bb, W_DQ, W_UQ, W_IUQ, W_w, W_KV_
     indices = None
     if topk > 0:
         indices = indexer_topk(q_idx, K_IComp, w_idx, topk, m=m, normalize_qk=normalize_qk, sorted_output=False)
+    if _aux is not None:
+        _aux.update(q_idx=q_idx, w_idx=w_idx, K_IComp=K_IComp, C_comp=C_comp, q=q)
     if scale is None:
         scale = 1.0 if normalize_qk else c ** -0.5
     # production geometry in bf16: unit keys are kept in bf16 for the tensor-core attention kernel

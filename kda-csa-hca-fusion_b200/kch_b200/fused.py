@@ -492,6 +492,10 @@ class HybridDecoding(nn.Module):
         (``CSADecodingCache.export_state`` / ``HCADecodingCache.export_state``).  Tensors stay on their device;
         move them with ``torch.save`` / ``.cpu()`` as needed."""
         model = self.model
+        dev = next(model.parameters()).device
+        if dev.type == "cuda":
+            with torch.cuda.device(dev):
+                _lib.raise_on_device_status("HybridDecoding.export_state")      # never checkpoint a broken session
         return {
             "layout": list(model.layout),
             "kda_state": None if model._kda_state is None else model._kda_state.clone(),
@@ -550,7 +554,9 @@ class HybridDecoding(nn.Module):
     def _ring_tail(cache, win):
         if cache._sw is None or win <= 1 or cache._sw.n_valid == 0:
             return None
-        return cache._sw.get()[:, -(win - 1):]
+        # a copy: while the ring is not full `get()` is a view of its storage, and the append that follows the
+        # call overwrites slots of that storage when the chunk wraps around
+        return cache._sw.get()[:, -(win - 1):].clone()
 
     def _csa_chunk(self, layer, cache, h):
         cfg = self.cfg

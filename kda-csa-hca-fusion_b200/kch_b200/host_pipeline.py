@@ -41,6 +41,9 @@ class HostPipeline:
             slot = i % 2
             if self._xd[slot] is None or self._xd[slot].shape != x.shape or self._xd[slot].dtype != x.dtype:
                 self._xd[slot] = torch.empty(x.shape, dtype=x.dtype, device=dev)
+                # allocated from the compute stream's pool but written on the upload stream: tell the allocator,
+                # so that a replaced buffer is not handed out again while an upload into it is still in flight
+                self._xd[slot].record_stream(self._up)
             with torch.cuda.stream(self._up):
                 if i >= 2:
                     self._up.wait_event(computed[i - 2])        # the pass that read this buffer has finished
@@ -62,4 +65,13 @@ class HostPipeline:
                 outputs[i].copy_(y, non_blocking=True)
             y.record_stream(self._down)
         compute.wait_stream(self._down)
+        self._raise_on_device_status()
         return outputs
+
+    def _raise_on_device_status(self):
+        """The kernels' bounded waits report through a sticky status word; once it is set, later kernels return
+        without writing their outputs.  Read it where the host waits anyway (the downloads have to complete
+        before the caller may use `outputs`), and turn it into an exception instead of silent garbage."""
+        from . import _lib
+        with torch.cuda.device(self.device):
+            _lib.raise_on_device_status("HostPipeline.run")

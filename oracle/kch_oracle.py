@@ -284,12 +284,20 @@ def _window_keys(local, t_lo, t_hi, win):
 # --------------------------------------------------------------------------------------
 # CSA / HCA full forward  (reference: ops_csa.py:576-1184, ops_hca.py:30-201)
 # --------------------------------------------------------------------------------------
+def _query_tiles(T, tile, query_rows):
+    """(lo, hi) tiles of at most ``tile`` queries covering ``[0,T)`` or the given ranges."""
+    spans = [(0, T)] if query_rows is None else [(max(0, lo), min(T, hi)) for lo, hi in query_rows]
+    return [(t, min(hi, t + tile)) for lo, hi in spans for t in range(lo, hi, tile)]
+
+
 def csa_forward(H, W_aKV, W_bKV, W_aZ, W_bZ, Ba, Bb, W_DQ, W_UQ, W_IUQ, W_w, W_KV_idx,
                 W_Z_idx, B_idx, *, m, topk, nh, nIh, c, c_I, dc, scale=None, sliding_window=0,
                 sink_logits=None, normalize_qk=False, tile=256, indices_override=None,
-                return_aux=False):
+                return_aux=False, query_rows=None):
     """CSA forward; same rounding points as the reference (each projection output is stored
-    in H.dtype; everything after is fp32).  Query-tiled."""
+    in H.dtype; everything after is fp32).  Query-tiled.  ``query_rows`` (list of ``(lo, hi)``)
+    restricts the indexer + attention stage to those query ranges (other output rows stay 0),
+    so that a few tiles of a long sequence can be checked without paying for all of them."""
     B, T, d = H.shape
     if T == 0:
         return torch.zeros(B, 0, nh * c, dtype=H.dtype)
@@ -320,8 +328,7 @@ def csa_forward(H, W_aKV, W_bKV, W_aZ, W_bZ, Ba, Bb, W_DQ, W_UQ, W_IUQ, W_w, W_K
     out = torch.zeros(B, T, nh, c, dtype=cd)
     all_idx = torch.full((B, T, topk), -1, dtype=torch.long)
     for b in range(B):
-        for t_lo in range(0, T, tile):
-            t_hi = min(T, t_lo + tile)
+        for t_lo, t_hi in _query_tiles(T, tile, query_rows):
             if indices_override is not None:
                 idx = indices_override[b:b + 1, t_lo:t_hi]
             else:
@@ -348,8 +355,9 @@ def csa_forward(H, W_aKV, W_bKV, W_aZ, W_bZ, Ba, Bb, W_DQ, W_UQ, W_IUQ, W_w, W_K
 
 def hca_forward(H, W_KV, W_Z, B_pos, W_DQ, W_UQ, *, m2, nh, c, dc, scale=1.0,
                 sliding_window=0, sink_logits=None, W_KV_local=None, tile=512,
-                return_aux=False):
-    """HCA forward (``ops_hca.py:117-201``): dense MQA over every visible compressed block."""
+                return_aux=False, query_rows=None):
+    """HCA forward (``ops_hca.py:117-201``): dense MQA over every visible compressed block.
+    ``query_rows``: as in ``csa_forward``."""
     B, T, d = H.shape
     if T == 0:
         return torch.zeros(B, 0, nh * c, dtype=H.dtype)
@@ -370,8 +378,7 @@ def hca_forward(H, W_KV, W_Z, B_pos, W_DQ, W_UQ, *, m2, nh, c, dc, scale=1.0,
     local = l2_normalize(loc_raw.to(cd))
     out = torch.zeros(B, T, nh, c, dtype=cd)
     for b in range(B):
-        for t_lo in range(0, T, tile):
-            t_hi = min(T, t_lo + tile)
+        for t_lo, t_hi in _query_tiles(T, tile, query_rows):
             nq = t_hi - t_lo
             vis = ((torch.arange(t_lo, t_hi) + 1) // m2).reshape(-1, 1)
             va = torch.arange(n).reshape(1, -1) < vis
@@ -624,10 +631,12 @@ class HybridSpec:
 
 
 def hybrid_forward(spec: HybridSpec, params: dict, x, kda_states=None, lookbacks=None,
-                   csa_indices=None):
+                   csa_indices=None, trace=None):
     """Pre-norm residual stack ``x = x + layer(LN(x))`` (``ops_fused.py:1075-1091``).
     ``params`` uses the reference's ``state_dict`` names (``layers.i.q_proj.weight`` ...).
-    Returns (y, list of KDA states, list of conv lookbacks)."""
+    Returns (y, list of KDA states, list of conv lookbacks).  ``trace`` (a list) receives one
+    dict per layer: its input ``x_in``, the operator output before ``o_proj`` (``core``) and
+    the residual stream after the layer (``x_out``)."""
     B, T, d = x.shape
     s = spec
     states, lbs = [], []
@@ -646,7 +655,8 @@ def hybrid_forward(spec: HybridSpec, params: dict, x, kda_states=None, lookbacks
                 o, st = chunk_kda(q, k, v, g, beta, sc, st0, s.kda_chunk_size)
             else:
                 o, st = recurrent_kda(q, k, v, g, beta, sc, st0)
-            o = F.linear(o.reshape(B, T, -1), p["o_proj.weight"])
+            core = o.reshape(B, T, -1)
+            o = F.linear(core, p["o_proj.weight"])
             states.append(st)
             lbs.append(lb)
             ki += 1
@@ -658,13 +668,17 @@ def hybrid_forward(spec: HybridSpec, params: dict, x, kda_states=None, lookbacks
                             c_I=s.csa_cI, dc=s.csa_dc, sliding_window=s.csa_sliding_window,
                             sink_logits=p["sink"], normalize_qk=True,
                             indices_override=None if csa_indices is None else csa_indices.get(i))
+            core = o
             o = F.linear(o, p["o_proj.weight"])
         else:
             o = hca_forward(h, p["W_KV.weight"], p["W_Z.weight"], p["B_pos"], p["W_DQ.weight"],
                             p["W_UQ.weight"], m2=s.hca_m2, nh=s.hca_nh, c=s.hca_c, dc=s.hca_dc,
                             sliding_window=s.hca_sliding_window, sink_logits=p["sink"])
+            core = o
             o = F.linear(o, p["o_proj.weight"])
-        x = x + o
+        x_in, x = x, x + o
+        if trace is not None:
+            trace.append(dict(kind=kind, x_in=x_in, core=core, x_out=x))
     return x, states, lbs
 
 

@@ -30,8 +30,11 @@ from kch_b200 import synthetic as syn  # noqa: E402
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", default=os.environ.get("KCH_REFERENCE_DIR"),
+                    help="checkout of 183600/kda-csa-hca-fusion (or set KCH_REFERENCE_DIR)")
     args = ap.parse_args()
+    if not args.reference or not os.path.isdir(args.reference):
+        ap.error("pass --reference <checkout of the reference> or set KCH_REFERENCE_DIR")
     sys.dont_write_bytecode = True
     sys.path.insert(0, args.reference)
     warnings.simplefilter("ignore")

@@ -106,9 +106,9 @@ def test_module_tree_uses_reference_state_dict_names():
 
 def test_install_is_reversible_when_reference_is_importable():
     import sys
-    ref = os.environ.get("KCH_REFERENCE_DIR", "/root/reference")
-    if not os.path.isdir(ref):
-        pytest.skip("reference checkout not present")
+    ref = os.environ.get("KCH_REFERENCE_DIR", "")
+    if not ref or not os.path.isdir(ref):
+        pytest.skip("set KCH_REFERENCE_DIR to a checkout of the reference to run this test")
     sys.path.insert(0, ref)
     try:
         import kch_b200
@@ -132,6 +132,24 @@ def test_install_is_reversible_when_reference_is_importable():
             ops_kda_backend.validate_kda_backend("b200")
     finally:
         sys.path.remove(ref)
+
+
+def test_ring_tail_does_not_alias_the_ring_storage():
+    """The window keys a chunked prefill takes from the ring before appending its own chunk must survive that
+    append: while the ring is not yet full its contents are a view of the storage, and a chunk that wraps around
+    overwrites the very slots the view shows."""
+    from types import SimpleNamespace
+    from kch_b200.decoding_cache import _SlidingWindowRingBuffer
+    from kch_b200.fused import HybridDecoding
+    for first, second in ((6, 6), (1, 9), (3, 20)):
+        ring = _SlidingWindowRingBuffer(1, 8, 2, "cpu", torch.float32)
+        rows = torch.arange(1, first + second + 1, dtype=torch.float32).view(1, -1, 1).expand(1, -1, 2)
+        ring.append(rows[:, :first])
+        tail = HybridDecoding._ring_tail(SimpleNamespace(_sw=ring), 8)
+        want = rows[:, max(0, first - 7):first].clone()
+        ring.append(rows[:, first:])
+        assert torch.equal(tail, want), (first, second, tail[0, :, 0].tolist())
+        assert torch.equal(ring.get(), rows[:, -8:])
 
 
 def test_projection_slices_are_read_in_place():
@@ -181,5 +199,5 @@ def test_bench_accounting():
     fpt = bench.algorithmic_flops_per_token(bench.C4, 32768)
     assert abs(fpt - 145.86e6) / 145.86e6 < 1e-3
     nbytes = bench.decode_state_bytes(bench.C4, 64, 131072, 2)
-    assert 1.0e9 < nbytes < 1.2e9
+    assert 0.80e9 < nbytes < 0.90e9          # indexer keys counted at their stored width (bf16 + fp32 norm per row)
     assert bench.decode_state_bytes(bench.C4, 64, 131072, 1.0625) < nbytes

@@ -62,6 +62,21 @@ def test_static_indexer_matches_workspace_indexer_twice():
     assert torch.equal(ref, out)
 
 
+def test_static_indexer_other_kernel_paths():
+    """The same comparison on the two other kernel combinations behind the entry point: an indexer width the
+    tensor-core logits kernel does not serve (c_I = 32), and rows longer than 8192 blocks, whose select stages
+    the row in shared memory instead of registers."""
+    from kch_b200 import _lib
+    lib = _lib.load()
+    q, k, w = _case(104, 2, 96, 160, 3, 32)
+    ref, out = _both(lib, q, k, w, topk=24, m=4, n_visible=-1)
+    assert torch.equal(ref, out)
+    q, k, w = _case(105, 1, 128, 8200, 4, 64)                    # 128 * 8200 logits < 4 Mi
+    ref, out = _both(lib, q, k, w, topk=64, m=0, n_visible=8199)
+    assert torch.equal(ref, out)
+    assert int((out >= 8199).sum()) == 0 and int((out >= 0).sum()) == 128 * 64
+
+
 def test_static_indexer_rejects_oversized_requests():
     from kch_b200 import _lib
     lib = _lib.load()
