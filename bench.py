@@ -8,9 +8,10 @@
 Workload ("hybrid_prefill_c4"): the 5-layer KDA-KDA-KDA-CSA-HCA stack, d_model 2048, 16 heads x 128,
 KDA chunk 64, CSA m=4 / top-k 1024 / 4x64 indexer / window 128 / sink, HCA ratio 128 / window 128 / sink,
 bf16, batch 4 x T=32768 of synthetic N(0,1) hidden states, random-init N(0,0.02) weights.  One step is
-one forward pass over the whole batch.  With N > 1 the total work stays fixed (strong scaling): the sequences of
-the batch are dealt out to the GPUs first (no exchange on the data path), and GPUs beyond the batch size split the
-heads of their sequences (tensor parallel, one all-gather of head outputs per layer); `--tp-only` shards heads only.
+one forward pass over the whole batch.  With N > 1 the total work stays fixed (strong scaling) and the heads are
+sharded over the GPUs (tensor parallel: 16/N heads per GPU, one all-gather of head outputs per layer).  The sequences
+of a batch are independent as well; `--dp-sequences` deals them out to the GPUs first (replicas with no exchange on
+the data path) and only splits heads beyond the batch size -- an extra, not the configuration of the metric.
 
 The JSON line carries: the device-timed value, `e2e` (host buffers, H2D + D2H inside the timed region,
 through the public module API), `roofline` for the dominant kernel (the tcgen05 GEMM) measured with CUDA
@@ -172,55 +173,60 @@ class GemmProbe:
                 for k, v in sorted(agg.items(), key=lambda kv: -kv[1][1])]
 
 
-def cpu_baseline_sample(seconds_hint=20):
-    """The oracle port of the same stack on the host cores, on a bounded sample: B=1, T=8192 of the
-    same geometry, all host threads (about 10-20 s)."""
-    from kch_b200 import synthetic as syn
-    from oracle import kch_oracle as orc
-    spec = orc.HybridSpec(**C4)
-    spec.build_layout(LAYERS)
-    params = syn.hybrid_params(SEED, spec, LAYERS, dtype=torch.bfloat16)
-    T = 8192
-    x = syn.hidden_states(SEED, 1, T, C4["d_model"], torch.bfloat16)
-    with torch.no_grad():
-        t0 = time.perf_counter()
-        orc.hybrid_forward(spec, params, x)
-        dt = time.perf_counter() - t0
-    return {"value": T / dt, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
-            "sample": f"oracle port, same stack, B=1 T={T} bf16, one pass, {dt:.1f} s"}
+def cpu_baseline_sample():
+    """The CPU arm (the installed reference, else the oracle port) on the host cores, on a bounded sample: one
+    sequence of T=4096 of the same geometry, one pass after none (about 10-20 s)."""
+    T = 4096
+    step, kind = cpu_arm(T)
+    t0 = time.perf_counter()
+    step()
+    dt = time.perf_counter() - t0
+    what = "the reference's own HybridKCHAttention" if kind == "reference" else "oracle port"
+    return {"value": T / dt, "unit": UNIT, "cores": torch.get_num_threads(), "kind": kind,
+            "sample": f"{what}, same stack, B=1 T={T} bf16, one pass, {dt:.1f} s"}
 
 
-def decode_state_bytes(cfg, B, context, kv_bytes):
-    """Bytes one decode step must move at this context (the algorithmic floor of the step): the three KDA
+def decode_state_bytes(cfg, B, context, kv_bytes, world=1):
+    """Bytes one GPU of `world` must move in a decode step at this context (the algorithmic floor of the step; with
+    heads sharded, the KDA states and the per-head weight rows divide by `world`, the rest is replicated): the three KDA
     states read and written in fp32, the CSA indexer keys as stored (bf16 row + one fp32 norm per row), the
     selected CSA rows, every HCA row, both windows, and the weights once."""
     HV, K, V = cfg["n_heads_v"], cfg["head_dim_k"], cfg["head_dim_v"]
-    kda = cfg["n_kda"] * B * HV * K * V * 4 * 2
+    kda = cfg["n_kda"] * B * HV * K * V * 4 * 2 // world
     nb, nb2 = context // cfg["csa_m"], context // cfg["hca_m2"]
     idx = B * nb * (cfg["csa_cI"] * 2 + 4)
     sel = B * min(nb, cfg["csa_topk"]) * cfg["csa_c"] * kv_bytes
     hca = B * nb2 * cfg["hca_c"] * kv_bytes
     win = B * (cfg["csa_sliding_window"] * cfg["csa_c"] + cfg["hca_sliding_window"] * cfg["hca_c"]) * 2
     d = cfg["d_model"]
-    w_kda = d * (2 * cfg["n_heads_qk"] * K + HV * V + K + HV) + K * HV * K + HV * V * d
+    w_kda = d * ((2 * cfg["n_heads_qk"] * K + HV * V + HV) // world + K) + K * HV * K // world + HV * V * d
     w_csa = d * (4 * cfg["csa_c"] + 2 * cfg["csa_cI"] + cfg["csa_dc"] + cfg["csa_nIh"]) + cfg["csa_dc"] * (
-        cfg["csa_nh"] * cfg["csa_c"] + cfg["csa_nIh"] * cfg["csa_cI"]) + cfg["csa_nh"] * cfg["csa_c"] * d
-    w_hca = d * (2 * cfg["hca_c"] + cfg["hca_dc"]) + cfg["hca_dc"] * cfg["hca_nh"] * cfg["hca_c"] + cfg["hca_nh"] * cfg["hca_c"] * d
+        cfg["csa_nh"] * cfg["csa_c"] // world + cfg["csa_nIh"] * cfg["csa_cI"]) + cfg["csa_nh"] * cfg["csa_c"] * d
+    w_hca = d * (2 * cfg["hca_c"] + cfg["hca_dc"]) + cfg["hca_dc"] * cfg["hca_nh"] * cfg["hca_c"] // world + \
+        cfg["hca_nh"] * cfg["hca_c"] * d
     weights = 2 * (cfg["n_kda"] * w_kda + cfg["n_csa"] * w_csa + cfg["n_hca"] * w_hca)
     return kda + idx + sel + hca + win + weights
 
 
-def decode_bench(model, cfg_dict, B, context, steps, warmup, dev, peak_gbs):
-    """One-token decode steps through `HybridDecoding` at a long context, bf16 and FP8 compressed rows."""
+def decode_bench(model, cfg_dict, B, context, steps, warmup, dev, peak_gbs, world=1):
+    """One-token decode steps through `HybridDecoding` at a long context, bf16 and FP8 compressed rows.  With
+    `world` > 1 every rank steps its head shard of the same batch (the compressed-KV, indexer and window caches are
+    replicated, the KDA states sharded) and the step time is the maximum over the ranks; the roofline fraction is
+    then taken against the bytes ONE GPU must move (its share of the states and per-head weights, all of the rest)."""
+    import torch.distributed as dist
+
     import kch_b200
     from kch_b200.synthetic import fill_decode_state
-    out = {"batch": B, "context": context, "steps": steps, "warmup": warmup}
-    x = torch.randn(B, 1, cfg_dict["d_model"], device=dev).to(torch.bfloat16)
+    out = {"batch": B, "context": context, "steps": steps, "warmup": warmup, "n_gpus": world}
+    x = torch.randn(B, 1, cfg_dict["d_model"], device=dev, generator=torch.Generator(device=dev).manual_seed(5)
+                    ).to(torch.bfloat16)
     for name, quant, kvb in (("bf16", None, 2), ("fp8", "fp8", 1.0625)):
         dec = kch_b200.HybridDecoding(model=model, kv_quant=quant, use_cuda_graph=True)
         fill_decode_state(dec, B, context, steps + warmup, dev, 11)
         for _ in range(warmup):
             dec(x)
+        if world > 1:
+            dist.barrier()
         torch.cuda.synchronize()
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record()
@@ -229,9 +235,13 @@ def decode_bench(model, cfg_dict, B, context, steps, warmup, dev, peak_gbs):
         b.record()
         torch.cuda.synchronize()
         us = a.elapsed_time(b) * 1e3 / steps
-        nbytes = decode_state_bytes(cfg_dict, B, context, kvb)
+        if world > 1:
+            t = torch.tensor([us], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            us = float(t.item())
+        nbytes = decode_state_bytes(cfg_dict, B, context, kvb, world)
         out[name] = {"us_per_step": us, "us_per_token": us / B, "tokens_per_s": B / (us * 1e-6),
-                     "algorithmic_bytes_per_step": nbytes, "achieved_gbs": nbytes / (us * 1e-6) / 1e9,
+                     "algorithmic_bytes_per_step_per_gpu": nbytes, "achieved_gbs_per_gpu": nbytes / (us * 1e-6) / 1e9,
                      "frac_of_hbm_peak": nbytes / (us * 1e-6) / 1e9 / peak_gbs,
                      "finite": bool(torch.isfinite(y.float()).all()), "cuda_graph": dec._graph is not None}
         dec.reset()
@@ -241,35 +251,78 @@ def decode_bench(model, cfg_dict, B, context, steps, warmup, dev, peak_gbs):
     return out
 
 
-def run_reference(args):
-    """CPU arm: the oracle port of the reference's PyTorch path on the host cores (the reference is Python
-    and is not present on the GPU box).  Each step is a bounded sample of the workload."""
-    rank = int(os.environ.get("RANK", "0"))
-    if rank != 0:
-        return
+REF_DIR = os.path.join(ROOT, "baseline", "_ref")
+
+
+def _host_cores():
+    """The cores this process may use (torchrun exports OMP_NUM_THREADS=1 to its ranks; the CPU arm takes the host)."""
+    return len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+
+
+def cpu_arm(T):
+    """(step function, kind) of the CPU arm on one sequence of T tokens of the benchmark geometry: the installed
+    reference when baseline/_ref holds it, else the oracle port."""
     from kch_b200 import synthetic as syn
+    x = syn.hidden_states(SEED, 1, T, C4["d_model"], torch.bfloat16)
+    if os.path.isfile(os.path.join(REF_DIR, "ops_fused.py")):
+        sys.dont_write_bytecode = True
+        if REF_DIR not in sys.path:
+            sys.path.insert(0, REF_DIR)
+        try:
+            import ops_fused
+            cfg = ops_fused.HybridConfig(kda_backend="reference", **C4)
+            model = ops_fused.HybridKCHAttention(cfg, LAYERS)
+            model.load_state_dict(syn.hybrid_params(SEED, cfg, LAYERS, dtype=torch.bfloat16), strict=True)
+            model = model.bfloat16().eval()
+
+            def step():
+                model.reset_state()
+                with torch.no_grad():
+                    return model(x)
+            return step, "reference"
+        except Exception as exc:                                  # an incomplete install: say so and use the port
+            sys.stderr.write(f"baseline/_ref is present but not usable ({exc!r}); timing the oracle port\n")
     from oracle import kch_oracle as orc
     spec = orc.HybridSpec(**C4)
     spec.build_layout(LAYERS)
     params = syn.hybrid_params(SEED, spec, LAYERS, dtype=torch.bfloat16)
-    T = 4096
-    x = syn.hidden_states(SEED, 1, T, C4["d_model"], torch.bfloat16)
+
+    def step():
+        with torch.no_grad():
+            return orc.hybrid_forward(spec, params, x)
+    return step, "port"
+
+
+def run_reference(args):
+    """CPU arm: the reference's own PyTorch path on the host cores.  When the reference is installed under
+    baseline/_ref (an offline `pip install --target`, git-ignored) its unmodified `ops_fused.HybridKCHAttention`
+    with `kda_backend="reference"` is what runs (`kind: "reference"`); otherwise the oracle port of the same
+    stack (`kind: "port"`).  Each step is a bounded sample of the workload: one sequence of the same geometry at a
+    length the monolithic reference can hold (its CSA gather is T x top-k x c fp32), so that the run ends in minutes."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    torch.set_num_threads(max(1, _host_cores()))
+    T = 4096 if args.steps + args.warmup <= 8 else 2048
+    step, kind = cpu_arm(T)
     times = []
     with torch.no_grad():
         for i in range(args.warmup + args.steps):
             t0 = time.perf_counter()
-            orc.hybrid_forward(spec, params, x)
+            step()
             if i >= args.warmup:
                 times.append(time.perf_counter() - t0)
     ms = 1e3 * sum(times) / len(times)
     val = T / (ms / 1e3)
-    sample = f"oracle port of the reference path, B=1 T={T} per step (bounded sample of B=4 T=32768)"
+    what = ("the reference's own ops_fused.HybridKCHAttention (kda_backend='reference')" if kind == "reference"
+            else "oracle port of the reference path")
+    sample = f"{what}, B=1 T={T} per step (bounded sample of B=4 T=32768), {torch.get_num_threads()} threads"
     print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic",
         "config": {"workload": "hybrid_prefill_c4", "B": 4, "T": 32768, "layers": LAYERS, **C4},
-        "cpu_baseline": {"value": val, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port", "sample": sample},
+        "cpu_baseline": {"value": val, "unit": UNIT, "cores": torch.get_num_threads(), "kind": kind, "sample": sample},
         "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }))
 
@@ -298,7 +351,7 @@ def run_b200(args):
     # the data path); GPUs beyond the batch size split the heads of their sequences (tp ranks, one all-gather
     # of head outputs per layer inside each tp group).  The total work stays that of one B x T batch.
     dp = 1
-    while dp * 2 <= world and B % (dp * 2) == 0 and world % (dp * 2) == 0 and not args.tp_only:
+    while dp * 2 <= world and B % (dp * 2) == 0 and world % (dp * 2) == 0 and args.dp_sequences:
         dp *= 2
     tp = world // dp
     dp_rank, tp_rank = rank // tp, rank % tp
@@ -386,13 +439,19 @@ def run_b200(args):
     barrier()
     e2e_serial_ms = e0.elapsed_time(e1)
     del xd
+    peaks = {}
+    try:
+        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+    except Exception:
+        pass
+    decode = None
+    if not args.no_decode and (dp == 1 or world == 1):          # every rank steps its head shard
+        del x, y, pipe
+        torch.cuda.empty_cache()
+        decode = decode_bench(model, C4, args.decode_batch, args.decode_context, args.decode_steps, 8, dev,
+                              float(peaks.get("hbm_gbs", 6650.0)), world)
     status = _lib.device_status()
     if rank == 0:
-        peaks = {}
-        try:
-            peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
-        except Exception:
-            pass
         peak_tf = float(peaks.get("bf16_tflops_sustained", 1400.0))
         peak_src = "measured (MEASURED_PEAKS.json bf16_tflops_sustained)" if peaks else "fallback 1.4 PFLOP/s sustained"
         gemm_ms, gemm_flops, gemm_calls = probe.summary()
@@ -405,17 +464,17 @@ def run_b200(args):
             "config": {"workload": "hybrid_prefill_c4", "B": B, "T": T, "layers": LAYERS, "layout": model.layout_str(),
                        "parallelism": ("single_gpu" if world == 1 else (f"dp{dp}_sequences" if tp == 1 else (
                            f"tp{tp}_heads" if dp == 1 else f"dp{dp}_sequences_x_tp{tp}_heads"))), "l2": "inputs larger than L2 (537 MB hidden states)", **C4},
-            "e2e": {"value": tokens / (e2e_ms / 1e3), "unit": UNIT, "h2d_bytes_per_step": x_host.numel() * 2 * dp,
-                    "d2h_bytes_per_step": y_host.numel() * 2 * dp, "steps": e2e_steps, "ms_per_step": e2e_ms,
+            "e2e": {"value": tokens / (e2e_ms / 1e3), "unit": UNIT, "h2d_bytes_per_step": x_host.numel() * 2 * world,
+                    "d2h_bytes_per_step": y_host.numel() * 2 * world, "steps": e2e_steps, "ms_per_step": e2e_ms,
                     "api": "kch_b200.HostPipeline.run (pinned host in / out, copies overlapped with the passes)",
                     "ms_per_step_without_overlap": e2e_serial_ms},
             "gpu_launches": launches,
             "roofline": {"bound": "tensor", "kernel": "gemm_tcgen05_kernel (all dense projections)",
                          "achieved": achieved, "peak": peak_tf, "unit": "TFLOP/s", "frac": achieved / peak_tf,
                          "peak_source": peak_src, "traffic": NCU_GEMM_DRAM_BYTES_M16384 * (B * T / 16384.0),
-                         "traffic_note": "DRAM bytes (read + write) of one N=2048 K=2048 launch: ncu capture at M=16384 "
-                                         "(profiles/gemm_tcgen05_M16384_N2048_K2048.md), scaled by M to this batch; the "
-                                         "algorithmic bytes of that launch are 2(MK + NK + MN)",
+                         "traffic_note": "DRAM bytes (read + write) of one N=2048 K=2048 launch: ncu capture at M=16384, "
+                                         "scaled by M to this batch; the algorithmic bytes of that launch are "
+                                         "2(MK + NK + MN)",
                          "launches": gemm_calls,
                          "flops_per_step": gemm_flops / max(1, args.steps), "ms_per_step": gemm_ms / max(1, args.steps),
                          "shapes": probe.by_shape()},
@@ -423,9 +482,8 @@ def run_b200(args):
                                "frac_of_tensor_peak": value * fpt / 1e12 / peak_tf},
             "clocks": clocks.summary(), "device_status": status,
         }
-        if world == 1 and not args.no_decode:
-            out["decode"] = decode_bench(model, C4, args.decode_batch, args.decode_context, args.decode_steps, 8, dev,
-                                         float(peaks.get("hbm_gbs", 6650.0)))
+        if decode is not None:
+            out["decode"] = decode
         if world == 1 and not args.no_cpu_baseline:
             out["cpu_baseline"] = cpu_baseline_sample()
         print(json.dumps(out))
@@ -443,7 +501,9 @@ def main():
     ap.add_argument("--seq-len", type=int, default=32768)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-decode", action="store_true")
-    ap.add_argument("--tp-only", action="store_true", help="N > 1: shard heads only (no sequence sharding)")
+    ap.add_argument("--dp-sequences", action="store_true",
+                    help="N > 1: deal the sequences of the batch out to the GPUs first (replicas), heads only beyond")
+    ap.add_argument("--tp-only", action="store_true", help="accepted for compatibility: heads-only is the default")
     ap.add_argument("--decode-batch", type=int, default=64)
     ap.add_argument("--decode-context", type=int, default=131072)
     ap.add_argument("--decode-steps", type=int, default=256)

@@ -72,15 +72,14 @@ struct PrepArgs {
 
 #define KM_LOG2E 1.4426950408889634f
 
-__global__ void __launch_bounds__(256, 2) kda_prepare_mma_kernel(PrepArgs a) {
-  extern __shared__ __align__(128) uint8_t sm[];
+// One chunk on the mma.sync path; `sm` needs PS_TOTAL bytes, 128-byte aligned.  Any log-decay down to the clamp.
+__device__ __forceinline__ void kda_prepare_chunk_mma(const PrepArgs& a, uint8_t* sm, const int n, const int hv, const int b) {
   float* sG = reinterpret_cast<float*>(sm + PS_G);     // gamma in log2 units: exp(x) == ex2_fast(x')
   float* sA = reinterpret_cast<float*>(sm + PS_A);
   float* sT = reinterpret_cast<float*>(sm + PS_T);
   float* sQ = reinterpret_cast<float*>(sm + PS_Q);
   float* sbeta = reinterpret_cast<float*>(sm + PS_BETA);
   float* sP = sbeta + 64;
-  const int n = blockIdx.x, hv = blockIdx.y, b = blockIdx.z;
   const int G = a.HV / a.H, h = hv / G;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g4 = lane >> 2, j4 = lane & 3;
   const int t0 = n * KM_C;
@@ -456,6 +455,13 @@ __global__ void __launch_bounds__(256, 2) kda_prepare_mma_kernel(PrepArgs a) {
   }
 }
 
+__global__ void __launch_bounds__(256, 2) kda_prepare_mma_kernel(PrepArgs a) {
+  extern __shared__ __align__(128) uint8_t sm[];
+  kda_prepare_chunk_mma(a, sm, blockIdx.x, blockIdx.y, blockIdx.z);
+}
+
+#include "kda_prepare_tc5.cuh"
+
 // =====================================================================================
 // Stage 2
 // =====================================================================================
@@ -714,9 +720,15 @@ int kch_kda_chunk_mma(const void* q, const void* k, const void* v, const void* g
   KCH_REQUIRE((ld_qk % 8) == 0 && (ld_v % 8) == 0 && (ld_g % 8) == 0 &&
               ((((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)g) & 15) == 0),
               "kch_kda_chunk: q/k/v/g must be 16-byte aligned with token strides that are multiples of 8 elements");
-  KCH_CUDA_OK(cudaFuncSetAttribute(kda_prepare_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PS_TOTAL));
-  kda_prepare_mma_kernel<<<dim3(NT, HV, B), 256, PS_TOTAL, s>>>(pa);
-  KCH_LAUNCH_OK();
+  static const bool prep_mma = [] { const char* e = getenv("KCH_KDA_PREPARE"); return e && e[0] == 'm'; }();
+  if (pa.umma && !prep_mma) {
+    int rc = launch_kda_prepare_tc5(pa, B, status, s);
+    if (rc != KCH_OK) return rc;
+  } else {
+    KCH_CUDA_OK(cudaFuncSetAttribute(kda_prepare_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PS_TOTAL));
+    kda_prepare_mma_kernel<<<dim3(NT, HV, B), 256, PS_TOTAL, s>>>(pa);
+    KCH_LAUNCH_OK();
+  }
   if (pa.umma) return kch_kda_scan_tc5(workspace, initial_state, o, final_state, B, T, HV, NT, status, s);
   ScanArgs sa;
   sa.ws = (const uint8_t*)workspace; sa.S0 = initial_state; sa.o = (bf16*)o; sa.S_out = final_state; sa.status = status;

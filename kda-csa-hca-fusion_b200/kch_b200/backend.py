@@ -10,6 +10,7 @@ reference's own modules run on these kernels.
 from __future__ import annotations
 
 import importlib
+import sys
 
 _saved = {}
 
@@ -27,6 +28,7 @@ def install():
     from . import csa, decoding_cache, hca, kda
 
     done = []
+    _try_import("ops_fused")           # before any rebinding: it copies kda_forward / naive_* into its own namespace
     okb = _try_import("ops_kda_backend")
     if okb is not None and "ops_kda_backend.kda_forward" not in _saved:
         okb._VALID_BACKENDS.add("b200")
@@ -40,11 +42,15 @@ def install():
 
         okb.kda_forward = kda_forward
         done.append("ops_kda_backend.kda_forward")
-        of = _try_import("ops_fused")
-        if of is not None:
-            _saved["ops_fused.kda_forward"] = (of, "kda_forward", of.kda_forward)
-            of.kda_forward = kda_forward
-            done.append("ops_fused.kda_forward")
+        # modules that did `from ops_kda_backend import kda_forward` hold their own reference to the original
+        # (ops_fused.py:36, run_decoding.py:47, run_benchmark.py:44): the stack module always, the runners when
+        # they are already imported (imported later, they pick up the wrapper by themselves)
+        holders = [_try_import("ops_fused")] + [sys.modules.get(n) for n in ("run_decoding", "run_benchmark")]
+        for mod in holders:
+            if mod is not None and getattr(mod, "kda_forward", None) is ref_forward:
+                _saved[f"{mod.__name__}.kda_forward"] = (mod, "kda_forward", ref_forward)
+                mod.kda_forward = kda_forward
+                done.append(f"{mod.__name__}.kda_forward")
 
     def dispatch(ref_fn, new_fn):
         def fn(H, *a, **kw):
@@ -52,15 +58,20 @@ def install():
         fn.__wrapped__ = ref_fn
         return fn
 
-    for modname in ("ops_fused", "run_decoding"):
-        mod = _try_import(modname)
-        if mod is None:
+    # the operators at their source (so that a runner imported after install() binds the dispatching version),
+    # then every module that already holds its own reference to the original
+    for src, attr, new in (("ops_csa", "naive_csa", csa.naive_csa), ("ops_hca", "naive_hca", hca.naive_hca)):
+        srcmod = _try_import(src)
+        if srcmod is None or f"{src}.{attr}" in _saved:
             continue
-        for attr, new in (("naive_csa", csa.naive_csa), ("naive_hca", hca.naive_hca)):
-            key = f"{modname}.{attr}"
-            if hasattr(mod, attr) and key not in _saved:
-                _saved[key] = (mod, attr, getattr(mod, attr))
-                setattr(mod, attr, dispatch(getattr(mod, attr), new))
+        ref_fn = getattr(srcmod, attr)
+        wrapped = dispatch(ref_fn, new)
+        holders = [srcmod, _try_import("ops_fused"), _try_import("run_decoding"), sys.modules.get("run_benchmark")]
+        for mod in holders:
+            if mod is not None and getattr(mod, attr, None) is ref_fn:
+                key = f"{mod.__name__}.{attr}"
+                _saved[key] = (mod, attr, ref_fn)
+                setattr(mod, attr, wrapped)
                 done.append(key)
     rd = _try_import("run_decoding")
     if rd is not None:

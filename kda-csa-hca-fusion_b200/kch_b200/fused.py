@@ -478,6 +478,9 @@ class HybridDecoding(nn.Module):
         # one-token steps are replayed from a captured CUDA graph once a first step has run eagerly; every
         # per-token quantity the kernels need is on the device (cache counters), so the launch arguments are static
         self.use_cuda_graph = use_cuda_graph
+        # with heads sharded over several GPUs the per-layer all-gather (NCCL) is captured with the step; every
+        # rank captures and replays the same sequence of collectives
+        self.graph_collectives = True
         self._caches = {}
         self._graph = None
         self._eager_token_steps = 0
@@ -677,7 +680,7 @@ class HybridDecoding(nn.Module):
             return None
         sig = [x.shape[0], x.dtype, 0 if st is None else st.data_ptr()]
         for i, (layer, kind) in enumerate(zip(model.layers, model.layout)):
-            if layer.tp is not None and layer.tp.world > 1:
+            if layer.tp is not None and layer.tp.world > 1 and not self.graph_collectives:
                 return None                                    # the head all-gather is launched eagerly
             if kind == "kda":
                 lb = layer._conv_lookback

@@ -106,9 +106,10 @@ def test_module_tree_uses_reference_state_dict_names():
 
 def test_install_is_reversible_when_reference_is_importable():
     import sys
-    ref = os.environ.get("KCH_REFERENCE_DIR", "")
-    if not ref or not os.path.isdir(ref):
-        pytest.skip("set KCH_REFERENCE_DIR to a checkout of the reference to run this test")
+    # a checkout named by the environment, else the offline install of the reference under baseline/_ref
+    ref = os.environ.get("KCH_REFERENCE_DIR") or os.path.join(ROOT, "baseline", "_ref")
+    if not os.path.isfile(os.path.join(ref, "ops_fused.py")):
+        pytest.skip("the reference is not installed (baseline/_ref) and KCH_REFERENCE_DIR is not set")
     sys.path.insert(0, ref)
     try:
         import kch_b200
@@ -117,6 +118,7 @@ def test_install_is_reversible_when_reference_is_importable():
         before = (ops_kda_backend.kda_forward, ops_fused.naive_csa, ops_fused.naive_hca)
         done = kch_b200.install()
         assert "ops_kda_backend.kda_forward" in done and "ops_fused.naive_csa" in done
+        assert "ops_csa.naive_csa" in done and "ops_hca.naive_hca" in done and "ops_fused.kda_forward" in done
         assert ops_kda_backend.validate_kda_backend("b200") == "b200"
         cfg = ops_fused.HybridConfig(kda_backend="b200")
         assert cfg.kda_backend == "b200"

@@ -637,9 +637,10 @@ def test_standalone_decode_modules_against_reference(kch, golden, kind):
 
 @pytest.mark.parametrize("kind,env,atol", [("attend", {"KCH_ATTEND": "t"}, 1e-3), ("attend", {"KCH_ATTEND": "l"}, 1e-3),
                                            ("kda", {"KCH_KDA_SCAN": "m"}, 2e-3), ("kda_long", {"KCH_KDA_SCAN": "m"}, 4e-3),
+                                           ("kda", {"KCH_KDA_PREPARE": "m"}, 2e-3), ("kda_long", {"KCH_KDA_PREPARE": "m"}, 4e-3),
                                            ("linear", {"KCH_GEMM": "1"}, 0.0)])
 def test_alternate_kernels_agree_with_defaults(kch, tmp_path, kind, env, atol):
-    """The kernels behind an environment switch (tcgen05 attention core, mma.sync KDA scan, one-CTA-per-tile GEMM)
+    """The kernels behind an environment switch (tcgen05 attention core, mma.sync KDA scan and prepare stage, one-CTA-per-tile GEMM)
     compute the same case as the default ones: the library reads the switch once, so the alternate runs in a child."""
     import os
     import subprocess
