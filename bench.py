@@ -155,6 +155,20 @@ class GemmProbe:
             return y
         return linear
 
+    def wrap_kslabs(self, fn):
+        def linear_kslabs(a_slabs, W, residual=None):
+            if not self.enabled:
+                return fn(a_slabs, W, residual)
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            y = fn(a_slabs, W, residual)
+            b.record()
+            M = a_slabs.shape[1]
+            self.calls.append((a, b, 2.0 * M * W.shape[0] * W.shape[1], M, W.shape[0], W.shape[1], False,
+                               residual is not None))
+            return y
+        return linear_kslabs
+
     def summary(self):
         ms = sum(a.elapsed_time(b) for a, b, *_ in self.calls)
         fl = sum(c[2] for c in self.calls)
@@ -377,6 +391,7 @@ def run_b200(args):
     wrapped = probe.wrap(csa_mod.linear)
     for mod in (csa_mod, hca_mod, fused_mod):
         mod.linear = wrapped
+    csa_mod.linear_kslabs = probe.wrap_kslabs(csa_mod.linear_kslabs)
 
     def barrier():
         if world > 1:

@@ -100,6 +100,14 @@ int kch_linear_ex(const void* A, const void* W, void* C, const void* residual, i
                   int64_t lda, int64_t ldw, int64_t ldc, int64_t ldr, int dtype, const kch_epilogue* epilogue,
                   void* stream);
 
+/* The output projection after an all-gather of per-GPU head slices (no counterpart in the reference, which has no
+ * distributed code; mathematically F.linear(concat_heads(A), W), ops_fused.py:609/713/739): A holds the K input
+ * columns as `n_slabs` slabs [n_slabs][M][K / n_slabs] one after the other -- the rank-major buffer ncclAllGather
+ * leaves behind -- and the K loop walks the slabs, so the gathered tensor is never re-laid out.  bf16 only; the slab
+ * width must be a multiple of 64.  C[M, N] = A_cat[M, K] W[N, K]^T (+ residual). */
+int kch_linear_kslabs(const void* A, const void* W, void* C, const void* residual, int64_t M, int N, int K, int n_slabs,
+                      int64_t ldw, int64_t ldc, int64_t ldr, int dtype, void* stream);
+
 /* Activation epilogues with the reference's rounding points, ops_fused.py:571-581.
  * x,y [rows,cols] in `dtype`, rows ldx / ldy elements apart (x may be a column slice of a fused
  * projection); `param` is the decay scale for KCH_ACT_NEG_SOFTPLUS; `group` is the head width for

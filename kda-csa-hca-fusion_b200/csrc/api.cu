@@ -29,12 +29,30 @@ int kch_linear_simt(const void* A, const void* W, void* C, const void* residual,
 bool kch_linear_tcgen05_supported(const void* A, const void* W, const void* C, const void* R, int64_t M, int N,
                                   int K, int64_t lda, int64_t ldw, int64_t ldc, int64_t ldr, int dtype);
 int kch_linear_tcgen05(const void* A, const void* W, void* C, const void* R, int64_t M, int N, int K, int64_t lda,
-                       int64_t ldw, int64_t ldc, int64_t ldr, const kch_epilogue* e, void* stream);
+                       int64_t ldw, int64_t ldc, int64_t ldr, const kch_epilogue* e, void* stream, int slab_k = 0);
 bool kch_linear_tcgen05_epilogue_ok(const kch_epilogue* e, int N);
 
 extern "C" int kch_linear(const void* A, const void* W, void* C, const void* residual, int64_t M, int N, int K,
                           int64_t lda, int64_t ldw, int64_t ldc, int64_t ldr, int dtype, void* stream) {
   return kch_linear_ex(A, W, C, residual, M, N, K, lda, ldw, ldc, ldr, dtype, nullptr, stream);
+}
+
+extern "C" int kch_linear_kslabs(const void* A, const void* W, void* C, const void* residual, int64_t M, int N, int K,
+                                 int n_slabs, int64_t ldw, int64_t ldc, int64_t ldr, int dtype, void* stream) {
+  KCH_REQUIRE(M >= 0 && N >= 32 && K >= 1 && n_slabs >= 1, "kch_linear_kslabs: M=%lld N=%d K=%d n_slabs=%d",
+              (long long)M, N, K, n_slabs);
+  KCH_REQUIRE(dtype == KCH_BF16, "kch_linear_kslabs: bf16 only (dtype tag %d)", dtype);
+  KCH_REQUIRE(K % n_slabs == 0 && (K / n_slabs) % 64 == 0,
+              "kch_linear_kslabs: K=%d must split into n_slabs=%d slabs whose width is a multiple of 64", K, n_slabs);
+  KCH_REQUIRE(ldw >= K && ldc >= N, "kch_linear_kslabs: leading dimensions ldw=%lld ldc=%lld too small", (long long)ldw,
+              (long long)ldc);
+  KCH_REQUIRE((int64_t)M * n_slabs <= 0x7FFFFFFFLL, "kch_linear_kslabs: M * n_slabs = %lld rows exceed the tensor-map range",
+              (long long)M * n_slabs);
+  if (M == 0) return KCH_OK;
+  const int slab_k = K / n_slabs;
+  KCH_REQUIRE(kch_linear_tcgen05_supported(A, W, C, residual, M, N, K, slab_k, ldw, ldc, ldr, dtype),
+              "kch_linear_kslabs: operands must be 16-byte aligned with strides that are multiples of 8 elements");
+  return kch_linear_tcgen05(A, W, C, residual, M, N, K, slab_k, ldw, ldc, ldr, nullptr, stream, n_slabs > 1 ? slab_k : 0);
 }
 
 extern "C" int kch_linear_ex(const void* A, const void* W, void* C, const void* residual, int64_t M, int N, int K,

@@ -228,6 +228,175 @@ __global__ void __launch_bounds__(AM_WARPS * 32, MINB) attn_mma_kernel(AttnMmaAr
   }
 }
 
+// Dense form (no selection list: every visible compressed block is attended, as in naive_hca): the AD_WARPS
+// consecutive queries of a CTA see the same blocks (their visible counts differ by at most one step of the causal
+// rule) and overlapping windows, so the CTA stages each key row ONCE in shared memory (16-byte cp.async by all
+// threads, 3-stage ring of 32-row tiles, one block barrier per tile) and every warp scores it under its own
+// validity mask.  Per-warp arithmetic is that of attn_mma_kernel; the L2 -> shared traffic per query drops by the
+// number of warps.  Entry list of the CTA: blocks [0, nvis(last query)), then window rows
+// [first query's window start, last query's position].
+#define AD_WARPS 8
+#define AD_STAGES 3
+
+__global__ void __launch_bounds__(AD_WARPS * 32, 2) attn_dense_mma_kernel(AttnMmaArgs a) {
+  extern __shared__ __align__(128) uint8_t smem_raw[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
+  const int tiles_per_seq = (a.T + AD_WARPS - 1) / AD_WARPS;
+  const int b = blockIdx.x / tiles_per_seq;
+  const int tq0 = (blockIdx.x % tiles_per_seq) * AD_WARPS;
+  const int t = tq0 + warp;
+  const bool active = t < a.T;
+  const int t_last = min(tq0 + AD_WARPS, a.T) - 1;
+  const int64_t bt = (int64_t)b * a.T + t;
+  const int g = lane >> 2, j = lane & 3;
+  uint8_t* ringp = smem_raw;
+  bf16* sq = reinterpret_cast<bf16*>(smem_raw + AD_STAGES * AM_TILE * AM_C * 2) + warp * (16 * AM_QLD);
+  const uint32_t ring = smem_addr(ringp);
+  auto nvis_of = [&](int tt) -> int {
+    int64_t nv64 = a.nvis_fixed >= 0 ? a.nvis_fixed : (a.m > 0 ? (a.t0 + tt + 1) / a.m : a.n_comp);
+    return (int)(nv64 < a.n_comp ? nv64 : a.n_comp);
+  };
+  const int nvis = active ? nvis_of(t) : 0;
+  const int ns = a.comp ? nvis_of(t_last) : 0;                   // blocks staged for the CTA
+  int nw = 0, wrow0 = 0;                                          // window rows staged for the CTA: [wrow0, wrow0 + nw)
+  const bool has_win = a.win_size > 0 && a.win;
+  if (has_win) { int lo = tq0 + a.win_t0 - a.win_size + 1; if (lo < 0) lo = 0; wrow0 = lo; nw = t_last + a.win_t0 - lo + 1; }
+  const int tw = t + a.win_t0;                                    // this query's own window: rows [tw - win + 1, tw]
+  const int E = ns + nw;
+  const int ntiles = (E + AM_TILE - 1) / AM_TILE;
+  const bf16* comp_b = a.comp ? a.comp + (int64_t)b * a.comp_batch_rows * AM_C : nullptr;
+  const bf16* win_b = has_win ? a.win + ((int64_t)b * a.win_batch_rows + wrow0) * a.win_ld : nullptr;
+
+  auto issue_tile = [&](int tile) {
+    const uint32_t dst0 = ring + (uint32_t)(tile % AD_STAGES) * (AM_TILE * AM_C * 2);
+#pragma unroll
+    for (int it = 0; it < (AM_TILE * 16) / (AD_WARPS * 32); ++it) {
+      const int idx = tid + it * (AD_WARPS * 32), r = idx >> 4, ch = idx & 15;
+      const int e = tile * AM_TILE + r;
+      const bf16* rp = nullptr;
+      if (e < ns) rp = comp_b + (int64_t)e * AM_C;
+      else if (e < E) rp = win_b + (int64_t)(e - ns) * a.win_ld;
+      const uint32_t dst = dst0 + r * (AM_C * 2) + ((ch ^ (r & 7)) << 4);
+      cp_async16(dst, rp ? (const void*)(rp + ch * 8) : (const void*)a.q, rp ? 16 : 0);
+    }
+    cp_commit();
+  };
+  // validity of entry tile*32 + lane for THIS warp's query
+  auto valid_mask = [&](int tile) -> uint32_t {
+    const int e = tile * AM_TILE + lane;
+    bool ok = false;
+    if (active) {
+      if (e < ns) ok = e < nvis;
+      else if (e < E) { const int r = wrow0 + (e - ns); ok = r <= tw && r > tw - a.win_size; }
+    }
+    return __ballot_sync(0xffffffffu, ok);
+  };
+#pragma unroll
+  for (int s = 0; s < AD_STAGES - 1; ++s) {
+    if (s < ntiles) issue_tile(s); else cp_commit();
+  }
+  // normalised query of this warp -> A fragments
+  {
+    const bf16* qrow = a.q + (active ? bt : (int64_t)b * a.T) * a.q_ld;
+    for (int h = 0; h < 16; ++h) {
+      float v[4] = {0.f, 0.f, 0.f, 0.f};
+      if (h < a.nh && active) {
+        uint2 raw = *reinterpret_cast<const uint2*>(qrow + h * AM_C + lane * 4);
+        __nv_bfloat162 p0 = *reinterpret_cast<__nv_bfloat162*>(&raw.x), p1 = *reinterpret_cast<__nv_bfloat162*>(&raw.y);
+        v[0] = __bfloat162float(p0.x); v[1] = __bfloat162float(p0.y);
+        v[2] = __bfloat162float(p1.x); v[3] = __bfloat162float(p1.y);
+      }
+      float ss = warp_sum(v[0] * v[0] + v[1] * v[1] + v[2] * v[2] + v[3] * v[3]);
+      float nrm = fmaxf(sqrtf(ss), 1e-12f);
+      uint2 o;
+      o.x = pack_bf16(v[0] / nrm, v[1] / nrm);
+      o.y = pack_bf16(v[2] / nrm, v[3] / nrm);
+      *reinterpret_cast<uint2*>(sq + h * AM_QLD + lane * 4) = o;
+    }
+  }
+  __syncwarp();
+  uint32_t qa[8][4];
+#pragma unroll
+  for (int ks = 0; ks < 8; ++ks) {
+    qa[ks][0] = *reinterpret_cast<const uint32_t*>(sq + g * AM_QLD + 16 * ks + 2 * j);
+    qa[ks][1] = *reinterpret_cast<const uint32_t*>(sq + (g + 8) * AM_QLD + 16 * ks + 2 * j);
+    qa[ks][2] = *reinterpret_cast<const uint32_t*>(sq + g * AM_QLD + 16 * ks + 8 + 2 * j);
+    qa[ks][3] = *reinterpret_cast<const uint32_t*>(sq + (g + 8) * AM_QLD + 16 * ks + 8 + 2 * j);
+  }
+  const float ascale = fabsf(a.scale);
+  float sink0 = -INFINITY, sink1 = -INFINITY;
+  if (a.sink) {
+    if (g < a.nh) sink0 = ld_any(a.sink, g, a.sink_dtype);
+    if (g + 8 < a.nh) sink1 = ld_any(a.sink, g + 8, a.sink_dtype);
+  }
+  const float shift0 = fmaxf(ascale, sink0), shift1 = fmaxf(ascale, sink1);
+  float o[16][4];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
+  float l0 = 0.f, l1 = 0.f;
+  bool any_valid = false;
+
+  for (int tile = 0; tile < ntiles; ++tile) {
+    cp_wait<AD_STAGES - 2>();                      // this thread's copies of `tile` have landed ...
+    __syncthreads();                               // ... and everybody's; all warps are done with tile - 1
+    if (tile + AD_STAGES - 1 < ntiles) issue_tile(tile + AD_STAGES - 1); else cp_commit();
+    const uint32_t vm = valid_mask(tile);
+    if (vm == 0) continue;                         // nothing of this tile is visible to this warp's query
+    any_valid = true;
+    const uint32_t tb = ring + (uint32_t)(tile % AD_STAGES) * (AM_TILE * AM_C * 2);
+    uint32_t pa[2][4];
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt) {
+      float s[4] = {0.f, 0.f, 0.f, 0.f};
+      const int krow = 8 * nt + (lane & 7);
+#pragma unroll
+      for (int qd = 0; qd < 4; ++qd) {
+        const int ch = 4 * qd + (lane >> 3);
+        uint32_t r0, r1, r2, r3;
+        ldsm4(tb + krow * (AM_C * 2) + ((ch ^ (krow & 7)) << 4), r0, r1, r2, r3);
+        mma16816(s, qa[2 * qd], r0, r1);
+        mma16816(s, qa[2 * qd + 1], r2, r3);
+      }
+      const int k0 = 8 * nt + 2 * j;
+      const bool v0 = (vm >> k0) & 1u, v1 = (vm >> (k0 + 1)) & 1u;
+      float p00 = v0 ? __expf(s[0] * a.scale - shift0) : 0.f;
+      float p01 = v1 ? __expf(s[1] * a.scale - shift0) : 0.f;
+      float p10 = v0 ? __expf(s[2] * a.scale - shift1) : 0.f;
+      float p11 = v1 ? __expf(s[3] * a.scale - shift1) : 0.f;
+      l0 += p00 + p01;
+      l1 += p10 + p11;
+      pa[nt >> 1][(nt & 1) * 2 + 0] = pack_bf16(p00, p01);
+      pa[nt >> 1][(nt & 1) * 2 + 1] = pack_bf16(p10, p11);
+    }
+#pragma unroll
+    for (int ks = 0; ks < 2; ++ks) {
+      const int krow = 16 * ks + ((lane >> 3) & 1) * 8 + (lane & 7);
+#pragma unroll
+      for (int dp = 0; dp < 8; ++dp) {
+        const int ch = 2 * dp + (lane >> 4);
+        uint32_t r0, r1, r2, r3;
+        ldsm4t(tb + krow * (AM_C * 2) + ((ch ^ (krow & 7)) << 4), r0, r1, r2, r3);
+        mma16816(o[2 * dp], pa[ks], r0, r1);
+        mma16816(o[2 * dp + 1], pa[ks], r2, r3);
+      }
+    }
+  }
+  cp_wait<0>();
+  if (!active) return;
+  l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+  l1 += __shfl_xor_sync(0xffffffffu, l1, 1); l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+  if (a.sink) { l0 += __expf(sink0 - shift0); l1 += __expf(sink1 - shift1); }
+  const float inv0 = (any_valid && l0 > 0.f) ? 1.f / l0 : 0.f;
+  const float inv1 = (any_valid && l1 > 0.f) ? 1.f / l1 : 0.f;
+  bf16* orow = a.out + bt * ((int64_t)a.nh * AM_C);
+#pragma unroll
+  for (int n = 0; n < 16; ++n) {
+    const int d = 8 * n + 2 * j;
+    if (g < a.nh) *reinterpret_cast<uint32_t*>(orow + g * AM_C + d) = pack_bf16(o[n][0] * inv0, o[n][1] * inv0);
+    if (g + 8 < a.nh) *reinterpret_cast<uint32_t*>(orow + (g + 8) * AM_C + d) = pack_bf16(o[n][2] * inv1, o[n][3] * inv1);
+  }
+}
+
 bool kch_attend_mma_supported(const kch_attend_args* p) {
   if (p->c != AM_C || p->nh > 16 || p->nh < 1) return false;
   if (p->q_dtype != KCH_BF16 || p->out_dtype != KCH_BF16 || !p->q_normalize) return false;
@@ -252,6 +421,16 @@ int kch_attend_mma(const kch_attend_args* p, void* stream) {
   a.win_size = has_win ? p->sliding_window : 0; a.win_t0 = p->win_t0;
   a.sink = p->sink; a.sink_dtype = p->sink_dtype; a.scale = p->scale; a.out = (bf16*)p->out;
   static_assert(16 * AM_QLD * 2 <= AM_TILE * AM_C * 2, "query staging tile must fit one ring stage");
+  // no selection list: the queries of a CTA share their staged keys (KCH_ATTEND_DENSE=w keeps one ring per warp)
+  static const bool dense_per_warp = [] { const char* e = getenv("KCH_ATTEND_DENSE"); return e && e[0] == 'w'; }();
+  if (!a.sel && !dense_per_warp) {
+    const size_t smem = (size_t)AD_STAGES * AM_TILE * AM_C * 2 + (size_t)AD_WARPS * 16 * AM_QLD * 2;
+    KCH_CUDA_OK(cudaFuncSetAttribute(attn_dense_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    const int64_t ctas = (int64_t)p->B * ((p->T + AD_WARPS - 1) / AD_WARPS);
+    attn_dense_mma_kernel<<<(unsigned)ctas, AD_WARPS * 32, smem, kch_stream(stream)>>>(a);
+    KCH_LAUNCH_OK();
+    return KCH_OK;
+  }
   int64_t nq = (int64_t)p->B * p->T;
   unsigned grid = (unsigned)((nq + AM_WARPS - 1) / AM_WARPS);
   // ring depth / resident CTAs per SM: two stages and three CTAs per SM (168 registers) measured fastest on

@@ -179,7 +179,10 @@ template <int BN, bool TWO>
 __global__ void __launch_bounds__(TG_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                     bf16* __restrict__ C, const bf16* __restrict__ R, int64_t M, int N, int K,
-                    int64_t ldc, int64_t ldr, int vec_ok, const TgEpilogue ep) {
+                    int64_t ldc, int64_t ldr, int vec_ok, const TgEpilogue ep, int slab_k, int64_t slab_rows) {
+  // slab_k > 0: the K columns of A lie in K / slab_k slabs of [slab_rows][slab_k] one after the other (the
+  // rank-major buffer an all-gather of per-GPU column slices leaves behind); map_a then describes all slabs as one
+  // [slabs * slab_rows][slab_k] matrix and k-block kb is read from slab kb * 64 / slab_k
   extern __shared__ uint8_t smem_raw[];
   TgSmem<BN, TWO>& sm = *reinterpret_cast<TgSmem<BN, TWO>*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   constexpr int TG_STAGES = TgSmem<BN, TWO>::STAGES;
@@ -226,16 +229,19 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         for (int kb = 0; kb < kblocks; ++kb, ++it) {
           const uint32_t s = it % TG_STAGES, ph = (it / TG_STAGES) & 1;
           if (!mbar_wait(&sm.empty[s], ph ^ 1, 1)) { ok = false; break; }
+          int kc = kb * TG_BK;
+          int64_t roff = 0;
+          if (slab_k > 0) { const int sidx = kc / slab_k; kc -= sidx * slab_k; roff = (int64_t)sidx * slab_rows; }
           if constexpr (TWO) {
             // this CTA's 128 rows of A and its half of the W tile; the bytes count on the even CTA's barrier, which
             // that CTA's producer arms for both (the odd CTA's bytes may land first: the count is signed)
             const uint32_t full_addr = mapa_u32(smem_u32(&sm.full[s]), 0);
             if (rank == 0) mbar_expect_tx(&sm.full[s], 2 * (TG_BM + BN / 2) * TG_BK * 2);
-            tma_load_2d_pair(sm.a[s], &map_a, kb * TG_BK, (int)(mb * BM_T + rank * TG_BM), full_addr);
+            tma_load_2d_pair(sm.a[s], &map_a, kc, (int)(mb * BM_T + rank * TG_BM + roff), full_addr);
             tma_load_2d_pair(sm.b[s], &map_w, kb * TG_BK, nb * BN + (int)rank * (BN / 2), full_addr);
           } else {
             mbar_expect_tx(&sm.full[s], (TG_BM + BN) * TG_BK * 2);
-            tma_load_2d(sm.a[s], &map_a, kb * TG_BK, (int)(mb * TG_BM), &sm.full[s]);
+            tma_load_2d(sm.a[s], &map_a, kc, (int)(mb * TG_BM + roff), &sm.full[s]);
             tma_load_2d(sm.b[s], &map_w, kb * TG_BK, nb * BN, &sm.full[s]);
           }
         }
@@ -471,9 +477,10 @@ bool kch_linear_tcgen05_supported(const void* A, const void* W, const void* C, c
 
 template <int BN>
 static int launch_tg(const void* A, const void* W, void* C, const void* R, int64_t M, int N, int K, int64_t lda,
-                     int64_t ldw, int64_t ldc, int64_t ldr, const TgEpilogue& ep, cudaStream_t s) {
+                     int64_t ldw, int64_t ldc, int64_t ldr, const TgEpilogue& ep, cudaStream_t s, int slab_k = 0) {
   CUtensorMap ma, mw;
-  int rc = make_map_2d(&ma, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, TG_BM, TG_BK);
+  int rc = slab_k > 0 ? make_map_2d(&ma, A, (uint64_t)M * (uint64_t)(K / slab_k), (uint64_t)slab_k, (uint64_t)slab_k, TG_BM, TG_BK)
+                      : make_map_2d(&ma, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, TG_BM, TG_BK);
   if (rc) return rc;
   rc = make_map_2d(&mw, W, (uint64_t)N, (uint64_t)K, (uint64_t)ldw, BN, TG_BK);
   if (rc) return rc;
@@ -488,7 +495,8 @@ static int launch_tg(const void* A, const void* W, void* C, const void* R, int64
   int64_t tiles = ((M + TG_BM - 1) / TG_BM) * ((N + BN - 1) / BN);
   int grid = (int)(tiles < sms ? tiles : sms);
   int vec_ok = (ldc % 8 == 0) && (((uintptr_t)C & 15) == 0) && (!R || ((ldr % 8 == 0) && (((uintptr_t)R & 15) == 0)));
-  gemm_tcgen05_kernel<BN, false><<<grid, TG_THREADS, smem, s>>>(ma, mw, (bf16*)C, (const bf16*)R, M, N, K, ldc, ldr, vec_ok, ep);
+  gemm_tcgen05_kernel<BN, false><<<grid, TG_THREADS, smem, s>>>(ma, mw, (bf16*)C, (const bf16*)R, M, N, K, ldc, ldr, vec_ok, ep,
+                                                               slab_k, M);
   KCH_LAUNCH_OK();
   return KCH_OK;
 }
@@ -496,10 +504,11 @@ static int launch_tg(const void* A, const void* W, void* C, const void* R, int64
 // 256 x 256 tiles on CTA pairs (clusters of two, tcgen05 cta_group::2): each CTA loads its 128 rows of A and half
 // of the W tile, so a CTA moves 32 KB per k-block instead of 48 KB and the ring holds six stages.
 static int launch_tg_pair(const void* A, const void* W, void* C, const void* R, int64_t M, int N, int K, int64_t lda,
-                          int64_t ldw, int64_t ldc, int64_t ldr, const TgEpilogue& ep, cudaStream_t s) {
+                          int64_t ldw, int64_t ldc, int64_t ldr, const TgEpilogue& ep, cudaStream_t s, int slab_k = 0) {
   constexpr int BN = 256;
   CUtensorMap ma, mw;
-  int rc = make_map_2d(&ma, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, TG_BM, TG_BK);
+  int rc = slab_k > 0 ? make_map_2d(&ma, A, (uint64_t)M * (uint64_t)(K / slab_k), (uint64_t)slab_k, (uint64_t)slab_k, TG_BM, TG_BK)
+                      : make_map_2d(&ma, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, TG_BM, TG_BK);
   if (rc) return rc;
   rc = make_map_2d(&mw, W, (uint64_t)N, (uint64_t)K, (uint64_t)ldw, BN / 2, TG_BK);
   if (rc) return rc;
@@ -523,7 +532,7 @@ static int launch_tg_pair(const void* A, const void* W, void* C, const void* R, 
   cfg.gridDim = dim3(2 * pairs);
   int vec_ok = (ldc % 8 == 0) && (((uintptr_t)C & 15) == 0) && (!R || ((ldr % 8 == 0) && (((uintptr_t)R & 15) == 0)));
   KCH_CUDA_OK(cudaLaunchKernelEx(&cfg, gemm_tcgen05_kernel<BN, true>, ma, mw, (bf16*)C, (const bf16*)R, M, N, K, ldc, ldr,
-                                 vec_ok, ep));
+                                 vec_ok, ep, slab_k, M));
   kch_note_launch(1);
   return KCH_OK;
 }
@@ -546,7 +555,7 @@ bool kch_linear_tcgen05_epilogue_ok(const kch_epilogue* e, int N) {
 }
 
 int kch_linear_tcgen05(const void* A, const void* W, void* C, const void* R, int64_t M, int N, int K, int64_t lda,
-                       int64_t ldw, int64_t ldc, int64_t ldr, const kch_epilogue* e, void* stream) {
+                       int64_t ldw, int64_t ldc, int64_t ldr, const kch_epilogue* e, void* stream, int slab_k) {
   cudaStream_t s = kch_stream(stream);
   TgEpilogue ep = {};
   if (e && e->n_segments) {
@@ -558,16 +567,16 @@ int kch_linear_tcgen05(const void* A, const void* W, void* C, const void* R, int
     // narrow tiles.  A fused L2-norm needs a whole 128-column head inside the tile.
     bool l2 = false;
     for (int i = 0; i < ep.nseg; ++i) l2 = l2 || ep.seg_act[i] == KCH_ACT_SILU_L2NORM;
-    if (l2) return launch_tg<128>(A, W, C, R, M, N, K, lda, ldw, ldc, ldr, ep, s);
-    return launch_tg<32>(A, W, C, R, M, N, K, lda, ldw, ldc, ldr, ep, s);
+    if (l2) return launch_tg<128>(A, W, C, R, M, N, K, lda, ldw, ldc, ldr, ep, s, slab_k);
+    return launch_tg<32>(A, W, C, R, M, N, K, lda, ldw, ldc, ldr, ep, s, slab_k);
   }
   // large products: 256 x 256 tiles on CTA pairs (KCH_GEMM=1 keeps one CTA per tile, for comparison)
   static const bool pair_on = [] { const char* e = getenv("KCH_GEMM"); return !(e && e[0] == '1'); }();
-  if (pair_on && N > 128 && M >= 4 * TG_BM) return launch_tg_pair(A, W, C, R, M, N, K, lda, ldw, ldc, ldr, ep, s);
-  if (N > 128) return launch_tg<256>(A, W, C, R, M, N, K, lda, ldw, ldc, ldr, ep, s);
-  if (N > 64) return launch_tg<128>(A, W, C, R, M, N, K, lda, ldw, ldc, ldr, ep, s);
-  if (N > 32) return launch_tg<64>(A, W, C, R, M, N, K, lda, ldw, ldc, ldr, ep, s);
-  return launch_tg<32>(A, W, C, R, M, N, K, lda, ldw, ldc, ldr, ep, s);
+  if (pair_on && N > 128 && M >= 4 * TG_BM) return launch_tg_pair(A, W, C, R, M, N, K, lda, ldw, ldc, ldr, ep, s, slab_k);
+  if (N > 128) return launch_tg<256>(A, W, C, R, M, N, K, lda, ldw, ldc, ldr, ep, s, slab_k);
+  if (N > 64) return launch_tg<128>(A, W, C, R, M, N, K, lda, ldw, ldc, ldr, ep, s, slab_k);
+  if (N > 32) return launch_tg<64>(A, W, C, R, M, N, K, lda, ldw, ldc, ldr, ep, s, slab_k);
+  return launch_tg<32>(A, W, C, R, M, N, K, lda, ldw, ldc, ldr, ep, s, slab_k);
 }
 
 // =====================================================================================================

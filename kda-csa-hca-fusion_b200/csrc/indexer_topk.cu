@@ -726,6 +726,125 @@ topk_select_reg_kernel(const float* __restrict__ logits, int32_t* __restrict__ o
   for (int i = tid; i < nsel; i += 256) orow[i] = 0x7FFFFFFF - (int)(uint32_t)(ssort[i] & 0xFFFFFFFFu);
 }
 
+// Long rows of a decode step (one query per sequence over tens of thousands of cached blocks): a thread-block
+// cluster of SC_CTAS CTAs per row instead of one CTA.  CTA r owns the contiguous index range
+// [r * seg, (r + 1) * seg) with its keys in registers (as topk_select_reg_kernel); each radix pass builds a
+// 256-bin histogram per CTA, and every CTA sums the SC_CTAS histograms through distributed shared memory, so all
+// of them agree on the threshold without a broadcast.  The histogram is double-buffered: one cluster barrier per
+// pass.  Same selection rule and output as topk_select_kernel (ties: lowest block index first, because rank
+// order is index order); output order is unspecified.  Row length and visible prefix come from the cache's
+// device counters.
+#define SC_CTAS 8
+__device__ __forceinline__ uint32_t sc_cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void sc_cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ int sc_ld_remote(const int* local, uint32_t rank) {
+  uint32_t addr = (uint32_t)__cvta_generic_to_shared(local), remote;
+  int v;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(addr), "r"(rank));
+  asm volatile("ld.shared::cluster.u32 %0, [%1];" : "=r"(v) : "r"(remote) : "memory");
+  return v;
+}
+
+template <int EPT>
+__global__ void __launch_bounds__(256)
+topk_select_cluster_kernel(const float* __restrict__ logits, int32_t* __restrict__ out, int64_t n_ld, int topk,
+                           const int32_t* __restrict__ ctr, int ctr_m) {
+  const int n = ctr[KCH_CTR_N_BLOCKS];
+  const int nv = min(ctr[KCH_CTR_TOKENS] / ctr_m, n);
+  const int b = blockIdx.y, tid = threadIdx.x;
+  const uint32_t rank = sc_cluster_rank();
+  const float* lg = logits + (int64_t)b * n_ld;
+  int32_t* orow = out + (int64_t)b * topk;
+  const int ksel = topk < n ? topk : n;
+  if (nv <= ksel) {                                       // uniform over the cluster: nobody reaches a barrier
+    if (rank == 0) for (int i = tid; i < topk; i += 256) orow[i] = i < nv ? i : -1;
+    return;
+  }
+  __shared__ int hist[2][256];
+  __shared__ int sbuf[9];
+  __shared__ uint32_t s_prefix;
+  __shared__ int s_need;
+  __shared__ int s_tot[2];
+  // slots per thread: this row's visible length over SC_CTAS x 256 threads, rounded up to 4 (<= EPT by the host's choice)
+  const int E = (((nv + SC_CTAS * 256 - 1) / (SC_CTAS * 256)) + 3) & ~3;
+  const int i0 = ((int)rank * 256 + tid) * E;
+  const int cnt_mine = max(0, min(E, nv - i0));
+  uint32_t u[EPT];
+#pragma unroll
+  for (int k4 = 0; k4 < EPT / 4; ++k4) {
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (4 * k4 < E && i0 + 4 * k4 < n_ld) v = *reinterpret_cast<const float4*>(lg + i0 + 4 * k4);   // row pad is readable
+    u[4 * k4] = f2ord(v.x); u[4 * k4 + 1] = f2ord(v.y); u[4 * k4 + 2] = f2ord(v.z); u[4 * k4 + 3] = f2ord(v.w);
+  }
+  uint32_t prefix = 0, pmask = 0;
+  int need = ksel;
+  for (int pass = 0; pass < 4; ++pass) {
+    const int shift = 24 - 8 * pass;
+    int* h = hist[pass & 1];
+    h[tid] = 0;
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < EPT; ++k)
+      if (k < cnt_mine && (u[k] & pmask) == prefix) atomicAdd(&h[(u[k] >> shift) & 255], 1);
+    sc_cluster_sync();                                    // every CTA's histogram of this pass is complete
+    const int bin = 255 - tid;
+    int cnt = 0;
+#pragma unroll
+    for (uint32_t r = 0; r < SC_CTAS; ++r) cnt += sc_ld_remote(&h[bin], r);
+    int tot;
+    const int cum = block_excl_scan(cnt, sbuf, &tot);
+    if (cum < need && cum + cnt >= need) {
+      s_prefix = prefix | ((uint32_t)bin << shift);
+      s_need = need - cum;
+    }
+    __syncthreads();
+    prefix = s_prefix;
+    need = s_need;
+    pmask |= 0xFFu << shift;
+  }
+  // ordered compaction: everything above the threshold, then `need` of the entries equal to it, lowest index first
+  const int n_gt = ksel - need;
+  int c_gt = 0, c_eq = 0;
+#pragma unroll
+  for (int k = 0; k < EPT; ++k)
+    if (k < cnt_mine) { c_gt += (u[k] > prefix); c_eq += (u[k] == prefix); }
+  int tot_gt, tot_eq;
+  int p_gt = block_excl_scan(c_gt, sbuf, &tot_gt);
+  int p_eq = block_excl_scan(c_eq, sbuf, &tot_eq);
+  if (tid == 0) { s_tot[0] = tot_gt; s_tot[1] = tot_eq; }
+  sc_cluster_sync();
+  for (uint32_t r = 0; r < rank; ++r) { p_gt += sc_ld_remote(&s_tot[0], r); p_eq += sc_ld_remote(&s_tot[1], r); }
+#pragma unroll
+  for (int k = 0; k < EPT; ++k)
+    if (k < cnt_mine) {
+      if (u[k] > prefix) orow[p_gt++] = i0 + k;
+      else if (u[k] == prefix) { if (p_eq < need) orow[n_gt + p_eq] = i0 + k; ++p_eq; }
+    }
+  if (rank == 0) for (int i = ksel + tid; i < topk; i += 256) orow[i] = -1;
+  sc_cluster_sync();                                      // nobody leaves while a neighbour may still read its totals
+}
+
+static int launch_topk_select_cluster(const float* logits, int32_t* indices, int B, int64_t n_ld, int topk,
+                                      const int32_t* counters, int ctr_m, int ept, cudaStream_t s) {
+  cudaLaunchConfig_t cfg = {};
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = SC_CTAS; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+  cfg.gridDim = dim3(SC_CTAS, (unsigned)B); cfg.blockDim = dim3(256); cfg.dynamicSmemBytes = 0; cfg.stream = s;
+  cfg.attrs = attr; cfg.numAttrs = 1;
+  if (ept <= 8) KCH_CUDA_OK(cudaLaunchKernelEx(&cfg, topk_select_cluster_kernel<8>, logits, indices, n_ld, topk, counters, ctr_m));
+  else if (ept <= 16) KCH_CUDA_OK(cudaLaunchKernelEx(&cfg, topk_select_cluster_kernel<16>, logits, indices, n_ld, topk, counters, ctr_m));
+  else KCH_CUDA_OK(cudaLaunchKernelEx(&cfg, topk_select_cluster_kernel<32>, logits, indices, n_ld, topk, counters, ctr_m));
+  kch_note_launch(1);
+  return KCH_OK;
+}
+
 // shared launcher of the selection: register variant when a row fits 256 x 32 logits, else the staged one
 static int launch_topk_select(const float* logits, int32_t* indices, int B, int T, int n_blocks, int64_t n_ld, int topk,
                               int m, int64_t t0, int n_visible, int sorted, size_t sort_smem, cudaStream_t s) {
@@ -1134,6 +1253,11 @@ extern "C" int kch_decode_indexer_topk(const void* q_idx, int q_dtype, int64_t q
   else { if (vec) GO(float, true); else GO(float, false); }
 #undef GO
   KCH_LAUNCH_OK();
+  // rows of up to 8 x 256 x 32 logits: a cluster of eight CTAs per row (KCH_SELECT_DECODE=s keeps one CTA per row)
+  static const bool one_cta = [] { const char* e = getenv("KCH_SELECT_DECODE"); return e && e[0] == 's'; }();
+  const int e_needed = (int)((((capacity + SC_CTAS * 256 - 1) / (SC_CTAS * 256)) + 3) & ~3LL);
+  if (!one_cta && e_needed <= 32 && (((uintptr_t)logits) & 15) == 0)
+    return launch_topk_select_cluster(logits, idx_out, B, n_ld, topk, counters, m, e_needed, s);
   // the whole row of logits is staged in shared memory when it fits (one CTA per SM at the largest size)
   const int cache_cap = (int)(n_ld <= 49152 ? ((n_ld + 1023) & ~1023LL) : 0);
   KCH_CUDA_OK(cudaFuncSetAttribute(topk_select_kernel<1024>, cudaFuncAttributeMaxDynamicSharedMemorySize, cache_cap * 4));

@@ -190,7 +190,8 @@ kda_prepare_tc5_kernel(PrepArgs a, const __grid_constant__ CUtensorMap vmap, uns
     }
     t5_commit(&bars[0]);
   }
-  bool ok = mbarrier_wait_bounded(&bars[0], 0, 61, PT_SPIN, status);
+  bool ok = true;
+  if (tid == 0) ok = mbarrier_wait_bounded(&bars[0], 0, 61, PT_SPIN, status);   // one poller; the others sleep at the barrier
   ok = __syncthreads_and(ok);
   t5_fence_after();
   const int q4 = warp & 3, hh = warp >> 2;                        // tensor-memory lane quarter, column half
@@ -232,72 +233,42 @@ kda_prepare_tc5_kernel(PrepArgs a, const __grid_constant__ CUtensorMap vmap, uns
         *reinterpret_cast<uint4*>(wsc + KM_OFF_AQK + 8192 + off) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
       }
     }
-    // blocks of T above the diagonal are zero
-    for (int idx = tid; idx < 6 * 256; idx += 256) {
-      const int bi = idx >> 8, rr = (idx >> 4) & 15, cc = idx & 15;
-      const int ub_a[6] = {0, 0, 0, 1, 1, 2}, ub_b[6] = {1, 2, 3, 2, 3, 3};
-      sT[(16 * ub_a[bi] + rr) * PS_LD + 16 * ub_b[bi] + cc] = 0.f;
-    }
   }
   __syncthreads();
   if (ok) {
-    // ---- (I + A)^-1 by block forward substitution (fp32): diagonal 16 x 16 blocks, four lanes per (block, column) ------
-    {
-      const int col = tid >> 2, q = tid & 3;
-      const int blk = col >> 4, cc = col & 15, base = 16 * blk;
-      float xs[4] = {0.f, 0.f, 0.f, 0.f};
+    // ---- T = (I + A)^-1 by forward substitution, one thread per column, the column in registers --------------------
+    // x_i = [i == c] - sum_{j < i} A[i][j] x_j: rows above the diagonal come out as zero by themselves, so every
+    // thread runs the same straight-line code; A[i][.] is a broadcast read.  64 threads carry this dependent chain
+    // (about 2000 FMAs each) while the other warps of the CTA and the second CTA of the SM keep the pipes busy.
+    if (tid < KM_C) {
+      const int c = tid;
+      float x[KM_C];
 #pragma unroll
-      for (int rr = 0; rr < 16; ++rr) {
-        float acc = 0.f;
+      for (int i = 0; i < KM_C; ++i) {
+        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+        const float4* arow = reinterpret_cast<const float4*>(sA + i * PS_LD);
 #pragma unroll
-        for (int m4 = 0; m4 < 4; ++m4) {
-          const int sidx = 4 * m4 + q;
-          if (sidx < rr && sidx >= cc) acc = fmaf(sA[(base + rr) * PS_LD + base + sidx], xs[m4], acc);
+        for (int j4 = 0; j4 < (i + 3) / 4; ++j4) {
+          const float4 av = arow[j4];                            // entries at and above the diagonal are stored as 0
+          if (4 * j4 < i) acc[0] = fmaf(av.x, x[4 * j4], acc[0]);
+          if (4 * j4 + 1 < i) acc[1] = fmaf(av.y, x[4 * j4 + 1], acc[1]);
+          if (4 * j4 + 2 < i) acc[2] = fmaf(av.z, x[4 * j4 + 2], acc[2]);
+          if (4 * j4 + 3 < i) acc[3] = fmaf(av.w, x[4 * j4 + 3], acc[3]);
         }
-        acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-        acc += __shfl_xor_sync(0xffffffffu, acc, 2);
-        const float x = (rr == cc) ? 1.f : (rr > cc ? -acc : 0.f);
-        if ((rr & 3) == q) xs[rr >> 2] = x;
-        if (q == 0) sT[(base + rr) * PS_LD + base + cc] = x;
+        x[i] = (i == c ? 1.f : 0.f) - ((acc[0] + acc[1]) + (acc[2] + acc[3]));
       }
-    }
-    __syncthreads();
-    // off-diagonal blocks by distance d from the diagonal: T_ab = -T_aa (sum_{b<=c<a} A_ac T_cb)
-    for (int d = 1; d < 4; ++d) {
-      const int nblk = 4 - d;
-      for (int idx = tid; idx < nblk * 256; idx += 256) {
-        const int bi = idx >> 8, rr = (idx >> 4) & 15, cc = idx & 15;
-        const int ba = bi + d, bb = bi;
-        float acc = 0.f;
-        for (int cblk = bb; cblk < ba; ++cblk)
-#pragma unroll 4
-          for (int s = 0; s < 16; ++s)
-            acc = fmaf(sA[(16 * ba + rr) * PS_LD + 16 * cblk + s], sT[(16 * cblk + s) * PS_LD + 16 * bb + cc], acc);
-        sP[(bi * 16 + rr) * 17 + cc] = acc;
-      }
-      __syncthreads();
-      for (int idx = tid; idx < nblk * 256; idx += 256) {
-        const int bi = idx >> 8, rr = (idx >> 4) & 15, cc = idx & 15;
-        const int ba = bi + d, bb = bi;
-        float acc = 0.f;
-#pragma unroll 4
-        for (int s = 0; s <= rr; ++s) acc = fmaf(sT[(16 * ba + rr) * PS_LD + 16 * ba + s], sP[(bi * 16 + s) * 17 + cc], acc);
-        sT[(16 * ba + rr) * PS_LD + 16 * bb + cc] = -acc;
-      }
-      __syncthreads();
-    }
-    // T diag(beta) as K-major hi / lo tiles (over the QG lo rows)
-    for (int idx = tid; idx < KM_C * 8; idx += 256) {
-      const int i = idx >> 3, ch = idx & 7;
-      uint32_t hi[4], lo[4];
+      // column c of T diag(beta) into the K-major hi / lo operand tiles (over the QG lo rows)
+      const float bc = sbeta[c];
+      uint8_t* th = sm + PT_TBH + 2 * (c & 7);
+      uint8_t* tl = sm + PT_TBL + 2 * (c & 7);
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int jj = 8 * ch + 2 * e;
-        split2_bf16(sT[i * PS_LD + jj] * sbeta[jj], sT[i * PS_LD + jj + 1] * sbeta[jj + 1], hi[e], lo[e]);
+      for (int i = 0; i < KM_C; ++i) {
+        bf16 hi, lo;
+        split1_bf16(x[i] * bc, hi, lo);
+        const uint32_t off = swz<128>(i, c >> 3);
+        *reinterpret_cast<bf16*>(th + off) = hi;
+        *reinterpret_cast<bf16*>(tl + off) = lo;
       }
-      const uint32_t off = swz<128>(i, ch);
-      *reinterpret_cast<uint4*>(sm + PT_TBH + off) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
-      *reinterpret_cast<uint4*>(sm + PT_TBL + off) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
     }
     t5_fence_async_smem();
   }
@@ -326,7 +297,7 @@ kda_prepare_tc5_kernel(PrepArgs a, const __grid_constant__ CUtensorMap vmap, uns
     }
     t5_commit(&bars[2]);
   }
-  if (ok) ok = mbarrier_wait_bounded(&bars[2], 0, 63, PT_SPIN, status);
+  if (ok && tid == 0) ok = mbarrier_wait_bounded(&bars[2], 0, 63, PT_SPIN, status);
   ok = __syncthreads_and(ok);
   t5_fence_after();
   if (ok) {

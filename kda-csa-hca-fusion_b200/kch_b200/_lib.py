@@ -74,6 +74,7 @@ PROTOTYPES = {
     "kch_short_conv": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp]),
     "kch_linear": (_i, [_vp, _vp, _vp, _vp, _i64, _i, _i, _i64, _i64, _i64, _i64, _i, _vp]),
     "kch_linear_ex": (_i, [_vp, _vp, _vp, _vp, _i64, _i, _i, _i64, _i64, _i64, _i64, _i, C.POINTER(Epilogue), _vp]),
+    "kch_linear_kslabs": (_i, [_vp, _vp, _vp, _vp, _i64, _i, _i, _i, _i64, _i64, _i64, _i, _vp]),
     "kch_activation": (_i, [_vp, _vp, _i64, _i, _i, _f, _i, _i, _i64, _i64, _vp]),
     "kch_rownorm": (_i, [_vp, _i64, _vp, _vp, _i64, _i, _i, _i, _vp]),
     "kch_kda_recurrent": (_i, [_vp] * 8 + [_i] * 6 + [_f, _f, _i, _i64, _i64, _i64, _i64, _vp]),

@@ -70,6 +70,34 @@ def linear(x, W, residual=None, epilogue=None, group=1):
     return out.reshape(*lead, N)
 
 
+def linear_kslabs(a_slabs, W, residual=None):
+    """``F.linear(cat(a_slabs, dim=-1), W)`` (+ residual) without forming the concatenation: ``a_slabs``
+    ``[n_slabs, M, K / n_slabs]`` contiguous bf16 (the rank-major buffer an all-gather of per-GPU head slices leaves
+    behind), W ``[N, K]``.  Returns ``[M, N]``."""
+    _lib.require_cuda(a_slabs, W, fn="linear_kslabs")
+    lib = _lib.load()
+    n_slabs, M, kl = a_slabs.shape
+    N, K = W.shape
+    if K != n_slabs * kl:
+        raise ValueError(f"linear_kslabs: weight has {K} input features, the slabs hold {n_slabs} x {kl}")
+    if a_slabs.dtype != torch.bfloat16 or W.dtype != torch.bfloat16:
+        raise ValueError("linear_kslabs: bf16 operands only")
+    a_slabs = a_slabs.contiguous()
+    if W.stride(-1) != 1:
+        W = W.contiguous()
+    out = torch.empty(M, N, dtype=a_slabs.dtype, device=a_slabs.device)
+    r2, ldr = None, 0
+    if residual is not None:
+        r2 = residual.reshape(-1, N)
+        if r2.stride(-1) != 1:
+            r2 = r2.contiguous()
+        ldr = r2.stride(0) if M > 1 else N
+    with torch.cuda.device(a_slabs.device):
+        _lib.check(lib.kch_linear_kslabs(_lib.ptr(a_slabs), _lib.ptr(W), _lib.ptr(out), _lib.ptr(r2), M, N, K, n_slabs,
+                                         W.stride(0), N, ldr, _lib.KCH_BF16, _lib.stream()))
+    return out
+
+
 def fuse_rows(*weights):
     """Row-concatenate weight matrices and zero-pad the row count to a multiple of 8, so that every column
     slice of the fused projection output keeps a 16-byte-aligned row stride (TMA-readable in place)."""

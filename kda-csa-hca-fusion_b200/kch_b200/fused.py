@@ -22,7 +22,7 @@ from .csa import attend, fuse_rows, indexer_topk, linear, mma_attention_eligible
 from .decoding_cache import CSADecodingCache, HCADecodingCache
 from .hca import naive_hca
 from .kda import chunk_gate_supported, kda_forward, validate_kda_backend
-from .tp import gather_heads
+from .tp import gather_heads, out_projection  # noqa: F401
 
 
 @dataclass
@@ -295,8 +295,7 @@ class KDAHybridLayer(nn.Module):
                                    output_final_state=True, chunk_size=cfg.kda_chunk_size, use_chunk=use_chunk,
                                    backend=cfg.kda_backend, state_out=None if use_chunk else state_out,
                                    gate_scale=cfg.kda_decay_scale if raw_gate else None)
-        o = gather_heads(o.reshape(B, T, HV * V), self.tp)
-        out = linear(o, self.o_proj.weight, residual=residual)
+        out = out_projection(o.reshape(B, T, HV * V), self.tp, self.o_proj.weight, residual=residual)
         return out, new_state, new_lb
 
 
@@ -345,7 +344,7 @@ class CSAHybridLayer(nn.Module):
                          _fused_weight=self.fused_weight(), _fused_q_weight=self.q_weight())
 
     def forward(self, x, state=None, residual=None):
-        return linear(gather_heads(self.core(x), self.tp), self.o_proj.weight, residual=residual), None
+        return out_projection(self.core(x), self.tp, self.o_proj.weight, residual=residual), None
 
 
 class HCAHybridLayer(nn.Module):
@@ -376,7 +375,7 @@ class HCAHybridLayer(nn.Module):
                          return_projections=return_projections, _fused_weight=self.fused_weight())
 
     def forward(self, x, state=None, residual=None):
-        return linear(gather_heads(self.core(x), self.tp), self.o_proj.weight, residual=residual), None
+        return out_projection(self.core(x), self.tp, self.o_proj.weight, residual=residual), None
 
 
 class _Fp32LayerNorm(nn.LayerNorm):
@@ -642,7 +641,7 @@ class HybridDecoding(nn.Module):
                                        topk=cfg.csa_topk, nh=nh, nIh=nIh, scale=1.0, sink_logits=layer.sink,
                                        use_ste=False, normalize_qk=True)
                 o_core = o.reshape(B, 1, nh * c).to(h.dtype)
-        return linear(gather_heads(o_core, layer.tp), layer.o_proj.weight, residual=residual)
+        return out_projection(o_core, layer.tp, layer.o_proj.weight, residual=residual)
 
     def _hca(self, i, layer, h, residual):
         cfg = self.cfg
@@ -667,7 +666,7 @@ class HybridDecoding(nn.Module):
                 qn = rownorm(q.view(B, 1, nh, c), True)
                 o = cache.forward_step(qn, nh=nh, scale=1.0, sink_logits=layer.sink)
                 o_core = o.reshape(B, 1, nh * c).to(h.dtype)
-        return linear(gather_heads(o_core, layer.tp), layer.o_proj.weight, residual=residual)
+        return out_projection(o_core, layer.tp, layer.o_proj.weight, residual=residual)
 
     # ---- CUDA-graph replay of one-token steps ------------------------------------------------------------------
     def _graph_signature(self, x):

@@ -60,6 +60,7 @@ def main():
     ap.add_argument("--topk", type=int, default=1024)
     ap.add_argument("--iters", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=2)
+    ap.add_argument("--gate-scale", type=float, default=0.1, help="kda: multiplies the synthetic log-decay")
     ap.add_argument("--kv-quant", default=None, choices=[None, "fp8", "int8"])
     ap.add_argument("--graph", action="store_true", help="decode: replay the step from a CUDA graph")
     ap.add_argument("--profile", action="store_true", help="bracket the timed iterations with cudaProfilerStart/Stop")
@@ -77,6 +78,7 @@ def main():
         out.update(M=a.M, N=a.N, K=a.K, ms=ms, tflops=fl / ms / 1e9, algorithmic_bytes=2.0 * (a.M * a.K + a.N * a.K + a.M * a.N))
     elif a.kernel in ("kda_chunk", "kda_recurrent"):
         q, k, v, gg, beta = (t.to(dev) for t in syn.kda_inputs(0, a.B, a.T, a.H, 128, 128, dtype=torch.bfloat16))
+        gg = (gg.float() * a.gate_scale).bfloat16()     # 0.1: the decay range of the layer's gate (-0.1 softplus)
         if a.kernel == "kda_chunk":
             fn = lambda: kch_b200.naive_chunk_kda(q, k, v, gg, beta, output_final_state=True)  # noqa: E731
         else:

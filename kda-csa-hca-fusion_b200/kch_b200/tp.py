@@ -68,6 +68,28 @@ def gather_heads(o_local, ctx: TPContext):
     return buf.view(ctx.world, rows, kl).permute(1, 0, 2).reshape(*lead, ctx.world * kl)
 
 
+def out_projection(o_local, ctx: TPContext, W, residual=None):
+    """``o_proj`` of a layer whose heads are sharded: all-gather of the per-rank head outputs ``[..., h_local*c]``,
+    then ``F.linear(cat over ranks, W)`` (+ residual) on every rank.  The gather lands rank-major
+    (``[world, rows, h_local*c]``); the GEMM walks those slabs along its K loop (``kch_linear_kslabs``), so the
+    gathered tensor is never permuted into ``[rows, h*c]``."""
+    from .csa import linear, linear_kslabs
+    if ctx is None or ctx.world == 1:
+        return linear(o_local, W, residual=residual)
+    lead = o_local.shape[:-1]
+    kl = o_local.shape[-1]
+    slab_ok = (o_local.dtype == torch.bfloat16 and W.dtype == torch.bfloat16 and kl % 64 == 0 and W.shape[0] >= 32
+               and W.data_ptr() % 16 == 0 and W.stride(0) % 8 == 0)
+    if not slab_ok:
+        return linear(gather_heads(o_local, ctx), W, residual=residual)
+    flat = o_local.reshape(-1, kl).contiguous()
+    rows = flat.shape[0]
+    buf = torch.empty(ctx.world * rows, kl, dtype=flat.dtype, device=flat.device)
+    dist.all_gather_into_tensor(buf, flat, group=ctx.group)
+    y = linear_kslabs(buf.view(ctx.world, rows, kl), W, residual=residual)
+    return y.reshape(*lead, W.shape[0])
+
+
 def build_tp_model(cfg, params, total_layers, ctx: TPContext, device, dtype):
     """A ``HybridKCHAttention`` holding rank ``ctx.rank``'s shard of ``params`` (full ``state_dict``)."""
     import torch.nn as nn

@@ -168,7 +168,7 @@ def test_topk_stage_long_rows(kch, n, topk, qdtype):
     picked = torch.gather(torch.cat([lg, torch.full_like(lg[..., :1], NEG_INF)], -1), -1, torch.where(mine < 0, n, mine))
     # descending, as torch.topk returns (the kernel orders by its own logits, which differ from the oracle's in the
     # last bit or two: neighbours closer than that may appear swapped)
-    assert bool((picked[..., :-1] >= picked[..., 1:] - 2e-6 * picked[..., 1:].abs() - 1e-9).all())
+    assert bool((picked[..., :-1] >= picked[..., 1:] - 1e-6).all())        # |logit| <= 0.4 here
     # unsorted output (what the layer asks for) selects the same set
     uns = csa_mod.indexer_topk(qd, k.to(DEV), w.to(DEV), topk, m=m, t0=t0, normalize_qk=True,
                                sorted_output=False).cpu().long()
@@ -333,10 +333,10 @@ def test_config5_shaped_decode_steps(kch, kind):
     oc.append(*[stc[n_][:, pre] for n_ in names], stc["Ba"], stc["Bb"], stc["B_idx"])
     oh.append(stc["Ca"][:, pre], stc["Za"][:, pre], stc["B_pos"])
     assert cc.n_blocks == ctx // m == 9216 and hc.n_blocks == ctx // m2
-    # stored rows: one rounding apart at most (bf16: 2^-8 relative; e4m3 payload: one step of 2^-3 relative, when
-    # the two fp32 rows straddle a rounding boundary of the 8-bit grid)
+    # stored rows: one rounding apart at most (bf16: a step of up to 2^-7 relative; e4m3 payload: up to 2^-3
+    # relative, when the two fp32 rows straddle a rounding boundary of the grid)
     a_, b_ = cc.C_comp.float().cpu(), oc.C_comp.float()
-    step = 2 ** -8 if kind is None else 2 ** -3
+    step = 2 ** -7 if kind is None else 2 ** -3
     excess = (a_ - b_).abs() - (step * b_.abs() + 1e-3)
     worst = int(excess.argmax())
     assert float(excess.max()) <= 0.0, (float(excess.max()), float(a_.flatten()[worst]), float(b_.flatten()[worst]))

@@ -54,6 +54,21 @@ def test_linear_bf16(kch, M, N, K):
     assert md(y2, ref2) == 0.0
 
 
+@pytest.mark.parametrize("M,N,slabs,kl", [(300, 256, 2, 128), (1000, 2048, 8, 256), (64, 2048, 4, 512)])
+def test_linear_kslabs_equals_linear_of_concatenation(kch, M, N, slabs, kl):
+    """The output projection over a rank-major all-gather buffer: same bits as F.linear of the concatenated heads."""
+    from kch_b200.csa import linear, linear_kslabs
+    g = torch.Generator().manual_seed(M + N + slabs)
+    a = torch.randn(slabs, M, kl, generator=g).bfloat16().to(DEV)
+    w = (torch.randn(N, slabs * kl, generator=g) * 0.05).bfloat16().to(DEV)
+    r = torch.randn(M, N, generator=g).bfloat16().to(DEV)
+    cat = a.permute(1, 0, 2).reshape(M, slabs * kl).contiguous()
+    assert torch.equal(linear_kslabs(a, w), linear(cat, w))
+    assert torch.equal(linear_kslabs(a, w, residual=r), linear(cat, w, residual=r))
+    with pytest.raises(ValueError, match="multiple of 64"):
+        linear_kslabs(a[..., :40].contiguous(), w[:, :slabs * 40].contiguous())
+
+
 def test_linear_f32_and_strided(kch):
     from kch_b200.csa import linear
     g = torch.Generator().manual_seed(5)
