@@ -376,7 +376,7 @@ def run_b200(args):
             if g == dp_rank:
                 tp_group = grp
     if tp > 1:
-        model = build_tp_model(cfg, params, LAYERS, TPContext(tp_rank, tp, tp_group), dev, torch.bfloat16)
+        model = build_tp_model(cfg, params, LAYERS, TPContext(tp_rank, tp, tp_group, args.tp_attn), dev, torch.bfloat16)
     else:
         model = kch_b200.HybridKCHAttention(cfg, LAYERS)
         model.load_state_dict(params, strict=True)
@@ -465,6 +465,35 @@ def run_b200(args):
         torch.cuda.empty_cache()
         decode = decode_bench(model, C4, args.decode_batch, args.decode_context, args.decode_steps, 8, dev,
                               float(peaks.get("hbm_gbs", 6650.0)), world)
+    layout_str = model.layout_str()
+    variant = None
+    if tp > 1 and dp == 1 and not args.no_variant:
+        # the same steps with the CSA / HCA layers divided the other way (device-timed only; an extra, not the metric)
+        other = "rows" if args.tp_attn == "heads" else "heads"
+        del model
+        torch.cuda.empty_cache()
+        params = syn.hybrid_params(SEED, cfg, LAYERS, dtype=torch.bfloat16)
+        model = build_tp_model(cfg, params, LAYERS, TPContext(tp_rank, tp, tp_group, other), dev, torch.bfloat16)
+        del params
+        xv = x_host.to(dev)
+        for _ in range(args.warmup):
+            model.reset_state()
+            model(xv)
+        barrier()
+        v0, v1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        v0.record()
+        for _ in range(args.steps):
+            model.reset_state()
+            yv = model(xv)
+        v1.record()
+        barrier()
+        t = torch.tensor([v0.elapsed_time(v1) / args.steps], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        vms = float(t.item())
+        variant = {"parallelism": f"tp{tp}_heads" if other == "heads" else f"tp{tp}_kda_heads_attn_rows",
+                   "ms_per_step": vms, "value": tokens / (vms / 1e3), "unit": UNIT,
+                   "finite": bool(torch.isfinite(yv.float()).all())}
+        del xv, yv
     status = _lib.device_status()
     if rank == 0:
         peak_tf = float(peaks.get("bf16_tflops_sustained", 1400.0))
@@ -476,9 +505,10 @@ def run_b200(args):
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic",
-            "config": {"workload": "hybrid_prefill_c4", "B": B, "T": T, "layers": LAYERS, "layout": model.layout_str(),
+            "config": {"workload": "hybrid_prefill_c4", "B": B, "T": T, "layers": LAYERS, "layout": layout_str,
                        "parallelism": ("single_gpu" if world == 1 else (f"dp{dp}_sequences" if tp == 1 else (
-                           f"tp{tp}_heads" if dp == 1 else f"dp{dp}_sequences_x_tp{tp}_heads"))), "l2": "inputs larger than L2 (537 MB hidden states)", **C4},
+                           (f"tp{tp}_heads" if args.tp_attn == "heads" else f"tp{tp}_kda_heads_attn_rows") if dp == 1
+                           else f"dp{dp}_sequences_x_tp{tp}_heads"))), "l2": "inputs larger than L2 (537 MB hidden states)", **C4},
             "e2e": {"value": tokens / (e2e_ms / 1e3), "unit": UNIT, "h2d_bytes_per_step": x_host.numel() * 2 * world,
                     "d2h_bytes_per_step": y_host.numel() * 2 * world, "steps": e2e_steps, "ms_per_step": e2e_ms,
                     "api": "kch_b200.HostPipeline.run (pinned host in / out, copies overlapped with the passes)",
@@ -499,11 +529,19 @@ def run_b200(args):
         }
         if decode is not None:
             out["decode"] = decode
+        if variant is not None:
+            out["tp_variant"] = variant
         if world == 1 and not args.no_cpu_baseline:
             out["cpu_baseline"] = cpu_baseline_sample()
         print(json.dumps(out))
     if world > 1:
-        dist.destroy_process_group()
+        # the decode legs captured NCCL all-gathers into CUDA graphs; tearing the process group down after that does
+        # not return on this stack, so every rank meets once more and leaves without it
+        sys.stdout.flush()
+        torch.cuda.synchronize()
+        dist.barrier()
+        torch.cuda.synchronize()
+        os._exit(0)
 
 
 def main():
@@ -519,6 +557,10 @@ def main():
     ap.add_argument("--dp-sequences", action="store_true",
                     help="N > 1: deal the sequences of the batch out to the GPUs first (replicas), heads only beyond")
     ap.add_argument("--tp-only", action="store_true", help="accepted for compatibility: heads-only is the default")
+    ap.add_argument("--tp-attn", default="heads", choices=["heads", "rows"],
+                    help="N > 1: how the CSA / HCA layers are divided: query heads like KDA (default), or the query rows "
+                         "(their indexer, top-k and gathers do not shrink with the head count); KDA is always by heads")
+    ap.add_argument("--no-variant", action="store_true", help="N > 1: skip the extra timing of the other --tp-attn mode")
     ap.add_argument("--decode-batch", type=int, default=64)
     ap.add_argument("--decode-context", type=int, default=131072)
     ap.add_argument("--decode-steps", type=int, default=256)

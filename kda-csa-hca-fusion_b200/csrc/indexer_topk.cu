@@ -607,6 +607,22 @@ topk_select_kernel(const float* __restrict__ logits, int32_t* __restrict__ out, 
   for (int i = tid; i < nsel; i += NT) orow[i] = 0x7FFFFFFF - (int)(uint32_t)(ssort[i] & 0xFFFFFFFFu);
 }
 
+// Histogram increment of one radix pass.  The two leading bytes of the order-preserving key (sign, exponent, top of
+// the mantissa) take only a handful of values in a row of logits, so plain shared-memory atomics would serialise on
+// a few addresses: the lanes of a warp that hit the same bin are found with match.any and their leader adds the
+// whole group.  The lower bytes are spread evenly and keep the plain atomic.
+__device__ __forceinline__ void hist_add(int* hist, bool act, uint32_t bin, bool aggregate) {
+  if (aggregate) {
+    const unsigned am = __ballot_sync(0xffffffffu, act);
+    if (act) {
+      const unsigned peers = __match_any_sync(am, bin);
+      if ((threadIdx.x & 31) == (unsigned)(__ffs(peers) - 1)) atomicAdd(&hist[bin], __popc(peers));
+    }
+  } else if (act) {
+    atomicAdd(&hist[bin], 1);
+  }
+}
+
 // Radix select of one row with SLOTS keys per thread in registers (E <= SLOTS elements owned by each thread).
 template <int EPT>
 __device__ __forceinline__ void select_row_regs(const float* __restrict__ lg, int32_t* __restrict__ orow, int nv, int ksel,
@@ -632,7 +648,7 @@ __device__ __forceinline__ void select_row_regs(const float* __restrict__ lg, in
       __syncthreads();
 #pragma unroll
       for (int k = 0; k < EPT; ++k)
-        if (k < cnt_mine && (u[k] & pmask) == prefix) atomicAdd(&hist[(u[k] >> shift) & 255], 1);
+        hist_add(hist, k < cnt_mine && (u[k] & pmask) == prefix, (u[k] >> shift) & 255, pass < 2);
       __syncthreads();
       const int bin = 255 - tid;
       const int cnt = hist[bin];
@@ -791,7 +807,7 @@ topk_select_cluster_kernel(const float* __restrict__ logits, int32_t* __restrict
     __syncthreads();
 #pragma unroll
     for (int k = 0; k < EPT; ++k)
-      if (k < cnt_mine && (u[k] & pmask) == prefix) atomicAdd(&h[(u[k] >> shift) & 255], 1);
+      hist_add(h, k < cnt_mine && (u[k] & pmask) == prefix, (u[k] >> shift) & 255, pass < 2);
     sc_cluster_sync();                                    // every CTA's histogram of this pass is complete
     const int bin = 255 - tid;
     int cnt = 0;

@@ -349,13 +349,16 @@ def naive_csa(H, W_aKV, W_bKV, W_aZ, W_bZ, Ba, Bb, W_DQ, W_UQ, W_IUQ, W_w, W_KV_
               m: int, topk: int, nh: int, nIh: int, c: int, c_I: int, dc: int, scale=None,
               sliding_window: int = 0, sink_logits=None, use_ste: bool = True, ste_mode: str = "topk_columns",
               normalize_qk: bool = False, fuse_projections: bool = True, return_projections: bool = False,
-              _fused_weight=None, _fused_q_weight=None, _return_indices: bool = False, _aux: dict | None = None):
+              _fused_weight=None, _fused_q_weight=None, _return_indices: bool = False, _aux: dict | None = None,
+              _q_rows=None):
     """Full CSA forward: ``[B,T,d] -> [B,T,nh*c]`` in ``H.dtype``; weights in ``nn.Linear`` layout.
 
     ``_fused_weight`` (optional) is the row-concatenation ``[W_aKV;W_bKV;W_aZ;W_bZ;W_KV_idx;W_Z_idx;
     W_DQ;W_w]`` prepared once by the layer object so the eight input projections run as one GEMM.
     ``_aux`` (a dict, for stage-by-stage checks) receives the intermediate tensors exactly as the kernels saw
     them: ``q_idx``, ``w_idx``, ``K_IComp``, ``C_comp``, ``q`` (padded length).
+    ``_q_rows = (lo, hi)`` (sharding by query rows): only the queries ``lo..hi-1`` are scored and attended, against
+    the keys of tokens ``0..hi-1`` (``H`` may be longer, the rest is not read); returns ``[B, hi-lo, nh*c]``.
     """
     B_, T, d = H.shape
     if m < 1:
@@ -396,6 +399,14 @@ def naive_csa(H, W_aKV, W_bKV, W_aZ, W_bZ, Ba, Bb, W_DQ, W_UQ, W_IUQ, W_w, W_KV_
         if w.shape[1] != d:
             raise ValueError(f"naive_csa: {name}.shape={tuple(w.shape)} — second dim (in_features) must "
                              f"equal d={d} (H.shape[-1]).")
+    q_lo = 0
+    if _q_rows is not None:
+        q_lo, q_hi = int(_q_rows[0]), int(_q_rows[1])
+        if not 0 <= q_lo < q_hi <= T:
+            raise ValueError(f"naive_csa: _q_rows={_q_rows} must satisfy 0 <= lo < hi <= T={T}")
+        if return_projections:
+            raise ValueError("naive_csa: _q_rows and return_projections cannot be combined")
+        H, T = H[:, :q_hi], q_hi
     original_T = T
     pad = (-T) % m
     if pad:
@@ -410,12 +421,15 @@ def naive_csa(H, W_aKV, W_bKV, W_aZ, W_bZ, Ba, Bb, W_DQ, W_UQ, W_IUQ, W_w, W_KV_
     C_comp = csa_compress_kv_overlapped(Ca, Cb, Za, Zb, Ba, Bb, m)      # [B,n,c] fp32
     K_IComp = csa_compress_kv(K_idx_raw, Z_idx, B_idx, m)               # [B,n,cI] fp32
     W_q = _fused_q_weight if _fused_q_weight is not None else torch.cat([W_UQ, W_IUQ], dim=0)
-    qq = linear(cQ, W_q)                                                # [B,T,nh*c + nIh*cI]
+    if q_lo:                                                            # the query side for this rank's rows only
+        cQ, w_idx = cQ[:, q_lo:], w_idx[:, q_lo:]
+    qq = linear(cQ, W_q)                                                # [B,Tq,nh*c + nIh*cI]
     q, q_idx = qq[..., :nh * c + nIh * c_I].split([nh * c, nIh * c_I], dim=-1)
     q_idx = q_idx.unflatten(-1, (nIh, c_I))                             # a view of the fused projection
     indices = None
     if topk > 0:
-        indices = indexer_topk(q_idx, K_IComp, w_idx, topk, m=m, normalize_qk=normalize_qk, sorted_output=False)
+        indices = indexer_topk(q_idx, K_IComp, w_idx, topk, m=m, t0=q_lo, normalize_qk=normalize_qk,
+                               sorted_output=False)
     if _aux is not None:
         _aux.update(q_idx=q_idx, w_idx=w_idx, K_IComp=K_IComp, C_comp=C_comp, q=q)
     if scale is None:
@@ -426,9 +440,10 @@ def naive_csa(H, W_aKV, W_bKV, W_aZ, W_bZ, Ba, Bb, W_DQ, W_UQ, W_IUQ, W_w, W_KV_
     local = None
     if sliding_window > 0:
         local = rownorm(Ca, normalize_qk, kdt) if normalize_qk else Ca
-    out = attend(q, C_comp_n if topk > 0 else None, nh=nh, c=c, sel=indices, m=m, q_normalize=normalize_qk,
-                 win=local, sliding_window=sliding_window, sink=sink_logits, scale=scale, out_dtype=H.dtype)
-    out_final = out[:, :original_T]
+    out = attend(q, C_comp_n if topk > 0 else None, nh=nh, c=c, sel=indices, m=m, t0=q_lo, q_normalize=normalize_qk,
+                 win=local, sliding_window=sliding_window, sink=sink_logits, scale=scale, out_dtype=H.dtype,
+                 win_t0=q_lo)
+    out_final = out[:, :original_T - q_lo]
     res = [out_final]
     if return_projections:
         res.append(tuple(x[:, :original_T] for x in (Ca, Cb, Za, Zb, K_idx_raw, Z_idx)))

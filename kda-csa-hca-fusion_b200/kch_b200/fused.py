@@ -22,7 +22,7 @@ from .csa import attend, fuse_rows, indexer_topk, linear, mma_attention_eligible
 from .decoding_cache import CSADecodingCache, HCADecodingCache
 from .hca import naive_hca
 from .kda import chunk_gate_supported, kda_forward, validate_kda_backend
-from .tp import gather_heads, out_projection  # noqa: F401
+from .tp import gather_heads, out_projection, out_projection_rows, row_span  # noqa: F401
 
 
 @dataclass
@@ -299,6 +299,28 @@ class KDAHybridLayer(nn.Module):
         return out, new_state, new_lb
 
 
+def _rows_mode(tp):
+    return tp is not None and tp.world > 1 and tp.attn_shard == "rows"
+
+
+def _forward_by_rows(layer, x, residual):
+    """CSA / HCA sub-layer with its QUERY ROWS sharded: this rank runs the operator for its contiguous run of the
+    flattened ``[B*T]`` rows (whole sequences, or a slice of one sequence against that sequence's prefix), the runs
+    are all-gathered along the row axis and ``o_proj`` (+ residual) follows on every rank."""
+    B, T, _ = x.shape
+    r0, per = row_span(B * T, layer.tp)
+    if per % T == 0:
+        b0 = r0 // T
+        o = layer.core(x[b0:b0 + per // T])
+    elif T % per == 0:
+        b, lo = r0 // T, r0 % T
+        o = layer.core(x[b:b + 1], q_rows=(lo, lo + per))
+    else:
+        raise ValueError(f"tensor parallelism by rows: {B} x {T} rows do not split over {layer.tp.world} ranks into "
+                         f"whole sequences or equal slices of a sequence")
+    return out_projection_rows(o, layer.tp, layer.o_proj.weight, residual, lead=(B, T))
+
+
 class CSAHybridLayer(nn.Module):
     """CSA sub-layer (compression + lightning indexer + sparse MQA + window + sink) and ``o_proj``."""
 
@@ -333,7 +355,7 @@ class CSAHybridLayer(nn.Module):
         return self._fused.get(self.W_aKV.weight, self.W_bKV.weight, self.W_aZ.weight, self.W_bZ.weight,
                                self.W_KV_idx.weight, self.W_Z_idx.weight, self.W_DQ.weight, self.W_w.weight)
 
-    def core(self, x, *, return_projections=False):
+    def core(self, x, *, return_projections=False, q_rows=None):
         cfg = self.cfg
         return naive_csa(x, self.W_aKV.weight, self.W_bKV.weight, self.W_aZ.weight, self.W_bZ.weight, self.Ba,
                          self.Bb, self.W_DQ.weight, self.W_UQ.weight, self.W_IUQ.weight, self.W_w.weight,
@@ -341,9 +363,11 @@ class CSAHybridLayer(nn.Module):
                          nh=cfg.csa_nh, nIh=cfg.csa_nIh, c=cfg.csa_c, c_I=cfg.csa_cI, dc=cfg.csa_dc,
                          sliding_window=cfg.csa_sliding_window, sink_logits=self.sink, use_ste=False,
                          normalize_qk=True, return_projections=return_projections,
-                         _fused_weight=self.fused_weight(), _fused_q_weight=self.q_weight())
+                         _fused_weight=self.fused_weight(), _fused_q_weight=self.q_weight(), _q_rows=q_rows)
 
     def forward(self, x, state=None, residual=None):
+        if _rows_mode(self.tp):
+            return _forward_by_rows(self, x, residual), None
         return out_projection(self.core(x), self.tp, self.o_proj.weight, residual=residual), None
 
 
@@ -367,14 +391,16 @@ class HCAHybridLayer(nn.Module):
     def fused_weight(self):
         return self._fused.get(self.W_KV.weight, self.W_Z.weight, self.W_DQ.weight)
 
-    def core(self, x, *, return_projections=False):
+    def core(self, x, *, return_projections=False, q_rows=None):
         cfg = self.cfg
         return naive_hca(x, self.W_KV.weight, self.W_Z.weight, self.B_pos, self.W_DQ.weight, self.W_UQ.weight,
                          m2=cfg.hca_m2, nh=cfg.hca_nh, c=cfg.hca_c, dc=cfg.hca_dc,
                          sliding_window=cfg.hca_sliding_window, sink_logits=self.sink,
-                         return_projections=return_projections, _fused_weight=self.fused_weight())
+                         return_projections=return_projections, _fused_weight=self.fused_weight(), _q_rows=q_rows)
 
     def forward(self, x, state=None, residual=None):
+        if _rows_mode(self.tp):
+            return _forward_by_rows(self, x, residual), None
         return out_projection(self.core(x), self.tp, self.o_proj.weight, residual=residual), None
 
 
@@ -611,8 +637,27 @@ class HybridDecoding(nn.Module):
         return attend(q, comp_n, nh=nh, c=c, sel=None, m=m2, t0=t0, q_normalize=True, win=local, sliding_window=win,
                       sink=layer.sink, scale=1.0, out_dtype=h.dtype, win_t0=P)
 
+    def _local_rows(self, layer, h):
+        """Rows mode of the head-sharded stack: this rank's sequences of the batch (the caches of a CSA / HCA layer
+        then hold those sequences only)."""
+        if not _rows_mode(layer.tp):
+            return h
+        B = h.shape[0]
+        if B % layer.tp.world != 0:
+            raise ValueError(f"decode with CSA / HCA sharded by rows needs the batch ({B}) to divide over "
+                             f"{layer.tp.world} ranks: a sequence's cache lives on one rank")
+        per = B // layer.tp.world
+        return h[layer.tp.rank * per:(layer.tp.rank + 1) * per]
+
+    def _project_out(self, layer, o_core, residual, B, T):
+        if _rows_mode(layer.tp):
+            return out_projection_rows(o_core, layer.tp, layer.o_proj.weight, residual, lead=(B, T))
+        return out_projection(o_core, layer.tp, layer.o_proj.weight, residual=residual)
+
     def _csa(self, i, layer, h, residual):
         cfg = self.cfg
+        B_all = h.shape[0]
+        h = self._local_rows(layer, h)
         B, T, _ = h.shape
         cache = self._cache(i, layer, h)
         if T > 1 and cache.n_tokens_seen > 0:
@@ -641,10 +686,12 @@ class HybridDecoding(nn.Module):
                                        topk=cfg.csa_topk, nh=nh, nIh=nIh, scale=1.0, sink_logits=layer.sink,
                                        use_ste=False, normalize_qk=True)
                 o_core = o.reshape(B, 1, nh * c).to(h.dtype)
-        return out_projection(o_core, layer.tp, layer.o_proj.weight, residual=residual)
+        return self._project_out(layer, o_core, residual, B_all, T)
 
     def _hca(self, i, layer, h, residual):
         cfg = self.cfg
+        B_all = h.shape[0]
+        h = self._local_rows(layer, h)
         B, T, _ = h.shape
         cache = self._cache(i, layer, h)
         if T > 1 and cache.n_tokens_seen > 0:
@@ -666,7 +713,7 @@ class HybridDecoding(nn.Module):
                 qn = rownorm(q.view(B, 1, nh, c), True)
                 o = cache.forward_step(qn, nh=nh, scale=1.0, sink_logits=layer.sink)
                 o_core = o.reshape(B, 1, nh * c).to(h.dtype)
-        return out_projection(o_core, layer.tp, layer.o_proj.weight, residual=residual)
+        return self._project_out(layer, o_core, residual, B_all, T)
 
     # ---- CUDA-graph replay of one-token steps ------------------------------------------------------------------
     def _graph_signature(self, x):
@@ -689,7 +736,8 @@ class HybridDecoding(nn.Module):
                 continue
             cache = self._caches.get(i)
             nh = cfg.csa_nh if kind == "csa" else cfg.hca_nh
-            if cache is None or cache.B != x.shape[0] or cache._comp is None or not cache._decode_attend_ok(nh):
+            b_local = x.shape[0] // layer.tp.world if _rows_mode(layer.tp) else x.shape[0]
+            if cache is None or cache.B != b_local or cache._comp is None or not cache._decode_attend_ok(nh):
                 return None
             if kind == "csa" and (cfg.csa_nIh > 64 or cfg.csa_nIh * cfg.csa_cI > 1024 or cfg.csa_topk < 1):
                 return None

@@ -14,9 +14,11 @@ from .csa import attend, csa_compress_kv, fuse_rows, linear, mma_attention_eligi
 
 def naive_hca(H, W_KV, W_Z, B_pos, W_DQ, W_UQ, *, m2: int, nh: int, c: int, dc: int, scale: float = 1.0,
               sliding_window: int = 0, sink_logits=None, return_projections: bool = False, W_KV_local=None,
-              _fused_weight=None):
+              _fused_weight=None, _q_rows=None):
     """``[B,T,d] -> [B,T,nh*c]`` in ``H.dtype``.  ``_fused_weight`` (optional) is ``[W_KV;W_Z;W_DQ]``
-    (plus ``W_KV_local`` when used) concatenated once by the layer object."""
+    (plus ``W_KV_local`` when used) concatenated once by the layer object.  ``_q_rows = (lo, hi)`` (sharding by
+    query rows): only the queries ``lo..hi-1`` are attended, against the keys of tokens ``0..hi-1``; returns
+    ``[B, hi-lo, nh*c]``."""
     B_, T, d = H.shape
     if m2 < 1:
         raise ValueError(f"heavy compression factor m2={m2} must be >= 1")
@@ -52,6 +54,14 @@ def naive_hca(H, W_KV, W_Z, B_pos, W_DQ, W_UQ, *, m2: int, nh: int, c: int, dc: 
             return out_empty, (torch.zeros(B_, 0, c, dtype=H.dtype, device=device),
                                torch.zeros(B_, 0, c, dtype=H.dtype, device=device))
         return out_empty
+    q_lo = 0
+    if _q_rows is not None:
+        q_lo, q_hi = int(_q_rows[0]), int(_q_rows[1])
+        if not 0 <= q_lo < q_hi <= T:
+            raise ValueError(f"naive_hca: _q_rows={_q_rows} must satisfy 0 <= lo < hi <= T={T}")
+        if return_projections:
+            raise ValueError("naive_hca: _q_rows and return_projections cannot be combined")
+        H, T = H[:, :q_hi], q_hi
     original_T = T
     pad = (-T) % m2
     if pad:
@@ -69,11 +79,11 @@ def naive_hca(H, W_KV, W_Z, B_pos, W_DQ, W_UQ, *, m2: int, nh: int, c: int, dc: 
     C_comp = csa_compress_kv(C, Z, B_pos, m2)
     kdt = torch.bfloat16 if mma_attention_eligible(H.dtype, c, nh, True, scale) else torch.float32
     C_comp_n = rownorm(C_comp, True, kdt)
-    q = linear(cQ, W_UQ)
+    q = linear(cQ[:, q_lo:] if q_lo else cQ, W_UQ)
     local = rownorm(C_loc, True, kdt) if sliding_window > 0 else None
-    out = attend(q, C_comp_n, nh=nh, c=c, sel=None, m=m2, q_normalize=True, win=local,
-                 sliding_window=sliding_window, sink=sink_logits, scale=scale, out_dtype=H.dtype)
-    out_final = out[:, :original_T]
+    out = attend(q, C_comp_n, nh=nh, c=c, sel=None, m=m2, t0=q_lo, q_normalize=True, win=local,
+                 sliding_window=sliding_window, sink=sink_logits, scale=scale, out_dtype=H.dtype, win_t0=q_lo)
+    out_final = out[:, :original_T - q_lo]
     if return_projections:
         return out_final, (C[:, :original_T], Z[:, :original_T])
     return out_final

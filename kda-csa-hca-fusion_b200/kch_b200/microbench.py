@@ -60,6 +60,7 @@ def main():
     ap.add_argument("--topk", type=int, default=1024)
     ap.add_argument("--iters", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=2)
+    ap.add_argument("--fp32-queries", action="store_true", help="indexer: fp32 queries (the mma.sync logits kernel)")
     ap.add_argument("--gate-scale", type=float, default=0.1, help="kda: multiplies the synthetic log-decay")
     ap.add_argument("--kv-quant", default=None, choices=[None, "fp8", "int8"])
     ap.add_argument("--graph", action="store_true", help="decode: replay the step from a CUDA graph")
@@ -118,6 +119,8 @@ def main():
         HI, DI, m = 4, 64, 4
         n = a.T // m
         qi = torch.randn(a.B, a.T, HI, DI, generator=g).to(dev)
+        if not a.fp32_queries:      # as in the layer: bf16 query rows, scored by the tcgen05 logits kernel
+            qi = qi.bfloat16()
         ki = torch.randn(a.B, n, DI, generator=g).to(dev)
         wi = (torch.randn(a.B, a.T, HI, generator=g) * 0.1).to(dev)
         ms = _time(lambda: csa.indexer_topk(qi, ki, wi, a.topk, m=m, normalize_qk=True, sorted_output=False),

@@ -21,16 +21,24 @@ class TPContext:
     rank: int
     world: int
     group: object = None
+    # how the CSA / HCA layers are divided.  "heads": query heads, like KDA (every rank scores and attends for all
+    # queries with its share of the heads).  "rows": the flattened query rows [B*T] in equal contiguous runs (whole
+    # sequences while world <= B, else a slice of one sequence): the indexer, the top-k and the gather of selected
+    # rows cost the same whatever the head count, so only this axis divides them.  One all-gather per layer either way.
+    attn_shard: str = "heads"
 
 
-def local_config(cfg, world):
-    """The per-rank geometry: head counts divided by the world size."""
-    for name in ("n_heads_qk", "n_heads_v", "csa_nh", "hca_nh"):
+def local_config(cfg, world, attn_shard="heads"):
+    """The per-rank geometry: head counts divided by the world size (CSA / HCA heads only when they are the
+    sharded axis of those layers)."""
+    names = ("n_heads_qk", "n_heads_v") + (("csa_nh", "hca_nh") if attn_shard == "heads" else ())
+    for name in names:
         if getattr(cfg, name) % world != 0:
             raise ValueError(f"tensor parallelism: {name}={getattr(cfg, name)} must be divisible by the "
                              f"world size {world}")
+    div = world if attn_shard == "heads" else 1
     return dataclasses.replace(cfg, n_heads_qk=cfg.n_heads_qk // world, n_heads_v=cfg.n_heads_v // world,
-                               csa_nh=cfg.csa_nh // world, hca_nh=cfg.hca_nh // world)
+                               csa_nh=cfg.csa_nh // div, hca_nh=cfg.hca_nh // div)
 
 
 def _rows(w, rank, world):
@@ -38,12 +46,13 @@ def _rows(w, rank, world):
     return w[rank * n:(rank + 1) * n].clone()
 
 
-def shard_state_dict(params, layout, rank, world):
+def shard_state_dict(params, layout, rank, world, attn_shard="heads"):
     """Slice a full ``state_dict`` for one rank.  Head-major row blocks of the per-head projections are
     cut; everything else (including every ``o_proj``) is kept whole."""
     out = {}
+    attn = ("W_UQ.weight", "sink") if attn_shard == "heads" else ()
     per_head = {"kda": ("q_proj.weight", "k_proj.weight", "v_proj.weight", "g_up.weight", "beta.weight"),
-                "csa": ("W_UQ.weight", "sink"), "hca": ("W_UQ.weight", "sink")}
+                "csa": attn, "hca": attn}
     for key, val in params.items():
         parts = key.split(".")
         if parts[0] == "layers":
@@ -66,6 +75,29 @@ def gather_heads(o_local, ctx: TPContext):
     buf = torch.empty(ctx.world * rows, kl, dtype=flat.dtype, device=flat.device)    # rank-major concatenation
     dist.all_gather_into_tensor(buf, flat, group=ctx.group)
     return buf.view(ctx.world, rows, kl).permute(1, 0, 2).reshape(*lead, ctx.world * kl)
+
+
+def row_span(n_rows, ctx: TPContext):
+    """``(first row, row count)`` of this rank's contiguous run of ``n_rows`` flattened query rows."""
+    if n_rows % ctx.world != 0:
+        raise ValueError(f"tensor parallelism by rows: {n_rows} query rows do not divide over {ctx.world} ranks")
+    per = n_rows // ctx.world
+    return ctx.rank * per, per
+
+
+def gather_rows(o_rows, ctx: TPContext, lead=None):
+    """All-gather of per-rank row runs ``[rows / world, width]`` along the row axis: rank order is row order, so the
+    result is the plain ``[rows, width]`` matrix (viewed as ``[*lead, width]`` when ``lead`` is given)."""
+    flat = o_rows.reshape(-1, o_rows.shape[-1]).contiguous()
+    buf = torch.empty(ctx.world * flat.shape[0], flat.shape[1], dtype=flat.dtype, device=flat.device)
+    dist.all_gather_into_tensor(buf, flat, group=ctx.group)
+    return buf if lead is None else buf.view(*lead, flat.shape[1])
+
+
+def out_projection_rows(o_rows, ctx: TPContext, W, residual=None, lead=None):
+    """``o_proj`` of a layer whose QUERY ROWS are sharded: ``gather_rows``, then ``F.linear`` (+ residual)."""
+    from .csa import linear
+    return linear(gather_rows(o_rows, ctx, lead), W, residual=residual)
 
 
 def out_projection(o_local, ctx: TPContext, W, residual=None):
@@ -96,13 +128,15 @@ def build_tp_model(cfg, params, total_layers, ctx: TPContext, device, dtype):
 
     from .fused import HybridKCHAttention
 
-    lcfg = local_config(cfg, ctx.world)
+    if ctx.attn_shard not in ("heads", "rows"):
+        raise ValueError(f"TPContext.attn_shard={ctx.attn_shard!r} must be 'heads' or 'rows'")
+    lcfg = local_config(cfg, ctx.world, ctx.attn_shard)
     model = HybridKCHAttention(lcfg, total_layers)
     for layer, kind in zip(model.layers, model.layout):
         full_in = {"kda": cfg.n_heads_v * cfg.head_dim_v, "csa": cfg.csa_nh * cfg.csa_c,
                    "hca": cfg.hca_nh * cfg.hca_c}[kind]
         layer.o_proj = nn.Linear(full_in, cfg.d_model, bias=False)
         layer.tp = ctx
-    local = shard_state_dict(params, model.layout, ctx.rank, ctx.world)
+    local = shard_state_dict(params, model.layout, ctx.rank, ctx.world, ctx.attn_shard)
     model.load_state_dict(local, strict=True)
     return model.to(dtype).to(device).eval()

@@ -222,8 +222,9 @@ def test_csa(kch, golden, name):
     W = [w[n] for n in syn.CSA_WEIGHT_ORDER]
     kw = _csa_kwargs(c, sink)
     dkw = dict(kw, sink_logits=None if kw["sink_logits"] is None else sink.to(DEV))
+    aux_k = {}
     out, proj, idx = kch.naive_csa(H.to(DEV), *[x.to(DEV) for x in W], use_ste=False, return_projections=True,
-                                   _return_indices=True, **dkw)
+                                   _return_indices=True, _aux=aux_k, **dkw)
     assert out.dtype == c["dtype"] and out.shape == (c["B"], c["T"], c["nh"] * c["c"])
     T, m = c["T"], c["m"]
     nb = (T + m - 1) // m
@@ -231,13 +232,28 @@ def test_csa(kch, golden, name):
     # stage 1: projections (bf16 GEMM: at most 1 ulp apart from the CPU GEMM)
     for mine, key in zip(proj, ("Ca", "Cb", "Za", "Zb", "K_idx", "Z_idx")):
         assert md(mine, aux[key]) <= (1e-5 if c["dtype"] == torch.float32 else 2e-2)
-    # stage 2: top-k on the kernel's own logits path vs the oracle: compare selected-logit multisets
-    _, lg = orc.lightning_indexer(aux["q_idx"][:, :T], aux["K_IComp"][:, :nb], aux["w_idx"][:, :T], c["topk"], m=m,
-                                  normalize_qk=c["normalize_qk"], return_logits=True)
+    # stage 2: top-k.  fp32: the kernel's picks against the oracle's own pipeline (identical inputs up to fp32
+    # round-off).  bf16: the oracle's projections differ from the kernel's by single bf16 roundings, so the selection
+    # is checked on exactly the tensors the indexer kernels read: index sets equal wherever the boundary gap exceeds
+    # 1e-6 relative, selected-logit multisets equal everywhere.
     idx = idx.cpu().long()
-    assert ((idx >= 0).sum(-1) == (aux["indices"][:, :T] >= 0).sum(-1)).all()
-    agree = _multiset_equal(lg, idx, aux["indices"][:, :T], rtol=1e-6 if c["dtype"] == torch.float32 else 1e-2)
-    assert agree.float().mean() >= (1.0 if c["dtype"] == torch.float32 else 0.97), agree.float().mean()
+    if c["dtype"] == torch.float32:
+        _, lg = orc.lightning_indexer(aux["q_idx"][:, :T], aux["K_IComp"][:, :nb], aux["w_idx"][:, :T], c["topk"], m=m,
+                                      normalize_qk=c["normalize_qk"], return_logits=True)
+        ref_idx = aux["indices"][:, :T]
+    else:
+        ref_idx, lg = orc.lightning_indexer(aux_k["q_idx"][:, :T].float().cpu(), aux_k["K_IComp"][:, :nb].float().cpu(),
+                                            aux_k["w_idx"][:, :T].float().cpu(), c["topk"], m=m,
+                                            normalize_qk=c["normalize_qk"], return_logits=True)
+    assert ((idx >= 0).sum(-1) == (ref_idx >= 0).sum(-1)).all()
+    agree = _multiset_equal(lg, idx, ref_idx, rtol=1e-6)
+    assert bool(agree.all()), float(agree.float().mean())
+    if lg.shape[-1] > c["topk"]:
+        sv = lg.sort(-1, descending=True).values
+        a_, b_ = sv[..., c["topk"] - 1], sv[..., c["topk"]]
+        clear = ((lg > float("-inf")).sum(-1) <= c["topk"]) | ((a_ - b_).abs() > 1e-6 * a_.abs().clamp_min(1e-30))
+        same = (idx.sort(-1).values == ref_idx.sort(-1).values).all(-1)
+        assert bool(same[clear].all()), int((~same[clear]).sum())
     # stage 3: outputs against the oracle evaluated on the kernel's selection
     idx_pad = torch.full((c["B"], aux["indices"].shape[1], c["topk"]), -1, dtype=torch.long)
     idx_pad[:, :T] = idx

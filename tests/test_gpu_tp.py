@@ -15,7 +15,7 @@ CFG = dict(d_model=256, n_heads_qk=4, n_heads_v=4, head_dim_k=128, head_dim_v=12
            hca_nh=4, hca_c=128, hca_dc=64, hca_sliding_window=16)
 
 
-def _worker(rank, world, port, out):
+def _worker(rank, world, port, out, attn):
     for p in (os.path.join(ROOT, "kda-csa-hca-fusion_b200"), ROOT):
         if p not in sys.path:
             sys.path.insert(0, p)
@@ -31,7 +31,7 @@ def _worker(rank, world, port, out):
         cfg = kch_b200.HybridConfig(**CFG)
         params = syn.hybrid_params(9, cfg, 5, dtype=torch.bfloat16, random_sink=True)
         x = syn.hidden_states(10, 2, 200, cfg.d_model, torch.bfloat16).to(dev)
-        tp = build_tp_model(cfg, params, 5, TPContext(rank, world, None), dev, torch.bfloat16)
+        tp = build_tp_model(cfg, params, 5, TPContext(rank, world, None, attn), dev, torch.bfloat16)
         y_tp = tp(x)
         full = kch_b200.HybridKCHAttention(cfg, 5)
         full.load_state_dict(params, strict=True)
@@ -40,21 +40,48 @@ def _worker(rank, world, port, out):
         # top-k = all blocks here, so sharding cannot change the selection; only bf16 rounding order differs
         d = (y_tp.float() - y.float()).abs()
         st = (tp._kda_state - full._kda_state[:, :, rank * 2:(rank + 1) * 2]).abs().max()
+        # one-token steps through the caches: the head-sharded stack replays its step (all-gathers included) from a
+        # CUDA graph and must follow the single-GPU decode
+        full.reset_state()
+        tp.reset_state()
+        dec_full = kch_b200.HybridDecoding(model=full, use_cuda_graph=False)
+        dec_tp = kch_b200.HybridDecoding(model=tp, use_cuda_graph=True)
+        ya, yb = [dec_full(x[:, :150])], [dec_tp(x[:, :150])]
+        for t in range(150, 170):
+            ya.append(dec_full(x[:, t:t + 1]))
+            yb.append(dec_tp(x[:, t:t + 1]))
+        dd = (torch.cat(ya, 1).float() - torch.cat(yb, 1).float()).abs()
+        graph_used = dec_tp._graph is not None
         torch.cuda.synchronize()
-        out[rank] = (float(d.max()), float(d.mean()), float(st), int(_lib.device_status()))
-    finally:
-        dist.destroy_process_group()
+        out[rank] = (float(d.max()), float(d.mean()), float(st), int(_lib.device_status()), float(dd.max()),
+                     float(dd.mean()), graph_used)
+        # a process group whose collectives were captured into a CUDA graph does not come down cleanly on this stack
+        # (destroy_process_group() never returns): drop the graph, meet the other rank, and leave without it
+        dec_tp.reset()
+        del dec_tp
+        torch.cuda.synchronize()
+        dist.barrier()
+        torch.cuda.synchronize()
+        os._exit(0)
+    except BaseException:
+        import traceback
+        traceback.print_exc()
+        os._exit(1)
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs at least 2 GPUs")
-def test_tp2_matches_single_gpu():
+@pytest.mark.parametrize("attn", ["heads", "rows"])
+def test_tp2_matches_single_gpu(attn):
+    """KDA by heads; CSA / HCA by heads or by query rows (2 sequences over 2 ranks: whole sequences per rank)."""
     world = 2
     port = 29700 + (os.getpid() % 1000)
     mgr = mp.Manager()
     out = mgr.dict()
-    mp.spawn(_worker, args=(world, port, out), nprocs=world, join=True)
+    mp.spawn(_worker, args=(world, port, out, attn), nprocs=world, join=True)
     for rank in range(world):
-        dmax, dmean, st, status = out[rank]
+        dmax, dmean, st, status, ddmax, ddmean, graph_used = out[rank]
         assert status == 0
+        assert graph_used, "the head-sharded decode step was not replayed from a CUDA graph"
+        assert ddmax <= 6.3e-2 and ddmean <= 2e-3, (rank, ddmax, ddmean)
         assert dmax <= 6.3e-2 and dmean <= 2e-3, (rank, dmax, dmean)      # bf16 residual stream, |x| ~ 4
         assert st <= 1e-3, (rank, st)

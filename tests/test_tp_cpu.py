@@ -72,6 +72,38 @@ def _worker(rank, world, port, out):
                                    m2=cfg.hca_m2, nh=nh, c=cfg.hca_c, dc=cfg.hca_dc,
                                    sliding_window=cfg.hca_sliding_window, sink_logits=p["sink"])
         res["hca"] = float((gather_heads(hca(pl, lcfg.hca_nh), ctx) - hca(pf, cfg.hca_nh)).abs().max())
+        # --- rows mode of CSA / HCA: this rank's contiguous run of the flattened [B*T] query rows, gathered along rows
+        from kch_b200.tp import gather_rows, row_span
+        rctx = TPContext(rank, world, None, attn_shard="rows")
+        rl = shard_state_dict(params, layout, rank, world, "rows")
+        res["rows_w_uq_full"] = tuple(rl["layers.3.W_UQ.weight"].shape) == tuple(params["layers.3.W_UQ.weight"].shape) \
+            and local_config(cfg, world, "rows").csa_nh == cfg.csa_nh and local_config(cfg, world, "rows").n_heads_v * world == cfg.n_heads_v
+        pf3 = {k[len("layers.3."):]: v for k, v in params.items() if k.startswith("layers.3.")}
+        pf4 = {k[len("layers.4."):]: v for k, v in params.items() if k.startswith("layers.4.")}
+        for name, xb in (("whole", x), ("slice", x[:1])):          # 2 sequences over 2 ranks; 1 sequence cut in two
+            Bx, Tx = xb.shape[0], xb.shape[1]
+            r0, per = row_span(Bx * Tx, rctx)
+            if per % Tx == 0:
+                xs, rows = xb[r0 // Tx:r0 // Tx + per // Tx], None
+            else:
+                xs, rows = xb[r0 // Tx:r0 // Tx + 1], [(r0 % Tx, r0 % Tx + per)]
+            def csa_rows(p, xi, qr):
+                y = orc.csa_forward(xi, p["W_aKV.weight"], p["W_bKV.weight"], p["W_aZ.weight"], p["W_bZ.weight"], p["Ba"],
+                                    p["Bb"], p["W_DQ.weight"], p["W_UQ.weight"], p["W_IUQ.weight"], p["W_w.weight"],
+                                    p["W_KV_idx.weight"], p["W_Z_idx.weight"], p["B_idx"], m=cfg.csa_m, topk=cfg.csa_topk,
+                                    nh=cfg.csa_nh, nIh=cfg.csa_nIh, c=cfg.csa_c, c_I=cfg.csa_cI, dc=cfg.csa_dc,
+                                    sliding_window=cfg.csa_sliding_window, sink_logits=p["sink"], normalize_qk=True,
+                                    query_rows=qr)
+                return y if qr is None else y[:, qr[0][0]:qr[0][1]]
+            def hca_rows(p, xi, qr):
+                y = orc.hca_forward(xi, p["W_KV.weight"], p["W_Z.weight"], p["B_pos"], p["W_DQ.weight"], p["W_UQ.weight"],
+                                    m2=cfg.hca_m2, nh=cfg.hca_nh, c=cfg.hca_c, dc=cfg.hca_dc,
+                                    sliding_window=cfg.hca_sliding_window, sink_logits=p["sink"], query_rows=qr)
+                return y if qr is None else y[:, qr[0][0]:qr[0][1]]
+            g3 = gather_rows(csa_rows(pf3, xs, rows), rctx, lead=(Bx, Tx))
+            g4 = gather_rows(hca_rows(pf4, xs, rows), rctx, lead=(Bx, Tx))
+            res[f"rows_csa_{name}"] = float((g3 - csa_rows(pf3, xb, None)).abs().max())
+            res[f"rows_hca_{name}"] = float((g4 - hca_rows(pf4, xb, None)).abs().max())
         # o_proj and the norms are replicated, per-head weights are halved
         res["o_proj_full"] = tuple(local["layers.0.o_proj.weight"].shape) == tuple(params["layers.0.o_proj.weight"].shape)
         res["q_rows"] = local["layers.0.q_proj.weight"].shape[0] * world == params["layers.0.q_proj.weight"].shape[0]
@@ -90,7 +122,9 @@ def test_head_sharding_and_gather_world2():
     for rank in range(world):
         r = out[rank]
         assert r["kda"] <= 1e-5 and r["csa"] <= 1e-5 and r["hca"] <= 1e-5, r
-        assert r["o_proj_full"] and r["q_rows"]
+        assert r["o_proj_full"] and r["q_rows"] and r["rows_w_uq_full"]
+        for name in ("whole", "slice"):
+            assert r[f"rows_csa_{name}"] <= 1e-6 and r[f"rows_hca_{name}"] <= 1e-6, r
 
 
 def test_local_config_rejects_indivisible_heads():
