@@ -607,22 +607,6 @@ topk_select_kernel(const float* __restrict__ logits, int32_t* __restrict__ out, 
   for (int i = tid; i < nsel; i += NT) orow[i] = 0x7FFFFFFF - (int)(uint32_t)(ssort[i] & 0xFFFFFFFFu);
 }
 
-// Histogram increment of one radix pass.  The two leading bytes of the order-preserving key (sign, exponent, top of
-// the mantissa) take only a handful of values in a row of logits, so plain shared-memory atomics would serialise on
-// a few addresses: the lanes of a warp that hit the same bin are found with match.any and their leader adds the
-// whole group.  The lower bytes are spread evenly and keep the plain atomic.
-__device__ __forceinline__ void hist_add(int* hist, bool act, uint32_t bin, bool aggregate) {
-  if (aggregate) {
-    const unsigned am = __ballot_sync(0xffffffffu, act);
-    if (act) {
-      const unsigned peers = __match_any_sync(am, bin);
-      if ((threadIdx.x & 31) == (unsigned)(__ffs(peers) - 1)) atomicAdd(&hist[bin], __popc(peers));
-    }
-  } else if (act) {
-    atomicAdd(&hist[bin], 1);
-  }
-}
-
 // Radix select of one row with SLOTS keys per thread in registers (E <= SLOTS elements owned by each thread).
 template <int EPT>
 __device__ __forceinline__ void select_row_regs(const float* __restrict__ lg, int32_t* __restrict__ orow, int nv, int ksel,
@@ -648,7 +632,7 @@ __device__ __forceinline__ void select_row_regs(const float* __restrict__ lg, in
       __syncthreads();
 #pragma unroll
       for (int k = 0; k < EPT; ++k)
-        hist_add(hist, k < cnt_mine && (u[k] & pmask) == prefix, (u[k] >> shift) & 255, pass < 2);
+        if (k < cnt_mine && (u[k] & pmask) == prefix) atomicAdd(&hist[(u[k] >> shift) & 255], 1);
       __syncthreads();
       const int bin = 255 - tid;
       const int cnt = hist[bin];
@@ -743,7 +727,8 @@ topk_select_reg_kernel(const float* __restrict__ logits, int32_t* __restrict__ o
 }
 
 // Long rows of a decode step (one query per sequence over tens of thousands of cached blocks): a thread-block
-// cluster of SC_CTAS CTAs per row instead of one CTA.  CTA r owns the contiguous index range
+// cluster of SC_CTAS CTAs per row instead of one CTA.  (Shared-memory atomics on a few hot bins are not the cost of
+// these passes: aggregating the increments of a warp with match.any first made the select 10 - 25 % slower.)  CTA r owns the contiguous index range
 // [r * seg, (r + 1) * seg) with its keys in registers (as topk_select_reg_kernel); each radix pass builds a
 // 256-bin histogram per CTA, and every CTA sums the SC_CTAS histograms through distributed shared memory, so all
 // of them agree on the threshold without a broadcast.  The histogram is double-buffered: one cluster barrier per
@@ -807,7 +792,7 @@ topk_select_cluster_kernel(const float* __restrict__ logits, int32_t* __restrict
     __syncthreads();
 #pragma unroll
     for (int k = 0; k < EPT; ++k)
-      hist_add(h, k < cnt_mine && (u[k] & pmask) == prefix, (u[k] >> shift) & 255, pass < 2);
+      if (k < cnt_mine && (u[k] & pmask) == prefix) atomicAdd(&h[(u[k] >> shift) & 255], 1);
     sc_cluster_sync();                                    // every CTA's histogram of this pass is complete
     const int bin = 255 - tid;
     int cnt = 0;
@@ -1182,10 +1167,9 @@ decode_indexer_logits_mma_kernel(const void* __restrict__ q, int q_dtype, int64_
   const float* nb = norms + (int64_t)b * cap;
   float* lg = logits + (int64_t)b * n_ld;
   const int wr0 = r0 + warp * (DIX_ROWS / 8);                 // 128 rows per warp, 8 groups of 16
-#pragma unroll 1
-  for (int gi = 0; gi < 8; gi += 2) {
-    uint4 raw[2][4];                                           // [group][row g chunk 0/1, row g+8 chunk 0/1]
-    float nv[2][2];
+  // two groups of 16 rows per step; the loads of the next step are issued before the products of the current one
+  // (register double buffer), so a warp keeps 256 bytes per lane in flight instead of 128
+  auto load_step = [&](int gi, uint4 (&raw)[2][4], float (&nv)[2][2]) {   // [group][row g chunk 0/1, row g+8 chunk 0/1]
 #pragma unroll
     for (int u = 0; u < 2; ++u) {
       const int rg = wr0 + (gi + u) * 16;
@@ -1202,6 +1186,8 @@ decode_indexer_logits_mma_kernel(const void* __restrict__ q, int q_dtype, int64_
         }
       }
     }
+  };
+  auto score_step = [&](int gi, const uint4 (&raw)[2][4], const float (&nv)[2][2]) {
 #pragma unroll
     for (int u = 0; u < 2; ++u) {
       const int rg = wr0 + (gi + u) * 16;
@@ -1226,7 +1212,17 @@ decode_indexer_logits_mma_kernel(const void* __restrict__ q, int q_dtype, int64_
         if (rg + g + 8 < nvis) lg[rg + g + 8] = o1;
       }
     }
-  }
+  };
+  uint4 rawA[2][4], rawB[2][4];
+  float nvA[2][2], nvB[2][2];
+  load_step(0, rawA, nvA);
+  load_step(2, rawB, nvB);
+  score_step(0, rawA, nvA);
+  load_step(4, rawA, nvA);
+  score_step(2, rawB, nvB);
+  load_step(6, rawB, nvB);
+  score_step(4, rawA, nvA);
+  score_step(6, rawB, nvB);
 }
 
 extern "C" int64_t kch_decode_indexer_workspace_bytes(int B, int64_t capacity) {

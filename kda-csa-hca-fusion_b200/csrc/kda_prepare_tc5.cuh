@@ -62,16 +62,28 @@ kda_prepare_tc5_kernel(PrepArgs a, const __grid_constant__ CUtensorMap vmap, uns
   const int rg = tid >> 4, c8 = tid & 15;
   const int64_t tok0 = (int64_t)b * a.T + t0 + 4 * rg;
 
-  // ---- log-decay of this thread's 4 x 8 block: activation, clamp, running sum (log2 units) -------------------
+  // ---- all twelve 16-byte loads of this thread's 4 x 8 block (g, k, q) are issued before anything waits on them ---
+  uint4 graw[4], kreg[4], qreg[4];
+#pragma unroll
+  for (int s = 0; s < 4; ++s) {
+    graw[s] = make_uint4(0u, 0u, 0u, 0u);
+    kreg[s] = make_uint4(0u, 0u, 0u, 0u);
+    qreg[s] = make_uint4(0u, 0u, 0u, 0u);
+    if (t0 + 4 * rg + s < a.T) {
+      graw[s] = *reinterpret_cast<const uint4*>(a.g + (tok0 + s) * a.ld_g + (int64_t)hv * KM_K + 8 * c8);
+      const int64_t off = (tok0 + s) * a.ld_qk + (int64_t)h * KM_K + 8 * c8;
+      kreg[s] = *reinterpret_cast<const uint4*>(a.k + off);
+      qreg[s] = *reinterpret_cast<const uint4*>(a.q + off);
+    }
+  }
+  // ---- log-decay: activation, clamp, running sum (log2 units) -------------------------------------------------
   float gam[4][8];
   {
     float run[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
 #pragma unroll
     for (int s = 0; s < 4; ++s) {
       const bool ok = t0 + 4 * rg + s < a.T;
-      uint4 raw = make_uint4(0u, 0u, 0u, 0u);
-      if (ok) raw = *reinterpret_cast<const uint4*>(a.g + (tok0 + s) * a.ld_g + (int64_t)hv * KM_K + 8 * c8);
-      const bf16* e = reinterpret_cast<const bf16*>(&raw);
+      const bf16* e = reinterpret_cast<const bf16*>(&graw[s]);
 #pragma unroll
       for (int x = 0; x < 8; ++x) {
         float gx = __bfloat162float(e[x]);
@@ -87,18 +99,6 @@ kda_prepare_tc5_kernel(PrepArgs a, const __grid_constant__ CUtensorMap vmap, uns
     float4* dst = reinterpret_cast<float4*>(tot + rg * 128 + 8 * c8);
     dst[0] = make_float4(run[0], run[1], run[2], run[3]);
     dst[1] = make_float4(run[4], run[5], run[6], run[7]);
-  }
-  // k and q rows of the same block: in flight while the group sums are combined
-  uint4 kreg[4], qreg[4];
-#pragma unroll
-  for (int s = 0; s < 4; ++s) {
-    kreg[s] = make_uint4(0u, 0u, 0u, 0u);
-    qreg[s] = make_uint4(0u, 0u, 0u, 0u);
-    if (t0 + 4 * rg + s < a.T) {
-      const int64_t off = (tok0 + s) * a.ld_qk + (int64_t)h * KM_K + 8 * c8;
-      kreg[s] = *reinterpret_cast<const uint4*>(a.k + off);
-      qreg[s] = *reinterpret_cast<const uint4*>(a.q + off);
-    }
   }
   if (tid < KM_C) sbeta[tid] = (t0 + tid < a.T) ? __bfloat162float(a.beta[((int64_t)b * a.T + t0 + tid) * a.ld_b + hv]) : 0.f;
   if (tid == 0) {
