@@ -43,7 +43,10 @@ C4 = dict(d_model=2048, n_heads_qk=16, n_heads_v=16, head_dim_k=128, head_dim_v=
           hca_nh=16, hca_c=128, hca_dc=128, hca_sliding_window=128, n_kda=3, n_csa=1, n_hca=1)
 LAYERS = 5
 SEED = 3
-NCU_GEMM_DRAM_BYTES_M16384 = 101.9e6    # dram__bytes_read.sum + dram__bytes_write.sum, one o_proj-shaped launch
+# dram__bytes_read.sum + dram__bytes_write.sum of one o_proj-shaped launch (M = 131072, N = K = 2048, no residual):
+# 546.1 MB + 512.6 MB from one ncu capture at the full size, where A and C (537 MB each) cannot sit in the 126 MB L2;
+# the algorithmic bytes of that launch, 2 (MK + NK + MN), are 1082 MB
+NCU_GEMM_DRAM_BYTES_M131072 = 1058.7e6
 
 
 def algorithmic_flops_per_token(cfg, T):
@@ -494,6 +497,12 @@ def run_b200(args):
                    "ms_per_step": vms, "value": tokens / (vms / 1e3), "unit": UNIT,
                    "finite": bool(torch.isfinite(yv.float()).all())}
         del xv, yv
+        if not args.no_decode and args.decode_batch % tp == 0:
+            torch.cuda.empty_cache()
+            vd = decode_bench(model, C4, args.decode_batch, args.decode_context, args.decode_steps, 8, dev,
+                              float(peaks.get("hbm_gbs", 6650.0)), world)
+            variant["decode"] = {k: ({kk: vv for kk, vv in v.items() if kk in ("us_per_step", "us_per_token", "finite", "cuda_graph")}
+                                     if isinstance(v, dict) else v) for k, v in vd.items()}
     status = _lib.device_status()
     if rank == 0:
         peak_tf = float(peaks.get("bf16_tflops_sustained", 1400.0))
@@ -516,10 +525,9 @@ def run_b200(args):
             "gpu_launches": launches,
             "roofline": {"bound": "tensor", "kernel": "gemm_tcgen05_kernel (all dense projections)",
                          "achieved": achieved, "peak": peak_tf, "unit": "TFLOP/s", "frac": achieved / peak_tf,
-                         "peak_source": peak_src, "traffic": NCU_GEMM_DRAM_BYTES_M16384 * (B * T / 16384.0),
-                         "traffic_note": "DRAM bytes (read + write) of one N=2048 K=2048 launch: ncu capture at M=16384, "
-                                         "scaled by M to this batch; the algorithmic bytes of that launch are "
-                                         "2(MK + NK + MN)",
+                         "peak_source": peak_src, "traffic": NCU_GEMM_DRAM_BYTES_M131072 * (B * T / 131072.0),
+                         "traffic_note": "DRAM bytes (read + write) of one N=2048 K=2048 launch, ncu capture at M=131072 "
+                                         "(this batch); the algorithmic bytes of that launch, 2(MK + NK + MN), are 1082 MB",
                          "launches": gemm_calls,
                          "flops_per_step": gemm_flops / max(1, args.steps), "ms_per_step": gemm_ms / max(1, args.steps),
                          "shapes": probe.by_shape()},

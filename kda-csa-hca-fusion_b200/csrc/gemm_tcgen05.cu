@@ -160,12 +160,17 @@ __device__ __forceinline__ float ep_silu(float x) { return __fdividef(x, 1.0f + 
 template <int BN>
 struct TgStages { static constexpr int value = BN >= 256 ? 4 : BN >= 128 ? 6 : BN >= 64 ? 8 : 10; };
 
-template <int BN, bool TWO = false>
+// SK ("skinny", a decode batch of at most 64 rows): the A box is 64 rows, so a stage is 8 KB smaller and the ring twice
+// as deep for the narrow tiles -- the launch is a stream of weights and wants bytes in flight.  The MMA still spans 128
+// rows: rows 64..127 of its A operand are whatever follows in shared memory (the next A stage, or the first W stage
+// behind the last one), which only reaches accumulator rows that are never stored.
+template <int BN, bool TWO = false, bool SK = false>
 struct TgSmem {
   // a CTA of a pair holds half of the W tile, which buys two more stages
-  static constexpr int STAGES = TWO ? 6 : TgStages<BN>::value;
+  static constexpr int A_ROWS = SK ? 64 : TG_BM;
+  static constexpr int STAGES = TWO ? 6 : SK ? (BN >= 128 ? 8 : BN >= 64 ? 12 : 16) : TgStages<BN>::value;
   static constexpr int B_ROWS = TWO ? BN / 2 : BN;
-  alignas(1024) bf16 a[STAGES][TG_BM * TG_BK];
+  alignas(1024) bf16 a[STAGES][A_ROWS * TG_BK];
   alignas(1024) bf16 b[STAGES][B_ROWS * TG_BK];
   alignas(16) uint8_t epi[8][32 * TG_EPI_LD];   // per epilogue warp: a 32 x 32 bf16 chunk, rows padded to 80 bytes
   alignas(8) uint64_t full[STAGES];
@@ -175,7 +180,7 @@ struct TgSmem {
   uint32_t tmem_base;
 };
 
-template <int BN, bool TWO>
+template <int BN, bool TWO, bool SK = false>
 __global__ void __launch_bounds__(TG_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                     bf16* __restrict__ C, const bf16* __restrict__ R, int64_t M, int N, int K,
@@ -184,8 +189,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   // rank-major buffer an all-gather of per-GPU column slices leaves behind); map_a then describes all slabs as one
   // [slabs * slab_rows][slab_k] matrix and k-block kb is read from slab kb * 64 / slab_k
   extern __shared__ uint8_t smem_raw[];
-  TgSmem<BN, TWO>& sm = *reinterpret_cast<TgSmem<BN, TWO>*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  constexpr int TG_STAGES = TgSmem<BN, TWO>::STAGES;
+  TgSmem<BN, TWO, SK>& sm = *reinterpret_cast<TgSmem<BN, TWO, SK>*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  constexpr int TG_STAGES = TgSmem<BN, TWO, SK>::STAGES;
+  constexpr int A_ROWS = TgSmem<BN, TWO, SK>::A_ROWS;
   constexpr int BM_T = TWO ? 2 * TG_BM : TG_BM;       // rows of a tile: a CTA pair takes 256, each CTA its 128
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = TWO ? cluster_ctarank() : 0u;
@@ -240,7 +246,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             tma_load_2d_pair(sm.a[s], &map_a, kc, (int)(mb * BM_T + rank * TG_BM + roff), full_addr);
             tma_load_2d_pair(sm.b[s], &map_w, kb * TG_BK, nb * BN + (int)rank * (BN / 2), full_addr);
           } else {
-            mbar_expect_tx(&sm.full[s], (TG_BM + BN) * TG_BK * 2);
+            mbar_expect_tx(&sm.full[s], (A_ROWS + BN) * TG_BK * 2);
             tma_load_2d(sm.a[s], &map_a, kc, (int)(mb * TG_BM + roff), &sm.full[s]);
             tma_load_2d(sm.b[s], &map_w, kb * TG_BK, nb * BN, &sm.full[s]);
           }
@@ -477,10 +483,13 @@ bool kch_linear_tcgen05_supported(const void* A, const void* W, const void* C, c
 
 template <int BN>
 static int launch_tg(const void* A, const void* W, void* C, const void* R, int64_t M, int N, int K, int64_t lda,
-                     int64_t ldw, int64_t ldc, int64_t ldr, const TgEpilogue& ep, cudaStream_t s, int slab_k = 0) {
+                     int64_t ldw, int64_t ldc, int64_t ldr, const TgEpilogue& ep, cudaStream_t s, int slab_k = 0,
+                     bool skinny = false) {
   CUtensorMap ma, mw;
-  int rc = slab_k > 0 ? make_map_2d(&ma, A, (uint64_t)M * (uint64_t)(K / slab_k), (uint64_t)slab_k, (uint64_t)slab_k, TG_BM, TG_BK)
-                      : make_map_2d(&ma, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, TG_BM, TG_BK);
+  skinny = skinny && BN <= 128 && M <= 64;
+  const uint32_t a_rows = skinny ? 64 : TG_BM;
+  int rc = slab_k > 0 ? make_map_2d(&ma, A, (uint64_t)M * (uint64_t)(K / slab_k), (uint64_t)slab_k, (uint64_t)slab_k, a_rows, TG_BK)
+                      : make_map_2d(&ma, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, a_rows, TG_BK);
   if (rc) return rc;
   rc = make_map_2d(&mw, W, (uint64_t)N, (uint64_t)K, (uint64_t)ldw, BN, TG_BK);
   if (rc) return rc;
@@ -490,11 +499,21 @@ static int launch_tg(const void* A, const void* W, void* C, const void* R, int64
     KCH_CUDA_OK(cudaGetDevice(&dev));
     KCH_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
   }
-  size_t smem = sizeof(TgSmem<BN>) + 1024;
-  KCH_CUDA_OK(cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   int64_t tiles = ((M + TG_BM - 1) / TG_BM) * ((N + BN - 1) / BN);
   int grid = (int)(tiles < sms ? tiles : sms);
   int vec_ok = (ldc % 8 == 0) && (((uintptr_t)C & 15) == 0) && (!R || ((ldr % 8 == 0) && (((uintptr_t)R & 15) == 0)));
+  if constexpr (BN <= 128) {
+    if (skinny) {
+      size_t smem = sizeof(TgSmem<BN, false, true>) + 1024;
+      KCH_CUDA_OK(cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+      gemm_tcgen05_kernel<BN, false, true><<<grid, TG_THREADS, smem, s>>>(ma, mw, (bf16*)C, (const bf16*)R, M, N, K, ldc, ldr,
+                                                                         vec_ok, ep, slab_k, M);
+      KCH_LAUNCH_OK();
+      return KCH_OK;
+    }
+  }
+  size_t smem = sizeof(TgSmem<BN>) + 1024;
+  KCH_CUDA_OK(cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   gemm_tcgen05_kernel<BN, false><<<grid, TG_THREADS, smem, s>>>(ma, mw, (bf16*)C, (const bf16*)R, M, N, K, ldc, ldr, vec_ok, ep,
                                                                slab_k, M);
   KCH_LAUNCH_OK();
@@ -567,8 +586,10 @@ int kch_linear_tcgen05(const void* A, const void* W, void* C, const void* R, int
     // narrow tiles.  A fused L2-norm needs a whole 128-column head inside the tile.
     bool l2 = false;
     for (int i = 0; i < ep.nseg; ++i) l2 = l2 || ep.seg_act[i] == KCH_ACT_SILU_L2NORM;
-    if (l2) return launch_tg<128>(A, W, C, R, M, N, K, lda, ldw, ldc, ldr, ep, s, slab_k);
-    return launch_tg<32>(A, W, C, R, M, N, K, lda, ldw, ldc, ldr, ep, s, slab_k);
+    // (KCH_GEMM_SKINNY=0 keeps the 128-row A box for a batch of at most 64 rows, for comparison)
+    static const bool sk_on = [] { const char* e = getenv("KCH_GEMM_SKINNY"); return !(e && e[0] == '0'); }();
+    if (l2) return launch_tg<128>(A, W, C, R, M, N, K, lda, ldw, ldc, ldr, ep, s, slab_k, sk_on);
+    return launch_tg<32>(A, W, C, R, M, N, K, lda, ldw, ldc, ldr, ep, s, slab_k, sk_on);
   }
   // large products: 256 x 256 tiles on CTA pairs (KCH_GEMM=1 keeps one CTA per tile, for comparison)
   static const bool pair_on = [] { const char* e = getenv("KCH_GEMM"); return !(e && e[0] == '1'); }();

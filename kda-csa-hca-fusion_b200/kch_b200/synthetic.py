@@ -149,7 +149,8 @@ def fill_decode_state(dec, B, context, extra_tokens, dev, seed):
     for i, layer in enumerate(model.layers):
         if not isinstance(layer, (CSAHybridLayer, HCAHybridLayer)):
             continue
-        cache = dec._cache(i, layer, h)
+        cache = dec._cache(i, layer, dec._local_rows(layer, h))    # rows-sharded layers cache this rank's sequences only
+        B = cache.B
         m = cache.m if isinstance(layer, CSAHybridLayer) else cache.m2
         nb = context // m
         cache.reserve(nb + extra_tokens // m + 2)
@@ -173,6 +174,7 @@ def fill_decode_state(dec, B, context, extra_tokens, dev, seed):
             cache._sw._buf.copy_(w / w.norm(dim=-1, keepdim=True))
             cache._sw._n = context
         cache._sync_counters()
+    B = h.shape[0]
     HV, K, V = cfg.n_heads_v, cfg.head_dim_k, cfg.head_dim_v
     model._kda_state = 0.02 * torch.randn(model.n_kda_layers, B, HV, K, V, device=dev, generator=g)
     for layer in model.layers:
