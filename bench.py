@@ -225,7 +225,7 @@ def decode_state_bytes(cfg, B, context, kv_bytes, world=1):
     return kda + idx + sel + hca + win + weights
 
 
-def decode_bench(model, cfg_dict, B, context, steps, warmup, dev, peak_gbs, world=1):
+def decode_bench(model, cfg_dict, B, context, steps, warmup, dev, peak_gbs, world=1, peer_gather=True):
     """One-token decode steps through `HybridDecoding` at a long context, bf16 and FP8 compressed rows.  With
     `world` > 1 every rank steps its head shard of the same batch (the compressed-KV, indexer and window caches are
     replicated, the KDA states sharded) and the step time is the maximum over the ranks; the roofline fraction is
@@ -235,6 +235,14 @@ def decode_bench(model, cfg_dict, B, context, steps, warmup, dev, peak_gbs, worl
     import kch_b200
     from kch_b200.synthetic import fill_decode_state
     out = {"batch": B, "context": context, "steps": steps, "warmup": warmup, "n_gpus": world}
+    if world > 1:
+        # the per-layer all-gather of a decode step (256 KiB over all ranks) by plain peer stores where the
+        # symmetric-memory allocator is usable, else the NCCL collective
+        from kch_b200.tp import enable_peer_gather
+        ctx = next((l.tp for l in model.layers if getattr(l, "tp", None) is not None), None)
+        if ctx is not None and ctx.peer is None and peer_gather:
+            enable_peer_gather(ctx, B * cfg_dict["d_model"] * 2, dev)
+        out["allgather"] = "peer_store" if (ctx is not None and ctx.peer is not None) else "nccl"
     x = torch.randn(B, 1, cfg_dict["d_model"], device=dev, generator=torch.Generator(device=dev).manual_seed(5)
                     ).to(torch.bfloat16)
     for name, quant, kvb in (("bf16", None, 2), ("fp8", "fp8", 1.0625)):
@@ -467,7 +475,7 @@ def run_b200(args):
         del x, y, pipe
         torch.cuda.empty_cache()
         decode = decode_bench(model, C4, args.decode_batch, args.decode_context, args.decode_steps, 8, dev,
-                              float(peaks.get("hbm_gbs", 6650.0)), world)
+                              float(peaks.get("hbm_gbs", 6650.0)), world, not args.no_peer_gather)
     layout_str = model.layout_str()
     variant = None
     if tp > 1 and dp == 1 and not args.no_variant:
@@ -500,7 +508,7 @@ def run_b200(args):
         if not args.no_decode and args.decode_batch % tp == 0:
             torch.cuda.empty_cache()
             vd = decode_bench(model, C4, args.decode_batch, args.decode_context, args.decode_steps, 8, dev,
-                              float(peaks.get("hbm_gbs", 6650.0)), world)
+                              float(peaks.get("hbm_gbs", 6650.0)), world, not args.no_peer_gather)
             variant["decode"] = {k: ({kk: vv for kk, vv in v.items() if kk in ("us_per_step", "us_per_token", "finite", "cuda_graph")}
                                      if isinstance(v, dict) else v) for k, v in vd.items()}
     status = _lib.device_status()
@@ -568,6 +576,8 @@ def main():
     ap.add_argument("--tp-attn", default="heads", choices=["heads", "rows"],
                     help="N > 1: how the CSA / HCA layers are divided: query heads like KDA (default), or the query rows "
                          "(their indexer, top-k and gathers do not shrink with the head count); KDA is always by heads")
+    ap.add_argument("--no-peer-gather", action="store_true",
+                    help="N > 1: keep the NCCL all-gather in the decode steps (default: plain peer stores when available)")
     ap.add_argument("--no-variant", action="store_true", help="N > 1: skip the extra timing of the other --tp-attn mode")
     ap.add_argument("--decode-batch", type=int, default=64)
     ap.add_argument("--decode-context", type=int, default=131072)

@@ -1124,7 +1124,7 @@ decode_indexer_logits_kernel(const void* __restrict__ q, int q_dtype, int64_t q_
 // fp32-grade.  A key row is 128 bytes: four lanes read it with 16-byte loads (fully coalesced, no shared
 // memory); the contraction index is permuted so that those 8 consecutive elements are the A fragments of two
 // k-steps, and the query fragments are built once with the same permutation.
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 3)      // three CTAs per SM: the key stream wants warps in flight, not registers
 decode_indexer_logits_mma_kernel(const void* __restrict__ q, int q_dtype, int64_t q_ld, const bf16* __restrict__ keys,
                                  const float* __restrict__ norms, const void* __restrict__ w, int w_dtype, int64_t w_ld,
                                  float* __restrict__ logits, int64_t cap, int64_t n_ld, int HI, int normalize,
@@ -1167,9 +1167,10 @@ decode_indexer_logits_mma_kernel(const void* __restrict__ q, int q_dtype, int64_
   const float* nb = norms + (int64_t)b * cap;
   float* lg = logits + (int64_t)b * n_ld;
   const int wr0 = r0 + warp * (DIX_ROWS / 8);                 // 128 rows per warp, 8 groups of 16
-  // two groups of 16 rows per step; the loads of the next step are issued before the products of the current one
-  // (register double buffer), so a warp keeps 256 bytes per lane in flight instead of 128
-  auto load_step = [&](int gi, uint4 (&raw)[2][4], float (&nv)[2][2]) {   // [group][row g chunk 0/1, row g+8 chunk 0/1]
+#pragma unroll 1
+  for (int gi = 0; gi < 8; gi += 2) {
+    uint4 raw[2][4];                                           // [group][row g chunk 0/1, row g+8 chunk 0/1]
+    float nv[2][2];
 #pragma unroll
     for (int u = 0; u < 2; ++u) {
       const int rg = wr0 + (gi + u) * 16;
@@ -1186,8 +1187,6 @@ decode_indexer_logits_mma_kernel(const void* __restrict__ q, int q_dtype, int64_
         }
       }
     }
-  };
-  auto score_step = [&](int gi, const uint4 (&raw)[2][4], const float (&nv)[2][2]) {
 #pragma unroll
     for (int u = 0; u < 2; ++u) {
       const int rg = wr0 + (gi + u) * 16;
@@ -1212,17 +1211,7 @@ decode_indexer_logits_mma_kernel(const void* __restrict__ q, int q_dtype, int64_
         if (rg + g + 8 < nvis) lg[rg + g + 8] = o1;
       }
     }
-  };
-  uint4 rawA[2][4], rawB[2][4];
-  float nvA[2][2], nvB[2][2];
-  load_step(0, rawA, nvA);
-  load_step(2, rawB, nvB);
-  score_step(0, rawA, nvA);
-  load_step(4, rawA, nvA);
-  score_step(2, rawB, nvB);
-  load_step(6, rawB, nvB);
-  score_step(4, rawA, nvA);
-  score_step(6, rawB, nvB);
+  }
 }
 
 extern "C" int64_t kch_decode_indexer_workspace_bytes(int B, int64_t capacity) {

@@ -61,6 +61,7 @@ class AttendDecodeArgs(C.Structure):
 CTR_ACC_LEN, CTR_N_BLOCKS, CTR_RING_N, CTR_HAS_PREV, CTR_TOKENS, CTR_WORDS = 0, 1, 2, 3, 4, 8
 STATUS_CACHE_CAPACITY = 64
 STATUS_SELFTEST_WAIT = 0x5E1F
+STATUS_PEER_GATHER = 0x9A7E
 
 
 # name -> (restype, argtypes); must list every symbol declared in include/kch_b200.h
@@ -75,6 +76,8 @@ PROTOTYPES = {
     "kch_linear": (_i, [_vp, _vp, _vp, _vp, _i64, _i, _i, _i64, _i64, _i64, _i64, _i, _vp]),
     "kch_linear_ex": (_i, [_vp, _vp, _vp, _vp, _i64, _i, _i, _i64, _i64, _i64, _i64, _i, C.POINTER(Epilogue), _vp]),
     "kch_linear_kslabs": (_i, [_vp, _vp, _vp, _vp, _i64, _i, _i, _i, _i64, _i64, _i64, _i, _vp]),
+    "kch_peer_gather_flag_words": (_i64, [_i]),
+    "kch_peer_allgather": (_i, [_vp, _i64, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), _i, _i, _vp]),
     "kch_activation": (_i, [_vp, _vp, _i64, _i, _i, _f, _i, _i, _i64, _i64, _vp]),
     "kch_rownorm": (_i, [_vp, _i64, _vp, _vp, _i64, _i, _i, _i, _vp]),
     "kch_kda_recurrent": (_i, [_vp] * 8 + [_i] * 6 + [_f, _f, _i, _i64, _i64, _i64, _i64, _vp]),

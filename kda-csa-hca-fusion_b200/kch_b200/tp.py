@@ -26,6 +26,64 @@ class TPContext:
     # sequences while world <= B, else a slice of one sequence): the indexer, the top-k and the gather of selected
     # rows cost the same whatever the head count, so only this axis divides them.  One all-gather per layer either way.
     attn_shard: str = "heads"
+    # optional PeerGather: decode-sized all-gathers by plain peer stores instead of the library collective
+    peer: object = None
+
+
+class PeerGather:
+    """Decode-sized all-gather over peer-mapped memory (``kch_peer_allgather``): every rank stores its slab into every
+    peer's gather buffer over NVLink and the ranks meet on flags, in one launch of one CTA -- a fraction of the
+    latency of a library collective for the 256 KiB a decode step gathers per layer.  The buffer and the flags live
+    in one allocation of torch's symmetric-memory allocator (CUDA VMM, mapped on every rank by ``rendezvous``).
+    Calls must be made by all ranks in the same order; the result of ``gather`` is a view of the buffer and stays
+    valid until the next call."""
+
+    def __init__(self, ctx, max_slab_bytes, device):
+        import ctypes
+
+        import torch.distributed._symmetric_memory as symm
+
+        from . import _lib
+        self._lib = _lib
+        lib = _lib.load()
+        self.rank, self.world = ctx.rank, ctx.world
+        self.flag_bytes = 256 * ((4 * int(lib.kch_peer_gather_flag_words(ctx.world)) + 255) // 256)
+        self.max_slab = (int(max_slab_bytes) + 15) // 16 * 16
+        group = ctx.group if ctx.group is not None else dist.group.WORLD
+        self.mem = symm.empty(self.flag_bytes + ctx.world * self.max_slab, dtype=torch.uint8, device=device)
+        self.mem.zero_()
+        self.hdl = symm.rendezvous(self.mem, group)
+        torch.cuda.synchronize(device)
+        dist.barrier(group=ctx.group)                    # every rank's flags are zero before anyone's first store
+        ptrs = [int(p) for p in self.hdl.buffer_ptrs]
+        self._flags = (ctypes.c_void_p * ctx.world)(*ptrs)
+        self._bufs = (ctypes.c_void_p * ctx.world)(*[p + self.flag_bytes for p in ptrs])
+
+    def fits(self, flat):
+        return flat.numel() * flat.element_size() <= self.max_slab and (flat.numel() * flat.element_size()) % 16 == 0
+
+    def gather(self, flat):
+        """``flat [rows, width]`` contiguous on this rank -> ``[world, rows, width]`` (rank-major), a view of the buffer."""
+        _lib = self._lib
+        nbytes = flat.numel() * flat.element_size()
+        with torch.cuda.device(flat.device):
+            _lib.check(_lib.load().kch_peer_allgather(_lib.ptr(flat), nbytes, self._bufs, self._flags, self.rank,
+                                                      self.world, _lib.stream()))
+        out = self.mem[self.flag_bytes:self.flag_bytes + self.world * nbytes].view(flat.dtype)
+        return out.view(self.world, flat.shape[0], flat.shape[1])
+
+
+def enable_peer_gather(ctx, max_slab_bytes, device):
+    """Give ``ctx`` a ``PeerGather`` for slabs of up to ``max_slab_bytes``; returns False (and leaves the library
+    collective in place) when the symmetric-memory allocator is not usable on this system."""
+    try:
+        ctx.peer = PeerGather(ctx, max_slab_bytes, device)
+        return True
+    except Exception as exc:                               # no peer mapping available: keep NCCL
+        import warnings
+        warnings.warn(f"kch_b200: peer-store all-gather unavailable ({exc!r}); using the NCCL all-gather")
+        ctx.peer = None
+        return False
 
 
 def local_config(cfg, world, attn_shard="heads"):
@@ -89,8 +147,11 @@ def gather_rows(o_rows, ctx: TPContext, lead=None):
     """All-gather of per-rank row runs ``[rows / world, width]`` along the row axis: rank order is row order, so the
     result is the plain ``[rows, width]`` matrix (viewed as ``[*lead, width]`` when ``lead`` is given)."""
     flat = o_rows.reshape(-1, o_rows.shape[-1]).contiguous()
-    buf = torch.empty(ctx.world * flat.shape[0], flat.shape[1], dtype=flat.dtype, device=flat.device)
-    dist.all_gather_into_tensor(buf, flat, group=ctx.group)
+    if ctx.peer is not None and ctx.peer.fits(flat):
+        buf = ctx.peer.gather(flat).view(ctx.world * flat.shape[0], flat.shape[1])
+    else:
+        buf = torch.empty(ctx.world * flat.shape[0], flat.shape[1], dtype=flat.dtype, device=flat.device)
+        dist.all_gather_into_tensor(buf, flat, group=ctx.group)
     return buf if lead is None else buf.view(*lead, flat.shape[1])
 
 
@@ -116,9 +177,13 @@ def out_projection(o_local, ctx: TPContext, W, residual=None):
         return linear(gather_heads(o_local, ctx), W, residual=residual)
     flat = o_local.reshape(-1, kl).contiguous()
     rows = flat.shape[0]
-    buf = torch.empty(ctx.world * rows, kl, dtype=flat.dtype, device=flat.device)
-    dist.all_gather_into_tensor(buf, flat, group=ctx.group)
-    y = linear_kslabs(buf.view(ctx.world, rows, kl), W, residual=residual)
+    if ctx.peer is not None and ctx.peer.fits(flat):
+        slabs = ctx.peer.gather(flat)
+    else:
+        buf = torch.empty(ctx.world * rows, kl, dtype=flat.dtype, device=flat.device)
+        dist.all_gather_into_tensor(buf, flat, group=ctx.group)
+        slabs = buf.view(ctx.world, rows, kl)
+    y = linear_kslabs(slabs, W, residual=residual)
     return y.reshape(*lead, W.shape[0])
 
 
