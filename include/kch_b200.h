@@ -75,6 +75,13 @@ int kch_layernorm_short_conv(const void* x, const void* ln_weight, const void* l
 int kch_short_conv_step(const void* x, void* lookback, const void* weight, const void* bias, void* y, int B, int d,
                         int dtype, void* stream);
 
+/* LayerNorm (ops_fused.py:52-60) and that one-token step in one launch, for the decode step of a KDA sub-layer:
+ * x [B,1,d] is the un-normalised residual stream, `lookback` [B,2,d] holds NORMALISED rows and slides in place.
+ * bf16, d % 256 == 0, d <= 2048; same rounding points as kch_layernorm followed by kch_short_conv_step. */
+int kch_layernorm_short_conv_step(const void* x, const void* ln_weight, const void* ln_bias, float eps,
+                                  void* lookback, const void* conv_weight, const void* conv_bias, void* y,
+                                  int B, int d, int dtype, int wdtype, void* stream);
+
 /* F.linear at ops_fused.py:571-581,609,713,739 and ops_csa.py:841-878, ops_hca.py:132-141:
  * C[M,N] = A[M,K] . W[N,K]^T, fp32 accumulation, rounded to `dtype`; if `residual` is given the
  * rounded product is added to it in fp32 and rounded again (x = residual + proj, ops_fused.py:1091).
@@ -272,6 +279,7 @@ int kch_attend(const kch_attend_args* args, void* stream);
 #define KCH_CTR_RING_N 2    /* tokens ever written to the window ring */
 #define KCH_CTR_HAS_PREV 3  /* CSA: a previous block's b-branch is held */
 #define KCH_CTR_TOKENS 4    /* tokens seen */
+#define KCH_CTR_ARRIVALS 5  /* CTAs of a fused append that have finished (kch_cache_append_token_advance) */
 #define KCH_CTR_WORDS 8
 #define KCH_STATUS_CACHE_CAPACITY 64  /* device status: an append found its counters out of range / storage full */
 int kch_cache_advance(int32_t* counters, int m, void* stream);
@@ -307,6 +315,9 @@ typedef struct kch_cache_append_args {
   const int32_t* counters;   /* optional device mirror, see above */
 } kch_cache_append_args;
 int kch_cache_append_token(const kch_cache_append_args* args, void* stream);
+/* The same with kch_cache_advance folded in (needs `counters`): the CTA that finishes last advances the device
+ * counters, one launch instead of two per layer and token. */
+int kch_cache_append_token_advance(const kch_cache_append_args* args, void* stream);
 
 /* Lightning indexer of one decode step over a cache's stored indexer keys
  * (CSADecodingCache.forward_step, ops_decoding_cache.py:903-1000): q_idx [B,HI*DI] rows q_ld apart in

@@ -558,7 +558,11 @@ static bool attend_decode_mma_ok(const kch_attend_decode_args* p) {
 
 extern "C" int kch_attend_decode_splits(int B) {
   if (B < 1) return 1;
-  int s = (8 * 148 + B - 1) / B;      // about eight 128-thread CTAs per SM: the row reads are latency bound
+  static const int forced = [] { const char* e = getenv("KCH_DECODE_SPLITS"); return e ? atoi(e) : 0; }();
+  // One wave of CTAs (three fit on an SM beside their tile rings): each warp then streams a few tiles through its
+  // ring instead of paying the query set-up and a partial-result round trip for a single tile.
+  // (KCH_DECODE_SPLITS=n overrides, for comparison.)
+  int s = forced > 0 ? forced : (3 * 148) / B;
   return s < 1 ? 1 : (s > AD_MAX_SPLITS ? AD_MAX_SPLITS : s);
 }
 

@@ -30,6 +30,8 @@ struct AppendArgs {
   int acc_len, m, c, cI, normalize, overlap;
   const int32_t* counters;                               // device-resident {acc_len, n_blocks, ring_n, has_prev, ...} or null
   unsigned int* status;
+  int advance;                                           // 1: the last CTA to finish advances the device counters
+  int n_ctas;
 };
 
 template <typename T>
@@ -40,6 +42,29 @@ __device__ __forceinline__ float block_sum_128(float v, float* red) {
   if (lane == 0) red[warp] = v;
   __syncthreads();
   return red[0] + red[1] + red[2] + red[3];
+}
+
+// With `advance` set the CTA that finishes last advances the device counters (every CTA read them when it started,
+// so nobody can see the new values too early) -- the separate one-thread kernel of kch_cache_advance folded in.
+__device__ __forceinline__ void cache_append_finish(const AppendArgs& a) {
+  if (!a.advance || !a.counters) return;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int32_t* ctr = const_cast<int32_t*>(a.counters);
+    __threadfence();
+    if (atomicAdd(&ctr[KCH_CTR_ARRIVALS], 1) == a.n_ctas - 1) {
+      ctr[KCH_CTR_ARRIVALS] = 0;
+      int acc = ctr[KCH_CTR_ACC_LEN] + 1;
+      ctr[KCH_CTR_RING_N] += 1;
+      ctr[KCH_CTR_TOKENS] += 1;
+      if (acc >= a.m) {
+        acc = 0;
+        ctr[KCH_CTR_N_BLOCKS] += 1;
+        ctr[KCH_CTR_HAS_PREV] = 1;
+      }
+      ctr[KCH_CTR_ACC_LEN] = acc;
+    }
+  }
 }
 
 template <typename T>
@@ -54,6 +79,7 @@ __global__ void __launch_bounds__(128) cache_append_kernel(AppendArgs a) {
     a.has_prev = a.counters[KCH_CTR_HAS_PREV];
     if (a.acc_len < 0 || a.acc_len >= a.m || (a.acc_len + 1 == a.m && (a.n_blocks >= a.cap || !a.comp))) {
       if (tid == 0) atomicCAS(a.status, 0u, (unsigned)KCH_STATUS_CACHE_CAPACITY);
+      cache_append_finish(a);
       return;
     }
   }
@@ -84,7 +110,7 @@ __global__ void __launch_bounds__(128) cache_append_kernel(AppendArgs a) {
     for (int d = tid; d < c; d += 128)
       stf((T*)a.ring + ((int64_t)b * a.win + a.ring_pos) * c + d, ldf((const T*)a.Ca + b * a.ld_c + d) / nrm);
   }
-  if (slot + 1 < m) return;
+  if (slot + 1 < m) { cache_append_finish(a); return; }
   __syncthreads();  // the accumulator rows written above are read below by other threads? no: same channel
   // 3. the block is complete: compress channel-wise
   const int64_t blk = (int64_t)b * m * c;
@@ -180,9 +206,21 @@ __global__ void __launch_bounds__(128) cache_append_kernel(AppendArgs a) {
       ((T*)a.prevZb)[blk + idx] = ((const T*)a.accZb)[blk + idx];
     }
   }
+  cache_append_finish(a);
 }
 
+static int cache_append_launch(const kch_cache_append_args* p, void* stream, int advance);
+
 extern "C" int kch_cache_append_token(const kch_cache_append_args* p, void* stream) {
+  return cache_append_launch(p, stream, 0);
+}
+
+extern "C" int kch_cache_append_token_advance(const kch_cache_append_args* p, void* stream) {
+  KCH_REQUIRE(p != nullptr && p->counters != nullptr, "kch_cache_append_token_advance: needs device counters");
+  return cache_append_launch(p, stream, 1);
+}
+
+static int cache_append_launch(const kch_cache_append_args* p, void* stream, int advance) {
   KCH_REQUIRE(p != nullptr, "kch_cache_append_token: null args");
   KCH_REQUIRE(p->B >= 1, "B=%d must be >= 1", p->B);
   KCH_REQUIRE(p->c >= 1, "c=%d must be >= 1", p->c);
@@ -212,6 +250,7 @@ extern "C" int kch_cache_append_token(const kch_cache_append_args* p, void* stre
   a.ring = p->win > 0 ? p->ring : nullptr; a.ring_pos = p->ring_pos; a.win = p->win;
   a.acc_len = p->acc_len; a.m = p->m; a.c = p->c; a.cI = p->c_I; a.normalize = p->normalize; a.overlap = p->Cb != nullptr;
   if (!a.Ki) a.cI = 0;
+  a.advance = advance; a.n_ctas = p->B;
   size_t smem = (size_t)(p->c > p->c_I ? p->c : p->c_I) * sizeof(float);
   cudaStream_t s = kch_stream(stream);
   if (p->dtype == KCH_BF16) cache_append_kernel<bf16><<<p->B, 128, smem, s>>>(a);

@@ -364,6 +364,95 @@ extern "C" int kch_short_conv_step(const void* x, void* lookback, const void* we
   return KCH_OK;
 }
 
+// LayerNorm + one-token conv step in one launch (the decode step of a KDA sub-layer: ops_fused.py:52-60 then
+// :560-569): one warp per batch row normalises it in registers, convolves with the two lookback rows of its own
+// channels and slides the lookback where it lies.  Same arithmetic and rounding points as kch_layernorm followed by
+// kch_short_conv_step (the normalised row is rounded to bf16 before the taps see it).
+template <typename TW, int NV>
+__global__ void __launch_bounds__(128)
+ln_conv_step_kernel_bf16(const bf16* __restrict__ x, const TW* __restrict__ lw, const TW* __restrict__ lb2, float eps,
+                         bf16* lookback, const bf16* __restrict__ cw, const bf16* __restrict__ cb,
+                         bf16* __restrict__ y, int B, int d) {
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= B) return;
+  const bf16* xr = x + (int64_t)row * d;
+  float v[NV][8];
+  float s = 0.f;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    uint4 raw = *reinterpret_cast<const uint4*>(xr + i * 256 + lane * 8);
+    const bf16* e = reinterpret_cast<const bf16*>(&raw);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) { v[i][k] = __bfloat162float(e[k]); s += v[i][k]; }
+  }
+  const float mean = warp_sum(s) / (float)d;
+  float q = 0.f;
+#pragma unroll
+  for (int i = 0; i < NV; ++i)
+#pragma unroll
+    for (int k = 0; k < 8; ++k) { float t = v[i][k] - mean; q += t * t; }
+  const float rstd = 1.0f / sqrtf(warp_sum(q) / (float)d + eps);
+  bf16* l0 = lookback + (int64_t)row * 2 * d;
+  bf16* l1 = l0 + d;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int c0 = i * 256 + lane * 8;
+    uint4 nv, r2 = *reinterpret_cast<const uint4*>(l0 + c0), r1 = *reinterpret_cast<const uint4*>(l1 + c0);
+    uint4 bv = *reinterpret_cast<const uint4*>(cb + c0);
+    bf16* xn = reinterpret_cast<bf16*>(&nv);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) xn[k] = __float2bfloat16_rn((v[i][k] - mean) * rstd * ldf(lw + c0 + k) + ldf(lb2 + c0 + k));
+    float wt[24];
+    const uint4* wp = reinterpret_cast<const uint4*>(cw + c0 * 3);
+#pragma unroll
+    for (int v3 = 0; v3 < 3; ++v3) {
+      uint4 raw = wp[v3];
+      const bf16* e = reinterpret_cast<const bf16*>(&raw);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) wt[8 * v3 + k] = __bfloat162float(e[k]);
+    }
+    const bf16* e2 = reinterpret_cast<const bf16*>(&r2);
+    const bf16* e1 = reinterpret_cast<const bf16*>(&r1);
+    const bf16* eb = reinterpret_cast<const bf16*>(&bv);
+    uint4 outv;
+    bf16* out = reinterpret_cast<bf16*>(&outv);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      float acc = wt[3 * k] * __bfloat162float(e2[k]);
+      acc = fmaf(wt[3 * k + 1], __bfloat162float(e1[k]), acc);
+      acc = fmaf(wt[3 * k + 2], __bfloat162float(xn[k]), acc);
+      out[k] = __float2bfloat16_rn(acc + __bfloat162float(eb[k]));
+    }
+    *reinterpret_cast<uint4*>(y + (int64_t)row * d + c0) = outv;
+    *reinterpret_cast<uint4*>(l0 + c0) = r1;
+    *reinterpret_cast<uint4*>(l1 + c0) = nv;
+  }
+}
+
+extern "C" int kch_layernorm_short_conv_step(const void* x, const void* ln_weight, const void* ln_bias, float eps,
+                                             void* lookback, const void* conv_weight, const void* conv_bias, void* y,
+                                             int B, int d, int dtype, int wdtype, void* stream) {
+  KCH_REQUIRE(dtype == KCH_BF16 && (d % 256) == 0 && d >= 256 && d <= 2048,
+              "kch_layernorm_short_conv_step: bf16 with d %% 256 == 0 and d <= 2048 only (dtype tag %d, d=%d)", dtype, d);
+  KCH_REQUIRE(B >= 1 && x && lookback && y, "kch_layernorm_short_conv_step: B=%d", B);
+  const uintptr_t al = (uintptr_t)x | (uintptr_t)y | (uintptr_t)conv_weight | (uintptr_t)conv_bias | (uintptr_t)lookback;
+  KCH_REQUIRE((al & 15) == 0, "kch_layernorm_short_conv_step: operands must be 16-byte aligned");
+  cudaStream_t s = kch_stream(stream);
+  dim3 grid((unsigned)((B + 3) / 4));
+#define LSV(NV)                                                                                                    \
+  KCH_DISPATCH_FLOAT(wdtype, TW, (ln_conv_step_kernel_bf16<TW, NV><<<grid, 128, 0, s>>>(                            \
+      (const bf16*)x, (const TW*)ln_weight, (const TW*)ln_bias, eps, (bf16*)lookback, (const bf16*)conv_weight,    \
+      (const bf16*)conv_bias, (bf16*)y, B, d)))
+  switch (d / 256) {
+    case 1: LSV(1); break; case 2: LSV(2); break; case 3: LSV(3); break; case 4: LSV(4); break;
+    case 5: LSV(5); break; case 6: LSV(6); break; case 7: LSV(7); break; default: LSV(8); break;
+  }
+#undef LSV
+  KCH_LAUNCH_OK();
+  return KCH_OK;
+}
+
 // ---------------------------------------------------------------------------------------
 // Activations applied to a projection output that is already stored in dtype T, reproducing
 // the reference's rounding points: each op reads T, computes in fp32, rounds to T.

@@ -61,7 +61,9 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, unsign
         "selp.b32 %0, 1, 0, p;\n\t}"
         : "=r"(ok) : "r"(addr), "r"(parity) : "memory");
     if (ok) return true;
-    if (*((volatile unsigned int*)&g_kch_status) != 0) return false;  // someone else already gave up
+    // someone else already gave up?  Looked at rarely: a global load after every failed try would sit on the
+    // critical path of each wake-up
+    if ((it & 1023) == 1023 && *((volatile unsigned int*)&g_kch_status) != 0) return false;
   }
   atomicCAS(&g_kch_status, 0u, code);
   return false;
@@ -157,22 +159,27 @@ __device__ __forceinline__ float bf16r(float v) { return __bfloat162float(__floa
 __device__ __forceinline__ float ep_silu(float x) { return __fdividef(x, 1.0f + __expf(-x)); }
 // Ring depth: as many (A tile + W tile) stages as fit in about 200 KB, so that narrow tiles (small BN) keep
 // the same number of bytes in flight per SM as the 256-wide tile does with 4 stages.
+// row pitch (in floats) of the fp32 partial tile a split-K CTA leaves in shared memory: 16 bytes of padding keep the
+// row-per-lane float4 stores free of bank conflicts
+#define TG_RED_LD(BN) ((BN) + 4)
 template <int BN>
 struct TgStages { static constexpr int value = BN >= 256 ? 4 : BN >= 128 ? 6 : BN >= 64 ? 8 : 10; };
 
-// SK ("skinny", a decode batch of at most 64 rows): the A box is 64 rows, so a stage is 8 KB smaller and the ring twice
-// as deep for the narrow tiles -- the launch is a stream of weights and wants bytes in flight.  The MMA still spans 128
-// rows: rows 64..127 of its A operand are whatever follows in shared memory (the next A stage, or the first W stage
-// behind the last one), which only reaches accumulator rows that are never stored.
+// SK ("skinny", a decode batch of at most 64 rows): the A box is 64 rows and the ring is sized to about 96 KB, so two
+// CTAs share an SM -- the launch is a stream of weights and wants many CTAs with bytes in flight, not a deep ring in
+// few.  The MMA still spans 128 rows: rows 64..127 of its A operand are whatever follows in shared memory (the next A
+// stage, or the first W stage behind the last one), which only reaches accumulator rows that are never stored.
+// With `ksplit` > 1 the K loop of a tile is divided over the CTAs of a cluster (see the kernel).
 template <int BN, bool TWO = false, bool SK = false>
 struct TgSmem {
   // a CTA of a pair holds half of the W tile, which buys two more stages
   static constexpr int A_ROWS = SK ? 64 : TG_BM;
-  static constexpr int STAGES = TWO ? 6 : SK ? (BN >= 128 ? 8 : BN >= 64 ? 12 : 16) : TgStages<BN>::value;
+  static constexpr int STAGES = TWO ? 6 : SK ? (BN >= 128 ? 4 : BN >= 64 ? 6 : 8) : TgStages<BN>::value;
   static constexpr int B_ROWS = TWO ? BN / 2 : BN;
+  static constexpr int EPI_WARPS = BN == 256 ? 8 : 4;   // narrower tiles are stored by warps 2..5 alone
   alignas(1024) bf16 a[STAGES][A_ROWS * TG_BK];
   alignas(1024) bf16 b[STAGES][B_ROWS * TG_BK];
-  alignas(16) uint8_t epi[8][32 * TG_EPI_LD];   // per epilogue warp: a 32 x 32 bf16 chunk, rows padded to 80 bytes
+  alignas(16) uint8_t epi[EPI_WARPS][32 * TG_EPI_LD];   // per epilogue warp: a 32 x 32 bf16 chunk, rows padded to 80 bytes
   alignas(8) uint64_t full[STAGES];
   uint64_t empty[STAGES];
   uint64_t acc_full[2];
@@ -181,10 +188,16 @@ struct TgSmem {
 };
 
 template <int BN, bool TWO, bool SK = false>
-__global__ void __launch_bounds__(TG_THREADS, 1)
+__global__ void __launch_bounds__(TG_THREADS, SK ? 2 : 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                     bf16* __restrict__ C, const bf16* __restrict__ R, int64_t M, int N, int K,
-                    int64_t ldc, int64_t ldr, int vec_ok, const TgEpilogue ep, int slab_k, int64_t slab_rows) {
+                    int64_t ldc, int64_t ldr, int vec_ok, const TgEpilogue ep, int slab_k, int64_t slab_rows,
+                    int ksplit) {
+  // ksplit > 1 (SK only; launched as clusters of `ksplit` CTAs, one tile per cluster): CTA r of the cluster runs
+  // k-blocks [r * kper, (r + 1) * kper) into its own tensor memory, leaves the fp32 partial tile in its shared
+  // memory, and after a cluster barrier finishes rows [r * 64 / ksplit, ...) of the tile: partials are summed in
+  // rank order through distributed shared memory (so the result does not depend on which CTA adds them), then the
+  // same activation / residual / rounding steps as the single-CTA epilogue.
   // slab_k > 0: the K columns of A lie in K / slab_k slabs of [slab_rows][slab_k] one after the other (the
   // rank-major buffer an all-gather of per-GPU column slices leaves behind); map_a then describes all slabs as one
   // [slabs * slab_rows][slab_k] matrix and k-block kb is read from slab kb * 64 / slab_k
@@ -195,11 +208,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   constexpr int BM_T = TWO ? 2 * TG_BM : TG_BM;       // rows of a tile: a CTA pair takes 256, each CTA its 128
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = TWO ? cluster_ctarank() : 0u;
-  const int64_t unit = TWO ? (blockIdx.x >> 1) : blockIdx.x, nunits = TWO ? (gridDim.x >> 1) : gridDim.x;
+  const bool split = SK && ksplit > 1;
+  const uint32_t ks = split ? cluster_ctarank() : 0u;
+  const int64_t unit = TWO ? (blockIdx.x >> 1) : split ? (blockIdx.x / ksplit) : blockIdx.x;
+  const int64_t nunits = TWO ? (gridDim.x >> 1) : split ? (gridDim.x / ksplit) : gridDim.x;
   const int n_tiles = (N + BN - 1) / BN;
   const int64_t m_tiles = (M + BM_T - 1) / BM_T;
   const int64_t total_tiles = m_tiles * n_tiles;
-  const int kblocks = (K + TG_BK - 1) / TG_BK;
+  const int kblocks_all = (K + TG_BK - 1) / TG_BK;
+  const int kper = split ? (kblocks_all + ksplit - 1) / ksplit : kblocks_all;
+  const int kb_first = (int)ks * kper;
+  const int kblocks = min(kblocks_all - kb_first, kper);     // this CTA's share (the host keeps every share non-empty)
   constexpr uint32_t ACC_COLS = BN;                 // fp32 accumulator columns per buffer
   constexpr uint32_t TMEM_COLS = (2 * ACC_COLS) < 32 ? 32 : 2 * ACC_COLS;  // power of two >= 32
 
@@ -235,7 +254,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         for (int kb = 0; kb < kblocks; ++kb, ++it) {
           const uint32_t s = it % TG_STAGES, ph = (it / TG_STAGES) & 1;
           if (!mbar_wait(&sm.empty[s], ph ^ 1, 1)) { ok = false; break; }
-          int kc = kb * TG_BK;
+          const int kcw = (kb_first + kb) * TG_BK;     // column of W; of A unless A lies in slabs
+          int kc = kcw;
           int64_t roff = 0;
           if (slab_k > 0) { const int sidx = kc / slab_k; kc -= sidx * slab_k; roff = (int64_t)sidx * slab_rows; }
           if constexpr (TWO) {
@@ -244,11 +264,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             const uint32_t full_addr = mapa_u32(smem_u32(&sm.full[s]), 0);
             if (rank == 0) mbar_expect_tx(&sm.full[s], 2 * (TG_BM + BN / 2) * TG_BK * 2);
             tma_load_2d_pair(sm.a[s], &map_a, kc, (int)(mb * BM_T + rank * TG_BM + roff), full_addr);
-            tma_load_2d_pair(sm.b[s], &map_w, kb * TG_BK, nb * BN + (int)rank * (BN / 2), full_addr);
+            tma_load_2d_pair(sm.b[s], &map_w, kcw, nb * BN + (int)rank * (BN / 2), full_addr);
           } else {
             mbar_expect_tx(&sm.full[s], (A_ROWS + BN) * TG_BK * 2);
             tma_load_2d(sm.a[s], &map_a, kc, (int)(mb * TG_BM + roff), &sm.full[s]);
-            tma_load_2d(sm.b[s], &map_w, kb * TG_BK, nb * BN, &sm.full[s]);
+            tma_load_2d(sm.b[s], &map_w, kcw, nb * BN, &sm.full[s]);
           }
         }
       }
@@ -305,6 +325,24 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     const int c_end = (BN == 256) ? c_begin + 128 : (half == 0 ? BN : 0);
     uint32_t tcount = 0;
     bool ok = true;
+    if (split) {
+      // this CTA's partial sums of rows 0..63, as fp32, to shared memory (the ring is drained: every MMA has retired)
+      if (quarter < 2 && unit < total_tiles && mbar_wait(&sm.acc_full[0], 0, 4)) {
+        tc_fence_after();
+        float* red = reinterpret_cast<float*>(&sm.a[0][0]) + (size_t)(quarter * 32 + lane) * TG_RED_LD(BN);
+        const uint32_t tbase = tmem_base + ((uint32_t)(quarter * 32) << 16);
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 32) {
+          uint32_t r[32];
+          tc_ld32(tbase + c0, r);
+          tc_wait_ld();
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            *reinterpret_cast<uint4*>(red + c0 + 4 * j) = make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+        }
+      }
+      ok = false;      // the tile is finished after the cluster barrier below
+    }
     for (int64_t tile = unit; tile < total_tiles && ok; tile += nunits, ++tcount) {
       const int64_t mb = tile / n_tiles;
       const int nb = (int)(tile % n_tiles);
@@ -426,6 +464,86 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   tc_fence_before();
   __syncthreads();
   if constexpr (TWO) cluster_sync_all();     // neither CTA leaves while the other may still touch its memory
+  if constexpr (SK) {
+    if (split) {
+      cluster_sync_all();                    // every CTA's partial tile is in its shared memory
+      constexpr int CPL = BN / 32;           // columns per lane: a warp covers one row of the tile
+      const int rows_per = 64 / ksplit;
+      const int nb = (int)(unit % n_tiles);
+      const uint32_t red0 = smem_u32(&sm.a[0][0]);
+      if (unit < total_tiles) {
+        for (int rr = warp; rr < rows_per; rr += TG_THREADS / 32) {
+          const int row = (int)ks * rows_per + rr;
+          if (row >= M) continue;
+          float v[CPL];
+#pragma unroll
+          for (int j = 0; j < CPL; ++j) v[j] = 0.f;
+          const uint32_t off = red0 + (uint32_t)(row * TG_RED_LD(BN) + lane * CPL) * 4u;
+          for (int p = 0; p < ksplit; ++p) {
+            const uint32_t src = mapa_u32(off, (uint32_t)p);
+            if constexpr (CPL == 4) {
+              float x0, x1, x2, x3;
+              asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(x0), "=f"(x1), "=f"(x2), "=f"(x3) : "r"(src) : "memory");
+              v[0] += x0; v[1] += x1; v[2] += x2; v[3] += x3;
+            } else if constexpr (CPL == 2) {
+              float x0, x1;
+              asm volatile("ld.shared::cluster.v2.f32 {%0, %1}, [%2];" : "=f"(x0), "=f"(x1) : "r"(src) : "memory");
+              v[0] += x0; v[1] += x1;
+            } else {
+              float x0;
+              asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(x0) : "r"(src) : "memory");
+              v[0] += x0;
+            }
+          }
+          const int col = nb * BN + lane * CPL;
+          int act = 0;
+          float prm = 0.f;
+          if (ep.nseg) {
+            int sidx = 0;
+            while (sidx < ep.nseg - 1 && col >= ep.seg_end[sidx]) ++sidx;
+            act = ep.seg_act[sidx];
+            prm = ep.seg_param[sidx];
+          }
+          // the head norm spans the 128 columns of the tile (the host pairs that activation with BN = 128)
+          float ss = 0.f;
+          if (act == KCH_ACT_SILU_L2NORM) {
+#pragma unroll
+            for (int j = 0; j < CPL; ++j) { v[j] = bf16r(ep_silu(bf16r(v[j]))); ss = fmaf(v[j], v[j], ss); }
+          }
+#pragma unroll
+          for (int o = 16; o >= 1; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+          if (act == KCH_ACT_SILU_L2NORM) {
+            const float nrm = __fdividef(1.0f, fmaxf(bf16r(sqrtf(ss)), 1e-12f));
+#pragma unroll
+            for (int j = 0; j < CPL; ++j) v[j] *= nrm;
+          } else if (act == KCH_ACT_SILU) {
+#pragma unroll
+            for (int j = 0; j < CPL; ++j) v[j] = ep_silu(bf16r(v[j]));
+          } else if (act == KCH_ACT_SIGMOID) {
+#pragma unroll
+            for (int j = 0; j < CPL; ++j) v[j] = __fdividef(1.0f, 1.0f + __expf(-bf16r(v[j])));
+          } else if (act == KCH_ACT_NEG_SOFTPLUS) {
+#pragma unroll
+            for (int j = 0; j < CPL; ++j) {
+              const float t = bf16r(v[j]);
+              v[j] = -bf16r(t > 20.f ? t : __logf(1.0f + __expf(t))) * prm;
+            }
+          }
+          bf16* cp = C + (int64_t)row * ldc + col;
+          const bf16* rp = R ? R + (int64_t)row * ldr + col : nullptr;
+#pragma unroll
+          for (int j = 0; j < CPL; ++j) {
+            if (col + j < N) {
+              float f = bf16r(v[j]);
+              if (rp) f += __bfloat162float(rp[j]);
+              cp[j] = __float2bfloat16_rn(f);
+            }
+          }
+        }
+      }
+      cluster_sync_all();                    // no CTA leaves while another may still read its partial tile
+    }
+  }
   if (warp == 1) {
     tc_fence_after();
     if constexpr (TWO)
@@ -506,8 +624,28 @@ static int launch_tg(const void* A, const void* W, void* C, const void* R, int64
     if (skinny) {
       size_t smem = sizeof(TgSmem<BN, false, true>) + 1024;
       KCH_CUDA_OK(cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+      // Split the K loop over a cluster when the tiles alone would leave most SMs idle: two CTAs fit on an SM, so up
+      // to 2 * sms CTAs run at once.  Every share of k-blocks must be non-empty.  (KCH_GEMM_KSPLIT=1 turns it off.)
+      static const int ks_max = [] { const char* e = getenv("KCH_GEMM_KSPLIT"); return e && e[0] >= '1' && e[0] <= '4' ? e[0] - '0' : 4; }();
+      const int kblocks = (K + TG_BK - 1) / TG_BK;
+      int ksplit = 1;
+      for (int c = 4; c >= 2; c >>= 1)
+        if (c <= ks_max && kblocks >= 4 * c && tiles * c <= 2 * (int64_t)sms) { ksplit = c; break; }
+      while (ksplit > 1 && (ksplit - 1) * ((kblocks + ksplit - 1) / ksplit) >= kblocks) ksplit >>= 1;
+      if (ksplit > 1) {
+        cudaLaunchConfig_t cfg = {};
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = (unsigned)ksplit; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+        cfg.gridDim = dim3((unsigned)(tiles * ksplit)); cfg.blockDim = dim3(TG_THREADS); cfg.dynamicSmemBytes = smem;
+        cfg.stream = s; cfg.attrs = attr; cfg.numAttrs = 1;
+        KCH_CUDA_OK(cudaLaunchKernelEx(&cfg, gemm_tcgen05_kernel<BN, false, true>, ma, mw, (bf16*)C, (const bf16*)R, M, N, K,
+                                       ldc, ldr, vec_ok, ep, slab_k, M, ksplit));
+        kch_note_launch(1);
+        return KCH_OK;
+      }
       gemm_tcgen05_kernel<BN, false, true><<<grid, TG_THREADS, smem, s>>>(ma, mw, (bf16*)C, (const bf16*)R, M, N, K, ldc, ldr,
-                                                                         vec_ok, ep, slab_k, M);
+                                                                         vec_ok, ep, slab_k, M, 1);
       KCH_LAUNCH_OK();
       return KCH_OK;
     }
@@ -515,7 +653,7 @@ static int launch_tg(const void* A, const void* W, void* C, const void* R, int64
   size_t smem = sizeof(TgSmem<BN>) + 1024;
   KCH_CUDA_OK(cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   gemm_tcgen05_kernel<BN, false><<<grid, TG_THREADS, smem, s>>>(ma, mw, (bf16*)C, (const bf16*)R, M, N, K, ldc, ldr, vec_ok, ep,
-                                                               slab_k, M);
+                                                               slab_k, M, 1);
   KCH_LAUNCH_OK();
   return KCH_OK;
 }
@@ -551,7 +689,7 @@ static int launch_tg_pair(const void* A, const void* W, void* C, const void* R, 
   cfg.gridDim = dim3(2 * pairs);
   int vec_ok = (ldc % 8 == 0) && (((uintptr_t)C & 15) == 0) && (!R || ((ldr % 8 == 0) && (((uintptr_t)R & 15) == 0)));
   KCH_CUDA_OK(cudaLaunchKernelEx(&cfg, gemm_tcgen05_kernel<BN, true>, ma, mw, (bf16*)C, (const bf16*)R, M, N, K, ldc, ldr,
-                                 vec_ok, ep, slab_k, M));
+                                 vec_ok, ep, slab_k, M, 1));
   kch_note_launch(1);
   return KCH_OK;
 }

@@ -58,7 +58,7 @@ class AttendDecodeArgs(C.Structure):
 
 
 # indices into a cache's device counters (include/kch_b200.h KCH_CTR_*)
-CTR_ACC_LEN, CTR_N_BLOCKS, CTR_RING_N, CTR_HAS_PREV, CTR_TOKENS, CTR_WORDS = 0, 1, 2, 3, 4, 8
+CTR_ACC_LEN, CTR_N_BLOCKS, CTR_RING_N, CTR_HAS_PREV, CTR_TOKENS, CTR_ARRIVALS, CTR_WORDS = 0, 1, 2, 3, 4, 5, 8
 STATUS_CACHE_CAPACITY = 64
 STATUS_SELFTEST_WAIT = 0x5E1F
 STATUS_PEER_GATHER = 0x9A7E
@@ -96,6 +96,7 @@ PROTOTYPES = {
     "kch_indexer_topk_static": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _i64, _i, _i64, _vp]),
     "kch_attend": (_i, [C.POINTER(AttendArgs), _vp]),
     "kch_cache_append_token": (_i, [C.POINTER(CacheAppendArgs), _vp]),
+    "kch_cache_append_token_advance": (_i, [C.POINTER(CacheAppendArgs), _vp]),
     "kch_quantize_rows": (_i, [_vp, _i64, _vp, _vp, _vp, _i64, _i, _i, _i, _vp]),
     "kch_cache_advance": (_i, [_vp, _i, _vp]),
     "kch_decode_indexer_workspace_bytes": (_i64, [_i, _i64]),
@@ -103,6 +104,7 @@ PROTOTYPES = {
                                      _vp, _i64, _vp]),
     "kch_short_conv_step": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
     "kch_layernorm_short_conv": (_i, [_vp, _vp, _vp, _f, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp]),
+    "kch_layernorm_short_conv_step": (_i, [_vp, _vp, _vp, _f, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp]),
     "kch_attend_decode_splits": (_i, [_i]),
     "kch_attend_decode_workspace_bytes": (_i64, [_i, _i, _i]),
     "kch_attend_decode": (_i, [C.POINTER(AttendDecodeArgs), _vp]),

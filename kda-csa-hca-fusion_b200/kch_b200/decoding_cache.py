@@ -420,8 +420,7 @@ class CSADecodingCache(_CacheBase):
         a.normalize = int(self._normalize_qk)
         a.counters = self._ctr.data_ptr()
         with torch.cuda.device(self.device):
-            _lib.check(lib.kch_cache_append_token(a, _lib.stream()))
-            _lib.check(lib.kch_cache_advance(self._ctr.data_ptr(), m, _lib.stream()))
+            _lib.check(lib.kch_cache_append_token_advance(a, _lib.stream()))   # the last CTA advances the device counters
         self._advance(m)
 
     def _append_many(self, new, biases):
@@ -648,8 +647,7 @@ class HCADecodingCache(_CacheBase):
         a.normalize = int(self._normalize_qk)
         a.counters = self._ctr.data_ptr()
         with torch.cuda.device(self.device):
-            _lib.check(lib.kch_cache_append_token(a, _lib.stream()))
-            _lib.check(lib.kch_cache_advance(self._ctr.data_ptr(), m, _lib.stream()))
+            _lib.check(lib.kch_cache_append_token_advance(a, _lib.stream()))   # the last CTA advances the device counters
         self._advance(m)
 
     def _append_many(self, new, bias):

@@ -161,6 +161,29 @@ def short_conv_step(x, weight, bias, lookback):
     return y
 
 
+def layernorm_short_conv_step_ok(x, lookback):
+    B, T, d = x.shape
+    return (x.is_cuda and T == 1 and x.dtype == torch.bfloat16 and d % 256 == 0 and d <= 2048
+            and lookback is not None and lookback.dtype == x.dtype and lookback.is_contiguous()
+            and tuple(lookback.shape) == (B, 2, d))
+
+
+def layernorm_short_conv_step(x, ln_weight, ln_bias, eps, weight, bias, lookback):
+    """``short_conv_step(layernorm(x))`` in one launch; ``lookback`` (normalised rows) slides in place."""
+    lib = _lib.load()
+    B, T, d = x.shape
+    x = x.contiguous()
+    w = weight.reshape(d, 3).to(x.dtype).contiguous()
+    b = bias.to(x.dtype).contiguous()
+    lw, lbias = ln_weight.contiguous(), ln_bias.contiguous()
+    y = torch.empty_like(x)
+    with torch.cuda.device(x.device):
+        _lib.check(lib.kch_layernorm_short_conv_step(_lib.ptr(x), _lib.ptr(lw), _lib.ptr(lbias), float(eps),
+                                                     _lib.ptr(lookback), _lib.ptr(w), _lib.ptr(b), _lib.ptr(y), B, d,
+                                                     _lib.dtype_tag(x.dtype), _lib.dtype_tag(lw.dtype), _lib.stream()))
+    return y
+
+
 def activation(x, act, *, param=0.0, group=1):
     """Activation with the reference's rounding points on a ``[..., cols]`` view (row-strided ok)."""
     lib = _lib.load()
@@ -250,9 +273,15 @@ class KDAHybridLayer(nn.Module):
         if lb is not None and lb.shape[0] != B:
             lb = None
         fused_norm = norm is not None and layernorm_short_conv_ok(x, lb)
-        if norm is not None and not fused_norm:
+        fused_step = (norm is not None and not fused_norm and lookback_in_place
+                      and layernorm_short_conv_step_ok(x, lb) and norm.weight.dtype == norm.bias.dtype)
+        if norm is not None and not (fused_norm or fused_step):
             x = norm(x)
-        if fused_norm:
+        if fused_step:
+            xc = layernorm_short_conv_step(x, norm.weight, norm.bias, norm.eps, self.short_conv.weight,
+                                           self.short_conv.bias, lb)
+            new_lb = lb
+        elif fused_norm:
             xc, new_lb = layernorm_short_conv(x, norm.weight, norm.bias, norm.eps, self.short_conv.weight,
                                               self.short_conv.bias, lb)
         elif (lookback_in_place and T == 1 and lb is not None and lb.dtype == x.dtype and lb.is_contiguous()

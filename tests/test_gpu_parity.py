@@ -54,6 +54,35 @@ def test_linear_bf16(kch, M, N, K):
     assert md(y2, ref2) == 0.0
 
 
+@pytest.mark.parametrize("M,N,K", [(64, 2048, 2048), (37, 776, 2048), (1, 384, 2048), (64, 1024, 128), (64, 6288, 2048)])
+def test_linear_decode_batch_split_k(kch, M, N, K):
+    """A decode batch (at most 64 rows) runs one tile per cluster with the K loop divided over its CTAs; the sum of the
+    partial tiles, the fused activations and the residual must match the single-CTA kernel that a taller batch of
+    the same rows takes (fp32 summation order differs: rare one-ulp flips of the bf16 rounding only)."""
+    from kch_b200 import _lib
+    from kch_b200.csa import linear
+    g = torch.Generator().manual_seed(M + N + K)
+    x = torch.randn(200, K, generator=g).bfloat16().to(DEV)
+    w = (torch.randn(N, K, generator=g) * 0.05).bfloat16().to(DEV)
+    r = torch.randn(200, N, generator=g).bfloat16().to(DEV)
+    ref = x[:M].float() @ w.float().T
+    y = linear(x[:M], w)
+    assert ((y.float() - ref).abs() <= ref.abs() * 2 ** -7 + 1e-4).all()
+    assert torch.equal(linear(x[:M], w, residual=r[:M]), (y.float() + r[:M].float()).bfloat16())
+    tall = linear(x, w)[:M]
+    assert (y != tall).float().mean() <= 0.01 and md(y, tall) <= float(ref.abs().max()) * 2 ** -7
+    if N == 6288:       # the KDA projection's epilogue: silu + per-head L2 norm | silu | none | sigmoid
+        segs = [(2048, _lib.ACT_SILU_L2NORM, 0.0), (2048, _lib.ACT_SILU_L2NORM, 0.0), (2048, _lib.ACT_SILU, 0.0),
+                (128, 0, 0.0), (16, _lib.ACT_SIGMOID, 0.0)]
+        ye = linear(x[:M], w, epilogue=segs, group=128)
+        te = linear(x, w, epilogue=segs, group=128)[:M]
+        assert (ye != te).float().mean() <= 0.01 and md(ye, te) <= 3.2e-2
+        import torch.nn.functional as F
+        q_ref = F.normalize(F.silu(ref[:, :2048]).view(M, 16, 128), dim=-1).view(M, 2048)
+        assert md(ye[:, :2048], q_ref) <= 4e-3
+        assert md(ye[:, 6272:], torch.sigmoid(ref[:, 6272:])) <= 4e-3
+
+
 @pytest.mark.parametrize("M,N,slabs,kl", [(300, 256, 2, 128), (1000, 2048, 8, 256), (64, 2048, 4, 512)])
 def test_linear_kslabs_equals_linear_of_concatenation(kch, M, N, slabs, kl):
     """The output projection over a rank-major all-gather buffer: same bits as F.linear of the concatenated heads."""
@@ -102,6 +131,16 @@ def test_glue_kernels(kch, d):
         ref, _ = orc.short_conv(x, cw, cb, look)
         assert (yc.cpu().float() - ref.float()).abs().max() <= 6.3e-2 and \
             ((yc.cpu() != ref).float().mean() <= 0.02)               # same fp32 formula: rare rounding flips only
+    if d % 256 == 0:
+        # the decode step's single launch: bit-identical to LayerNorm followed by the one-token conv step
+        from kch_b200.fused import layernorm_short_conv_step, short_conv_step
+        x1 = x[:, :1].contiguous().to(DEV)
+        lb_a, lb_b = lb.to(DEV).clone(), lb.to(DEV).clone()
+        for _ in range(3):                                         # three steps: the lookback slides in place
+            ya = short_conv_step(layernorm(x1, w.to(DEV), b.to(DEV)), cw.to(DEV), cb.to(DEV), lb_a)
+            yb = layernorm_short_conv_step(x1, w.to(DEV), b.to(DEV), 1e-5, cw.to(DEV), cb.to(DEV), lb_b)
+            assert torch.equal(ya, yb) and torch.equal(lb_a, lb_b)
+            x1 = (x1.float() * 0.5 + 1.0).bfloat16()
     xs = x.to(DEV)
     assert md(activation(xs, _lib.ACT_SILU), F.silu(x)) <= 3.2e-2
     assert md(activation(xs, _lib.ACT_SIGMOID), torch.sigmoid(x)) <= 4e-3
