@@ -68,12 +68,74 @@ __global__ void layernorm_kernel_bf16_vec(const bf16* __restrict__ x, const TW* 
   }
 }
 
+// A few rows only (a decode batch): one CTA per row, 8 channels per thread, so every load of the row and of the
+// parameters is issued at once and the launch is one memory round trip plus two block reductions.
+template <typename TW>
+__device__ __forceinline__ void ld8p(const TW* p, float (&o)[8]) {
+  if constexpr (sizeof(TW) == 2) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(p);
+    const bf16* e = reinterpret_cast<const bf16*>(&raw);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) o[k] = __bfloat162float(e[k]);
+  } else {
+    const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+    o[0] = a.x; o[1] = a.y; o[2] = a.z; o[3] = a.w; o[4] = b.x; o[5] = b.y; o[6] = b.z; o[7] = b.w;
+  }
+}
+// sum over the 256 threads of a CTA; `red` is 8 floats of shared memory (reusable after the call returns)
+__device__ __forceinline__ float block_sum_256(float v, float* red) {
+  v = warp_sum(v);
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+  __syncthreads();
+  return ((red[0] + red[1]) + (red[2] + red[3])) + ((red[4] + red[5]) + (red[6] + red[7]));
+}
+
+template <typename TW>
+__global__ void __launch_bounds__(256)
+layernorm_row_kernel_bf16(const bf16* __restrict__ x, const TW* __restrict__ w, const TW* __restrict__ b,
+                          bf16* __restrict__ y, int d, float eps) {
+  __shared__ float red[8];
+  const int c0 = threadIdx.x * 8;
+  const bool on = c0 < d;
+  const int64_t row = blockIdx.x;
+  float v[8], wv[8], bv[8];
+#pragma unroll
+  for (int k = 0; k < 8; ++k) v[k] = wv[k] = bv[k] = 0.f;
+  if (on) { ld8p(x + row * d + c0, v); ld8p(w + c0, wv); ld8p(b + c0, bv); }
+  float s = 0.f;
+#pragma unroll
+  for (int k = 0; k < 8; ++k) s += v[k];
+  const float mean = block_sum_256(s, red) / (float)d;
+  float q = 0.f;
+  if (on) {
+#pragma unroll
+    for (int k = 0; k < 8; ++k) { const float t = v[k] - mean; q += t * t; }
+  }
+  const float rstd = 1.0f / sqrtf(block_sum_256(q, red) / (float)d + eps);
+  if (on) {
+    uint4 outv;
+    bf16* out = reinterpret_cast<bf16*>(&outv);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) out[k] = __float2bfloat16_rn((v[k] - mean) * rstd * wv[k] + bv[k]);
+    *reinterpret_cast<uint4*>(y + row * d + c0) = outv;
+  }
+}
+
 extern "C" int kch_layernorm(const void* x, const void* weight, const void* bias, void* y,
                              int64_t rows, int d, float eps, int dtype, int wdtype, void* stream) {
   KCH_REQUIRE(rows >= 0 && d >= 1, "kch_layernorm: rows=%lld d=%d", (long long)rows, d);
   if (rows == 0) return KCH_OK;
   const int wpb = 8;
   dim3 grid((unsigned)ceil_div64(rows, wpb)), block(wpb * 32);
+  if (dtype == KCH_BF16 && rows <= 512 && (d % 8) == 0 && d <= 2048 &&
+      (((uintptr_t)x | (uintptr_t)y | (uintptr_t)weight | (uintptr_t)bias) & 15) == 0) {
+    cudaStream_t s = kch_stream(stream);
+    KCH_DISPATCH_FLOAT(wdtype, TW, (layernorm_row_kernel_bf16<TW><<<(unsigned)rows, 256, 0, s>>>(
+        (const bf16*)x, (const TW*)weight, (const TW*)bias, (bf16*)y, d, eps)));
+    KCH_LAUNCH_OK();
+    return KCH_OK;
+  }
   if (dtype == KCH_BF16 && (d % 256) == 0 && d <= 2048 && (((uintptr_t)x | (uintptr_t)y) & 15) == 0) {
     cudaStream_t s = kch_stream(stream);
 #define LNV(NV)                                                                                              \
@@ -365,69 +427,61 @@ extern "C" int kch_short_conv_step(const void* x, void* lookback, const void* we
 }
 
 // LayerNorm + one-token conv step in one launch (the decode step of a KDA sub-layer: ops_fused.py:52-60 then
-// :560-569): one warp per batch row normalises it in registers, convolves with the two lookback rows of its own
+// :560-569): one CTA per batch row normalises it in registers (8 channels per thread), convolves with the two lookback rows of its own
 // channels and slides the lookback where it lies.  Same arithmetic and rounding points as kch_layernorm followed by
 // kch_short_conv_step (the normalised row is rounded to bf16 before the taps see it).
-template <typename TW, int NV>
-__global__ void __launch_bounds__(128)
+template <typename TW>
+__global__ void __launch_bounds__(256)
 ln_conv_step_kernel_bf16(const bf16* __restrict__ x, const TW* __restrict__ lw, const TW* __restrict__ lb2, float eps,
                          bf16* lookback, const bf16* __restrict__ cw, const bf16* __restrict__ cb,
-                         bf16* __restrict__ y, int B, int d) {
-  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  const int lane = threadIdx.x & 31;
-  if (row >= B) return;
-  const bf16* xr = x + (int64_t)row * d;
-  float v[NV][8];
+                         bf16* __restrict__ y, int d) {
+  __shared__ float red[8];
+  const int c0 = threadIdx.x * 8;
+  const bool on = c0 < d;
+  const int64_t row = blockIdx.x;
+  bf16* l0 = lookback + row * 2 * d;
+  bf16* l1 = l0 + d;
+  float v[8], wv[8], bv[8];
+  uint4 r2 = make_uint4(0u, 0u, 0u, 0u), r1 = r2, cbv = r2, cwv[3] = {r2, r2, r2};
+#pragma unroll
+  for (int k = 0; k < 8; ++k) v[k] = wv[k] = bv[k] = 0.f;
+  if (on) {
+    ld8p(x + row * d + c0, v); ld8p(lw + c0, wv); ld8p(lb2 + c0, bv);
+    r2 = *reinterpret_cast<const uint4*>(l0 + c0);
+    r1 = *reinterpret_cast<const uint4*>(l1 + c0);
+    cbv = *reinterpret_cast<const uint4*>(cb + c0);
+    const uint4* wp = reinterpret_cast<const uint4*>(cw + c0 * 3);   // taps of 8 channels: 24 consecutive bf16
+    cwv[0] = wp[0]; cwv[1] = wp[1]; cwv[2] = wp[2];
+  }
   float s = 0.f;
 #pragma unroll
-  for (int i = 0; i < NV; ++i) {
-    uint4 raw = *reinterpret_cast<const uint4*>(xr + i * 256 + lane * 8);
-    const bf16* e = reinterpret_cast<const bf16*>(&raw);
-#pragma unroll
-    for (int k = 0; k < 8; ++k) { v[i][k] = __bfloat162float(e[k]); s += v[i][k]; }
-  }
-  const float mean = warp_sum(s) / (float)d;
+  for (int k = 0; k < 8; ++k) s += v[k];
+  const float mean = block_sum_256(s, red) / (float)d;
   float q = 0.f;
+  if (on) {
 #pragma unroll
-  for (int i = 0; i < NV; ++i)
-#pragma unroll
-    for (int k = 0; k < 8; ++k) { float t = v[i][k] - mean; q += t * t; }
-  const float rstd = 1.0f / sqrtf(warp_sum(q) / (float)d + eps);
-  bf16* l0 = lookback + (int64_t)row * 2 * d;
-  bf16* l1 = l0 + d;
-#pragma unroll
-  for (int i = 0; i < NV; ++i) {
-    const int c0 = i * 256 + lane * 8;
-    uint4 nv, r2 = *reinterpret_cast<const uint4*>(l0 + c0), r1 = *reinterpret_cast<const uint4*>(l1 + c0);
-    uint4 bv = *reinterpret_cast<const uint4*>(cb + c0);
-    bf16* xn = reinterpret_cast<bf16*>(&nv);
-#pragma unroll
-    for (int k = 0; k < 8; ++k) xn[k] = __float2bfloat16_rn((v[i][k] - mean) * rstd * ldf(lw + c0 + k) + ldf(lb2 + c0 + k));
-    float wt[24];
-    const uint4* wp = reinterpret_cast<const uint4*>(cw + c0 * 3);
-#pragma unroll
-    for (int v3 = 0; v3 < 3; ++v3) {
-      uint4 raw = wp[v3];
-      const bf16* e = reinterpret_cast<const bf16*>(&raw);
-#pragma unroll
-      for (int k = 0; k < 8; ++k) wt[8 * v3 + k] = __bfloat162float(e[k]);
-    }
-    const bf16* e2 = reinterpret_cast<const bf16*>(&r2);
-    const bf16* e1 = reinterpret_cast<const bf16*>(&r1);
-    const bf16* eb = reinterpret_cast<const bf16*>(&bv);
-    uint4 outv;
-    bf16* out = reinterpret_cast<bf16*>(&outv);
-#pragma unroll
-    for (int k = 0; k < 8; ++k) {
-      float acc = wt[3 * k] * __bfloat162float(e2[k]);
-      acc = fmaf(wt[3 * k + 1], __bfloat162float(e1[k]), acc);
-      acc = fmaf(wt[3 * k + 2], __bfloat162float(xn[k]), acc);
-      out[k] = __float2bfloat16_rn(acc + __bfloat162float(eb[k]));
-    }
-    *reinterpret_cast<uint4*>(y + (int64_t)row * d + c0) = outv;
-    *reinterpret_cast<uint4*>(l0 + c0) = r1;
-    *reinterpret_cast<uint4*>(l1 + c0) = nv;
+    for (int k = 0; k < 8; ++k) { const float t = v[k] - mean; q += t * t; }
   }
+  const float rstd = 1.0f / sqrtf(block_sum_256(q, red) / (float)d + eps);
+  if (!on) return;
+  uint4 nv, outv;
+  bf16* xn = reinterpret_cast<bf16*>(&nv);
+  bf16* out = reinterpret_cast<bf16*>(&outv);
+  const bf16* wt = reinterpret_cast<const bf16*>(cwv);
+  const bf16* e2 = reinterpret_cast<const bf16*>(&r2);
+  const bf16* e1 = reinterpret_cast<const bf16*>(&r1);
+  const bf16* eb = reinterpret_cast<const bf16*>(&cbv);
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    xn[k] = __float2bfloat16_rn((v[k] - mean) * rstd * wv[k] + bv[k]);
+    float acc = __bfloat162float(wt[3 * k]) * __bfloat162float(e2[k]);
+    acc = fmaf(__bfloat162float(wt[3 * k + 1]), __bfloat162float(e1[k]), acc);
+    acc = fmaf(__bfloat162float(wt[3 * k + 2]), __bfloat162float(xn[k]), acc);
+    out[k] = __float2bfloat16_rn(acc + __bfloat162float(eb[k]));
+  }
+  *reinterpret_cast<uint4*>(y + row * d + c0) = outv;
+  *reinterpret_cast<uint4*>(l0 + c0) = r1;
+  *reinterpret_cast<uint4*>(l1 + c0) = nv;
 }
 
 extern "C" int kch_layernorm_short_conv_step(const void* x, const void* ln_weight, const void* ln_bias, float eps,
@@ -438,17 +492,12 @@ extern "C" int kch_layernorm_short_conv_step(const void* x, const void* ln_weigh
   KCH_REQUIRE(B >= 1 && x && lookback && y, "kch_layernorm_short_conv_step: B=%d", B);
   const uintptr_t al = (uintptr_t)x | (uintptr_t)y | (uintptr_t)conv_weight | (uintptr_t)conv_bias | (uintptr_t)lookback;
   KCH_REQUIRE((al & 15) == 0, "kch_layernorm_short_conv_step: operands must be 16-byte aligned");
+  KCH_REQUIRE(((((uintptr_t)ln_weight) | ((uintptr_t)ln_bias)) & 15) == 0,
+              "kch_layernorm_short_conv_step: LayerNorm parameters must be 16-byte aligned");
   cudaStream_t s = kch_stream(stream);
-  dim3 grid((unsigned)((B + 3) / 4));
-#define LSV(NV)                                                                                                    \
-  KCH_DISPATCH_FLOAT(wdtype, TW, (ln_conv_step_kernel_bf16<TW, NV><<<grid, 128, 0, s>>>(                            \
-      (const bf16*)x, (const TW*)ln_weight, (const TW*)ln_bias, eps, (bf16*)lookback, (const bf16*)conv_weight,    \
-      (const bf16*)conv_bias, (bf16*)y, B, d)))
-  switch (d / 256) {
-    case 1: LSV(1); break; case 2: LSV(2); break; case 3: LSV(3); break; case 4: LSV(4); break;
-    case 5: LSV(5); break; case 6: LSV(6); break; case 7: LSV(7); break; default: LSV(8); break;
-  }
-#undef LSV
+  KCH_DISPATCH_FLOAT(wdtype, TW, (ln_conv_step_kernel_bf16<TW><<<(unsigned)B, 256, 0, s>>>(
+      (const bf16*)x, (const TW*)ln_weight, (const TW*)ln_bias, eps, (bf16*)lookback, (const bf16*)conv_weight,
+      (const bf16*)conv_bias, (bf16*)y, d)));
   KCH_LAUNCH_OK();
   return KCH_OK;
 }
