@@ -50,6 +50,9 @@ long long kch_launch_count(int reset);      /* kernels launched by this library 
  * returns at its first poll, so read and clear it before launching real work.  No counterpart in the reference
  * (it has no device code): its nearest relative is the non-finite-output warning, ops_kda.py:151-172. */
 #define KCH_STATUS_SELFTEST_WAIT 0x5E1F
+#define KCH_STATUS_GEMM_DECODE 0x6D01   /* status word: a wait of the decode-batch GEMM (operands / accumulator) expired */
+#define KCH_STATUS_KDA_STEP 0x6D03       /* status word: the state copy of the one-token KDA step did not arrive */
+#define KCH_STATUS_INDEXER_DECODE 0x6D02 /* status word: a wait of the one-token indexer (key tiles / accumulator) expired */
 int kch_selftest_bounded_wait(unsigned int limit_polls, unsigned int* polls_out, void* stream);
 
 /* ---- layer glue ---------------------------------------------------------------------------- */

@@ -588,6 +588,23 @@ int kch_make_tensor_map_2d_bf16(CUtensorMap* map, const void* base, uint64_t row
   return make_map_2d(map, base, rows, cols, ld_elems, box_rows, box_cols);
 }
 
+// bf16 [rows][64 * katoms] matrix seen as {64 elements, rows, katoms}: a box of `box_katoms` k-blocks lands as that
+// many consecutive [box_rows x 128 bytes] stages under the 128-byte swizzle (one copy instead of one per k-block)
+int kch_make_tensor_map_katoms_bf16(CUtensorMap* map, const void* base, uint64_t rows, uint64_t katoms, uint64_t ld_elems,
+                                    uint32_t box_rows, uint32_t box_katoms) {
+  PFN_cuTensorMapEncodeTiled_v12000 enc = get_encode_fn();
+  if (!enc) { kch_set_error("cuTensorMapEncodeTiled is not available from the driver"); return KCH_ERR_CUDA; }
+  cuuint64_t gdim[3] = {64, rows, katoms};
+  cuuint64_t gstr[2] = {ld_elems * 2, 128};
+  cuuint32_t box[3] = {64, box_rows, box_katoms};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), gdim, gstr, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) { kch_set_error("cuTensorMapEncodeTiled (k-block view) failed with code %d", (int)r); return KCH_ERR_CUDA; }
+  return KCH_OK;
+}
+
 bool kch_linear_tcgen05_supported(const void* A, const void* W, const void* C, const void* R, int64_t M, int N,
                                   int K, int64_t lda, int64_t ldw, int64_t ldc, int64_t ldr, int dtype) {
   if (dtype != KCH_BF16) return false;
@@ -711,6 +728,9 @@ bool kch_linear_tcgen05_epilogue_ok(const kch_epilogue* e, int N) {
   return start == N;
 }
 
+int kch_linear_decode_tc5(const void* A, const void* W, void* C, const void* R, int64_t M, int N, int K, int64_t lda,
+                          int64_t ldw, int64_t ldc, int64_t ldr, const kch_epilogue* e, void* stream);
+
 int kch_linear_tcgen05(const void* A, const void* W, void* C, const void* R, int64_t M, int N, int K, int64_t lda,
                        int64_t ldw, int64_t ldc, int64_t ldr, const kch_epilogue* e, void* stream, int slab_k) {
   cudaStream_t s = kch_stream(stream);
@@ -718,6 +738,11 @@ int kch_linear_tcgen05(const void* A, const void* W, void* C, const void* R, int
   if (e && e->n_segments) {
     ep.nseg = e->n_segments;
     for (int i = 0; i < e->n_segments; ++i) { ep.seg_end[i] = e->seg_end[i]; ep.seg_act[i] = e->seg_act[i]; ep.seg_param[i] = e->seg_param[i]; }
+  }
+  if (M <= 64 && slab_k == 0) {
+    // a decode batch: the kernel built for it (one copy per operand, K split over a cluster); -100 = not its shape
+    const int rc = kch_linear_decode_tc5(A, W, C, R, M, N, K, lda, ldw, ldc, ldr, e, stream);
+    if (rc != -100) return rc;
   }
   if (M <= TG_BM && N > 128) {
     // One row of tiles (a decode batch): the launch is a weight stream, so spread it over many SMs with

@@ -1214,6 +1214,10 @@ decode_indexer_logits_mma_kernel(const void* __restrict__ q, int q_dtype, int64_
   }
 }
 
+int kch_decode_indexer_logits_tc5(const void* q, int q_dtype, int64_t q_ld, const void* keys, const float* norms,
+                                  const void* w, int w_dtype, int64_t w_ld, float* logits, int B, int64_t cap, int64_t n_ld,
+                                  int HI, int normalize, float scale, int m, const int32_t* ctr, cudaStream_t s);
+
 extern "C" int64_t kch_decode_indexer_workspace_bytes(int B, int64_t capacity) {
   if (B < 1 || capacity < 1) return 0;
   return (int64_t)B * ((capacity + 3) & ~3LL) * 4;
@@ -1247,13 +1251,23 @@ extern "C" int kch_decode_indexer_topk(const void* q_idx, int q_dtype, int64_t q
 #define GO(T_, V_) decode_indexer_logits_kernel<T_, V_><<<grid, 256, 0, s>>>(q_idx, q_dtype, q_ld, (const T_*)keys, k_norms, \
       w, w_dtype, w_ld, logits, capacity, n_ld, HI, DI, normalize, scale, m, counters)
   static const bool force_simt = [] { const char* e = getenv("KCH_INDEXER_DECODE"); return e && e[0] == 's'; }();
-  if (!force_simt && k_dtype == KCH_BF16 && DI == 64 && HI <= 8 && ((uintptr_t)keys & 15) == 0)
-    decode_indexer_logits_mma_kernel<<<grid, 256, 0, s>>>(q_idx, q_dtype, q_ld, (const bf16*)keys, k_norms, w, w_dtype, w_ld,
-                                                          logits, capacity, n_ld, HI, normalize, scale, m, counters);
-  else if (k_dtype == KCH_BF16) { if (vec) GO(bf16, true); else GO(bf16, false); }
-  else { if (vec) GO(float, true); else GO(float, false); }
+  // (KCH_INDEXER_DECODE=m keeps the mma.sync kernel, =s the scalar one, for comparison)
+  static const bool force_mma = [] { const char* e = getenv("KCH_INDEXER_DECODE"); return e && e[0] == 'm'; }();
+  int tc5_rc = -100;
+  if (!force_simt && !force_mma && k_dtype == KCH_BF16 && DI == 64 && HI <= 8)
+    tc5_rc = kch_decode_indexer_logits_tc5(q_idx, q_dtype, q_ld, keys, k_norms, w, w_dtype, w_ld, logits, B, capacity, n_ld, HI,
+                                           normalize, scale, m, counters, s);
+  if (tc5_rc != -100) {
+    if (tc5_rc != KCH_OK) return tc5_rc;
+  } else {
+    if (!force_simt && k_dtype == KCH_BF16 && DI == 64 && HI <= 8 && ((uintptr_t)keys & 15) == 0)
+      decode_indexer_logits_mma_kernel<<<grid, 256, 0, s>>>(q_idx, q_dtype, q_ld, (const bf16*)keys, k_norms, w, w_dtype, w_ld,
+                                                            logits, capacity, n_ld, HI, normalize, scale, m, counters);
+    else if (k_dtype == KCH_BF16) { if (vec) GO(bf16, true); else GO(bf16, false); }
+    else { if (vec) GO(float, true); else GO(float, false); }
+    KCH_LAUNCH_OK();
+  }
 #undef GO
-  KCH_LAUNCH_OK();
   // rows of up to 8 x 256 x 32 logits: a cluster of eight CTAs per row (KCH_SELECT_DECODE=s keeps one CTA per row)
   static const bool one_cta = [] { const char* e = getenv("KCH_SELECT_DECODE"); return e && e[0] == 's'; }();
   const int e_needed = (int)((((capacity + SC_CTAS * 256 - 1) / (SC_CTAS * 256)) + 3) & ~3LL);

@@ -3,8 +3,10 @@
 //   chunked WY form  : naive_chunk_kda     (ops_kda.py:375-424 prepare, 509-535 chain)
 // All arithmetic is fp32; inputs are fp32 or bf16; the carried state is fp32 [B,HV,K,V].
 #include <math.h>
+#include <stdlib.h>
 
 #include "kch_common.cuh"
+#include "mma_utils.cuh"
 
 // =====================================================================================
 // Token recurrence.  One CTA owns 32 value columns of one (batch, value head); its 4 warps
@@ -83,6 +85,87 @@ kda_recurrent_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* 
   }
 }
 
+// One-token step (T = 1, K = V = 128), the form a decode step takes.  The 64 KB state of one (batch, value head) is
+// contiguous: one bulk copy brings it into shared memory (no registers, no per-thread loads: three CTAs per SM keep
+// 192 KB of requests in flight), one thread per value column walks its 128 K rows there -- the two contractions over
+// K (k^T S and q^T S) are private sums, no exchange between warps -- and one bulk copy writes the state back.  Decay,
+// key and scaled query of a K row travel as one float4 broadcast.  The sums are taken in the same order as
+// kda_recurrent_kernel (four runs of 32 rows, added left to right), so both kernels return the same bits.
+// The wait for the copy is bounded (status word, see kch_device_status).
+#define KDS_STATE_BYTES (128 * 128 * 4)
+#define KDS_SMEM (KDS_STATE_BYTES + 128 * 16 + 16)
+template <typename T>
+__global__ void __launch_bounds__(128)
+kda_decode_step_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v,
+                       const T* __restrict__ g, const T* __restrict__ beta, const float* S0, T* __restrict__ o,
+                       float* S_out, int H, int HV, float scale, float g_min, int64_t ld_qk, int64_t ld_v,
+                       int64_t ld_g, int64_t ld_b, unsigned int* status) {
+  constexpr int K = 128, V = 128;
+  extern __shared__ __align__(128) uint8_t kds_raw[];
+  float* st = reinterpret_cast<float*>(kds_raw);                                   // [K][V]
+  float4* sgkq = reinterpret_cast<float4*>(kds_raw + KDS_STATE_BYTES);             // {exp(g), k, scale * q, -} of K row i
+  uint64_t* bar = reinterpret_cast<uint64_t*>(kds_raw + KDS_STATE_BYTES + 128 * 16);
+  const int hv = blockIdx.x, b = blockIdx.y, tid = threadIdx.x;
+  const int h = hv / (HV / H);
+  const int64_t sbase = ((int64_t)b * HV + hv) * K * V;
+  if (tid == 0) {
+    mbarrier_init(bar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    if (S0) {
+      mbarrier_expect_tx(bar, KDS_STATE_BYTES);
+      bulk_copy_g2s(st, S0 + sbase, KDS_STATE_BYTES, bar);
+    }
+  }
+  {
+    const int64_t qoff = (int64_t)b * ld_qk + (int64_t)h * K, goff = (int64_t)b * ld_g + (int64_t)hv * K;
+    sgkq[tid] = make_float4(expf(fmaxf(ldf(g + goff + tid), g_min)), ldf(k + qoff + tid), ldf(q + qoff + tid) * scale, 0.f);
+  }
+  const float bt = ldf(beta + (int64_t)b * ld_b + hv);
+  const float vv = ldf(v + (int64_t)b * ld_v + (int64_t)hv * V + tid);
+  if (!S0) {
+    for (int i = 0; i < K; ++i) st[i * V + tid] = 0.f;
+  }
+  __syncthreads();
+  bool ok = true;
+  if (S0) ok = mbarrier_wait_bounded(bar, 0, KCH_STATUS_KDA_STEP, 1u << 24, status);
+  float* col = st + tid;
+  float p[4], r[4];
+#pragma unroll
+  for (int run = 0; run < 4; ++run) {
+    float acc = 0.f;
+#pragma unroll 8
+    for (int i = 32 * run; i < 32 * run + 32; ++i) {
+      const float4 c = sgkq[i];
+      acc = fmaf(c.y, col[i * V] * c.x, acc);
+    }
+    p[run] = acc;
+  }
+  const float delta = bt * (vv - (p[0] + p[1] + p[2] + p[3]));
+#pragma unroll
+  for (int run = 0; run < 4; ++run) {
+    float acc = 0.f;
+#pragma unroll 8
+    for (int i = 32 * run; i < 32 * run + 32; ++i) {
+      const float4 c = sgkq[i];
+      const float sv = fmaf(c.y, delta, col[i * V] * c.x);
+      col[i * V] = sv;
+      acc = fmaf(c.z, sv, acc);
+    }
+    r[run] = acc;
+  }
+  if (ok) stf(o + ((int64_t)b * HV + hv) * V + tid, r[0] + r[1] + r[2] + r[3]);
+  if (S_out) {
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");       // the bulk store reads what the threads wrote
+    __syncthreads();
+    if (tid == 0 && ok) {
+      asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
+                   ::"l"(S_out + sbase), "r"(smem_addr_u32(st)), "r"((uint32_t)KDS_STATE_BYTES) : "memory");
+      asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+      asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");   // shared memory must outlive the copy
+    }
+  }
+}
+
 extern "C" int kch_kda_recurrent(const void* q, const void* k, const void* v, const void* g,
                                  const void* beta, const float* initial_state, void* o,
                                  float* final_state, int B, int T, int H, int HV, int K, int V,
@@ -102,6 +185,20 @@ extern "C" int kch_kda_recurrent(const void* q, const void* k, const void* v, co
   if (T == 0 && !final_state) return KCH_OK;
   dim3 grid((V + 31) / 32, HV, B), block(128);
   cudaStream_t s = kch_stream(stream);
+  // (KCH_KDA_DECODE=o keeps the general kernel for the one-token step, for comparison)
+  static const bool old_step = [] { const char* e = getenv("KCH_KDA_DECODE"); return e && e[0] == 'o'; }();
+  if (T == 1 && K == 128 && V == 128 && !old_step && (((uintptr_t)initial_state | (uintptr_t)final_state) & 15) == 0) {
+    unsigned int* status = kch_status_device_ptr();
+    KCH_REQUIRE(status != nullptr, "kch_kda_recurrent: cannot resolve the device status word");
+    KCH_DISPATCH_FLOAT(dtype, T_, {
+      KCH_CUDA_OK(cudaFuncSetAttribute(kda_decode_step_kernel<T_>, cudaFuncAttributeMaxDynamicSharedMemorySize, KDS_SMEM));
+      kda_decode_step_kernel<T_><<<dim3(HV, B), 128, KDS_SMEM, s>>>(
+        (const T_*)q, (const T_*)k, (const T_*)v, (const T_*)g, (const T_*)beta, initial_state, (T_*)o, final_state, H, HV,
+        scale, g_clamp_min, ld_qk, ld_v, ld_g, ld_beta, status);
+    });
+    KCH_LAUNCH_OK();
+    return KCH_OK;
+  }
   int kpt = (K + 3) / 4;
 #define GO(T_, KPT)                                                                              \
   kda_recurrent_kernel<T_, KPT><<<grid, block, 0, s>>>((const T_*)q, (const T_*)k, (const T_*)v, \
