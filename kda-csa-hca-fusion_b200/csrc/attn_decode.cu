@@ -307,12 +307,28 @@ __global__ void __launch_bounds__(ADM_WARPS * 32) attn_decode_mma_kernel(AdArgs 
   const int my_tiles = tile_hi > tile_lo + warp ? (tile_hi - tile_lo - warp + ADM_WARPS - 1) / ADM_WARPS : 0;
   const int32_t* selrow = a.sel ? a.sel + (int64_t)b * a.topk : nullptr;
   // ---- the query, normalised in fp32, as two bf16 terms (the whole CTA shares it) ----------------------------
-  for (int h = warp; h < 16; h += ADM_WARPS) {
-    float v[4] = {0.f, 0.f, 0.f, 0.f};
-    if (h < a.nh) {
+  auto fetch_id = [&](int t_local) -> int {
+    if (t_local >= my_tiles) return -1;
+    const int tile = tile_lo + warp + t_local * ADM_WARPS;
+    const int e = tile * ADM_TILE + lane;
+    if (tile * ADM_TILE >= ns_pad || e >= ns) return -1;
+    return selrow ? selrow[e] : e;
+  };
+  int id_pre[ADM_STAGES];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) v[i] = ld_any(a.q, (int64_t)b * a.q_ld + h * AD_C + lane * 4 + i, a.q_dtype);
-    }
+  for (int s2 = 0; s2 < ADM_STAGES; ++s2) id_pre[s2] = fetch_id(s2);       // with the query loads below: one round trip
+  float qv[16 / ADM_WARPS][4];                         // every head's loads are in flight before the first norm
+#pragma unroll
+  for (int hh = 0; hh < 16 / ADM_WARPS; ++hh) {
+    const int h = warp + hh * ADM_WARPS;
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+      qv[hh][i] = h < a.nh ? ld_any(a.q, (int64_t)b * a.q_ld + h * AD_C + lane * 4 + i, a.q_dtype) : 0.f;
+  }
+#pragma unroll
+  for (int hh = 0; hh < 16 / ADM_WARPS; ++hh) {
+    const int h = warp + hh * ADM_WARPS;
+    float v[4] = {qv[hh][0], qv[hh][1], qv[hh][2], qv[hh][3]};
     if (a.q_normalize) {
       const float nrm = fmaxf(sqrtf(warp_sum(v[0] * v[0] + v[1] * v[1] + v[2] * v[2] + v[3] * v[3])), 1e-12f);
 #pragma unroll
@@ -339,22 +355,25 @@ __global__ void __launch_bounds__(ADM_WARPS * 32) attn_decode_mma_kernel(AdArgs 
   }
   // ---- tile streaming -----------------------------------------------------------------------------------
   // lane e of tile t resolves entry 32 t + e: row pointer (nullptr = invalid, zero-filled), value factors va / vb
-  struct Meta { float va, vb; uint32_t valid; bool q8; };
-  auto issue_tile = [&](int t_local, Meta& mt) {
+  // The chain selected index -> row address -> row bytes is two dependent round trips per tile; they are taken apart:
+  // the index of a tile is fetched one tile ahead of the copy that needs it (`fetch_id`), and the row's norm and scales
+  // are only loaded at issue time -- the division happens when the tile is consumed, two tiles later.
+  struct Meta { float va, vb, nrm; uint32_t valid; bool q8; };    // value factors are va / nrm, vb / nrm
+  auto issue_tile = [&](int t_local, int id, Meta& mt) {
     const int tile = tile_lo + warp + t_local * ADM_WARPS;
     const int e = tile * ADM_TILE + lane;
     const bool comp_tile = tile * ADM_TILE < ns_pad;
     const uint8_t* p = nullptr;
     mt.va = mt.vb = 0.f;
+    mt.nrm = 1.f;
     if (comp_tile) {
       if (e < ns) {
-        const int id = selrow ? selrow[e] : e;
         if (id >= 0 && id < nvis) {
           const int64_t row = (int64_t)b * a.cap + id;
           p = (const uint8_t*)a.comp + row * (Q8 ? AD_C : AD_C * 2);
-          const float nrm = a.comp_norms[row];
-          if (Q8) { mt.va = a.comp_scales[row * 2] / nrm; mt.vb = a.comp_scales[row * 2 + 1] / nrm; }
-          else { mt.va = mt.vb = 1.f / nrm; }
+          mt.nrm = a.comp_norms[row];
+          if (Q8) { mt.va = a.comp_scales[row * 2]; mt.vb = a.comp_scales[row * 2 + 1]; }
+          else { mt.va = mt.vb = 1.f; }
         }
       }
     } else if (e - ns_pad < nw) {
@@ -387,11 +406,12 @@ __global__ void __launch_bounds__(ADM_WARPS * 32) attn_decode_mma_kernel(AdArgs 
   };
   Meta meta[ADM_STAGES];
 #pragma unroll
-  for (int s2 = 0; s2 < ADM_STAGES; ++s2) { meta[s2].va = meta[s2].vb = 0.f; meta[s2].valid = 0; meta[s2].q8 = false; }
+  for (int s2 = 0; s2 < ADM_STAGES; ++s2) { meta[s2].va = meta[s2].vb = 0.f; meta[s2].nrm = 1.f; meta[s2].valid = 0; meta[s2].q8 = false; }
 #pragma unroll
   for (int s2 = 0; s2 < ADM_STAGES - 1; ++s2) {
-    if (s2 < my_tiles) issue_tile(s2, meta[s2]); else adm_commit();
+    if (s2 < my_tiles) issue_tile(s2, id_pre[s2], meta[s2]); else adm_commit();
   }
+  int id_next = id_pre[ADM_STAGES - 1];                                    // index of tile t + ADM_STAGES - 1, fetched a tile ahead
   const float ascale = fabsf(a.scale);
   float sink0 = -INFINITY, sink1 = -INFINITY;
   if (a.sink) {
@@ -409,15 +429,18 @@ __global__ void __launch_bounds__(ADM_WARPS * 32) attn_decode_mma_kernel(AdArgs 
   for (int t = 0; t < my_tiles; ++t) {
     {
       const int nt = t + ADM_STAGES - 1;
-      Meta mt; mt.va = mt.vb = 0.f; mt.valid = 0; mt.q8 = false;
-      if (nt < my_tiles) issue_tile(nt, mt); else adm_commit();
+      Meta mt; mt.va = mt.vb = 0.f; mt.nrm = 1.f; mt.valid = 0; mt.q8 = false;
+      if (nt < my_tiles) issue_tile(nt, id_next, mt); else adm_commit();
+      id_next = fetch_id(nt + 1);
       // the register array is indexed with compile-time constants only
       if (nt % ADM_STAGES == 0) meta[0] = mt; else if (nt % ADM_STAGES == 1) meta[1] = mt; else meta[2] = mt;
     }
     adm_wait<ADM_STAGES - 1>();
     __syncwarp();
     const int st = t % ADM_STAGES;
-    const Meta mt = st == 0 ? meta[0] : (st == 1 ? meta[1] : meta[2]);
+    Meta mt = st == 0 ? meta[0] : (st == 1 ? meta[1] : meta[2]);
+    mt.va = mt.va / mt.nrm;                       // same operands as scale / norm (1 / norm for bf16 rows)
+    mt.vb = mt.vb / mt.nrm;
     any_valid |= mt.valid != 0;
     uint32_t tb = ring + (uint32_t)st * ADM_STAGE_BYTES;
     if (Q8 && mt.q8) {
