@@ -318,12 +318,41 @@ __global__ void __launch_bounds__(ADM_WARPS * 32) attn_decode_mma_kernel(AdArgs 
 #pragma unroll
   for (int s2 = 0; s2 < ADM_STAGES; ++s2) id_pre[s2] = fetch_id(s2);       // with the query loads below: one round trip
   float qv[16 / ADM_WARPS][4];                         // every head's loads are in flight before the first norm
+  if (a.q_dtype == KCH_BF16 && ((((uintptr_t)a.q) | (uintptr_t)(a.q_ld * 2)) & 7) == 0) {
+    // raw 8-byte loads first, conversions after: a conversion next to its load would wait for it, head after head
+    uint2 raw[16 / ADM_WARPS];
 #pragma unroll
-  for (int hh = 0; hh < 16 / ADM_WARPS; ++hh) {
-    const int h = warp + hh * ADM_WARPS;
+    for (int hh = 0; hh < 16 / ADM_WARPS; ++hh) {
+      const int h = min(warp + hh * ADM_WARPS, a.nh - 1);
+      raw[hh] = *reinterpret_cast<const uint2*>((const bf16*)a.q + (int64_t)b * a.q_ld + h * AD_C + lane * 4);
+    }
 #pragma unroll
-    for (int i = 0; i < 4; ++i)
-      qv[hh][i] = h < a.nh ? ld_any(a.q, (int64_t)b * a.q_ld + h * AD_C + lane * 4 + i, a.q_dtype) : 0.f;
+    for (int hh = 0; hh < 16 / ADM_WARPS; ++hh) {
+      const bool on = warp + hh * ADM_WARPS < a.nh;
+      qv[hh][0] = on ? __uint_as_float(raw[hh].x << 16) : 0.f; qv[hh][1] = on ? __uint_as_float(raw[hh].x & 0xFFFF0000u) : 0.f;
+      qv[hh][2] = on ? __uint_as_float(raw[hh].y << 16) : 0.f; qv[hh][3] = on ? __uint_as_float(raw[hh].y & 0xFFFF0000u) : 0.f;
+    }
+  } else if (a.q_dtype == KCH_F32 && ((((uintptr_t)a.q) | (uintptr_t)(a.q_ld * 4)) & 15) == 0) {
+    float4 raw[16 / ADM_WARPS];
+#pragma unroll
+    for (int hh = 0; hh < 16 / ADM_WARPS; ++hh) {
+      const int h = min(warp + hh * ADM_WARPS, a.nh - 1);
+      raw[hh] = *reinterpret_cast<const float4*>((const float*)a.q + (int64_t)b * a.q_ld + h * AD_C + lane * 4);
+    }
+#pragma unroll
+    for (int hh = 0; hh < 16 / ADM_WARPS; ++hh) {
+      const bool on = warp + hh * ADM_WARPS < a.nh;
+      qv[hh][0] = on ? raw[hh].x : 0.f; qv[hh][1] = on ? raw[hh].y : 0.f;
+      qv[hh][2] = on ? raw[hh].z : 0.f; qv[hh][3] = on ? raw[hh].w : 0.f;
+    }
+  } else {
+#pragma unroll
+    for (int hh = 0; hh < 16 / ADM_WARPS; ++hh) {
+      const int h = warp + hh * ADM_WARPS;
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        qv[hh][i] = h < a.nh ? ld_any(a.q, (int64_t)b * a.q_ld + h * AD_C + lane * 4 + i, a.q_dtype) : 0.f;
+    }
   }
 #pragma unroll
   for (int hh = 0; hh < 16 / ADM_WARPS; ++hh) {
