@@ -8,10 +8,12 @@
 Workload ("hybrid_prefill_c4"): the 5-layer KDA-KDA-KDA-CSA-HCA stack, d_model 2048, 16 heads x 128,
 KDA chunk 64, CSA m=4 / top-k 1024 / 4x64 indexer / window 128 / sink, HCA ratio 128 / window 128 / sink,
 bf16, batch 4 x T=32768 of synthetic N(0,1) hidden states, random-init N(0,0.02) weights.  One step is
-one forward pass over the whole batch.  With N > 1 the total work stays fixed (strong scaling) and the heads are
-sharded over the GPUs (tensor parallel: 16/N heads per GPU, one all-gather of head outputs per layer).  The sequences
-of a batch are independent as well; `--dp-sequences` deals them out to the GPUs first (replicas with no exchange on
-the data path) and only splits heads beyond the batch size -- an extra, not the configuration of the metric.
+one forward pass over the whole batch.  With N > 1 the total work stays fixed (strong scaling) and every layer is
+tensor parallel with one all-gather per layer: the KDA layers by heads (16/N heads per GPU), the CSA / HCA layers by
+query rows (`--tp-attn rows`, the default: their indexer, top-k and row gathers cost the same whatever the head count,
+so only the row axis divides them) or by heads as well (`--tp-attn heads`); the mode that was not asked for is timed in
+the same run and reported as `tp_variant`.  The sequences of a batch are independent as well; `--dp-sequences` deals
+them out to the GPUs first (replicas with no exchange on the data path) -- an extra, not the configuration of the metric.
 
 The JSON line carries: the device-timed value, `e2e` (host buffers, H2D + D2H inside the timed region,
 through the public module API), `roofline` for the dominant kernel (the tcgen05 GEMM) measured with CUDA
@@ -572,10 +574,11 @@ def main():
     ap.add_argument("--no-decode", action="store_true")
     ap.add_argument("--dp-sequences", action="store_true",
                     help="N > 1: deal the sequences of the batch out to the GPUs first (replicas), heads only beyond")
-    ap.add_argument("--tp-only", action="store_true", help="accepted for compatibility: heads-only is the default")
-    ap.add_argument("--tp-attn", default="heads", choices=["heads", "rows"],
-                    help="N > 1: how the CSA / HCA layers are divided: query heads like KDA (default), or the query rows "
-                         "(their indexer, top-k and gathers do not shrink with the head count); KDA is always by heads")
+    ap.add_argument("--tp-only", action="store_true", help="accepted for compatibility: tensor parallelism is the default")
+    ap.add_argument("--tp-attn", default="rows", choices=["heads", "rows"],
+                    help="N > 1: how the CSA / HCA layers are divided: the query rows (default: their indexer, top-k and "
+                         "gathers do not shrink with the head count), or query heads like KDA; KDA is always by heads, "
+                         "and either way there is one all-gather per layer.  The other mode is timed too (tp_variant)")
     ap.add_argument("--no-peer-gather", action="store_true",
                     help="N > 1: keep the NCCL all-gather in the decode steps (default: plain peer stores when available)")
     ap.add_argument("--no-variant", action="store_true", help="N > 1: skip the extra timing of the other --tp-attn mode")

@@ -47,6 +47,28 @@ def run(kind, dev="cuda:0"):
         w = (torch.randn(772, 2048, generator=g) * 0.05).bfloat16().to(dev)
         r = torch.randn(1000, 772, generator=g).bfloat16().to(dev)
         return linear(x, w, residual=r).float().cpu()
+    if kind == "select":        # odd number of rows, rows shorter than top-k, ties (relu zeros): exact indices
+        from kch_b200.csa import indexer_topk
+        B, T, HI, DI, m, topk = 1, 1531, 4, 64, 1, 256
+        qi = torch.randn(B, T, HI, DI, generator=g).bfloat16().to(dev)
+        ki = torch.randn(B, T // m, DI, generator=g).to(dev)
+        wi = (torch.randn(B, T, HI, generator=g) * 0.1).to(dev)
+        idx = indexer_topk(qi, ki, wi, topk, m=m, normalize_qk=True, sorted_output=False)
+        return idx.sort(dim=-1).values.float().cpu()
+    if kind == "decode_step":   # one-token steps of the small stack: indexer, KDA step, decode GEMMs, attention
+        cfg = kch_b200.HybridConfig(d_model=256, n_heads_qk=2, n_heads_v=2, head_dim_k=128, head_dim_v=128, kda_chunk_size=64,
+                                    csa_m=4, csa_topk=64, csa_nh=4, csa_c=128, csa_dc=64, csa_nIh=2, csa_cI=64,
+                                    csa_sliding_window=16, hca_m2=16, hca_nh=4, hca_c=128, hca_dc=64, hca_sliding_window=16)
+        model = kch_b200.HybridKCHAttention(cfg, 5)
+        model.load_state_dict(syn.hybrid_params(91, cfg, 5, dtype=torch.bfloat16), strict=True)
+        model = model.bfloat16().to(dev).eval()
+        x = syn.hidden_states(92, 3, 120, cfg.d_model, torch.bfloat16).to(dev)
+        dec = kch_b200.HybridDecoding(model=model, use_cuda_graph=False)
+        dec.reset()
+        ys = [dec(x[:, :70])]
+        for t in range(70, 120):
+            ys.append(dec(x[:, t:t + 1]))
+        return torch.cat(ys, 1).float().cpu()
     raise ValueError(kind)
 
 
