@@ -45,7 +45,8 @@
 struct PrepArgs {
   const bf16 *q, *k, *v, *g, *beta;
   uint8_t* ws;
-  int T, H, HV, NT;
+  int T, H, HV, NT;                  // T: tokens from the first chunk of this launch to the end of the sequence
+  int Tb;                            // tokens between consecutive batch entries (the whole sequence length)
   float scale, g_min;
   float gate_scale;                  // != 0: g holds the gate's pre-activation x; the decay is -softplus(x) * gate_scale
   int umma;                          // 1: operand tiles in the tcgen05 layout (see kda_scan_tc5.cu) instead of the ldmatrix one
@@ -85,9 +86,9 @@ __device__ __forceinline__ void kda_prepare_chunk_mma(const PrepArgs& a, uint8_t
   const int t0 = n * KM_C;
   const int64_t bh = (int64_t)b * a.HV + hv;
   uint8_t* wsc = a.ws + (bh * a.NT + n) * (int64_t)KM_CHUNK_BYTES;
-  auto qk_off = [&](int i) { return ((int64_t)b * a.T + t0 + i) * a.ld_qk + (int64_t)h * KM_K; };
-  auto g_off = [&](int i) { return ((int64_t)b * a.T + t0 + i) * a.ld_g + (int64_t)hv * KM_K; };
-  auto v_off = [&](int i) { return ((int64_t)b * a.T + t0 + i) * a.ld_v + (int64_t)hv * KM_V; };
+  auto qk_off = [&](int i) { return ((int64_t)b * a.Tb + t0 + i) * a.ld_qk + (int64_t)h * KM_K; };
+  auto g_off = [&](int i) { return ((int64_t)b * a.Tb + t0 + i) * a.ld_g + (int64_t)hv * KM_K; };
+  auto v_off = [&](int i) { return ((int64_t)b * a.Tb + t0 + i) * a.ld_v + (int64_t)hv * KM_V; };
   auto load8 = [&](const bf16* p, bool ok, float (&out)[8]) {
     uint4 raw = make_uint4(0u, 0u, 0u, 0u);
     if (ok) raw = *reinterpret_cast<const uint4*>(p);
@@ -117,7 +118,7 @@ __device__ __forceinline__ void kda_prepare_chunk_mma(const PrepArgs& a, uint8_t
     dst[0] = make_float4(gv[0], gv[1], gv[2], gv[3]);
     dst[1] = make_float4(gv[4], gv[5], gv[6], gv[7]);
   }
-  if (tid < KM_C) sbeta[tid] = (t0 + tid < a.T) ? __bfloat162float(a.beta[((int64_t)b * a.T + t0 + tid) * a.ld_b + hv]) : 0.f;
+  if (tid < KM_C) sbeta[tid] = (t0 + tid < a.T) ? __bfloat162float(a.beta[((int64_t)b * a.Tb + t0 + tid) * a.ld_b + hv]) : 0.f;
   for (int idx = tid; idx < KM_C * PS_LD; idx += 256) { sA[idx] = 0.f; sQ[idx] = 0.f; }
   // Every elementwise stage below maps thread -> (row r0 + 16*s, 8-channel chunk c8) with r0 = tid/16 and
   // c8 = tid%16, so the k and q values a thread ever needs are these 4 x 8: keep them in registers.
@@ -687,16 +688,41 @@ __global__ void __launch_bounds__(160, 1) kda_scan_mma_kernel(ScanArgs a) {
 // ---- host -------------------------------------------------------------------------------------------
 bool kch_kda_scan_tc5_enabled();      // kda_scan_tc5.cu
 int kch_kda_scan_tc5(const void* workspace, const float* initial_state, void* o, float* final_state, int B, int T,
-                     int HV, int NT, unsigned int* status, cudaStream_t s);
+                     int Tb, int HV, int NT, unsigned int* status, cudaStream_t s);
 
 bool kch_kda_mma_supported(int K, int V, int chunk_size, float g_clamp_min, int dtype) {
   static const bool force_generic = [] { const char* e = getenv("KCH_KDA"); return e && e[0] == 'g'; }();
   return !force_generic && dtype == KCH_BF16 && K == KM_K && V == KM_V && chunk_size == KM_C && g_clamp_min >= -10.0f;
 }
 
+// chunk records, then one fp32 state per (batch, head): the carry between the segments of a long sequence
 int64_t kch_kda_mma_workspace_bytes(int B, int T, int HV) {
   int64_t NT = (T + KM_C - 1) / KM_C;
-  return (int64_t)B * HV * NT * KM_CHUNK_BYTES;
+  return (int64_t)B * HV * NT * KM_CHUNK_BYTES + (int64_t)B * HV * KM_K * KM_V * 4;
+}
+
+// Side stream and events of the segmented driver below (one set per device, created on first use).
+#define KM_MAX_SEG 8
+struct KmSideStream {
+  cudaStream_t hp = nullptr;
+  cudaEvent_t prep_done[KM_MAX_SEG] = {};
+  cudaEvent_t scan_done = nullptr;
+};
+static int km_side_stream(KmSideStream** out) {
+  static KmSideStream per_dev[16];
+  int dev = 0;
+  KCH_CUDA_OK(cudaGetDevice(&dev));
+  KCH_REQUIRE(dev >= 0 && dev < 16, "kch_kda_chunk: device ordinal %d", dev);
+  KmSideStream& ss = per_dev[dev];
+  if (!ss.hp) {
+    int least = 0, greatest = 0;
+    KCH_CUDA_OK(cudaDeviceGetStreamPriorityRange(&least, &greatest));
+    KCH_CUDA_OK(cudaStreamCreateWithPriority(&ss.hp, cudaStreamNonBlocking, greatest));
+    for (int i = 0; i < KM_MAX_SEG; ++i) KCH_CUDA_OK(cudaEventCreateWithFlags(&ss.prep_done[i], cudaEventDisableTiming));
+    KCH_CUDA_OK(cudaEventCreateWithFlags(&ss.scan_done, cudaEventDisableTiming));
+  }
+  *out = &ss;
+  return KCH_OK;
 }
 
 int kch_kda_chunk_mma(const void* q, const void* k, const void* v, const void* g, const void* beta,
@@ -713,7 +739,7 @@ int kch_kda_chunk_mma(const void* q, const void* k, const void* v, const void* g
   cudaStream_t s = kch_stream(stream);
   PrepArgs pa;
   pa.q = (const bf16*)q; pa.k = (const bf16*)k; pa.v = (const bf16*)v; pa.g = (const bf16*)g; pa.beta = (const bf16*)beta;
-  pa.ws = (uint8_t*)workspace; pa.T = T; pa.H = H; pa.HV = HV; pa.NT = NT; pa.scale = scale; pa.g_min = g_clamp_min; pa.gate_scale = gate_scale;
+  pa.ws = (uint8_t*)workspace; pa.T = T; pa.Tb = T; pa.H = H; pa.HV = HV; pa.NT = NT; pa.scale = scale; pa.g_min = g_clamp_min; pa.gate_scale = gate_scale;
   pa.umma = kch_kda_scan_tc5_enabled() ? 1 : 0;
   pa.ld_qk = ld_qk; pa.ld_v = ld_v; pa.ld_g = ld_g; pa.ld_b = ld_beta;
   // 16-byte vector loads: token strides and base pointers must be multiples of 8 elements / 16 bytes
@@ -721,6 +747,58 @@ int kch_kda_chunk_mma(const void* q, const void* k, const void* v, const void* g
               ((((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)g) & 15) == 0),
               "kch_kda_chunk: q/k/v/g must be 16-byte aligned with token strides that are multiples of 8 elements");
   static const bool prep_mma = [] { const char* e = getenv("KCH_KDA_PREPARE"); return e && e[0] == 'm'; }();
+  // Long sequences in segments: the sequential stage holds 64 SMs (one CTA per batch entry and head) for a dependent
+  // chain, the parallel stage wants all of them for independent chunks.  Segment i + 1 is prepared on the caller's
+  // stream while segment i is scanned on a high-priority side stream (its CTAs take their SMs first at the moment both
+  // become runnable; the prepare CTAs fill the rest), the state travels between segments through global memory.
+  // (KCH_KDA_SEGMENTS=1 runs the two stages one after the other, for comparison.)
+  static const int seg_env = [] { const char* e = getenv("KCH_KDA_SEGMENTS"); return e ? atoi(e) : 0; }();
+  int nsegs = seg_env > 0 ? seg_env : (NT >= 64 ? 4 : 1);
+  if (nsegs > KM_MAX_SEG) nsegs = KM_MAX_SEG;
+  if (nsegs > NT) nsegs = NT > 0 ? NT : 1;
+  if (pa.umma && !prep_mma && nsegs > 1) {
+    KmSideStream* ss = nullptr;
+    int rc = km_side_stream(&ss);
+    if (rc != KCH_OK) return rc;
+    const int per = (NT + nsegs - 1) / nsegs;
+    float* carry = final_state ? final_state
+                               : reinterpret_cast<float*>((uint8_t*)workspace + (int64_t)B * HV * NT * KM_CHUNK_BYTES);
+    auto seg_args = [&](int i, PrepArgs& sp, int& n0, int& cnt) {
+      n0 = i * per;
+      cnt = NT - n0 < per ? NT - n0 : per;
+      const int64_t tok = (int64_t)n0 * KM_C;
+      sp = pa;
+      sp.q = pa.q + tok * ld_qk; sp.k = pa.k + tok * ld_qk; sp.v = pa.v + tok * ld_v; sp.g = pa.g + tok * ld_g;
+      sp.beta = pa.beta + tok * ld_beta;
+      sp.ws = pa.ws + (int64_t)B * HV * n0 * KM_CHUNK_BYTES;
+      sp.T = T - (int)tok; sp.NT = cnt;
+    };
+    PrepArgs sp;
+    int n0, cnt;
+    seg_args(0, sp, n0, cnt);
+    rc = launch_kda_prepare_tc5(sp, B, status, s);
+    if (rc != KCH_OK) return rc;
+    KCH_CUDA_OK(cudaEventRecord(ss->prep_done[0], s));
+    for (int i = 0; i < nsegs && i * per < NT; ++i) {
+      seg_args(i, sp, n0, cnt);
+      const bool last = (i + 1) * per >= NT;
+      KCH_CUDA_OK(cudaStreamWaitEvent(ss->hp, ss->prep_done[i], 0));
+      rc = kch_kda_scan_tc5(sp.ws, i == 0 ? initial_state : carry, (bf16*)o + (int64_t)n0 * KM_C * HV * KM_V,
+                            last ? final_state : carry, B, sp.T, T, HV, cnt, status, ss->hp);
+      if (rc != KCH_OK) return rc;
+      if (!last) {
+        PrepArgs np;
+        int m0, mc;
+        seg_args(i + 1, np, m0, mc);
+        rc = launch_kda_prepare_tc5(np, B, status, s);
+        if (rc != KCH_OK) return rc;
+        KCH_CUDA_OK(cudaEventRecord(ss->prep_done[i + 1], s));
+      }
+    }
+    KCH_CUDA_OK(cudaEventRecord(ss->scan_done, ss->hp));
+    KCH_CUDA_OK(cudaStreamWaitEvent(s, ss->scan_done, 0));
+    return KCH_OK;
+  }
   if (pa.umma && !prep_mma) {
     int rc = launch_kda_prepare_tc5(pa, B, status, s);
     if (rc != KCH_OK) return rc;
@@ -729,7 +807,7 @@ int kch_kda_chunk_mma(const void* q, const void* k, const void* v, const void* g
     kda_prepare_mma_kernel<<<dim3(NT, HV, B), 256, PS_TOTAL, s>>>(pa);
     KCH_LAUNCH_OK();
   }
-  if (pa.umma) return kch_kda_scan_tc5(workspace, initial_state, o, final_state, B, T, HV, NT, status, s);
+  if (pa.umma) return kch_kda_scan_tc5(workspace, initial_state, o, final_state, B, T, T, HV, NT, status, s);
   ScanArgs sa;
   sa.ws = (const uint8_t*)workspace; sa.S0 = initial_state; sa.o = (bf16*)o; sa.S_out = final_state; sa.status = status;
   sa.T = T; sa.HV = HV; sa.NT = NT;

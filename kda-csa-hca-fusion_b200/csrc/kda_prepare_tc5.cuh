@@ -60,7 +60,7 @@ kda_prepare_tc5_kernel(PrepArgs a, const __grid_constant__ CUtensorMap vmap, uns
   uint8_t* wsc = a.ws + (bh * a.NT + n) * (int64_t)KM_CHUNK_BYTES;
   // thread -> rows 4 rg .. 4 rg + 3, channels 8 c8 .. 8 c8 + 7
   const int rg = tid >> 4, c8 = tid & 15;
-  const int64_t tok0 = (int64_t)b * a.T + t0 + 4 * rg;
+  const int64_t tok0 = (int64_t)b * a.Tb + t0 + 4 * rg;
 
   // ---- all twelve 16-byte loads of this thread's 4 x 8 block (g, k, q) are issued before anything waits on them ---
   uint4 graw[4], kreg[4], qreg[4];
@@ -100,7 +100,7 @@ kda_prepare_tc5_kernel(PrepArgs a, const __grid_constant__ CUtensorMap vmap, uns
     dst[0] = make_float4(run[0], run[1], run[2], run[3]);
     dst[1] = make_float4(run[4], run[5], run[6], run[7]);
   }
-  if (tid < KM_C) sbeta[tid] = (t0 + tid < a.T) ? __bfloat162float(a.beta[((int64_t)b * a.T + t0 + tid) * a.ld_b + hv]) : 0.f;
+  if (tid < KM_C) sbeta[tid] = (t0 + tid < a.T) ? __bfloat162float(a.beta[((int64_t)b * a.Tb + t0 + tid) * a.ld_b + hv]) : 0.f;
   if (tid == 0) {
     mbarrier_init(&bars[0], 1); mbarrier_init(&bars[1], 1); mbarrier_init(&bars[2], 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -201,8 +201,8 @@ kda_prepare_tc5_kernel(PrepArgs a, const __grid_constant__ CUtensorMap vmap, uns
   if (ok) {
     if (tid == 0) {                                               // V tile: the QG rows of the hi panels are free now
       mbarrier_expect_tx(&bars[1], 16384);
-      t5_tma_load_2d(sm + PT_VT, &vmap, hv * KM_V, (int)((int64_t)b * a.T + t0), &bars[1]);
-      t5_tma_load_2d(sm + PT_VT + 16384, &vmap, hv * KM_V + 64, (int)((int64_t)b * a.T + t0), &bars[1]);
+      t5_tma_load_2d(sm + PT_VT, &vmap, hv * KM_V, (int)((int64_t)b * a.Tb + t0), &bars[1]);
+      t5_tma_load_2d(sm + PT_VT + 16384, &vmap, hv * KM_V + 64, (int)((int64_t)b * a.Tb + t0), &bars[1]);
     }
     uint32_t r[32];
     t5_ld32(tmem + lane_base + 32 * hh, r);
@@ -352,7 +352,7 @@ int kch_make_tensor_map_2d_bf16(CUtensorMap* map, const void* base, uint64_t row
 
 static int launch_kda_prepare_tc5(const PrepArgs& pa, int B, unsigned int* status, cudaStream_t s) {
   CUtensorMap vmap;
-  int rc = kch_make_tensor_map_2d_bf16(&vmap, pa.v, (uint64_t)B * pa.T, (uint64_t)pa.HV * KM_V, (uint64_t)pa.ld_v, 64, 64);
+  int rc = kch_make_tensor_map_2d_bf16(&vmap, pa.v, (uint64_t)(B - 1) * pa.Tb + pa.T, (uint64_t)pa.HV * KM_V, (uint64_t)pa.ld_v, 64, 64);
   if (rc != KCH_OK) return rc;
   KCH_CUDA_OK(cudaFuncSetAttribute(kda_prepare_tc5_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PT_DYN));
   KCH_CUDA_OK(cudaFuncSetAttribute(kda_prepare_tc5_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, 100));

@@ -50,7 +50,8 @@ struct T5Args {
   bf16* o;
   float* S_out;
   unsigned int* status;
-  int T, HV, NT;
+  int T, HV, NT;                     // T: tokens from the first chunk of this launch to the end of the sequence
+  int Tb;                            // tokens between consecutive batch entries (the whole sequence length)
 };
 
 // shared-memory map (bytes, 1024-aligned operand tiles)
@@ -243,7 +244,7 @@ __global__ void __launch_bounds__(T5_THREADS, 1) kda_scan_tc5_kernel(T5Args a) {
 #pragma unroll
         for (int j = 0; j < 32; ++j) {
           const int t = (n - 1) * 64 + 32 * sub + j;
-          a.o[(((int64_t)b * a.T + t) * a.HV + hv) * 128 + v] = __float2bfloat16_rn(__uint_as_float(ro[j]));
+          a.o[(((int64_t)b * a.Tb + t) * a.HV + hv) * 128 + v] = __float2bfloat16_rn(__uint_as_float(ro[j]));
         }
       }
       // ---- vt^T = u^T - D1w -> operand images, 16 tokens at a time ---------------------------------------------
@@ -280,7 +281,7 @@ __global__ void __launch_bounds__(T5_THREADS, 1) kda_scan_tc5_kernel(T5Args a) {
 #pragma unroll
       for (int j = 0; j < 32; ++j) {
         const int t = (a.NT - 1) * 64 + 32 * sub + j;
-        if (t < a.T) a.o[(((int64_t)b * a.T + t) * a.HV + hv) * 128 + v] = __float2bfloat16_rn(__uint_as_float(ro[j]));
+        if (t < a.T) a.o[(((int64_t)b * a.Tb + t) * a.HV + hv) * 128 + v] = __float2bfloat16_rn(__uint_as_float(ro[j]));
       }
       if (a.S_out) {
 #pragma unroll
@@ -310,10 +311,10 @@ bool kch_kda_scan_tc5_enabled() {
 }
 
 int kch_kda_scan_tc5(const void* workspace, const float* initial_state, void* o, float* final_state, int B, int T,
-                     int HV, int NT, unsigned int* status, cudaStream_t s) {
+                     int Tb, int HV, int NT, unsigned int* status, cudaStream_t s) {
   T5Args a;
   a.ws = (const uint8_t*)workspace; a.S0 = initial_state; a.o = (bf16*)o; a.S_out = final_state; a.status = status;
-  a.T = T; a.HV = HV; a.NT = NT;
+  a.T = T; a.Tb = Tb; a.HV = HV; a.NT = NT;
   const int smem = T5_TOTAL + 1024;
   KCH_CUDA_OK(cudaFuncSetAttribute(kda_scan_tc5_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
   kda_scan_tc5_kernel<<<dim3(HV, B), T5_THREADS, smem, s>>>(a);
