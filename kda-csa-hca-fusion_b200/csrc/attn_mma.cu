@@ -397,6 +397,11 @@ __global__ void __launch_bounds__(AD_WARPS * 32, 2) attn_dense_mma_kernel(AttnMm
   }
 }
 
+int kch_attend_dense_tc5(const bf16* q, int64_t q_ld, int B, int T, int nh, const bf16* comp, int64_t comp_batch_rows,
+                         int n_comp, int m, int64_t t0, int nvis_fixed, const bf16* win, int64_t win_ld,
+                         int64_t win_batch_rows, int win_size, int win_t0, const void* sink, int sink_dtype, float scale,
+                         bf16* out, cudaStream_t s);
+
 bool kch_attend_mma_supported(const kch_attend_args* p) {
   if (p->c != AM_C || p->nh > 16 || p->nh < 1) return false;
   if (p->q_dtype != KCH_BF16 || p->out_dtype != KCH_BF16 || !p->q_normalize) return false;
@@ -423,6 +428,14 @@ int kch_attend_mma(const kch_attend_args* p, void* stream) {
   static_assert(16 * AM_QLD * 2 <= AM_TILE * AM_C * 2, "query staging tile must fit one ring stage");
   // no selection list: the queries of a CTA share their staged keys (KCH_ATTEND_DENSE=w keeps one ring per warp)
   static const bool dense_per_warp = [] { const char* e = getenv("KCH_ATTEND_DENSE"); return e && e[0] == 'w'; }();
+  // ... and on tcgen05 where nothing is gathered at all (KCH_ATTEND_DENSE=m keeps the mma.sync shared-ring kernel)
+  static const bool dense_mma = [] { const char* e = getenv("KCH_ATTEND_DENSE"); return e && e[0] == 'm'; }();
+  if (!a.sel && !dense_per_warp && !dense_mma) {
+    const int rc = kch_attend_dense_tc5(a.q, a.q_ld, a.B, a.T, a.nh, a.comp, a.comp_batch_rows, a.n_comp, a.m, a.t0, a.nvis_fixed,
+                                        a.win, a.win_ld, a.win_batch_rows, a.win_size, a.win_t0, a.sink, a.sink_dtype, a.scale,
+                                        a.out, kch_stream(stream));
+    if (rc != -100) return rc;
+  }
   if (!a.sel && !dense_per_warp) {
     const size_t smem = (size_t)AD_STAGES * AM_TILE * AM_C * 2 + (size_t)AD_WARPS * 16 * AM_QLD * 2;
     KCH_CUDA_OK(cudaFuncSetAttribute(attn_dense_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));

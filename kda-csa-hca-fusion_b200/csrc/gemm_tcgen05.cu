@@ -605,6 +605,24 @@ int kch_make_tensor_map_katoms_bf16(CUtensorMap* map, const void* base, uint64_t
   return KCH_OK;
 }
 
+// bf16 [rows][nh * 128] activations seen as {128 channels, nh heads, rows}: a box {64, box_heads, box_rows} lands as
+// one 64-channel panel of a [box_rows x box_heads rows][64] operand tile (row = token-major, head-minor) under the
+// 128-byte swizzle; heads beyond nh read as zeros
+int kch_make_tensor_map_qtile_bf16(CUtensorMap* map, const void* base, uint64_t rows, uint32_t nh, uint64_t ld_elems,
+                                   uint32_t box_heads, uint32_t box_rows) {
+  PFN_cuTensorMapEncodeTiled_v12000 enc = get_encode_fn();
+  if (!enc) { kch_set_error("cuTensorMapEncodeTiled is not available from the driver"); return KCH_ERR_CUDA; }
+  cuuint64_t gdim[3] = {128, nh, rows};
+  cuuint64_t gstr[2] = {256, ld_elems * 2};
+  cuuint32_t box[3] = {64, box_heads, box_rows};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), gdim, gstr, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) { kch_set_error("cuTensorMapEncodeTiled (query tile view) failed with code %d", (int)r); return KCH_ERR_CUDA; }
+  return KCH_OK;
+}
+
 bool kch_linear_tcgen05_supported(const void* A, const void* W, const void* C, const void* R, int64_t M, int N,
                                   int K, int64_t lda, int64_t ldw, int64_t ldc, int64_t ldr, int dtype) {
   if (dtype != KCH_BF16) return false;
