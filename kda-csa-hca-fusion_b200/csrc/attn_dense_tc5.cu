@@ -186,7 +186,8 @@ attn_dense_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_con
           }
         }
     }
-    const float qscale = a.scale / fmaxf(sqrtf(ss), 1e-12f);
+    // exp(s * scale / ||q|| - shift) = 2^(s * qs2 - sh2): one FMA and one ex2 per entry
+    const float qs2 = a.scale / fmaxf(sqrtf(ss), 1e-12f) * 1.4426950408889634f, sh2 = shift * 1.4426950408889634f;
     float l = 0.f;
     bool any_valid = false;
     const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
@@ -207,20 +208,28 @@ attn_dense_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_con
       lo = max(lo, 0); hi = min(hi, DT_KT);
       any_valid = any_valid || hi > lo;
       uint8_t* prow = reinterpret_cast<uint8_t*>(sm.p[pb]) + r * 128;
+      uint32_t sv[2][32];                                            // both halves of the score row requested at once
+      t5_ld32(tS + 64u * pb + lane_base, sv[0]);
+      t5_ld32(tS + 64u * pb + lane_base + 32, sv[1]);
+      t5_wait_ld();
+      const bool full = __all_sync(0xffffffffu, lo == 0 && hi == DT_KT);   // interior tile: no entry of any row masked
+      float la = 0.f, lb = 0.f;
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
-        uint32_t sv[32];
-        t5_ld32(tS + 64u * pb + lane_base + 32 * half, sv);
-        t5_wait_ld();
 #pragma unroll
         for (int c = 0; c < 4; ++c) {                               // 8 keys = one 16-byte chunk of the P row
           uint32_t o4[4];
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
             const int j0 = 32 * half + 8 * c + 2 * e;
-            const float p0 = (j0 >= lo && j0 < hi) ? __expf(__uint_as_float(sv[8 * c + 2 * e]) * qscale - shift) : 0.f;
-            const float p1 = (j0 + 1 >= lo && j0 + 1 < hi) ? __expf(__uint_as_float(sv[8 * c + 2 * e + 1]) * qscale - shift) : 0.f;
-            l += p0 + p1;
+            float p0 = ex2_fast(fmaf(__uint_as_float(sv[half][8 * c + 2 * e]), qs2, -sh2));
+            float p1 = ex2_fast(fmaf(__uint_as_float(sv[half][8 * c + 2 * e + 1]), qs2, -sh2));
+            if (!full) {
+              p0 = (j0 >= lo && j0 < hi) ? p0 : 0.f;
+              p1 = (j0 + 1 >= lo && j0 + 1 < hi) ? p1 : 0.f;
+            }
+            la += p0;
+            lb += p1;
             __nv_bfloat162 hp = __floats2bfloat162_rn(p0, p1);
             o4[e] = *reinterpret_cast<uint32_t*>(&hp);
           }
@@ -228,6 +237,7 @@ attn_dense_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_con
           *reinterpret_cast<uint4*>(prow + ((ch ^ (r & 7)) << 4)) = make_uint4(o4[0], o4[1], o4[2], o4[3]);
         }
       }
+      l += la + lb;
       t5_fence_async_smem();                                        // the MMA reads P through the async proxy
       t5_fence_before();
       __syncwarp();
