@@ -388,8 +388,17 @@ def run_b200(args):
             grp = dist.new_group(list(range(g * tp, (g + 1) * tp)))
             if g == dp_rank:
                 tp_group = grp
+    allgather = None
     if tp > 1:
-        model = build_tp_model(cfg, params, LAYERS, TPContext(tp_rank, tp, tp_group, args.tp_attn), dev, torch.bfloat16)
+        ctx = TPContext(tp_rank, tp, tp_group, args.tp_attn)
+        model = build_tp_model(cfg, params, LAYERS, ctx, dev, torch.bfloat16)
+        allgather = "nccl"
+        if not args.no_peer_gather:
+            # the per-layer all-gather by plain peer stores into symmetric memory (one slab of B*T/tp rows, or of
+            # h/tp heads, per rank: the same bytes either way) where that allocator is usable, else NCCL
+            from kch_b200.tp import enable_peer_gather
+            if enable_peer_gather(ctx, (B // dp) * T * cfg.d_model * 2 // tp, dev):
+                allgather = "peer_store"
     else:
         model = kch_b200.HybridKCHAttention(cfg, LAYERS)
         model.load_state_dict(params, strict=True)
@@ -486,7 +495,11 @@ def run_b200(args):
         del model
         torch.cuda.empty_cache()
         params = syn.hybrid_params(SEED, cfg, LAYERS, dtype=torch.bfloat16)
-        model = build_tp_model(cfg, params, LAYERS, TPContext(tp_rank, tp, tp_group, other), dev, torch.bfloat16)
+        vctx = TPContext(tp_rank, tp, tp_group, other)
+        model = build_tp_model(cfg, params, LAYERS, vctx, dev, torch.bfloat16)
+        if not args.no_peer_gather:
+            from kch_b200.tp import enable_peer_gather
+            enable_peer_gather(vctx, (B // dp) * T * cfg.d_model * 2 // tp, dev)
         del params
         xv = x_host.to(dev)
         for _ in range(args.warmup):
@@ -527,7 +540,8 @@ def run_b200(args):
             "config": {"workload": "hybrid_prefill_c4", "B": B, "T": T, "layers": LAYERS, "layout": layout_str,
                        "parallelism": ("single_gpu" if world == 1 else (f"dp{dp}_sequences" if tp == 1 else (
                            (f"tp{tp}_heads" if args.tp_attn == "heads" else f"tp{tp}_kda_heads_attn_rows") if dp == 1
-                           else f"dp{dp}_sequences_x_tp{tp}_heads"))), "l2": "inputs larger than L2 (537 MB hidden states)", **C4},
+                           else f"dp{dp}_sequences_x_tp{tp}_heads"))), "allgather": allgather,
+                       "l2": "inputs larger than L2 (537 MB hidden states)", **C4},
             "e2e": {"value": tokens / (e2e_ms / 1e3), "unit": UNIT, "h2d_bytes_per_step": x_host.numel() * 2 * world,
                     "d2h_bytes_per_step": y_host.numel() * 2 * world, "steps": e2e_steps, "ms_per_step": e2e_ms,
                     "api": "kch_b200.HostPipeline.run (pinned host in / out, copies overlapped with the passes)",
@@ -580,7 +594,7 @@ def main():
                          "gathers do not shrink with the head count), or query heads like KDA; KDA is always by heads, "
                          "and either way there is one all-gather per layer.  The other mode is timed too (tp_variant)")
     ap.add_argument("--no-peer-gather", action="store_true",
-                    help="N > 1: keep the NCCL all-gather in the decode steps (default: plain peer stores when available)")
+                    help="N > 1: keep the NCCL all-gather (default: plain peer stores into symmetric memory when available)")
     ap.add_argument("--no-variant", action="store_true", help="N > 1: skip the extra timing of the other --tp-attn mode")
     ap.add_argument("--decode-batch", type=int, default=64)
     ap.add_argument("--decode-context", type=int, default=131072)

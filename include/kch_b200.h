@@ -118,14 +118,15 @@ int kch_linear_ex(const void* A, const void* W, void* C, const void* residual, i
 int kch_linear_kslabs(const void* A, const void* W, void* C, const void* residual, int64_t M, int N, int K, int n_slabs,
                       int64_t ldw, int64_t ldc, int64_t ldr, int dtype, void* stream);
 
-/* All-gather of decode-sized per-GPU slabs by plain peer stores (no counterpart in the reference, which has no
+/* All-gather of per-GPU slabs by plain peer stores (no counterpart in the reference, which has no
  * distributed code): rank `rank` of `world` writes `slab_bytes` from `src` into slot `rank` of every rank's gather
  * buffer and the ranks meet on arrival / data flags next to the buffers (bounded waits; a wait that runs out records
  * KCH_STATUS_PEER_GATHER in the status word and the kernel returns).  `bufs[p]` / `flags[p]` (HOST arrays of `world`
  * device pointers) are rank p's buffer ([world][slab_bytes]) and flag block (kch_peer_gather_flag_words(world) zeroed
- * 32-bit words) as mapped on this GPU: memory every rank has mapped from every peer (CUDA VMM / IPC).  One launch, one
- * CTA; the call counter lives in the flag block, so a captured CUDA graph replays it unchanged.  All ranks must make the
- * same sequence of calls on a buffer.  slab_bytes: multiple of 16, at most 8 MiB. */
+ * 32-bit words) as mapped on this GPU: memory every rank has mapped from every peer (CUDA VMM / IPC).  The call counter
+ * lives in the flag block, so a captured CUDA graph replays it unchanged.  All ranks must make the
+ * same sequence of calls on a buffer.  slab_bytes: multiple of 16; up to 1 MiB runs as one launch of one CTA, larger slabs as
+ * three launches (arrival, a copy kernel over all SMs, data flags). */
 #define KCH_STATUS_PEER_GATHER 0x9A7E
 int64_t kch_peer_gather_flag_words(int world);
 int kch_peer_allgather(const void* src, int64_t slab_bytes, void* const* bufs, void* const* flags, int rank, int world,

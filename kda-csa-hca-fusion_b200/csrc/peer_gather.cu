@@ -15,6 +15,10 @@
 // (the context stays usable; the gathered data of that call is not valid).  No multicast, no multimem, no library
 // kernel touches a peer pointer: plain loads and stores of this kernel only.
 //
+// Large slabs (the gathers of a prefill pass: tens of megabytes per rank) take the same three steps as three launches on
+// the caller's stream: the arrival step (one CTA), a copy kernel of many CTAs that stores the slab to every peer with
+// 16-byte stores, and the data-flag step (one CTA); the kernel boundaries order them.
+//
 // The buffers and flags must be memory that every rank has mapped from every peer (CUDA VMM / IPC; the Python side
 // uses torch's symmetric-memory allocator) and zero-initialised flags.  The reference has no counterpart (it has no
 // distributed code).
@@ -31,6 +35,7 @@ struct PeerGatherArgs {
   uint8_t* bufs[PG_MAX_WORLD];      // gather buffer of every rank, as mapped on THIS rank: [world][slab_bytes]
   uint32_t* flags[PG_MAX_WORLD];    // flag block of every rank: [0, world) arrival, [world, 2 world) data, [2 world] seq
   int rank, world;
+  int phase;                        // 0: arrival, copy and data flags in this one CTA; 1: arrival only; 2: data flags only
   unsigned int* status;
 };
 
@@ -60,20 +65,22 @@ __global__ void __launch_bounds__(1024) peer_allgather_kernel(PeerGatherArgs a) 
   if (tid == 0) s_ok = 1;
   __syncthreads();
   // 1. arrival
-  if (tid < a.world) {
+  if (a.phase != 2 && tid < a.world) {
     pg_store_release_sys(a.flags[tid] + a.rank, seq);
     if (!pg_wait(mine + tid, seq, a.status)) s_ok = 0;
   }
   __syncthreads();
-  if (!s_ok) return;
+  if (!s_ok || a.phase == 1) return;
   // 2. the slab into slot `rank` of every rank's buffer
-  const int64_t n16 = a.slab_bytes >> 4;
-  for (int p = 0; p < a.world; ++p) {
-    uint4* dst = reinterpret_cast<uint4*>(a.bufs[p] + (int64_t)a.rank * a.slab_bytes);
-    for (int64_t i = tid; i < n16; i += blockDim.x) dst[i] = a.src[i];
+  if (a.phase == 0) {
+    const int64_t n16 = a.slab_bytes >> 4;
+    for (int p = 0; p < a.world; ++p) {
+      uint4* dst = reinterpret_cast<uint4*>(a.bufs[p] + (int64_t)a.rank * a.slab_bytes);
+      for (int64_t i = tid; i < n16; i += blockDim.x) dst[i] = a.src[i];
+    }
+    __threadfence_system();
+    __syncthreads();
   }
-  __threadfence_system();
-  __syncthreads();
   // 3. data flags
   if (tid < a.world) {
     pg_store_release_sys(a.flags[tid] + a.world + a.rank, seq);
@@ -81,6 +88,17 @@ __global__ void __launch_bounds__(1024) peer_allgather_kernel(PeerGatherArgs a) 
   }
   __syncthreads();
   if (tid == 0 && s_ok) mine[2 * a.world] = seq;
+}
+
+// the copy step of a large gather: grid-stride over 16-byte words, every word stored to each rank's buffer
+__global__ void __launch_bounds__(512) peer_allgather_copy_kernel(PeerGatherArgs a) {
+  const int64_t n16 = a.slab_bytes >> 4;
+  if (*((volatile unsigned int*)a.status) != 0) return;       // the arrival step gave up: leave the peers' buffers alone
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n16; i += (int64_t)gridDim.x * blockDim.x) {
+    const uint4 v = a.src[i];
+    for (int p = 0; p < a.world; ++p)
+      reinterpret_cast<uint4*>(a.bufs[p] + (int64_t)a.rank * a.slab_bytes)[i] = v;
+  }
 }
 
 extern "C" int64_t kch_peer_gather_flag_words(int world) { return world >= 1 ? 2 * (int64_t)world + 2 : 0; }
@@ -92,8 +110,7 @@ extern "C" int kch_peer_allgather(const void* src, int64_t slab_bytes, void* con
   KCH_REQUIRE(src && bufs && flags && slab_bytes >= 16 && (slab_bytes % 16) == 0 && (((uintptr_t)src) & 15) == 0,
               "kch_peer_allgather: the slab must be 16-byte aligned and a multiple of 16 bytes (slab_bytes=%lld)",
               (long long)slab_bytes);
-  KCH_REQUIRE(slab_bytes <= (8LL << 20), "kch_peer_allgather: slab_bytes=%lld: this kernel is for decode-sized slabs "
-              "(<= 8 MiB); use the library collective for larger ones", (long long)slab_bytes);
+  KCH_REQUIRE(slab_bytes <= (4LL << 30), "kch_peer_allgather: slab_bytes=%lld exceeds 4 GiB", (long long)slab_bytes);
   unsigned int* status = kch_status_device_ptr();
   KCH_REQUIRE(status != nullptr, "kch_peer_allgather: cannot resolve the device status word");
   PeerGatherArgs a = {};
@@ -103,6 +120,24 @@ extern "C" int kch_peer_allgather(const void* src, int64_t slab_bytes, void* con
     a.bufs[p] = (uint8_t*)bufs[p];
     a.flags[p] = (uint32_t*)flags[p];
   }
+  if (slab_bytes <= (1LL << 20)) {
+    a.phase = 0;
+    peer_allgather_kernel<<<1, 1024, 0, kch_stream(stream)>>>(a);
+    KCH_LAUNCH_OK();
+    return KCH_OK;
+  }
+  static int sms = 0;
+  if (!sms) {
+    int dev = 0;
+    KCH_CUDA_OK(cudaGetDevice(&dev));
+    KCH_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  }
+  a.phase = 1;
+  peer_allgather_kernel<<<1, 1024, 0, kch_stream(stream)>>>(a);
+  KCH_LAUNCH_OK();
+  peer_allgather_copy_kernel<<<2 * sms, 512, 0, kch_stream(stream)>>>(a);
+  KCH_LAUNCH_OK();
+  a.phase = 2;
   peer_allgather_kernel<<<1, 1024, 0, kch_stream(stream)>>>(a);
   KCH_LAUNCH_OK();
   return KCH_OK;

@@ -33,6 +33,19 @@ def _worker(rank, world, port, out, attn):
         x = syn.hidden_states(10, 2, 200, cfg.d_model, torch.bfloat16).to(dev)
         ctx = TPContext(rank, world, None, attn.split("+")[0])
         tp = build_tp_model(cfg, params, 5, ctx, dev, torch.bfloat16)
+        peer_ok = None
+        if attn.endswith("+peer"):          # all-gathers by plain peer stores (symmetric memory) instead of NCCL
+            from kch_b200.tp import enable_peer_gather
+            peer_ok = enable_peer_gather(ctx, 4 << 20, dev)
+            if peer_ok:
+                # a 4 MiB slab takes the three-launch path (arrival, copy over all SMs, data flags); the small slabs of
+                # this model's layers the single-CTA one: both against the library collective
+                big = (torch.randn(8192, 256, device=dev) * (rank + 1)).bfloat16()
+                ref = torch.empty(world * 8192, 256, dtype=big.dtype, device=dev)
+                dist.all_gather_into_tensor(ref, big)
+                for _ in range(3):
+                    got = ctx.peer.gather(big).reshape(world * 8192, 256)
+                    assert torch.equal(got, ref)
         y_tp = tp(x)
         full = kch_b200.HybridKCHAttention(cfg, 5)
         full.load_state_dict(params, strict=True)
@@ -45,10 +58,6 @@ def _worker(rank, world, port, out, attn):
         # CUDA graph and must follow the single-GPU decode
         full.reset_state()
         tp.reset_state()
-        peer_ok = None
-        if attn.endswith("+peer"):          # decode all-gathers by plain peer stores (symmetric memory) instead of NCCL
-            from kch_b200.tp import enable_peer_gather
-            peer_ok = enable_peer_gather(ctx, 2 * 1024 * 2, dev)
         dec_full = kch_b200.HybridDecoding(model=full, use_cuda_graph=False)
         dec_tp = kch_b200.HybridDecoding(model=tp, use_cuda_graph=True)
         ya, yb = [dec_full(x[:, :150])], [dec_tp(x[:, :150])]
