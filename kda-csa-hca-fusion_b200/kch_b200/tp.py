@@ -156,9 +156,20 @@ def gather_rows(o_rows, ctx: TPContext, lead=None):
 
 
 def out_projection_rows(o_rows, ctx: TPContext, W, residual=None, lead=None):
-    """``o_proj`` of a layer whose QUERY ROWS are sharded: ``gather_rows``, then ``F.linear`` (+ residual)."""
+    """``o_proj`` of a layer whose QUERY ROWS are sharded: every rank projects ITS rows (+ its rows of the residual),
+    then the projected rows are all-gathered along the row axis -- the same bytes on the wire as gathering the head
+    outputs first, and the projection costs a 1/world share instead of being repeated on every rank."""
     from .csa import linear
-    return linear(gather_rows(o_rows, ctx, lead), W, residual=residual)
+    flat = o_rows.reshape(-1, o_rows.shape[-1])
+    per = flat.shape[0]
+    res = None
+    if residual is not None:
+        res = residual.reshape(-1, residual.shape[-1])[ctx.rank * per:(ctx.rank + 1) * per]
+    y = linear(flat, W, residual=res)
+    out = gather_rows(y, ctx, lead)
+    if ctx.peer is not None and ctx.peer.fits(y):
+        out = out.clone()          # a view of the peer buffer, which the next layer's gather overwrites: this one lives on
+    return out
 
 
 def out_projection(o_local, ctx: TPContext, W, residual=None):
