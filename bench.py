@@ -454,7 +454,9 @@ def run_b200(args):
     # downloads its output; HostPipeline overlaps those copies with the neighbouring steps' kernels
     y_host = torch.empty(B_local, T, cfg.d_model, dtype=torch.bfloat16).pin_memory()
     e2e_steps = max(1, args.steps)
-    pipe = kch_b200.HostPipeline(model, dev)
+    # (under tensor parallelism each rank uploads and downloads its 1/tp run of the rows; the runs are all-gathered on the
+    # device, so the host moves one copy of the batch per step, not one per GPU)
+    pipe = kch_b200.HostPipeline(model, dev, tp=ctx if (tp > 1 and dp == 1) else None)
     pipe.run([x_host], [y_host])
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -542,8 +544,10 @@ def run_b200(args):
                            (f"tp{tp}_heads" if args.tp_attn == "heads" else f"tp{tp}_kda_heads_attn_rows") if dp == 1
                            else f"dp{dp}_sequences_x_tp{tp}_heads"))), "allgather": allgather,
                        "l2": "inputs larger than L2 (537 MB hidden states)", **C4},
-            "e2e": {"value": tokens / (e2e_ms / 1e3), "unit": UNIT, "h2d_bytes_per_step": x_host.numel() * 2 * world,
-                    "d2h_bytes_per_step": y_host.numel() * 2 * world, "steps": e2e_steps, "ms_per_step": e2e_ms,
+            "e2e": {"value": tokens / (e2e_ms / 1e3), "unit": UNIT,
+                    "h2d_bytes_per_step": x_host.numel() * 2 * (dp if (tp > 1 and dp == 1) or tp == 1 else world),
+                    "d2h_bytes_per_step": y_host.numel() * 2 * (dp if (tp > 1 and dp == 1) or tp == 1 else world),
+                    "steps": e2e_steps, "ms_per_step": e2e_ms,
                     "api": "kch_b200.HostPipeline.run (pinned host in / out, copies overlapped with the passes)",
                     "ms_per_step_without_overlap": e2e_serial_ms},
             "gpu_launches": launches,

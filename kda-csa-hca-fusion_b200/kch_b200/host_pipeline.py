@@ -6,6 +6,11 @@ forward pass; at the benchmark size those copies (2 x 537 MB) cost about a third
 ``HostPipeline`` runs a sequence of passes with three CUDA streams: while pass ``i`` computes, the input of
 pass ``i+1`` is uploaded into the other of two device buffers and the output of pass ``i-1`` is downloaded.
 Every copy still happens, once per pass; only the first upload and the last download are exposed.
+
+Under tensor parallelism (``tp=`` a ``TPContext`` of more than one rank) every rank needs the whole batch on its GPU, but
+it does not have to come over every rank's PCIe link: each rank uploads its 1/N run of the flattened ``[B*T]`` rows, the
+runs are all-gathered over NVLink (one collective per pass, on the compute stream), and each rank downloads its run of
+the output only -- the host moves one copy of the batch per pass instead of N.
 """
 from __future__ import annotations
 
@@ -13,8 +18,10 @@ import torch
 
 
 class HostPipeline:
-    def __init__(self, model, device=None):
+    def __init__(self, model, device=None, tp=None):
         self.model = model
+        self.tp = tp if (tp is not None and tp.world > 1) else None
+        self._xfull = None
         self.device = torch.device(device) if device is not None else next(model.parameters()).device
         if self.device.type != "cuda":
             raise RuntimeError("HostPipeline requires a CUDA device; there is no CPU path")
@@ -25,7 +32,9 @@ class HostPipeline:
     @torch.no_grad()
     def run(self, inputs, outputs, *, reset_state=True):
         """``inputs[i]`` (pinned host ``[B,T,d]``) -> ``outputs[i]`` (pinned host, same shape).  Passes are
-        independent prefill passes when ``reset_state`` (the KDA state is cleared before each)."""
+        independent prefill passes when ``reset_state`` (the KDA state is cleared before each).  With ``tp`` every rank
+        passes the same ``inputs`` and finds ITS run of rows filled in ``outputs[i]`` (the runs of all ranks make up
+        the whole output)."""
         if len(inputs) != len(outputs):
             raise ValueError(f"HostPipeline.run: {len(inputs)} inputs but {len(outputs)} outputs")
         dev = self.device
@@ -36,8 +45,17 @@ class HostPipeline:
         self._up.wait_stream(compute)
         self._down.wait_stream(compute)
 
+        tp = self.tp
+
+        def my_rows(t):                          # this rank's run of the flattened rows of a host tensor
+            flat = t.reshape(-1, t.shape[-1])
+            if flat.shape[0] % tp.world != 0:
+                raise ValueError(f"HostPipeline.run: {flat.shape[0]} rows do not divide over {tp.world} ranks")
+            per = flat.shape[0] // tp.world
+            return flat[tp.rank * per:(tp.rank + 1) * per]
+
         def upload(i):
-            x = inputs[i]
+            x = inputs[i] if tp is None else my_rows(inputs[i])
             slot = i % 2
             if self._xd[slot] is None or self._xd[slot].shape != x.shape or self._xd[slot].dtype != x.dtype:
                 self._xd[slot] = torch.empty(x.shape, dtype=x.dtype, device=dev)
@@ -58,11 +76,23 @@ class HostPipeline:
             compute.wait_event(uploaded[i])
             if reset_state:
                 self.model.reset_state()
-            y = self.model(self._xd[i % 2])
+            if tp is None:
+                xin = self._xd[i % 2]
+            else:
+                import torch.distributed as dist
+                full_shape = inputs[i].shape
+                if self._xfull is None or self._xfull.shape != full_shape or self._xfull.dtype != inputs[i].dtype:
+                    self._xfull = torch.empty(full_shape, dtype=inputs[i].dtype, device=dev)
+                dist.all_gather_into_tensor(self._xfull.view(-1, full_shape[-1]), self._xd[i % 2], group=tp.group)
+                xin = self._xfull
+            y = self.model(xin)
             computed[i].record(compute)
             with torch.cuda.stream(self._down):
                 self._down.wait_event(computed[i])
-                outputs[i].copy_(y, non_blocking=True)
+                if tp is None:
+                    outputs[i].copy_(y, non_blocking=True)
+                else:
+                    my_rows(outputs[i]).copy_(my_rows(y), non_blocking=True)
             y.record_stream(self._down)
         compute.wait_stream(self._down)
         self._raise_on_device_status()

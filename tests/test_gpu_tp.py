@@ -47,6 +47,13 @@ def _worker(rank, world, port, out, attn):
                     got = ctx.peer.gather(big).reshape(world * 8192, 256)
                     assert torch.equal(got, ref)
         y_tp = tp(x)
+        # host-resident batch through the sharded pipeline: this rank uploads / downloads its run of rows only
+        xh = x.cpu().pin_memory()
+        yh = torch.zeros_like(xh).pin_memory()
+        kch_b200.HostPipeline(tp, dev, tp=ctx).run([xh], [yh])
+        per = (x.shape[0] * x.shape[1]) // world
+        mine = slice(rank * per, (rank + 1) * per)
+        assert torch.equal(yh.view(-1, cfg.d_model)[mine].to(dev), y_tp.reshape(-1, cfg.d_model)[mine])
         full = kch_b200.HybridKCHAttention(cfg, 5)
         full.load_state_dict(params, strict=True)
         full = full.bfloat16().to(dev).eval()
