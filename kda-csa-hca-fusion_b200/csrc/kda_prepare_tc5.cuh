@@ -236,38 +236,133 @@ kda_prepare_tc5_kernel(PrepArgs a, const __grid_constant__ CUtensorMap vmap, uns
   }
   __syncthreads();
   if (ok) {
-    // ---- T = (I + A)^-1 by forward substitution, one thread per column, the column in registers --------------------
-    // x_i = [i == c] - sum_{j < i} A[i][j] x_j: rows above the diagonal come out as zero by themselves, so every
-    // thread runs the same straight-line code; A[i][.] is a broadcast read.  64 threads carry this dependent chain
-    // (about 2000 FMAs each) while the other warps of the CTA and the second CTA of the SM keep the pipes busy.
-    if (tid < KM_C) {
-      const int c = tid;
-      float x[KM_C];
+    // ---- T = (I + A)^-1, blocked: [[M00, 0], [M10, M11]]^-1 = [[T00, 0], [-T11 M10 T00, T11]] on two levels ----------
+    // All 256 threads work in every phase, and every phase is a short dependent chain: the four 16 x 16 diagonal
+    // blocks by substitution (four steps at a time), then the 16 x 16 blocks under them, then the 32 x 32 block.
+    // A (row-major, zero at and above the diagonal) is only read; T is built in place in sT, whose upper triangle
+    // serves as scratch for the intermediate products and is masked out when T is converted.
+    {
+      // (a) the diagonal blocks: thread = (block, column, 4 of its 16 rows); the owner of the four rows of a step group
+      // solves them locally, the others of its column take the values by shuffle and update their rows.
+      const int db = tid >> 6, c = (tid & 63) >> 2, p = tid & 3;
+      const float* ab = sA + (16 * db + 4 * p) * PS_LD + 16 * db;
+      float v[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int i = 0; i < KM_C; ++i) {
-        float acc[4] = {0.f, 0.f, 0.f, 0.f};
-        const float4* arow = reinterpret_cast<const float4*>(sA + i * PS_LD);
+      for (int kb = 0; kb < 4; ++kb) {
+        float4 a4[4];
 #pragma unroll
-        for (int j4 = 0; j4 < (i + 3) / 4; ++j4) {
-          const float4 av = arow[j4];                            // entries at and above the diagonal are stored as 0
-          if (4 * j4 < i) acc[0] = fmaf(av.x, x[4 * j4], acc[0]);
-          if (4 * j4 + 1 < i) acc[1] = fmaf(av.y, x[4 * j4 + 1], acc[1]);
-          if (4 * j4 + 2 < i) acc[2] = fmaf(av.z, x[4 * j4 + 2], acc[2]);
-          if (4 * j4 + 3 < i) acc[3] = fmaf(av.w, x[4 * j4 + 3], acc[3]);
-        }
-        x[i] = (i == c ? 1.f : 0.f) - ((acc[0] + acc[1]) + (acc[2] + acc[3]));
+        for (int i = 0; i < 4; ++i) a4[i] = *reinterpret_cast<const float4*>(ab + i * PS_LD + 4 * kb);
+        const bool dg = (c >> 2) == kb;
+        const int cj = c & 3;
+        const float x0 = ((dg && cj == 0) ? 1.f : 0.f) - v[0];
+        const float x1 = fmaf(-a4[1].x, x0, ((dg && cj == 1) ? 1.f : 0.f) - v[1]);
+        const float x2 = fmaf(-a4[2].y, x1, fmaf(-a4[2].x, x0, ((dg && cj == 2) ? 1.f : 0.f) - v[2]));
+        const float x3 = fmaf(-a4[3].z, x2, fmaf(-a4[3].y, x1, fmaf(-a4[3].x, x0, ((dg && cj == 3) ? 1.f : 0.f) - v[3])));
+        const int src = (lane & ~3) | kb;
+        const float y0 = __shfl_sync(0xffffffffu, x0, src), y1 = __shfl_sync(0xffffffffu, x1, src),
+                    y2 = __shfl_sync(0xffffffffu, x2, src), y3 = __shfl_sync(0xffffffffu, x3, src);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) v[i] = fmaf(a4[i].w, y3, fmaf(a4[i].z, y2, fmaf(a4[i].y, y1, fmaf(a4[i].x, y0, v[i]))));
+        if (p == kb) { v[0] = x0; v[1] = x1; v[2] = x2; v[3] = x3; }
       }
-      // column c of T diag(beta) into the K-major hi / lo operand tiles (over the QG lo rows)
-      const float bc = sbeta[c];
-      uint8_t* th = sm + PT_TBH + 2 * (c & 7);
-      uint8_t* tl = sm + PT_TBL + 2 * (c & 7);
 #pragma unroll
-      for (int i = 0; i < KM_C; ++i) {
-        bf16 hi, lo;
-        split1_bf16(x[i] * bc, hi, lo);
-        const uint32_t off = swz<128>(i, c >> 3);
-        *reinterpret_cast<bf16*>(th + off) = hi;
-        *reinterpret_cast<bf16*>(tl + off) = lo;
+      for (int i = 0; i < 4; ++i) sT[(16 * db + 4 * p + i) * PS_LD + 16 * db + c] = v[i];
+    }
+    __syncthreads();
+    {
+      // (b) blocks (1,0) and (3,2): P = A10 T00 (kept in rows 0..15 of the upper triangle), then T10 = -T11 P;
+      // thread = (pair, row, two columns)
+      const int pr = tid >> 7, r = (tid & 127) >> 3, q = tid & 7;
+      const int K0 = 32 * pr;
+      float* pbuf = sT + 16 + 32 * pr + 2 * q;
+      float ak[16];
+      {
+        const float* arow = sA + (K0 + 16 + r) * PS_LD + K0;
+#pragma unroll
+        for (int kq = 0; kq < 4; ++kq) {
+          const float4 t = *reinterpret_cast<const float4*>(arow + 4 * kq);
+          ak[4 * kq] = t.x; ak[4 * kq + 1] = t.y; ak[4 * kq + 2] = t.z; ak[4 * kq + 3] = t.w;
+        }
+        float p0 = 0.f, p1 = 0.f;
+#pragma unroll
+        for (int kq = 0; kq < 16; ++kq) {
+          const float2 t = *reinterpret_cast<const float2*>(sT + (K0 + kq) * PS_LD + K0 + 2 * q);
+          p0 = fmaf(ak[kq], t.x, p0); p1 = fmaf(ak[kq], t.y, p1);
+        }
+        *reinterpret_cast<float2*>(pbuf + r * PS_LD) = make_float2(p0, p1);
+      }
+      __syncthreads();
+      {
+        const float* trow = sT + (K0 + 16 + r) * PS_LD + K0 + 16;
+#pragma unroll
+        for (int kq = 0; kq < 4; ++kq) {
+          const float4 t = *reinterpret_cast<const float4*>(trow + 4 * kq);
+          ak[4 * kq] = t.x; ak[4 * kq + 1] = t.y; ak[4 * kq + 2] = t.z; ak[4 * kq + 3] = t.w;
+        }
+        float p0 = 0.f, p1 = 0.f;
+#pragma unroll
+        for (int kq = 0; kq < 16; ++kq) {
+          const float2 t = *reinterpret_cast<const float2*>(pbuf + kq * PS_LD);
+          p0 = fmaf(ak[kq], t.x, p0); p1 = fmaf(ak[kq], t.y, p1);
+        }
+        *reinterpret_cast<float2*>(sT + (K0 + 16 + r) * PS_LD + K0 + 2 * q) = make_float2(-p0, -p1);
+      }
+    }
+    __syncthreads();
+    {
+      // (c) the 32 x 32 block: P = A[32.., ..31] T[..31, ..31] (into rows 0..31, columns 32..63), then
+      // T[32.., ..31] = -T[32.., 32..] P; thread = (row = lane, four columns = warp).  T[..31, ..31] is lower
+      // triangular, so the columns of warp q need k >= 4 q only.
+      const int q = warp, r = lane;
+      float acc[4] = {0.f, 0.f, 0.f, 0.f};
+      const float* arow = sA + (32 + r) * PS_LD;
+#pragma unroll 2
+      for (int k4 = q; k4 < 8; ++k4) {
+        const float4 av = *reinterpret_cast<const float4*>(arow + 4 * k4);
+        const float aa[4] = {av.x, av.y, av.z, av.w};
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk) {
+          const float4 t = *reinterpret_cast<const float4*>(sT + (4 * k4 + kk) * PS_LD + 4 * q);
+          acc[0] = fmaf(aa[kk], t.x, acc[0]); acc[1] = fmaf(aa[kk], t.y, acc[1]);
+          acc[2] = fmaf(aa[kk], t.z, acc[2]); acc[3] = fmaf(aa[kk], t.w, acc[3]);
+        }
+      }
+      // (rows 0..15 of that region were the scratch of (b), dead since the barrier above)
+      *reinterpret_cast<float4*>(sT + r * PS_LD + 32 + 4 * q) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+      __syncthreads();
+      float ac2[4] = {0.f, 0.f, 0.f, 0.f};
+      const float* trow = sT + (32 + r) * PS_LD + 32;
+#pragma unroll
+      for (int k4 = 0; k4 < 8; ++k4) {
+        float4 av = *reinterpret_cast<const float4*>(trow + 4 * k4);
+        if (k4 >= 4 && r < 16) av = make_float4(0.f, 0.f, 0.f, 0.f);   // block (2,3) of T was never written: it is zero
+        const float aa[4] = {av.x, av.y, av.z, av.w};
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk) {
+          const float4 t = *reinterpret_cast<const float4*>(sT + (4 * k4 + kk) * PS_LD + 32 + 4 * q);
+          ac2[0] = fmaf(aa[kk], t.x, ac2[0]); ac2[1] = fmaf(aa[kk], t.y, ac2[1]);
+          ac2[2] = fmaf(aa[kk], t.z, ac2[2]); ac2[3] = fmaf(aa[kk], t.w, ac2[3]);
+        }
+      }
+      *reinterpret_cast<float4*>(sT + (32 + r) * PS_LD + 4 * q) = make_float4(-ac2[0], -ac2[1], -ac2[2], -ac2[3]);
+    }
+    __syncthreads();
+    {
+      // T diag(beta) into the K-major hi / lo operand tiles (over the QG lo rows): thread = (row, 16 columns)
+      const int i = tid >> 2, ch = tid & 3;
+#pragma unroll
+      for (int hc = 0; hc < 2; ++hc) {
+        const int c0 = 16 * ch + 8 * hc;
+        const float4 ta = *reinterpret_cast<const float4*>(sT + i * PS_LD + c0), tb = *reinterpret_cast<const float4*>(sT + i * PS_LD + c0 + 4);
+        const float4 ba = *reinterpret_cast<const float4*>(sbeta + c0), bb = *reinterpret_cast<const float4*>(sbeta + c0 + 4);
+        const float tv[8] = {ta.x * ba.x, ta.y * ba.y, ta.z * ba.z, ta.w * ba.w, tb.x * bb.x, tb.y * bb.y, tb.z * bb.z, tb.w * bb.w};
+        uint32_t hi[4], lo[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+          split2_bf16(c0 + 2 * e <= i ? tv[2 * e] : 0.f, c0 + 2 * e + 1 <= i ? tv[2 * e + 1] : 0.f, hi[e], lo[e]);
+        const uint32_t off = swz<128>(i, 2 * ch + hc);
+        *reinterpret_cast<uint4*>(sm + PT_TBH + off) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+        *reinterpret_cast<uint4*>(sm + PT_TBL + off) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
       }
     }
     t5_fence_async_smem();
